@@ -1,0 +1,190 @@
+/*
+ * lutmac_b200 -- C ABI of the B200 (sm_100a) implementation of LutMac's LUT-GEMV decode path.
+ *
+ * Every entry point is extern "C", takes plain pointers / sizes / opaque handles and returns
+ * an int status (0 = LMB_OK).  There is no CPU fallback: every compute call needs a CUDA
+ * device and fails with LMB_ERR_CUDA otherwise.
+ *
+ * Each declaration cites the reference interface (YASSERRMD/lutmac, file:line) it replaces.
+ */
+#ifndef LUTMAC_B200_H
+#define LUTMAC_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes --------------------------------------------------------------------- */
+enum {
+  LMB_OK = 0,
+  LMB_ERR_ARG = 1,      /* bad argument (null pointer, unknown kind, bad shape)            */
+  LMB_ERR_CUDA = 2,     /* a CUDA runtime call failed; see lmb_last_error()                 */
+  LMB_ERR_ALLOC = 3,    /* host or device allocation failed                                */
+  LMB_ERR_TIMEOUT = 4,  /* a bounded device-side wait expired                              */
+  LMB_ERR_FORMAT = 5,   /* malformed .lutmac file                                          */
+  LMB_ERR_LIMIT = 6,    /* size beyond a documented limit of the entry point               */
+  LMB_ERR_STATE = 7     /* call not valid in the handle's current state                    */
+};
+const char *lmb_strerror(int status);
+/* Text of the most recent failure on the calling thread (CUDA error string etc.). */
+const char *lmb_last_error(void);
+
+/* ---- block kinds ------------------------------------------------------------------------
+ * One per block struct of include/lutmac/types.hpp; the value is PackedTensor::quant_bits
+ * for that block vector (types.hpp:470-484), ternary = 0.  256 weights per block. */
+enum {
+  LMB_TERNARY = 0, /* BitPlaneBlock  68 B  types.hpp:126-137 */
+  LMB_BINARY = 1,  /* BinaryBlock    36 B  types.hpp:394-401 */
+  LMB_INT2 = 2,    /* Int2Block      72 B  types.hpp:209-215 (RRQ: scale, scale2) */
+  LMB_INT3 = 3,    /* Int3Block     100 B  types.hpp:249-254 */
+  LMB_INT4 = 4,    /* Int4Block     132 B  types.hpp:174-181 */
+  LMB_INT5 = 5,    /* Int5Block     164 B  types.hpp:296-301 */
+  LMB_INT6 = 6,    /* Int6Block     196 B  types.hpp:344-349 */
+  LMB_INT8 = 8     /* Int8Block     260 B  types.hpp:434-438 */
+};
+/* sizeof the reference block struct of a kind (0 for an unknown kind). */
+size_t lmb_block_bytes(int kind);
+
+/* ---- flags for lmb_linear* ---------------------------------------------------------------- */
+enum {
+  LMB_ROTATE = 1u,      /* apply the block-wise 256-point FWHT/16 to the (zero-padded) input   */
+  LMB_AUTO_ROTATE = 2u  /* rotate iff the reference's lut_linear would (lut_gemm_scalar.cpp:92-93) */
+};
+
+typedef struct lmb_ctx lmb_ctx;       /* one device + one stream + scratch                   */
+typedef struct lmb_weight lmb_weight; /* a weight matrix resident on the device              */
+typedef struct lmb_model lmb_model;   /* a device-resident decoder (weights, KV cache, scratch) */
+
+/* ---- context ---------------------------------------------------------------------------------
+ * Not thread-safe per context; independent contexts may be used from different threads.  */
+int lmb_ctx_create(int device, lmb_ctx **out);
+int lmb_ctx_destroy(lmb_ctx *ctx);
+/* Run all later work of this context on an existing CUDA stream (a cudaStream_t passed as a
+ * pointer); NULL returns to the context's own stream. */
+int lmb_ctx_set_stream(lmb_ctx *ctx, void *cuda_stream);
+int lmb_ctx_sync(lmb_ctx *ctx);
+int lmb_device_count(int *out);
+/* Number of kernels this library has launched on the context since creation. */
+int lmb_ctx_launch_count(lmb_ctx *ctx, uint64_t *out);
+
+/* Device memory helpers for hosts that have no CUDA binding of their own. */
+int lmb_malloc(lmb_ctx *ctx, size_t bytes, void **d_ptr);
+int lmb_free(lmb_ctx *ctx, void *d_ptr);
+int lmb_memcpy_h2d(lmb_ctx *ctx, void *d_dst, const void *h_src, size_t bytes);
+int lmb_memcpy_d2h(lmb_ctx *ctx, void *h_dst, const void *d_src, size_t bytes);
+int lmb_memset(lmb_ctx *ctx, void *d_dst, int value, size_t bytes);
+int lmb_host_alloc_pinned(size_t bytes, void **h_ptr);
+int lmb_host_free_pinned(void *h_ptr);
+
+/* CUDA-event timing on the context's stream. */
+int lmb_timer_start(lmb_ctx *ctx);
+int lmb_timer_stop(lmb_ctx *ctx, float *ms_out); /* records, synchronises, returns elapsed ms */
+
+/* ---- weights: replaces the host block vectors of PackedTensor (types.hpp:470-492) and the
+ * raw struct reads of load_lutmac (src/format.cpp:463-496) --------------------------------------
+ * `blocks` is the reference's row-major block array: row r starts at blocks + r*ceil(K/256).
+ * The array is re-tiled once into the device layout and may be freed after the call.
+ * lmb_weight_upload_shard keeps rows [row0,row1) and 256-column blocks [blk0,blk1) of every
+ * kept row (tensor-parallel shards); the shard behaves as an (row1-row0) x ((blk1-blk0)*256)
+ * matrix. */
+int lmb_weight_upload(lmb_ctx *ctx, int kind, const void *blocks, size_t M, size_t K, lmb_weight **out);
+int lmb_weight_upload_shard(lmb_ctx *ctx, int kind, const void *blocks, size_t M, size_t K,
+                            size_t row0, size_t row1, size_t blk0, size_t blk1, lmb_weight **out);
+int lmb_weight_free(lmb_weight *w);
+int lmb_weight_info(const lmb_weight *w, int *kind, size_t *M, size_t *K, size_t *device_bytes);
+/* Reads the device copy back and converts it to the reference block layout (the inverse of
+ * the upload re-tiling; bit-exact for blocks in the canonical form the reference's own
+ * quantizers emit). `blocks_out` holds M*ceil(K/256) blocks. */
+int lmb_weight_download(lmb_ctx *ctx, const lmb_weight *w, void *blocks_out);
+/* The same two conversions on the host only (no device needed). `tiled` holds
+ * lmb_tiled_bytes(kind, M, K) bytes. */
+size_t lmb_tiled_bytes(int kind, size_t M, size_t K);
+int lmb_retile_host(int kind, const void *blocks, size_t M, size_t K, void *tiled);
+int lmb_untile_host(int kind, const void *tiled, size_t M, size_t K, void *blocks_out);
+
+/* ---- layer API on device pointers: replaces lut_linear (include/lutmac/lut_gemm.hpp:419,
+ * src/kernels/lut_gemm_scalar.cpp:68-180) ---------------------------------------------------------
+ * y[b] = W * rot?(pad(x[b])) + bias for b < batch.  d_x holds batch rows of x_stride floats of
+ * which the first x_len are read (the rest of each 256-block counts as zero, which is the
+ * reference's zero padding); d_y holds batch rows of M floats.  d_bias is NULL or M floats. */
+int lmb_linear(lmb_ctx *ctx, const lmb_weight *w, const float *d_bias, const float *d_x, size_t x_len,
+               size_t x_stride, float *d_y, size_t batch, unsigned flags);
+
+/* ---- kernel API on host pointers: replaces the dispatchers lut_gemv, lut_gemv_binary,
+ * int2_gemv ... int8_gemv (include/lutmac/lut_gemm.hpp:172-408) -----------------------------------
+ * Same arguments as the reference: activations must be readable for ceil(K/256)*256 floats,
+ * num_blocks is ignored, output receives M floats.  Each call uploads the blocks, runs the
+ * CUDA kernel on the default context of the current device and copies the result back. */
+int lmb_gemv_host(int kind, const void *blocks, size_t num_blocks, const float *activations, float *output,
+                  size_t M, size_t K);
+/* Layer API on host pointers: lut_linear for a weight already resident (lmb_weight_upload),
+ * host input/output, host<->device copies included. */
+int lmb_linear_host(lmb_ctx *ctx, const lmb_weight *w, const float *bias, const float *input, float *output,
+                    size_t batch, unsigned flags);
+/* Several independent lut_linear calls (batch 1 each) issued together: one staged input
+ * copy, the kernels, one staged output copy.  inputs[i] holds K_i floats, outputs[i] M_i. */
+int lmb_linear_host_multi(lmb_ctx *ctx, size_t n, const lmb_weight *const *ws, const float *const *inputs,
+                          float *const *outputs, unsigned flags);
+
+/* ---- transform API: replaces fwht_256 / apply_hadamard_rotation
+ * (include/lutmac/transform.hpp:14,19; src/kernels/transform_simd.cpp:26-110) --------------------- */
+int lmb_fwht256(lmb_ctx *ctx, float *d_x, size_t n);                 /* in place, device pointer */
+int lmb_apply_hadamard_rotation_host(float *data, size_t n);         /* in place, host pointer   */
+
+/* ---- debug views used by the parity tests ----------------------------------------------------------
+ * LUT tables exactly as the kernel prologue builds them: ceil(x_len/256)*64 groups x 16 entries
+ * (precompute_luts, lut_gemm.hpp:53-58), after optional rotation. */
+int lmb_debug_luts(lmb_ctx *ctx, const float *d_x, size_t x_len, unsigned flags, float *d_luts_out);
+/* Ternary LUT indices as the kernel consumes them: for every row and group of 4 weights the
+ * (pos, neg) nibbles of extract_indices (lut_gemm.hpp:79-99); out = M*ceil(K/256)*64*2 bytes. */
+int lmb_debug_ternary_indices(lmb_ctx *ctx, const lmb_weight *w, uint8_t *h_out);
+
+/* ---- model API: replaces Model::allocate / Model::forward / get_logits / reset_cache
+ * (include/lutmac/model.hpp:88-141, src/model.cpp:47-453) ------------------------------------------- */
+typedef struct {
+  size_t vocab_size, hidden_size, intermediate_size, num_hidden_layers;
+  size_t num_attention_heads, num_key_value_heads, head_dim, max_seq_len;
+  float rope_theta, rope_scaling_factor, rms_norm_eps;
+  size_t max_batch;  /* sequences decoded together (the reference decodes one) */
+  int tp_rank, tp_size; /* tensor-parallel position of this process (0,1 = unsharded) */
+} lmb_model_config;
+
+enum { /* tensor slots of lmb_model_set_weight */
+  LMB_SLOT_EMBED = 0, LMB_SLOT_LM_HEAD = 1, LMB_SLOT_Q = 2, LMB_SLOT_K = 3, LMB_SLOT_V = 4,
+  LMB_SLOT_O = 5, LMB_SLOT_GATE = 6, LMB_SLOT_UP = 7, LMB_SLOT_DOWN = 8
+};
+enum { /* vector slots of lmb_model_set_vector */
+  LMB_VEC_INPUT_NORM = 0, LMB_VEC_POST_NORM = 1, LMB_VEC_Q_BIAS = 2, LMB_VEC_K_BIAS = 3,
+  LMB_VEC_V_BIAS = 4, LMB_VEC_FINAL_NORM = 5
+};
+
+int lmb_model_create(lmb_ctx *ctx, const lmb_model_config *cfg, lmb_model **out);
+int lmb_model_destroy(lmb_model *m);
+/* Full (unsharded) reference block arrays; the model keeps only its tensor-parallel shard. */
+int lmb_model_set_weight(lmb_model *m, int layer, int slot, int kind, int quant_bits, const void *blocks,
+                         size_t M, size_t K);
+int lmb_model_set_vector(lmb_model *m, int layer, int which, const float *data, size_t n);
+/* One decode step for `batch` sequences: token_ids[b] at positions[b].  h_logits is NULL or
+ * batch*vocab floats on the host. */
+int lmb_model_forward(lmb_model *m, const int *token_ids, const size_t *positions, size_t batch, float *h_logits);
+int lmb_model_logits_dev(lmb_model *m, const float **d_logits);
+int lmb_model_reset(lmb_model *m);
+/* KV cache exchange in the reference layout [layer][2][max_seq][kv_heads][head_dim]
+ * (types.hpp:599-627) for sequence `seq`. */
+int lmb_model_kv_export(lmb_model *m, size_t seq, float *h_out);
+int lmb_model_kv_import(lmb_model *m, size_t seq, const float *h_in);
+/* Algorithmic bytes one decode step reads at the given context length (weights + KV + embedding row). */
+int lmb_model_step_bytes(lmb_model *m, size_t position, uint64_t *bytes_out);
+/* Tensor parallelism: the host owns the communicator.  all_reduce(user, d_buf, n_floats,
+ * cuda_stream) must sum d_buf in place over the ranks on that stream. */
+typedef int (*lmb_allreduce_fn)(void *user, float *d_buf, size_t n_floats, void *cuda_stream);
+typedef int (*lmb_allgather_fn)(void *user, const float *d_send, float *d_recv, size_t n_floats_per_rank, void *cuda_stream);
+int lmb_model_set_collectives(lmb_model *m, lmb_allreduce_fn ar, lmb_allgather_fn ag, void *user);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LUTMAC_B200_H */

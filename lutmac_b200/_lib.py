@@ -1,0 +1,115 @@
+"""ctypes binding of the C ABI declared in include/lutmac_b200.h.
+
+The shared library is built in-tree (lutmac_b200/liblutmac_b200.so).  There is no fallback:
+importing this module without the library raises, and every compute call fails with
+LMB_ERR_CUDA on a machine without a B200-class GPU.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "liblutmac_b200.so")
+
+OK = 0
+ERR_ARG, ERR_CUDA, ERR_ALLOC, ERR_TIMEOUT, ERR_FORMAT, ERR_LIMIT, ERR_STATE = 1, 2, 3, 4, 5, 6, 7
+
+ROTATE = 1
+AUTO_ROTATE = 2
+
+f32p = C.POINTER(C.c_float)
+vp = C.c_void_p
+sz = C.c_size_t
+
+
+class ModelConfig(C.Structure):
+    _fields_ = [("vocab_size", sz), ("hidden_size", sz), ("intermediate_size", sz), ("num_hidden_layers", sz),
+                ("num_attention_heads", sz), ("num_key_value_heads", sz), ("head_dim", sz), ("max_seq_len", sz),
+                ("rope_theta", C.c_float), ("rope_scaling_factor", C.c_float), ("rms_norm_eps", C.c_float),
+                ("max_batch", sz), ("tp_rank", C.c_int), ("tp_size", C.c_int)]
+
+
+ALLREDUCE_FN = C.CFUNCTYPE(C.c_int, vp, vp, sz, vp)
+ALLGATHER_FN = C.CFUNCTYPE(C.c_int, vp, vp, vp, sz, vp)
+
+# name -> (restype, argtypes); every symbol include/lutmac_b200.h declares
+SIGNATURES = {
+    "lmb_strerror": (C.c_char_p, [C.c_int]),
+    "lmb_last_error": (C.c_char_p, []),
+    "lmb_block_bytes": (sz, [C.c_int]),
+    "lmb_ctx_create": (C.c_int, [C.c_int, C.POINTER(vp)]),
+    "lmb_ctx_destroy": (C.c_int, [vp]),
+    "lmb_ctx_set_stream": (C.c_int, [vp, vp]),
+    "lmb_ctx_sync": (C.c_int, [vp]),
+    "lmb_device_count": (C.c_int, [C.POINTER(C.c_int)]),
+    "lmb_ctx_launch_count": (C.c_int, [vp, C.POINTER(C.c_uint64)]),
+    "lmb_malloc": (C.c_int, [vp, sz, C.POINTER(vp)]),
+    "lmb_free": (C.c_int, [vp, vp]),
+    "lmb_memcpy_h2d": (C.c_int, [vp, vp, vp, sz]),
+    "lmb_memcpy_d2h": (C.c_int, [vp, vp, vp, sz]),
+    "lmb_memset": (C.c_int, [vp, vp, C.c_int, sz]),
+    "lmb_host_alloc_pinned": (C.c_int, [sz, C.POINTER(vp)]),
+    "lmb_host_free_pinned": (C.c_int, [vp]),
+    "lmb_timer_start": (C.c_int, [vp]),
+    "lmb_timer_stop": (C.c_int, [vp, f32p]),
+    "lmb_weight_upload": (C.c_int, [vp, C.c_int, vp, sz, sz, C.POINTER(vp)]),
+    "lmb_weight_upload_shard": (C.c_int, [vp, C.c_int, vp, sz, sz, sz, sz, sz, sz, C.POINTER(vp)]),
+    "lmb_weight_free": (C.c_int, [vp]),
+    "lmb_weight_info": (C.c_int, [vp, C.POINTER(C.c_int), C.POINTER(sz), C.POINTER(sz), C.POINTER(sz)]),
+    "lmb_weight_download": (C.c_int, [vp, vp, vp]),
+    "lmb_tiled_bytes": (sz, [C.c_int, sz, sz]),
+    "lmb_retile_host": (C.c_int, [C.c_int, vp, sz, sz, vp]),
+    "lmb_untile_host": (C.c_int, [C.c_int, vp, sz, sz, vp]),
+    "lmb_linear": (C.c_int, [vp, vp, vp, vp, sz, sz, vp, sz, C.c_uint]),
+    "lmb_gemv_host": (C.c_int, [C.c_int, vp, sz, vp, vp, sz, sz]),
+    "lmb_linear_host": (C.c_int, [vp, vp, vp, vp, vp, sz, C.c_uint]),
+    "lmb_linear_host_multi": (C.c_int, [vp, sz, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), C.c_uint]),
+    "lmb_fwht256": (C.c_int, [vp, vp, sz]),
+    "lmb_apply_hadamard_rotation_host": (C.c_int, [vp, sz]),
+    "lmb_debug_luts": (C.c_int, [vp, vp, sz, C.c_uint, vp]),
+    "lmb_debug_ternary_indices": (C.c_int, [vp, vp, vp]),
+    "lmb_model_create": (C.c_int, [vp, C.POINTER(ModelConfig), C.POINTER(vp)]),
+    "lmb_model_destroy": (C.c_int, [vp]),
+    "lmb_model_set_weight": (C.c_int, [vp, C.c_int, C.c_int, C.c_int, C.c_int, vp, sz, sz]),
+    "lmb_model_set_vector": (C.c_int, [vp, C.c_int, C.c_int, vp, sz]),
+    "lmb_model_forward": (C.c_int, [vp, C.POINTER(C.c_int), C.POINTER(sz), sz, vp]),
+    "lmb_model_logits_dev": (C.c_int, [vp, C.POINTER(vp)]),
+    "lmb_model_reset": (C.c_int, [vp]),
+    "lmb_model_kv_export": (C.c_int, [vp, sz, vp]),
+    "lmb_model_kv_import": (C.c_int, [vp, sz, vp]),
+    "lmb_model_step_bytes": (C.c_int, [vp, sz, C.POINTER(C.c_uint64)]),
+    "lmb_model_set_collectives": (C.c_int, [vp, ALLREDUCE_FN, ALLGATHER_FN, vp]),
+}
+
+
+class LutmacError(RuntimeError):
+    def __init__(self, status: int, text: str, detail: str):
+        super().__init__(f"lutmac_b200: {text} (status {status}){': ' + detail if detail else ''}")
+        self.status = status
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """Load the shared library (once) and attach the signatures."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(
+                f"{LIB_PATH} is missing: build it with `python -m lutmac_b200.build` "
+                "(there is no CPU fallback for the CUDA path)")
+        L = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(L, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = L
+    return _lib
+
+
+def check(status: int) -> None:
+    if status != OK:
+        L = lib()
+        raise LutmacError(status, L.lmb_strerror(status).decode(), L.lmb_last_error().decode())

@@ -1,0 +1,146 @@
+// Shared definitions of the lutmac_b200 CUDA library: block kinds, the device tile layout,
+// error plumbing and the context object.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+#include <string>
+
+#include "../../include/lutmac_b200.h"
+
+namespace lmb {
+
+constexpr int BLK = 256;       // weights per block (every reference block struct)
+constexpr int TILE_ROWS = 32;  // rows per device tile: one warp lane per row
+constexpr int SM_COUNT_HINT = 148;
+
+// ---------------------------------------------------------------------------------------------
+// Device tile layout
+//
+// A weight matrix of M rows and bpr = ceil(K/256) block-columns is stored as tiles of 32 rows
+// x 1 block-column, row-tile major: tile (rt, b) starts at ((rt * bpr) + b) * tile_bytes.
+// Inside a tile:
+//     payload  [chunk c][lane l][16 bytes]     c < chunks(kind), l = row within the tile
+//     scales   [scale s][lane l] float          s < nscales(kind)
+// so that lane l of a warp reads its row with 128-bit loads that are contiguous across the
+// warp (512 B per load).  tile_bytes = 32 * sizeof(reference block): the device copy has
+// exactly the reference's bytes.  Rows beyond M are padded with zero-weight blocks.
+//
+// What a lane's chunks hold, per kind (256 weights w0..w255 of one reference block):
+//   TERNARY  4 chunks; chunk c = { P[8c..8c+7], N[8c..8c+7] } where P = ~zero & ~sign and
+//            N = ~zero & sign are the positive / negative masks of extract_indices
+//            (lut_gemm.hpp:79-99), same byte order and MSB-first bit order as the planes.
+//   BINARY   2 chunks; chunk c = data[16c..16c+15] unchanged.
+//   INT2     4 chunks; chunk c = { B1[8c..8c+7], B2[8c..8c+7] }: the primary and residual
+//            bits of the interleaved (b1,b2) pairs split into two MSB-first bit planes.
+//   INT3     6 chunks; chunk 3j+p = Q_{2-p}[16j..16j+15] (j < 2): bit planes of the 3-bit
+//            code, most significant plane first.
+//   INT4     8 chunks; chunk c = data[16c..16c+15] unchanged (weight 2i in the high nibble).
+//   INT5     10 chunks; 0..7 = low nibbles packed like INT4, 8..9 = bit-4 plane.
+//   INT6     12 chunks; 0..7 = low nibbles, 8..9 = bit-4 plane, 10..11 = bit-5 plane.
+//   INT8     16 chunks; chunk c = data[16c..16c+15] unchanged.
+// ---------------------------------------------------------------------------------------------
+struct KindInfo {
+  int ref_bytes;   // sizeof the reference block struct
+  int chunks;      // 16-byte payload chunks per row-block
+  int nscales;     // floats per row-block
+  bool lut;        // evaluated by group-of-4 table lookups (else dequantise + FMA)
+};
+
+__host__ __device__ constexpr KindInfo kind_info(int kind) {
+  return kind == LMB_TERNARY ? KindInfo{68, 4, 1, true}
+       : kind == LMB_BINARY  ? KindInfo{36, 2, 1, true}
+       : kind == LMB_INT2    ? KindInfo{72, 4, 2, true}
+       : kind == LMB_INT3    ? KindInfo{100, 6, 1, true}
+       : kind == LMB_INT4    ? KindInfo{132, 8, 1, false}
+       : kind == LMB_INT5    ? KindInfo{164, 10, 1, false}
+       : kind == LMB_INT6    ? KindInfo{196, 12, 1, false}
+       : kind == LMB_INT8    ? KindInfo{260, 16, 1, false}
+                             : KindInfo{0, 0, 0, false};
+}
+
+__host__ __device__ constexpr size_t tile_bytes(int kind) { return size_t(TILE_ROWS) * kind_info(kind).ref_bytes; }
+
+inline bool kind_valid(int kind) { return kind_info(kind).ref_bytes != 0; }
+
+// ---------------------------------------------------------------------------------------------
+// Errors
+// ---------------------------------------------------------------------------------------------
+void set_last_error(const std::string &msg);
+int cuda_fail(cudaError_t e, const char *what);
+
+#define LMB_CUDA(call)                                              \
+  do {                                                              \
+    cudaError_t _e = (call);                                        \
+    if (_e != cudaSuccess) return ::lmb::cuda_fail(_e, #call);      \
+  } while (0)
+
+#define LMB_REQUIRE(cond, msg)                                      \
+  do {                                                              \
+    if (!(cond)) {                                                  \
+      ::lmb::set_last_error(msg);                                   \
+      return LMB_ERR_ARG;                                           \
+    }                                                               \
+  } while (0)
+
+}  // namespace lmb
+
+// ---------------------------------------------------------------------------------------------
+// Opaque handles of the C ABI
+// ---------------------------------------------------------------------------------------------
+struct lmb_ctx {
+  int device = 0;
+  cudaStream_t own_stream = nullptr;
+  cudaStream_t stream = nullptr;  // the stream work is issued on (own_stream unless overridden)
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  int sm_count = lmb::SM_COUNT_HINT;
+  size_t smem_optin = 0;  // max dynamic shared memory per block
+  uint64_t launches = 0;
+  // scratch for split-K partial sums and its arrival counters (grown on demand)
+  float *scratch = nullptr;
+  size_t scratch_floats = 0;
+  unsigned *counters = nullptr;
+  size_t n_counters = 0;
+  // staging buffers of the host-pointer entry points
+  void *h_stage = nullptr;
+  size_t h_stage_bytes = 0;
+  float *d_stage = nullptr;
+  size_t d_stage_bytes = 0;
+};
+
+struct lmb_weight {
+  int kind = 0;
+  int device = 0;
+  size_t M = 0, K = 0;   // logical shape (of the shard, if sharded)
+  size_t bpr = 0;        // block-columns
+  size_t row_tiles = 0;  // ceil(M / 32)
+  uint8_t *d_tiles = nullptr;
+  size_t bytes = 0;
+};
+
+namespace lmb {
+
+// Launchers (implemented in the kernel files).  All pointers are device pointers.
+struct LinearArgs {
+  const lmb_weight *w;
+  const float *bias;
+  const float *x;
+  size_t x_len, x_stride;
+  float *y;
+  size_t y_stride;
+  size_t batch;
+  bool rotate;
+};
+int configure_gemv_lut(lmb_ctx *ctx);
+int configure_gemv_dq(lmb_ctx *ctx);
+int launch_gemv_lut(lmb_ctx *ctx, const LinearArgs &a);
+int launch_gemv_dq(lmb_ctx *ctx, const LinearArgs &a);
+int launch_fwht256(lmb_ctx *ctx, float *d_x, size_t n);
+int launch_debug_luts(lmb_ctx *ctx, const float *d_x, size_t x_len, bool rotate, float *d_out);
+
+int ensure_scratch(lmb_ctx *ctx, size_t floats, size_t counters);
+int ensure_stage(lmb_ctx *ctx, size_t bytes);
+
+}  // namespace lmb
