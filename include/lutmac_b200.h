@@ -178,11 +178,18 @@ int lmb_model_kv_export(lmb_model *m, size_t seq, float *h_out);
 int lmb_model_kv_import(lmb_model *m, size_t seq, const float *h_in);
 /* Algorithmic bytes one decode step reads at the given context length (weights + KV + embedding row). */
 int lmb_model_step_bytes(lmb_model *m, size_t position, uint64_t *bytes_out);
-/* Tensor parallelism: the host owns the communicator.  all_reduce(user, d_buf, n_floats,
- * cuda_stream) must sum d_buf in place over the ranks on that stream. */
-typedef int (*lmb_allreduce_fn)(void *user, float *d_buf, size_t n_floats, void *cuda_stream);
-typedef int (*lmb_allgather_fn)(void *user, const float *d_send, float *d_recv, size_t n_floats_per_rank, void *cuda_stream);
-int lmb_model_set_collectives(lmb_model *m, lmb_allreduce_fn ar, lmb_allgather_fn ag, void *user);
+
+/* ---- tensor parallelism (no counterpart in the reference, which is single-process) ---------------
+ * One process per GPU.  Rank 0 obtains a 128-byte NCCL unique id, the host distributes it by
+ * whatever means it has, every rank calls lmb_tp_init with it.  Collectives run on the
+ * context's stream.  A model created on a context with tp_size > 1 in its config keeps only
+ * its shard: q/k/v/gate/up by output rows (whole heads), o/down by 256-column blocks, lm_head
+ * by vocabulary rows; it all-reduces after o_proj and down_proj and all-gathers the logits. */
+int lmb_tp_unique_id(void *id128_out);
+int lmb_tp_init(lmb_ctx *ctx, const void *id128, int rank, int size);
+int lmb_tp_destroy(lmb_ctx *ctx);
+int lmb_allreduce_sum(lmb_ctx *ctx, float *d_buf, size_t n_floats);
+int lmb_allgather(lmb_ctx *ctx, const float *d_send, float *d_recv, size_t n_floats_per_rank);
 
 #ifdef __cplusplus
 }

@@ -30,9 +30,6 @@ class ModelConfig(C.Structure):
                 ("max_batch", sz), ("tp_rank", C.c_int), ("tp_size", C.c_int)]
 
 
-ALLREDUCE_FN = C.CFUNCTYPE(C.c_int, vp, vp, sz, vp)
-ALLGATHER_FN = C.CFUNCTYPE(C.c_int, vp, vp, vp, sz, vp)
-
 # name -> (restype, argtypes); every symbol include/lutmac_b200.h declares
 SIGNATURES = {
     "lmb_strerror": (C.c_char_p, [C.c_int]),
@@ -79,7 +76,11 @@ SIGNATURES = {
     "lmb_model_kv_export": (C.c_int, [vp, sz, vp]),
     "lmb_model_kv_import": (C.c_int, [vp, sz, vp]),
     "lmb_model_step_bytes": (C.c_int, [vp, sz, C.POINTER(C.c_uint64)]),
-    "lmb_model_set_collectives": (C.c_int, [vp, ALLREDUCE_FN, ALLGATHER_FN, vp]),
+    "lmb_tp_unique_id": (C.c_int, [vp]),
+    "lmb_tp_init": (C.c_int, [vp, vp, C.c_int, C.c_int]),
+    "lmb_tp_destroy": (C.c_int, [vp]),
+    "lmb_allreduce_sum": (C.c_int, [vp, vp, sz]),
+    "lmb_allgather": (C.c_int, [vp, vp, vp, sz]),
 }
 
 
@@ -101,6 +102,9 @@ def lib() -> C.CDLL:
                 f"{LIB_PATH} is missing: build it with `python -m lutmac_b200.build` "
                 "(there is no CPU fallback for the CUDA path)")
         L = C.CDLL(LIB_PATH)
+        missing = [name for name in SIGNATURES if not hasattr(L, name)]
+        if missing:
+            raise ImportError(f"{LIB_PATH} does not export {missing}: rebuild it (python -m lutmac_b200.build --force)")
         for name, (res, args) in SIGNATURES.items():
             fn = getattr(L, name)
             fn.restype = res

@@ -1,0 +1,261 @@
+// Glue kernels of one decode step, all fp32 like the reference: embedding-row dequantisation
+// (src/model.cpp:58-252), RMSNorm with fused residual add (src/layers/norm.cpp:18-34,
+// model.cpp:385-399), bias + RoPE + KV-cache write (model.cpp:312-335,
+// src/layers/embedding.cpp:36-75), GQA decode attention (model.cpp:338-372,
+// src/layers/attention.cpp:23-42) and SiLU(gate)*up (model.cpp:36,414-416).
+#include "decode_ops.cuh"
+
+namespace lmb {
+
+namespace {
+
+// Dequantised weight (row, col) out of the device tile layout: Block::get of types.hpp.
+__device__ float tile_elem(int kind, const uint8_t *tiles, size_t bpr, size_t row, size_t col) {
+  const size_t rt = row / TILE_ROWS, l = row % TILE_ROWS, b = col / BLK, j = col % BLK;
+  const KindInfo ki = kind_info(kind);
+  const uint8_t *tile = tiles + (rt * bpr + b) * (size_t(TILE_ROWS) * ki.ref_bytes);
+  const float *sc = reinterpret_cast<const float *>(tile + size_t(ki.chunks) * TILE_ROWS * 16);
+  const float s0 = sc[l];
+  auto pay = [&](size_t chunk, size_t byte) { return tile[(chunk * TILE_ROWS + l) * 16 + byte]; };
+  const unsigned bit = 7u - unsigned(j % 8);
+  switch (kind) {
+  case LMB_INT8: return float(int8_t(pay(j / 16, j % 16))) * s0;
+  case LMB_INT4: {
+    const uint8_t byte = pay((j / 2) / 16, (j / 2) % 16);
+    const int nib = (j % 2 == 0) ? (byte >> 4) : (byte & 15);
+    return float(nib - 8) * s0;
+  }
+  case LMB_TERNARY: {
+    const size_t jb = j / 8;
+    const unsigned p = (pay(jb / 8, jb % 8) >> bit) & 1u, n = (pay(jb / 8, 8 + jb % 8) >> bit) & 1u;
+    return p ? s0 : (n ? -s0 : 0.0f);
+  }
+  case LMB_INT2: {
+    const size_t jb = j / 8;
+    const unsigned b1 = (pay(jb / 8, jb % 8) >> bit) & 1u, b2 = (pay(jb / 8, 8 + jb % 8) >> bit) & 1u;
+    const float s1 = sc[TILE_ROWS + l];
+    return (b1 ? s0 : -s0) + (b2 ? s1 : -s1);
+  }
+  case LMB_INT3: {
+    const size_t jb = j / 8, jj = jb / 16;
+    unsigned code = 0;
+    for (unsigned q = 0; q < 3; ++q) code |= ((pay(3 * jj + (2 - q), jb % 16) >> bit) & 1u) << q;
+    return float(int(code) - 4) * s0;
+  }
+  case LMB_BINARY: return (((pay((j / 8) / 16, (j / 8) % 16)) >> bit) & 1u) ? s0 : -s0;
+  default: return 0.0f;
+  }
+}
+
+__global__ void k_embed_rows(const int *tokens, int kind, const uint8_t *tiles, size_t bpr, size_t vocab, size_t h,
+                             float *hidden) {
+  const size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= h) return;
+  const int tok = tokens[blockIdx.y];
+  // rows beyond the table read as zero (model.cpp:95-104)
+  hidden[size_t(blockIdx.y) * h + i] = (tok >= 0 && size_t(tok) < vocab) ? tile_elem(kind, tiles, bpr, size_t(tok), i) : 0.0f;
+}
+
+__device__ __forceinline__ float block_sum(float v, float *red) {
+#pragma unroll
+  for (int m = 16; m > 0; m >>= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (lane < nw) ? red[lane] : 0.0f;
+#pragma unroll
+  for (int m = 16; m > 0; m >>= 1) t += __shfl_xor_sync(0xffffffffu, t, m);
+  return t;
+}
+
+__device__ __forceinline__ float block_max(float v, float *red) {
+#pragma unroll
+  for (int m = 16; m > 0; m >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, m));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (lane < nw) ? red[lane] : -INFINITY;
+#pragma unroll
+  for (int m = 16; m > 0; m >>= 1) t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, m));
+  return t;
+}
+
+// hidden += add (if given); out = hidden * rsqrt(mean(hidden^2) + eps) * w.  One CTA per sequence.
+__global__ void __launch_bounds__(1024) k_add_rmsnorm(float *hidden, const float *add, const float *w, float *out,
+                                                      size_t h, float eps) {
+  __shared__ float red[32];
+  float *x = hidden + size_t(blockIdx.x) * h;
+  const float *a = add ? add + size_t(blockIdx.x) * h : nullptr;
+  float *o = out + size_t(blockIdx.x) * h;
+  float ss = 0.0f;
+  for (size_t i = threadIdx.x; i < h; i += blockDim.x) {
+    float v = x[i];
+    if (a) {
+      v += a[i];
+      x[i] = v;
+    }
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / float(h) + eps);
+  for (size_t i = threadIdx.x; i < h; i += blockDim.x) o[i] = x[i] * inv * w[i];
+}
+
+// q/k/v bias, rotary embedding of q and k (pairs d, d + hd/2), K/V written into the cache.
+__global__ void k_rope_kv(float *q, float *k, const float *v, const float *qb, const float *kb, const float *vb,
+                          const float *cs_table, const size_t *positions, float *kv, size_t layer, RopeDims d) {
+  const size_t b = blockIdx.x, pos = positions[b], half = d.hd / 2;
+  const float *cs = cs_table + pos * d.hd;  // [half cos | half sin]
+  float *qs = q + b * d.nh * d.hd, *ks = k + b * d.nkv * d.hd;
+  const float *vs = v + b * d.nkv * d.hd;
+  const size_t kv_dim = d.nkv * d.hd;
+  float *kc = kv + b * d.seq_stride + (layer * 2) * d.max_seq * kv_dim + pos * kv_dim;
+  float *vc = kc + d.max_seq * kv_dim;
+  for (size_t i = threadIdx.x; i < d.nh * half; i += blockDim.x) {
+    const size_t hh = i / half, dd = i % half, i0 = hh * d.hd + dd, i1 = i0 + half;
+    float a = qs[i0], c = qs[i1];
+    if (qb) {
+      a += qb[i0];
+      c += qb[i1];
+    }
+    qs[i0] = a * cs[dd] - c * cs[half + dd];
+    qs[i1] = a * cs[half + dd] + c * cs[dd];
+  }
+  for (size_t i = threadIdx.x; i < d.nkv * half; i += blockDim.x) {
+    const size_t hh = i / half, dd = i % half, i0 = hh * d.hd + dd, i1 = i0 + half;
+    float a = ks[i0], c = ks[i1];
+    if (kb) {
+      a += kb[i0];
+      c += kb[i1];
+    }
+    const float r0 = a * cs[dd] - c * cs[half + dd], r1 = a * cs[half + dd] + c * cs[dd];
+    ks[i0] = r0;
+    ks[i1] = r1;
+    kc[i0] = r0;
+    kc[i1] = r1;
+    float v0 = vs[i0], v1 = vs[i1];
+    if (vb) {
+      v0 += vb[i0];
+      v1 += vb[i1];
+    }
+    vc[i0] = v0;
+    vc[i1] = v1;
+  }
+}
+
+// One CTA per (head, sequence): scores over the cached keys, softmax, weighted sum of values.
+__global__ void __launch_bounds__(256) k_decode_attn(const float *q, const float *kv, const size_t *positions, float *out,
+                                                     size_t layer, RopeDims d) {
+  extern __shared__ float sm[];
+  float *sc = sm;                 // [max_seq]
+  float *qs = sc + d.max_seq;     // [hd]
+  float *acc = qs + d.hd;         // [groups][hd]
+  __shared__ float red[32];
+  const size_t head = blockIdx.x, b = blockIdx.y, seq = positions[b] + 1;
+  const size_t kvh = head / (d.nh / d.nkv), kv_dim = d.nkv * d.hd;
+  const float *kc = kv + b * d.seq_stride + (layer * 2) * d.max_seq * kv_dim + kvh * d.hd;
+  const float *vc = kc + d.max_seq * kv_dim;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (size_t i = threadIdx.x; i < d.hd; i += blockDim.x) qs[i] = q[(b * d.nh + head) * d.hd + i];
+  __syncthreads();
+  const float scale = 1.0f / sqrtf(float(d.hd));
+  for (size_t t = warp; t < seq; t += nw) {
+    const float *kt = kc + t * kv_dim;
+    float s = 0.0f;
+    for (size_t i = lane; i < d.hd; i += 32) s += qs[i] * kt[i];
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) s += __shfl_xor_sync(0xffffffffu, s, m);
+    if (lane == 0) sc[t] = s * scale;
+  }
+  __syncthreads();
+  float mx = -INFINITY;
+  for (size_t t = threadIdx.x; t < seq; t += blockDim.x) mx = fmaxf(mx, sc[t]);
+  mx = block_max(mx, red);
+  float sum = 0.0f;
+  for (size_t t = threadIdx.x; t < seq; t += blockDim.x) {
+    const float e = expf(sc[t] - mx);
+    sc[t] = e;
+    sum += e;
+  }
+  sum = block_sum(sum, red);
+  const float inv = 1.0f / sum;
+  __syncthreads();
+  const size_t groups = blockDim.x / d.hd, g = threadIdx.x / d.hd, dd = threadIdx.x % d.hd;
+  if (g < groups) {
+    float a = 0.0f;
+    for (size_t t = g; t < seq; t += groups) a += (sc[t] * inv) * vc[t * kv_dim + dd];
+    acc[g * d.hd + dd] = a;
+  }
+  __syncthreads();
+  if (threadIdx.x < d.hd) {
+    float a = 0.0f;
+    for (size_t k2 = 0; k2 < groups; ++k2) a += acc[k2 * d.hd + threadIdx.x];
+    out[(b * d.nh + head) * d.hd + threadIdx.x] = a;
+  }
+}
+
+__global__ void k_silu_mul(const float *gate, const float *up, float *out, size_t n) {
+  const size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < n) {
+    const float g = gate[i];
+    out[i] = (g / (1.0f + expf(-g))) * up[i];
+  }
+}
+
+}  // namespace
+
+int launch_embed_rows(lmb_ctx *ctx, const int *d_tokens, const lmb_weight *embed, size_t vocab, size_t h, size_t batch,
+                      float *d_hidden) {
+  dim3 grid(unsigned((h + 255) / 256), unsigned(batch));
+  k_embed_rows<<<grid, 256, 0, ctx->stream>>>(d_tokens, embed->kind, embed->d_tiles, embed->bpr, vocab, h, d_hidden);
+  ctx->launches++;
+  LMB_CUDA(cudaGetLastError());
+  return LMB_OK;
+}
+
+int launch_add_rmsnorm(lmb_ctx *ctx, float *d_hidden, const float *d_add, const float *d_w, float *d_out, size_t h,
+                       size_t batch, float eps) {
+  const int threads = h >= 4096 ? 1024 : (h >= 1024 ? 512 : 256);
+  k_add_rmsnorm<<<unsigned(batch), threads, 0, ctx->stream>>>(d_hidden, d_add, d_w, d_out, h, eps);
+  ctx->launches++;
+  LMB_CUDA(cudaGetLastError());
+  return LMB_OK;
+}
+
+int launch_rope_kv(lmb_ctx *ctx, float *q, float *k, const float *v, const float *qb, const float *kb, const float *vb,
+                   const float *cs_table, const size_t *positions, float *kv, size_t layer, const RopeDims &d, size_t batch) {
+  k_rope_kv<<<unsigned(batch), 256, 0, ctx->stream>>>(q, k, v, qb, kb, vb, cs_table, positions, kv, layer, d);
+  ctx->launches++;
+  LMB_CUDA(cudaGetLastError());
+  return LMB_OK;
+}
+
+int launch_decode_attn(lmb_ctx *ctx, const float *q, const float *kv, const size_t *positions, float *out, size_t layer,
+                       const RopeDims &d, size_t batch) {
+  if (d.hd > 256 || d.hd == 0 || 256 % d.hd != 0) {
+    set_last_error("decode attention: head_dim must divide 256");
+    return LMB_ERR_ARG;
+  }
+  const size_t smem = (d.max_seq + d.hd + 256) * sizeof(float);
+  dim3 grid(unsigned(d.nh), unsigned(batch));
+  k_decode_attn<<<grid, 256, smem, ctx->stream>>>(q, kv, positions, out, layer, d);
+  ctx->launches++;
+  LMB_CUDA(cudaGetLastError());
+  return LMB_OK;
+}
+
+int launch_silu_mul(lmb_ctx *ctx, const float *gate, const float *up, float *out, size_t n) {
+  k_silu_mul<<<unsigned((n + 255) / 256), 256, 0, ctx->stream>>>(gate, up, out, n);
+  ctx->launches++;
+  LMB_CUDA(cudaGetLastError());
+  return LMB_OK;
+}
+
+int configure_decode_ops(lmb_ctx *ctx) {
+  LMB_CUDA(cudaFuncSetAttribute(k_decode_attn, cudaFuncAttributeMaxDynamicSharedMemorySize, int(ctx->smem_optin)));
+  return LMB_OK;
+}
+
+}  // namespace lmb

@@ -1,0 +1,25 @@
+// Launchers of the decode-step glue kernels (decode_ops.cu).
+#pragma once
+
+#include "common.cuh"
+
+namespace lmb {
+
+struct RopeDims {
+  size_t nh, nkv, hd;   // local query heads, local KV heads, head dim
+  size_t max_seq;       // cache slots per sequence
+  size_t seq_stride;    // floats between the caches of consecutive sequences
+};
+
+int configure_decode_ops(lmb_ctx *ctx);
+int launch_embed_rows(lmb_ctx *ctx, const int *d_tokens, const lmb_weight *embed, size_t vocab, size_t h, size_t batch,
+                      float *d_hidden);
+int launch_add_rmsnorm(lmb_ctx *ctx, float *d_hidden, const float *d_add, const float *d_w, float *d_out, size_t h,
+                       size_t batch, float eps);
+int launch_rope_kv(lmb_ctx *ctx, float *q, float *k, const float *v, const float *qb, const float *kb, const float *vb,
+                   const float *cs_table, const size_t *positions, float *kv, size_t layer, const RopeDims &d, size_t batch);
+int launch_decode_attn(lmb_ctx *ctx, const float *q, const float *kv, const size_t *positions, float *out, size_t layer,
+                       const RopeDims &d, size_t batch);
+int launch_silu_mul(lmb_ctx *ctx, const float *gate, const float *up, float *out, size_t n);
+
+}  // namespace lmb
