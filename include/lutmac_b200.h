@@ -83,6 +83,15 @@ int lmb_host_free_pinned(void *h_ptr);
 int lmb_timer_start(lmb_ctx *ctx);
 int lmb_timer_stop(lmb_ctx *ctx, float *ms_out); /* records, synchronises, returns elapsed ms */
 
+/* CUDA-graph capture of the work a context issues (kernel launches only; no host-pointer entry
+ * point may be called while capturing).  lmb_graph_end returns an executable graph that
+ * lmb_graph_launch replays on the context's stream. */
+typedef struct lmb_graph lmb_graph;
+int lmb_graph_begin(lmb_ctx *ctx);
+int lmb_graph_end(lmb_ctx *ctx, lmb_graph **out);
+int lmb_graph_launch(lmb_ctx *ctx, lmb_graph *g);
+int lmb_graph_destroy(lmb_graph *g);
+
 /* ---- weights: replaces the host block vectors of PackedTensor (types.hpp:470-492) and the
  * raw struct reads of load_lutmac (src/format.cpp:463-496) --------------------------------------
  * `blocks` is the reference's row-major block array: row r starts at blocks + r*ceil(K/256).

@@ -50,6 +50,10 @@ SIGNATURES = {
     "lmb_host_free_pinned": (C.c_int, [vp]),
     "lmb_timer_start": (C.c_int, [vp]),
     "lmb_timer_stop": (C.c_int, [vp, f32p]),
+    "lmb_graph_begin": (C.c_int, [vp]),
+    "lmb_graph_end": (C.c_int, [vp, C.POINTER(vp)]),
+    "lmb_graph_launch": (C.c_int, [vp, vp]),
+    "lmb_graph_destroy": (C.c_int, [vp]),
     "lmb_weight_upload": (C.c_int, [vp, C.c_int, vp, sz, sz, C.POINTER(vp)]),
     "lmb_weight_upload_shard": (C.c_int, [vp, C.c_int, vp, sz, sz, sz, sz, sz, sz, C.POINTER(vp)]),
     "lmb_weight_free": (C.c_int, [vp]),

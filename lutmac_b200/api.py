@@ -71,6 +71,15 @@ class Context:
         check(lib().lmb_timer_stop(self.h, C.byref(ms)))
         return ms.value
 
+    # CUDA graphs -----------------------------------------------------------------------------
+    def graph_begin(self):
+        check(lib().lmb_graph_begin(self.h))
+
+    def graph_end(self) -> "Graph":
+        g = C.c_void_p()
+        check(lib().lmb_graph_end(self.h, C.byref(g)))
+        return Graph(self, g)
+
     # weights -----------------------------------------------------------------------------------
     def upload(self, t: PackedTensor, rows=None, blks=None) -> "DeviceWeight":
         return DeviceWeight(self, t, rows, blks)
@@ -91,6 +100,24 @@ def default_context(device: int = 0) -> Context:
     if device not in _default_ctx:
         _default_ctx[device] = Context(device)
     return _default_ctx[device]
+
+
+class Graph:
+    """An instantiated CUDA graph of kernel launches captured on a context."""
+
+    def __init__(self, ctx: Context, h):
+        self.ctx, self.h = ctx, h
+
+    def launch(self):
+        check(lib().lmb_graph_launch(self.ctx.h, self.h))
+
+    def __del__(self):
+        try:
+            if self.h:
+                lib().lmb_graph_destroy(self.h)
+                self.h = None
+        except Exception:
+            pass
 
 
 class DeviceBuffer:

@@ -281,6 +281,55 @@ int lmb_timer_stop(lmb_ctx *ctx, float *ms_out) {
   return LMB_OK;
 }
 
+// ---- CUDA graphs ------------------------------------------------------------------------------------
+struct lmb_graph {
+  cudaGraphExec_t exec = nullptr;
+  uint64_t launches = 0;  // kernels captured in the graph
+};
+
+int lmb_graph_begin(lmb_ctx *ctx) {
+  LMB_REQUIRE(ctx, "lmb_graph_begin: null context");
+  ctx->capture_base = ctx->launches;
+  LMB_CUDA(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+  return LMB_OK;
+}
+
+int lmb_graph_end(lmb_ctx *ctx, lmb_graph **out) {
+  LMB_REQUIRE(ctx && out, "lmb_graph_end: null argument");
+  *out = nullptr;
+  cudaGraph_t g = nullptr;
+  LMB_CUDA(cudaStreamEndCapture(ctx->stream, &g));
+  lmb_graph *h = new (std::nothrow) lmb_graph();
+  if (!h) {
+    cudaGraphDestroy(g);
+    return LMB_ERR_ALLOC;
+  }
+  cudaError_t e = cudaGraphInstantiate(&h->exec, g, 0);
+  cudaGraphDestroy(g);
+  if (e != cudaSuccess) {
+    delete h;
+    return cuda_fail(e, "cudaGraphInstantiate");
+  }
+  h->launches = ctx->launches - ctx->capture_base;
+  ctx->launches = ctx->capture_base;  // captured launches have not run yet
+  *out = h;
+  return LMB_OK;
+}
+
+int lmb_graph_launch(lmb_ctx *ctx, lmb_graph *g) {
+  LMB_REQUIRE(ctx && g && g->exec, "lmb_graph_launch: null argument");
+  LMB_CUDA(cudaGraphLaunch(g->exec, ctx->stream));
+  ctx->launches += g->launches;
+  return LMB_OK;
+}
+
+int lmb_graph_destroy(lmb_graph *g) {
+  if (!g) return LMB_OK;
+  if (g->exec) cudaGraphExecDestroy(g->exec);
+  delete g;
+  return LMB_OK;
+}
+
 // ---- weights ---------------------------------------------------------------------------------------
 int lmb_weight_upload_shard(lmb_ctx *ctx, int kind, const void *blocks, size_t M, size_t K, size_t row0,
                             size_t row1, size_t blk0, size_t blk1, lmb_weight **out) {

@@ -98,6 +98,7 @@ struct lmb_ctx {
   int sm_count = lmb::SM_COUNT_HINT;
   size_t smem_optin = 0;  // max dynamic shared memory per block
   uint64_t launches = 0;
+  uint64_t capture_base = 0;
   // scratch for split-K partial sums and its arrival counters (grown on demand)
   float *scratch = nullptr;
   size_t scratch_floats = 0;
