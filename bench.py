@@ -193,9 +193,26 @@ def run_ours(args):
             for w, x, y, K in row:
                 ctx.linear(w, x, y, flags=0, x_len=K, x_stride=K)
 
+    # throughput form: the 112 independent GEMVs of a pass as one prepared group (one launch);
+    # latency form (reported beside it): the same 112 GEMVs as a chain of single launches.
+    from lutmac_b200.api import Group
+    flat = [e for row in dev for e in row]
+    group = Group(ctx, [e[0] for e in flat], [e[1] for e in flat], [e[2] for e in flat], flags=0)
+    issue_suite()  # sizes the split-K scratch before capture
+    ctx.sync()
     ctx.graph_begin()
     issue_suite()
-    graph = ctx.graph_end()
+    chain = ctx.graph_end()
+    for _ in range(3):
+        chain.launch()
+    ctx.sync()
+    ctx.timer_start()
+    for _ in range(10):
+        chain.launch()
+    chain_ms = ctx.timer_stop() / 10
+
+    class graph:  # the timed step
+        launch = staticmethod(group.launch)
 
     def barrier():
         ctx.sync()
@@ -256,15 +273,16 @@ def run_ours(args):
     if rank != 0:
         return
     peak, peak_src = load_peaks()
-    per_launch_bytes = step_bytes / (N_LAYERS * 7)
+    per_launch_bytes = step_bytes  # one launch per step
     achieved = step_bytes * args.steps / (ms * 1e-3) / 1e9  # this rank: all launches are the same kernel
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
             "config": {"workload": WORKLOAD, "l2_policy": "inputs larger than L2 (501.7 MB of weights per step)",
-                       "launch": "one CUDA graph of 112 GEMV launches per step"},
+                       "launch": "112 GEMVs per step as one prepared group launch (lmb_group_launch)",
+                       "chain_of_112_single_launches_gbs": step_bytes / (chain_ms * 1e-3) / 1e9},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,
-                         "peak_source": peak_src, "kernel": "k_gemv_dq<int4>",
+                         "peak_source": peak_src, "kernel": "k_gemv<int4>",
                          "algorithmic_bytes_per_launch": per_launch_bytes, "traffic": load_traffic()},
             "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "call": "lmb_linear_host_multi per layer (7 lut_linear, host in/out)"},

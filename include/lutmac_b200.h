@@ -122,6 +122,15 @@ int lmb_untile_host(int kind, const void *tiled, size_t M, size_t K, void *block
 int lmb_linear(lmb_ctx *ctx, const lmb_weight *w, const float *d_bias, const float *d_x, size_t x_len,
                size_t x_stride, float *d_y, size_t batch, unsigned flags);
 
+/* Prepared group: n independent batch-1 lut_linear calls of one block kind (inputs d_xs[i] of K_i
+ * floats, outputs d_ys[i] of M_i floats, device pointers) planned once and issued as a single
+ * kernel launch.  The reference issues them one by one (e.g. q/k/v at src/model.cpp:307-309). */
+typedef struct lmb_group lmb_group;
+int lmb_group_create(lmb_ctx *ctx, size_t n, const lmb_weight *const *ws, const float *const *d_xs, float *const *d_ys,
+                     unsigned flags, lmb_group **out);
+int lmb_group_launch(lmb_ctx *ctx, lmb_group *g);
+int lmb_group_destroy(lmb_group *g);
+
 /* ---- kernel API on host pointers: replaces the dispatchers lut_gemv, lut_gemv_binary,
  * int2_gemv ... int8_gemv (include/lutmac/lut_gemm.hpp:172-408) -----------------------------------
  * Same arguments as the reference: activations must be readable for ceil(K/256)*256 floats,

@@ -120,6 +120,32 @@ class Graph:
             pass
 
 
+class Group:
+    """n independent batch-1 lut_linear calls of one block kind, planned once, one launch."""
+
+    def __init__(self, ctx: Context, weights, xs, ys, flags: int = _lib.AUTO_ROTATE):
+        n = len(weights)
+        self.ctx = ctx
+        self._keep = (list(weights), list(xs), list(ys))
+        W = (C.c_void_p * n)(*[w.h for w in weights])
+        X = (C.c_void_p * n)(*[x.ptr for x in xs])
+        Y = (C.c_void_p * n)(*[y.ptr for y in ys])
+        h = C.c_void_p()
+        check(lib().lmb_group_create(ctx.h, n, W, X, Y, flags, C.byref(h)))
+        self.h = h
+
+    def launch(self):
+        check(lib().lmb_group_launch(self.ctx.h, self.h))
+
+    def __del__(self):
+        try:
+            if self.h:
+                lib().lmb_group_destroy(self.h)
+                self.h = None
+        except Exception:
+            pass
+
+
 class DeviceBuffer:
     def __init__(self, ctx: Context, nbytes: int):
         self.ctx = ctx

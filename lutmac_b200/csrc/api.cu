@@ -103,7 +103,7 @@ static int linear_impl(lmb_ctx *ctx, const lmb_weight *w, const float *d_bias, c
   // (lut_gemm_scalar.cpp:92-93): ternary, binary and 2-bit tensors.
   const bool auto_rot = (w->kind == LMB_TERNARY || w->kind == LMB_BINARY || w->kind == LMB_INT2);
   a.rotate = (flags & LMB_ROTATE) || ((flags & LMB_AUTO_ROTATE) && auto_rot);
-  return kind_info(w->kind).lut ? launch_gemv_lut(ctx, a) : launch_gemv_dq(ctx, a);
+  return launch_gemv(ctx, &a, 1, a.rotate);
 }
 
 static std::mutex g_default_mu;
@@ -177,8 +177,10 @@ int lmb_ctx_create(int device, lmb_ctx **out) {
     return cuda_fail(e, "lmb_ctx_create");
   }
   ctx->stream = ctx->own_stream;
-  int st = configure_gemv_lut(ctx);
-  if (st == LMB_OK) st = configure_gemv_dq(ctx);
+  const char *pdl_env = getenv("LMB_PDL");
+  ctx->pdl = !(pdl_env && pdl_env[0] == '0');
+  int st = configure_gemv(ctx);
+  if (st == LMB_OK) st = ensure_scratch(ctx, size_t(4) << 20, size_t(1) << 16);
   if (st != LMB_OK) {
     lmb_ctx_destroy(ctx);
     return st;

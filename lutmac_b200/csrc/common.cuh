@@ -99,6 +99,9 @@ struct lmb_ctx {
   size_t smem_optin = 0;  // max dynamic shared memory per block
   uint64_t launches = 0;
   uint64_t capture_base = 0;
+  void *comm = nullptr;  // NCCL communicator (tensor parallelism)
+  int tp_rank = 0, tp_size = 1;
+  bool pdl = true;  // programmatic dependent launch between consecutive kernels
   // scratch for split-K partial sums and its arrival counters (grown on demand)
   float *scratch = nullptr;
   size_t scratch_floats = 0;
@@ -134,10 +137,8 @@ struct LinearArgs {
   size_t batch;
   bool rotate;
 };
-int configure_gemv_lut(lmb_ctx *ctx);
-int configure_gemv_dq(lmb_ctx *ctx);
-int launch_gemv_lut(lmb_ctx *ctx, const LinearArgs &a);
-int launch_gemv_dq(lmb_ctx *ctx, const LinearArgs &a);
+int configure_gemv(lmb_ctx *ctx);
+int launch_gemv(lmb_ctx *ctx, const LinearArgs *args, int njobs, bool rotate);
 int launch_fwht256(lmb_ctx *ctx, float *d_x, size_t n);
 int launch_debug_luts(lmb_ctx *ctx, const float *d_x, size_t x_len, bool rotate, float *d_out);
 

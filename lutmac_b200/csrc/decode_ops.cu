@@ -254,7 +254,7 @@ int launch_silu_mul(lmb_ctx *ctx, const float *gate, const float *up, float *out
 }
 
 int configure_decode_ops(lmb_ctx *ctx) {
-  LMB_CUDA(cudaFuncSetAttribute(k_decode_attn, cudaFuncAttributeMaxDynamicSharedMemorySize, int(ctx->smem_optin)));
+  LMB_CUDA(cudaFuncSetAttribute(k_decode_attn, cudaFuncAttributeMaxDynamicSharedMemorySize, int(ctx->smem_optin) - 1024));
   return LMB_OK;
 }
 

@@ -1,0 +1,644 @@
+// GEMV kernels for every block kind, with the lut_linear prologue (zero padding, block-wise
+// FWHT rotation, group-of-4 table construction) and epilogue (block scales, RRQ residual
+// plane, bias) fused in.
+//
+// Replaces, for the bit-plane kinds (ternary, binary, RRQ 2-bit, 3-bit): lut_gemv /
+// lut_gemv_binary / int2_gemv / int3_gemv (include/lutmac/lut_gemm.hpp:172-334, scalar loops
+// src/kernels/lut_gemm_scalar.cpp:7-61,228-259,298-350) in the lookup formulation of the
+// reference's table kernels -- ternary L[pos]-L[neg] (lut_gemm_simd.cpp:203-221), n-bit planes
+// sum_p 2^p L[idx_p] - zero_point*L[15] (lut_gemm_simd.cpp:352-366), RRQ primary*scale +
+// residual*scale2 (lut_gemm_simd.cpp:326-328) -- and for the nibble/byte kinds (4-bit, 8-bit):
+// int4_gemv / int8_gemv (lut_gemm.hpp:238-250,396-408; lut_gemm_scalar.cpp:186-222,265-292).
+// Prologue/epilogue: lut_linear (lut_gemm_scalar.cpp:85-113,174-178), precompute_luts
+// (lut_gemm.hpp:53-58), apply_hadamard_rotation (transform_simd.cpp:101-110).
+//
+// Work decomposition.  One launch serves up to MAX_JOBS independent GEMVs of one kind (q/k/v
+// or gate/up of a layer share a launch).  A CTA of 8 warps owns a work item = (job, group of R
+// row-tiles of 32 rows, slice of S consecutive 256-column blocks).  A warp streams the weight
+// tiles of one row-tile, one row per lane, with 128-bit coalesced loads.  Bit-plane kinds look
+// each 4-bit plane nibble up in the 16-entry table of its group: all lanes of a warp address
+// the same 64-byte table, 16 entries in 16 distinct banks, so lookups never conflict.  When K
+// is split over several CTAs, partial sums go to a scratch buffer and the last CTA to arrive
+// for a row group adds them in slice order (deterministic).
+//
+// Programmatic dependent launch: a kernel lets its successor start at once, the successor
+// prefetches its first weight tiles (weights never depend on a predecessor) and only then
+// waits for the predecessor's results before touching activations or writing anything.
+#include <new>
+#include <vector>
+
+#include "common.cuh"
+#include "device_utils.cuh"
+
+namespace lmb {
+
+namespace {
+
+constexpr int WARPS = 8;
+constexpr int THREADS = WARPS * 32;
+constexpr int MAX_JOBS = 4;
+
+struct Job {
+  const uint8_t *tiles;
+  const float *x;
+  float *y;
+  const float *bias;
+  float *scratch;       // [batch][n_ks][mp] partial sums (n_ks > 1 only)
+  unsigned *counters;   // [batch][n_rg] arrival counters (n_ks > 1 only)
+  int M, mp, bpr, row_tiles;
+  int R, S, n_rg, n_ks;
+  int cta_end;          // exclusive prefix of CTAs over the jobs of the launch
+  unsigned x_len, x_stride, y_stride;
+};
+
+struct GemvParams {
+  Job job[MAX_JOBS];
+  int njobs;
+  int rotate;
+  // a prepared group of any number of jobs: job table and per-CTA (job, first CTA of the job)
+  // pairs in device memory; null for ordinary launches
+  const Job *jobs_dev;
+  const int2 *cta_map;
+};
+
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+template <int IMM> __device__ __forceinline__ float lds_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1+%2];" : "=f"(v) : "r"(addr), "n"(IMM) : "memory");
+  return v;
+}
+// (a & b) | c in one LOP3
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t r;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+  return r;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Bit-plane kinds: table lookups
+// ---------------------------------------------------------------------------------------------
+
+// Sum of the 8 lookups addressed by the 8 nibbles of `w` (4 plane bytes, little endian; byte k
+// holds group 2k in its high nibble and group 2k+1 in its low nibble) into 8 consecutive group
+// tables; `tb` is the shared-memory byte address of the block's tables (1 KiB aligned) and G0
+// the first group.  Index extraction is one shift and one LOP3 that masks the nibble (already
+// scaled by 4) and ORs in the table base; the group offset rides in the load's immediate.
+template <int G0> __device__ __forceinline__ float lut_word(uint32_t w, uint32_t tb) {
+  float s0, s1;
+  s0 = lds_f32<(G0 + 0) * 64>(and_or(w >> 2, 0x3Cu, tb));
+  s1 = lds_f32<(G0 + 1) * 64>(and_or(w << 2, 0x3Cu, tb));
+  s0 += lds_f32<(G0 + 2) * 64>(and_or(w >> 10, 0x3Cu, tb));
+  s1 += lds_f32<(G0 + 3) * 64>(and_or(w >> 6, 0x3Cu, tb));
+  s0 += lds_f32<(G0 + 4) * 64>(and_or(w >> 18, 0x3Cu, tb));
+  s1 += lds_f32<(G0 + 5) * 64>(and_or(w >> 14, 0x3Cu, tb));
+  s0 += lds_f32<(G0 + 6) * 64>(and_or(w >> 26, 0x3Cu, tb));
+  s1 += lds_f32<(G0 + 7) * 64>(and_or(w >> 22, 0x3Cu, tb));
+  return s0 + s1;
+}
+template <int G0> __device__ __forceinline__ float lut_8bytes(uint32_t lo, uint32_t hi, uint32_t tb) {
+  return lut_word<G0>(lo, tb) + lut_word<G0 + 8>(hi, tb);
+}
+template <int G0> __device__ __forceinline__ float lut_16bytes(const uint4 v, uint32_t tb) {
+  return (lut_word<G0>(v.x, tb) + lut_word<G0 + 8>(v.y, tb)) + (lut_word<G0 + 16>(v.z, tb) + lut_word<G0 + 24>(v.w, tb));
+}
+
+template <int KIND> struct Unit;  // one (row-tile, 256-column block): a lane's payload + scales
+
+template <int KIND> struct LutUnit {
+  static constexpr int C = kind_info(KIND).chunks;
+  static constexpr int NS = kind_info(KIND).nscales;
+  static constexpr int FPB = 1024;  // shared-memory floats per 256-column block: 64 tables x 16
+  uint4 v[C];
+  float sc[NS];
+
+  __device__ __forceinline__ void load(const uint8_t *tile, int lane) {
+#pragma unroll
+    for (int c = 0; c < C; ++c) v[c] = ld_stream_v4(tile + (size_t(c) * TILE_ROWS + lane) * 16);
+#pragma unroll
+    for (int s = 0; s < NS; ++s) sc[s] = ld_stream_f32(tile + size_t(C) * TILE_ROWS * 16 + (size_t(s) * TILE_ROWS + lane) * 4);
+  }
+
+  // scale * sum_i w_i x_i of this row-block
+  __device__ __forceinline__ float eval(const float *blk, float xsum) const {
+    const uint32_t tb = smem_u32(blk);
+    if constexpr (KIND == LMB_TERNARY) {
+      const float p = (lut_8bytes<0>(v[0].x, v[0].y, tb) + lut_8bytes<16>(v[1].x, v[1].y, tb)) +
+                      (lut_8bytes<32>(v[2].x, v[2].y, tb) + lut_8bytes<48>(v[3].x, v[3].y, tb));
+      const float n = (lut_8bytes<0>(v[0].z, v[0].w, tb) + lut_8bytes<16>(v[1].z, v[1].w, tb)) +
+                      (lut_8bytes<32>(v[2].z, v[2].w, tb) + lut_8bytes<48>(v[3].z, v[3].w, tb));
+      return (p - n) * sc[0];
+    } else if constexpr (KIND == LMB_BINARY) {
+      const float a = lut_16bytes<0>(v[0], tb) + lut_16bytes<32>(v[1], tb);
+      return (2.0f * a - xsum) * sc[0];
+    } else if constexpr (KIND == LMB_INT2) {
+      const float a1 = (lut_8bytes<0>(v[0].x, v[0].y, tb) + lut_8bytes<16>(v[1].x, v[1].y, tb)) +
+                       (lut_8bytes<32>(v[2].x, v[2].y, tb) + lut_8bytes<48>(v[3].x, v[3].y, tb));
+      const float a2 = (lut_8bytes<0>(v[0].z, v[0].w, tb) + lut_8bytes<16>(v[1].z, v[1].w, tb)) +
+                       (lut_8bytes<32>(v[2].z, v[2].w, tb) + lut_8bytes<48>(v[3].z, v[3].w, tb));
+      return (2.0f * a1 - xsum) * sc[0] + (2.0f * a2 - xsum) * sc[1];
+    } else {  // LMB_INT3: chunk 3j+p holds plane 2-p of weights 128j..128j+127
+      const float q2 = lut_16bytes<0>(v[0], tb) + lut_16bytes<32>(v[3], tb);
+      const float q1 = lut_16bytes<0>(v[1], tb) + lut_16bytes<32>(v[4], tb);
+      const float q0 = lut_16bytes<0>(v[2], tb) + lut_16bytes<32>(v[5], tb);
+      return ((4.0f * q2 + 2.0f * q1 + q0) - 4.0f * xsum) * sc[0];
+    }
+  }
+
+  // Prologue for one 256-block by one warp: load (zero padded), optionally rotate, stage the
+  // 256 values in the block's table area, then build the 64 tables with one (group,
+  // quarter-table) pair per lane and pass, so that the 128-bit table stores are contiguous
+  // across the warp (no bank conflicts).  Addition order per entry is the reference's
+  // (a0, a1, a2, a3 left to right, lut_gemm.hpp:30-44).
+  static __device__ __forceinline__ void prologue(const float *x, size_t x_len, size_t b, bool rotate, int lane,
+                                                  float *blk, float *xsum) {
+    float v[8];
+    load_x8(x, x_len, b, lane, v);
+    if (rotate) fwht256_warp(v, lane);
+    float s = (((v[0] + v[1]) + v[2]) + v[3]) + (((v[4] + v[5]) + v[6]) + v[7]);
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) s += __shfl_xor_sync(0xffffffffu, s, m);
+    if (lane == 0) *xsum = s;
+    float *stage = blk + 768;  // read back in full before any table is stored
+    reinterpret_cast<float4 *>(stage)[2 * lane] = make_float4(v[0], v[1], v[2], v[3]);
+    reinterpret_cast<float4 *>(stage)[2 * lane + 1] = make_float4(v[4], v[5], v[6], v[7]);
+    __syncwarp();
+    const int q = lane & 3;
+    float4 a[8];
+#pragma unroll
+    for (int pass = 0; pass < 8; ++pass) a[pass] = reinterpret_cast<const float4 *>(stage)[pass * 8 + (lane >> 2)];
+    __syncwarp();
+#pragma unroll
+    for (int pass = 0; pass < 8; ++pass) {
+      const int g = pass * 8 + (lane >> 2);
+      const float a0 = a[pass].x, a1 = a[pass].y, a2 = a[pass].z, a3 = a[pass].w;
+      const float base = (q == 0) ? 0.0f : (q == 1) ? a1 : (q == 2) ? a0 : (a0 + a1);
+      const float e2 = base + a2;
+      reinterpret_cast<float4 *>(blk + g * 16)[q] = make_float4(base, base + a3, e2, e2 + a3);
+    }
+  }
+};
+
+template <> struct Unit<LMB_TERNARY> : LutUnit<LMB_TERNARY> {};
+template <> struct Unit<LMB_BINARY> : LutUnit<LMB_BINARY> {};
+template <> struct Unit<LMB_INT2> : LutUnit<LMB_INT2> {};
+template <> struct Unit<LMB_INT3> : LutUnit<LMB_INT3> {};
+
+// ---------------------------------------------------------------------------------------------
+// Nibble / byte kinds: dequantise + FMA.  Codes become fp32 without integer-to-float
+// conversions: a nibble (or byte) is OR-ed into the mantissa of 2^23 and one exact subtraction
+// removes 2^23 together with the code's zero point (8 for 4-bit; 128 after the sign flip for
+// 8-bit).  A nibble that sits p bits up in its word is not shifted down: it yields (q-8)*2^p,
+// is accumulated in a slot of its own, and the slot is rescaled by 2^-p once per row-block
+// (both scalings are exact).  Subtract and multiply-add run as packed fp32 pairs.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float as_f(uint32_t u) { return __uint_as_float(u); }
+constexpr uint32_t MAGIC = 0x4B000000u;  // 2^23
+__device__ __forceinline__ constexpr float nib_bias(int p) { return -(8388608.0f + 8.0f * float(1 << p)); }
+
+// 8 weights of one word of 4-bit codes (byte j: weight 2j in the high nibble, 2j+1 in the low
+// nibble, types.hpp:184-190) times 8 activations {xa, xb}.
+__device__ __forceinline__ void int4_word(uint32_t w, const float4 xa, const float4 xb, float2 acc[4]) {
+  const uint32_t h = w >> 12;  // brings bits 20..31 down to 8..19
+  float2 g;
+  g = add2(make_float2(as_f((w & 0x000000F0u) | MAGIC), as_f((w & 0x0000000Fu) | MAGIC)), make_float2(nib_bias(4), nib_bias(0)));
+  fma2(acc[0], g, make_float2(xa.x, xa.y));
+  g = add2(make_float2(as_f((w & 0x0000F000u) | MAGIC), as_f((w & 0x00000F00u) | MAGIC)), make_float2(nib_bias(12), nib_bias(8)));
+  fma2(acc[1], g, make_float2(xa.z, xa.w));
+  g = add2(make_float2(as_f((h & 0x00000F00u) | MAGIC), as_f((w & 0x000F0000u) | MAGIC)), make_float2(nib_bias(8), nib_bias(16)));
+  fma2(acc[2], g, make_float2(xb.x, xb.y));
+  g = add2(make_float2(as_f((h & 0x000F0000u) | MAGIC), as_f((h & 0x0000F000u) | MAGIC)), make_float2(nib_bias(16), nib_bias(12)));
+  fma2(acc[3], g, make_float2(xb.z, xb.w));
+}
+__device__ __forceinline__ float int4_finish(const float2 acc[4]) {
+  // slot scalings: acc0 (2^4, 1), acc1 (2^12, 2^8), acc2 (2^8, 2^16), acc3 (2^16, 2^12)
+  const float s0 = acc[0].y + acc[0].x * 0.0625f;
+  const float s8 = (acc[1].y + acc[2].x) * (1.0f / 256.0f);
+  const float s12 = (acc[1].x + acc[3].y) * (1.0f / 4096.0f);
+  const float s16 = (acc[2].y + acc[3].x) * (1.0f / 65536.0f);
+  return (s0 + s8) + (s12 + s16);
+}
+// 4 weights of one word of int8 codes times 4 activations.
+__device__ __forceinline__ void int8_word(uint32_t w, const float4 xv, float2 acc[2]) {
+  const uint32_t u = w ^ 0x80808080u;  // q + 128 in every byte
+  const float2 c = make_float2(-(8388608.0f + 128.0f), -(8388608.0f + 128.0f));
+  float2 g;
+  g = add2(make_float2(as_f(__byte_perm(u, MAGIC, 0x7540)), as_f(__byte_perm(u, MAGIC, 0x7541))), c);
+  fma2(acc[0], g, make_float2(xv.x, xv.y));
+  g = add2(make_float2(as_f(__byte_perm(u, MAGIC, 0x7542)), as_f(__byte_perm(u, MAGIC, 0x7543))), c);
+  fma2(acc[1], g, make_float2(xv.z, xv.w));
+}
+
+// Shared prologue of the dequantise kinds: the (padded, optionally rotated) block itself.
+__device__ __forceinline__ void dq_prologue(const float *x, size_t x_len, size_t b, bool rotate, int lane, float *blk) {
+  float v[8];
+  load_x8(x, x_len, b, lane, v);
+  if (rotate) fwht256_warp(v, lane);
+  reinterpret_cast<float4 *>(blk)[2 * lane] = make_float4(v[0], v[1], v[2], v[3]);
+  reinterpret_cast<float4 *>(blk)[2 * lane + 1] = make_float4(v[4], v[5], v[6], v[7]);
+}
+
+template <> struct Unit<LMB_INT4> {
+  static constexpr int FPB = 256;
+  uint4 v[8];
+  float sc;
+  __device__ __forceinline__ void load(const uint8_t *tile, int lane) {
+#pragma unroll
+    for (int c = 0; c < 8; ++c) v[c] = ld_stream_v4(tile + (size_t(c) * TILE_ROWS + lane) * 16);
+    sc = ld_stream_f32(tile + size_t(8) * TILE_ROWS * 16 + size_t(lane) * 4);
+  }
+  __device__ __forceinline__ float eval(const float *blk, float) const {
+    const float4 *x4 = reinterpret_cast<const float4 *>(blk);
+    float2 acc[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      int4_word(v[c].x, x4[8 * c + 0], x4[8 * c + 1], acc);
+      int4_word(v[c].y, x4[8 * c + 2], x4[8 * c + 3], acc);
+      int4_word(v[c].z, x4[8 * c + 4], x4[8 * c + 5], acc);
+      int4_word(v[c].w, x4[8 * c + 6], x4[8 * c + 7], acc);
+    }
+    return int4_finish(acc) * sc;
+  }
+  static __device__ __forceinline__ void prologue(const float *x, size_t x_len, size_t b, bool rotate, int lane,
+                                                  float *blk, float *) {
+    dq_prologue(x, x_len, b, rotate, lane, blk);
+  }
+};
+
+template <> struct Unit<LMB_INT8> {
+  static constexpr int FPB = 256;
+  uint4 v[16];
+  float sc;
+  __device__ __forceinline__ void load(const uint8_t *tile, int lane) {
+#pragma unroll
+    for (int c = 0; c < 16; ++c) v[c] = ld_stream_v4(tile + (size_t(c) * TILE_ROWS + lane) * 16);
+    sc = ld_stream_f32(tile + size_t(16) * TILE_ROWS * 16 + size_t(lane) * 4);
+  }
+  __device__ __forceinline__ float eval(const float *blk, float) const {
+    const float4 *x4 = reinterpret_cast<const float4 *>(blk);
+    float2 acc[2] = {{0.f, 0.f}, {0.f, 0.f}};
+#pragma unroll
+    for (int c = 0; c < 16; ++c) {
+      int8_word(v[c].x, x4[4 * c + 0], acc);
+      int8_word(v[c].y, x4[4 * c + 1], acc);
+      int8_word(v[c].z, x4[4 * c + 2], acc);
+      int8_word(v[c].w, x4[4 * c + 3], acc);
+    }
+    return ((acc[0].x + acc[0].y) + (acc[1].x + acc[1].y)) * sc;
+  }
+  static __device__ __forceinline__ void prologue(const float *x, size_t x_len, size_t b, bool rotate, int lane,
+                                                  float *blk, float *) {
+    dq_prologue(x, x_len, b, rotate, lane, blk);
+  }
+};
+
+// ---------------------------------------------------------------------------------------------
+// The kernel
+// ---------------------------------------------------------------------------------------------
+template <int KIND>
+__global__ void __launch_bounds__(THREADS) k_gemv(const __grid_constant__ GemvParams p) {
+  using U = Unit<KIND>;
+  constexpr int FPB = U::FPB;
+  constexpr bool PREFETCH = kind_info(KIND).chunks <= 8;  // double-buffer a unit in registers
+  constexpr size_t TB = tile_bytes(KIND);
+  extern __shared__ __align__(1024) float smem[];
+  __shared__ float part[THREADS];
+  __shared__ float xsum[64];
+  __shared__ int is_last;
+
+  pdl_launch_dependents();
+
+  // work item of this CTA
+  int j = 0, first = 0;
+  if (p.jobs_dev) {
+    const int2 m = p.cta_map[blockIdx.x];
+    j = m.x;
+    first = m.y;
+  } else {
+    while (j + 1 < p.njobs && int(blockIdx.x) >= p.job[j].cta_end) ++j;
+    first = j ? p.job[j - 1].cta_end : 0;
+  }
+  const Job &job = p.jobs_dev ? p.jobs_dev[j] : p.job[j];
+  const int local = int(blockIdx.x) - first;
+  const int rg = local / job.n_ks, ks = local - rg * job.n_ks;
+  const int batch = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rt0 = rg * job.R;
+  const int nrt = min(job.R, job.row_tiles - rt0);
+  const int wpr = WARPS / job.R;  // warps sharing one row-tile
+  const int rtl = warp / wpr, sub = warp - rtl * wpr;
+  const int b0 = ks * job.S;
+  const int ns = min(job.S, job.bpr - b0);
+  const bool active = rtl < nrt && sub < ns;
+  const uint8_t *row_tiles = job.tiles + (size_t(rt0 + rtl) * job.bpr + b0) * TB;
+
+  // weights do not depend on the preceding kernel: fetch the first unit before waiting for it
+  U cur;
+  if (active) cur.load(row_tiles + size_t(sub) * TB, lane);
+
+  pdl_wait();
+
+  const float *x = job.x + size_t(batch) * job.x_stride;
+  for (int bl = warp; bl < ns; bl += WARPS)
+    U::prologue(x, job.x_len, size_t(b0 + bl), p.rotate != 0, lane, smem + size_t(bl) * FPB, xsum + bl);
+  __syncthreads();
+
+  float acc = 0.0f;
+  if (active) {
+    for (int bl = sub; bl < ns; bl += wpr) {
+      const bool more = bl + wpr < ns;
+      if constexpr (PREFETCH) {
+        U nxt;
+        if (more) nxt.load(row_tiles + size_t(bl + wpr) * TB, lane);
+        acc += cur.eval(smem + size_t(bl) * FPB, xsum[bl]);
+        if (more) cur = nxt;
+      } else {
+        acc += cur.eval(smem + size_t(bl) * FPB, xsum[bl]);
+        if (more) cur.load(row_tiles + size_t(bl + wpr) * TB, lane);
+      }
+    }
+  }
+
+  // combine the warps that share a row-tile, in warp order: thread t ends up with row rt0*32 + t
+  part[threadIdx.x] = acc;
+  __syncthreads();
+  const int t = threadIdx.x;
+  const bool owns_row = t < nrt * TILE_ROWS;
+  float s = 0.0f;
+  if (owns_row) {
+    const int r = t >> 5;
+    for (int k = 0; k < wpr; ++k) s += part[(r * wpr + k) * 32 + (t & 31)];
+  }
+  const int row = rt0 * TILE_ROWS + t;
+  if (job.n_ks == 1) {
+    if (owns_row && row < job.M) {
+      if (job.bias) s += job.bias[row];
+      job.y[size_t(batch) * job.y_stride + row] = s;
+    }
+    return;
+  }
+  // split K: publish the partial sums, the last slice to arrive adds them in slice order
+  float *scr = job.scratch + size_t(batch) * job.n_ks * job.mp;
+  if (owns_row) scr[size_t(ks) * job.mp + row] = s;
+  __threadfence();
+  __syncthreads();
+  unsigned *ctr = job.counters + size_t(batch) * job.n_rg + rg;
+  if (t == 0) is_last = (atomicAdd(ctr, 1u) == unsigned(job.n_ks - 1));
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  if (owns_row && row < job.M) {
+    float tot = 0.0f;
+    for (int k = 0; k < job.n_ks; ++k) tot += __ldcg(scr + size_t(k) * job.mp + row);
+    if (job.bias) tot += job.bias[row];
+    job.y[size_t(batch) * job.y_stride + row] = tot;
+  }
+  if (t == 0) *ctr = 0u;  // ready for the next launch
+}
+
+// Tables only (debug view used by the parity tests): the same prologue, one warp per block.
+__global__ void k_debug_luts(const float *x, size_t x_len, int nblocks, int rotate, float *out) {
+  __shared__ __align__(1024) float tab[WARPS][1024];
+  __shared__ float xs[WARPS];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.x * WARPS + warp;
+  if (b < nblocks) {
+    LutUnit<LMB_TERNARY>::prologue(x, x_len, size_t(b), rotate != 0, lane, tab[warp], &xs[warp]);
+    __syncwarp();
+    for (int i = lane; i < 1024; i += 32) out[size_t(b) * 1024 + i] = tab[warp][i];
+  }
+}
+
+struct Plan {
+  int R, S, n_rg, n_ks, ctas;
+};
+
+Plan make_plan(int kind, size_t row_tiles, size_t bpr, size_t batch, int sm_count) {
+  Plan pl;
+  int R = 8;
+  while (R > 1 && size_t(R) > row_tiles) R >>= 1;
+  pl.R = R;
+  pl.n_rg = int((row_tiles + R - 1) / R);
+  const int s_cap = kind_info(kind).lut ? 12 : 48;  // 48 KiB of tables / activations per CTA
+  const size_t target = size_t(2) * sm_count;  // split K only while the row groups alone leave SMs idle
+  size_t n_ks = (target + pl.n_rg * batch - 1) / (pl.n_rg * batch);
+  n_ks = n_ks < 1 ? 1 : (n_ks > bpr ? bpr : n_ks);
+  size_t S = (bpr + n_ks - 1) / n_ks;
+  if (S > size_t(s_cap)) S = s_cap;
+  pl.S = int(S);
+  pl.n_ks = int((bpr + S - 1) / S);
+  pl.ctas = pl.n_rg * pl.n_ks;
+  return pl;
+}
+
+// Plans every job of a launch and fills the job descriptors (scratch regions are carved out of
+// the context's scratch buffer, which is grown here when the stream is not capturing).
+int prepare_jobs(lmb_ctx *ctx, int kind, const LinearArgs *args, int njobs, Job *jobs, int *ctas_out, int *s_max_out,
+                 std::vector<int2> *cta_map) {
+  const size_t batch = args[0].batch;
+  std::vector<Plan> plans(static_cast<size_t>(njobs));
+  size_t scratch_need = 0, counter_need = 0;
+  for (int j = 0; j < njobs; ++j) {
+    const lmb_weight *w = args[j].w;
+    plans[size_t(j)] = make_plan(kind, w->row_tiles, w->bpr, batch, ctx->sm_count);
+    if (plans[size_t(j)].n_ks > 1) {
+      scratch_need += batch * plans[size_t(j)].n_ks * w->row_tiles * TILE_ROWS;
+      counter_need += batch * plans[size_t(j)].n_rg;
+    }
+  }
+  if (scratch_need > ctx->scratch_floats || counter_need > ctx->n_counters) {
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    LMB_CUDA(cudaStreamIsCapturing(ctx->stream, &cs));
+    if (cs != cudaStreamCaptureStatusNone) {
+      set_last_error("split-K scratch too small while the stream is capturing; run the call once outside capture");
+      return LMB_ERR_STATE;
+    }
+    LMB_CUDA(cudaStreamSynchronize(ctx->stream));
+    int st = ensure_scratch(ctx, scratch_need, counter_need);
+    if (st != LMB_OK) return st;
+  }
+  size_t scratch_off = 0, counter_off = 0;
+  int ctas = 0, s_max = 1;
+  for (int j = 0; j < njobs; ++j) {
+    const lmb_weight *w = args[j].w;
+    const Plan &pl = plans[size_t(j)];
+    Job &jb = jobs[j];
+    jb.tiles = w->d_tiles;
+    jb.x = args[j].x;
+    jb.y = args[j].y;
+    jb.bias = args[j].bias;
+    jb.M = int(w->M);
+    jb.mp = int(w->row_tiles * TILE_ROWS);
+    jb.bpr = int(w->bpr);
+    jb.row_tiles = int(w->row_tiles);
+    jb.R = pl.R;
+    jb.S = pl.S;
+    jb.n_rg = pl.n_rg;
+    jb.n_ks = pl.n_ks;
+    jb.x_len = unsigned(args[j].x_len);
+    jb.x_stride = unsigned(args[j].x_stride);
+    jb.y_stride = unsigned(args[j].y_stride);
+    jb.scratch = ctx->scratch + scratch_off;
+    jb.counters = ctx->counters + counter_off;
+    if (pl.n_ks > 1) {
+      scratch_off += batch * pl.n_ks * jb.mp;
+      counter_off += batch * pl.n_rg;
+    }
+    if (cta_map)
+      for (int c = 0; c < pl.ctas; ++c) cta_map->push_back(make_int2(j, ctas));
+    ctas += pl.ctas;
+    jb.cta_end = ctas;
+    s_max = pl.S > s_max ? pl.S : s_max;
+  }
+  *ctas_out = ctas;
+  *s_max_out = s_max;
+  return LMB_OK;
+}
+
+template <int KIND> int launch_params(lmb_ctx *ctx, const GemvParams &p, int ctas, int s_max, size_t batch) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(unsigned(ctas), unsigned(batch));
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = size_t(s_max) * Unit<KIND>::FPB * sizeof(float);
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = ctx->pdl ? 1 : 0;
+  LMB_CUDA(cudaLaunchKernelEx(&cfg, k_gemv<KIND>, p));
+  ctx->launches++;
+  return LMB_OK;
+}
+
+int launch_params_kind(lmb_ctx *ctx, int kind, const GemvParams &p, int ctas, int s_max, size_t batch) {
+  switch (kind) {
+  case LMB_TERNARY: return launch_params<LMB_TERNARY>(ctx, p, ctas, s_max, batch);
+  case LMB_BINARY: return launch_params<LMB_BINARY>(ctx, p, ctas, s_max, batch);
+  case LMB_INT2: return launch_params<LMB_INT2>(ctx, p, ctas, s_max, batch);
+  case LMB_INT3: return launch_params<LMB_INT3>(ctx, p, ctas, s_max, batch);
+  case LMB_INT4: return launch_params<LMB_INT4>(ctx, p, ctas, s_max, batch);
+  case LMB_INT8: return launch_params<LMB_INT8>(ctx, p, ctas, s_max, batch);
+  default: set_last_error("launch_gemv: kind has no device kernel"); return LMB_ERR_ARG;
+  }
+}
+
+}  // namespace
+
+int configure_gemv(lmb_ctx *ctx) {
+  const int bytes = 64 * 1024;
+  LMB_CUDA(cudaFuncSetAttribute(k_gemv<LMB_TERNARY>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  LMB_CUDA(cudaFuncSetAttribute(k_gemv<LMB_BINARY>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  LMB_CUDA(cudaFuncSetAttribute(k_gemv<LMB_INT2>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  LMB_CUDA(cudaFuncSetAttribute(k_gemv<LMB_INT3>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  LMB_CUDA(cudaFuncSetAttribute(k_gemv<LMB_INT4>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  LMB_CUDA(cudaFuncSetAttribute(k_gemv<LMB_INT8>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  return LMB_OK;
+}
+
+// Up to MAX_JOBS independent GEMVs of one kind and one batch size in a single launch.
+int launch_gemv(lmb_ctx *ctx, const LinearArgs *args, int njobs, bool rotate) {
+  if (njobs < 1 || njobs > MAX_JOBS) {
+    set_last_error("launch_gemv: between 1 and 4 jobs per launch");
+    return LMB_ERR_ARG;
+  }
+  const int kind = args[0].w->kind;
+  for (int j = 1; j < njobs; ++j)
+    if (args[j].w->kind != kind || args[j].batch != args[0].batch) {
+      set_last_error("launch_gemv: jobs of one launch must share block kind and batch size");
+      return LMB_ERR_ARG;
+    }
+  GemvParams p;
+  p.njobs = njobs;
+  p.rotate = rotate ? 1 : 0;
+  p.jobs_dev = nullptr;
+  p.cta_map = nullptr;
+  int ctas = 0, s_max = 1;
+  int st = prepare_jobs(ctx, kind, args, njobs, p.job, &ctas, &s_max, nullptr);
+  if (st != LMB_OK) return st;
+  return launch_params_kind(ctx, kind, p, ctas, s_max, args[0].batch);
+}
+
+}  // namespace lmb
+
+// ---- prepared groups: any number of independent batch-1 GEMVs of one kind in one launch ---------
+struct lmb_group {
+  int kind = 0, ctas = 0, s_max = 1, njobs = 0;
+  bool rotate = false;
+  lmb::Job *d_jobs = nullptr;
+  int2 *d_map = nullptr;
+};
+
+extern "C" {
+
+int lmb_group_create(lmb_ctx *ctx, size_t n, const lmb_weight *const *ws, const float *const *d_xs, float *const *d_ys,
+                     unsigned flags, lmb_group **out) {
+  using namespace lmb;
+  LMB_REQUIRE(ctx && ws && d_xs && d_ys && out && n > 0, "lmb_group_create: null argument");
+  *out = nullptr;
+  std::vector<LinearArgs> args(n);
+  for (size_t i = 0; i < n; ++i) {
+    LMB_REQUIRE(ws[i] && d_xs[i] && d_ys[i], "lmb_group_create: null entry");
+    LMB_REQUIRE(ws[i]->kind == ws[0]->kind, "lmb_group_create: all weights of a group must share a block kind");
+    args[i] = LinearArgs{ws[i], nullptr, d_xs[i], ws[i]->K, ws[i]->K, d_ys[i], ws[i]->M, 1, false};
+  }
+  const int kind = ws[0]->kind;
+  const bool auto_rot = (kind == LMB_TERNARY || kind == LMB_BINARY || kind == LMB_INT2);
+  std::vector<Job> jobs(n);
+  std::vector<int2> map;
+  lmb_group *g = new (std::nothrow) lmb_group();
+  if (!g) return LMB_ERR_ALLOC;
+  g->kind = kind;
+  g->njobs = int(n);
+  g->rotate = (flags & LMB_ROTATE) || ((flags & LMB_AUTO_ROTATE) && auto_rot);
+  int st = prepare_jobs(ctx, kind, args.data(), int(n), jobs.data(), &g->ctas, &g->s_max, &map);
+  if (st == LMB_OK) {
+    cudaError_t e = cudaMalloc(&g->d_jobs, n * sizeof(Job));
+    if (e == cudaSuccess) e = cudaMalloc(&g->d_map, map.size() * sizeof(int2));
+    if (e == cudaSuccess) e = cudaMemcpy(g->d_jobs, jobs.data(), n * sizeof(Job), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMemcpy(g->d_map, map.data(), map.size() * sizeof(int2), cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) st = cuda_fail(e, "lmb_group_create");
+  }
+  if (st != LMB_OK) {
+    lmb_group_destroy(g);
+    return st;
+  }
+  *out = g;
+  return LMB_OK;
+}
+
+int lmb_group_launch(lmb_ctx *ctx, lmb_group *g) {
+  using namespace lmb;
+  LMB_REQUIRE(ctx && g, "lmb_group_launch: null argument");
+  GemvParams p;
+  p.njobs = g->njobs;
+  p.rotate = g->rotate ? 1 : 0;
+  p.jobs_dev = g->d_jobs;
+  p.cta_map = g->d_map;
+  return launch_params_kind(ctx, g->kind, p, g->ctas, g->s_max, 1);
+}
+
+int lmb_group_destroy(lmb_group *g) {
+  if (!g) return LMB_OK;
+  if (g->d_jobs) cudaFree(g->d_jobs);
+  if (g->d_map) cudaFree(g->d_map);
+  delete g;
+  return LMB_OK;
+}
+
+}  // extern "C"
+
+namespace lmb {
+
+int launch_debug_luts(lmb_ctx *ctx, const float *d_x, size_t x_len, bool rotate, float *d_out) {
+  const int nblocks = int((x_len + BLK - 1) / BLK);
+  k_debug_luts<<<(nblocks + WARPS - 1) / WARPS, THREADS, 0, ctx->stream>>>(d_x, x_len, nblocks, rotate ? 1 : 0, d_out);
+  ctx->launches++;
+  LMB_CUDA(cudaGetLastError());
+  return LMB_OK;
+}
+
+}  // namespace lmb

@@ -1,20 +1,464 @@
-// placeholder until the decode step lands
-#include "common.cuh"
-extern "C" {
-#define STUB { lmb::set_last_error("not implemented yet"); return LMB_ERR_STATE; }
-int lmb_model_create(lmb_ctx *, const lmb_model_config *, lmb_model **) STUB
-int lmb_model_destroy(lmb_model *) STUB
-int lmb_model_set_weight(lmb_model *, int, int, int, int, const void *, size_t, size_t) STUB
-int lmb_model_set_vector(lmb_model *, int, int, const float *, size_t) STUB
-int lmb_model_forward(lmb_model *, const int *, const size_t *, size_t, float *) STUB
-int lmb_model_logits_dev(lmb_model *, const float **) STUB
-int lmb_model_reset(lmb_model *) STUB
-int lmb_model_kv_export(lmb_model *, size_t, float *) STUB
-int lmb_model_kv_import(lmb_model *, size_t, const float *) STUB
-int lmb_model_step_bytes(lmb_model *, size_t, uint64_t *) STUB
-int lmb_tp_unique_id(void *) STUB
-int lmb_tp_init(lmb_ctx *, const void *, int, int) STUB
-int lmb_tp_destroy(lmb_ctx *) STUB
-int lmb_allreduce_sum(lmb_ctx *, float *, size_t) STUB
-int lmb_allgather(lmb_ctx *, const float *, float *, size_t) STUB
+// Device-resident decoder: replaces Model::allocate / Model::forward / get_logits / reset_cache
+// (include/lutmac/model.hpp:88-141, src/model.cpp:47-453) for the llama-type path (RMSNorm,
+// RoPE half-split pairs, GQA attention over an fp32 KV cache, SwiGLU FFN, quantised lm_head).
+// Only token ids and positions go in and logits come out; weights, activations and the KV
+// cache stay in HBM.  Batched decode runs `batch` independent sequences through the same
+// weights; tensor parallelism keeps a shard per rank and adds two all-reduces per layer.
+#include <dlfcn.h>
+
+#include <cmath>
+#include <cstring>
+#include <new>
+#include <vector>
+
+#include "decode_ops.cuh"
+
+namespace lmb {
+
+// ---- NCCL, bound at run time (the process may already hold a libnccl.so.2 of its own) ----------
+struct Nccl {
+  typedef struct { char internal[128]; } UniqueId;
+  int (*GetUniqueId)(UniqueId *) = nullptr;
+  int (*CommInitRank)(void **, int, UniqueId, int) = nullptr;
+  int (*CommDestroy)(void *) = nullptr;
+  int (*AllReduce)(const void *, void *, size_t, int, int, void *, cudaStream_t) = nullptr;
+  int (*AllGather)(const void *, void *, size_t, int, void *, cudaStream_t) = nullptr;
+  const char *(*GetErrorString)(int) = nullptr;
+  bool ok = false;
+};
+
+static Nccl &nccl() {
+  static Nccl n;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void *h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (h) {
+      n.GetUniqueId = reinterpret_cast<decltype(n.GetUniqueId)>(dlsym(h, "ncclGetUniqueId"));
+      n.CommInitRank = reinterpret_cast<decltype(n.CommInitRank)>(dlsym(h, "ncclCommInitRank"));
+      n.CommDestroy = reinterpret_cast<decltype(n.CommDestroy)>(dlsym(h, "ncclCommDestroy"));
+      n.AllReduce = reinterpret_cast<decltype(n.AllReduce)>(dlsym(h, "ncclAllReduce"));
+      n.AllGather = reinterpret_cast<decltype(n.AllGather)>(dlsym(h, "ncclAllGather"));
+      n.GetErrorString = reinterpret_cast<decltype(n.GetErrorString)>(dlsym(h, "ncclGetErrorString"));
+      n.ok = n.GetUniqueId && n.CommInitRank && n.CommDestroy && n.AllReduce && n.AllGather && n.GetErrorString;
+    }
+  }
+  return n;
 }
+
+static int nccl_fail(int rc, const char *what) {
+  set_last_error(std::string(what) + ": " + (nccl().GetErrorString ? nccl().GetErrorString(rc) : "NCCL error"));
+  return LMB_ERR_CUDA;
+}
+
+constexpr int NCCL_FLOAT = 7, NCCL_SUM = 0;
+
+}  // namespace lmb
+
+using namespace lmb;
+
+struct LayerW {
+  lmb_weight *w[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};  // q k v o gate up down
+  bool rot[7] = {false, false, false, false, false, false, false};
+  float *in_norm = nullptr, *post_norm = nullptr, *qb = nullptr, *kb = nullptr, *vb = nullptr;
+};
+
+struct lmb_model {
+  lmb_ctx *ctx = nullptr;
+  lmb_model_config cfg;
+  size_t nh = 0, nkv = 0, inter = 0, vocab_local = 0;  // this rank's share
+  lmb_weight *embed = nullptr, *lm_head = nullptr;
+  bool head_tied = false, head_rot = false;
+  const void *embed_host = nullptr;
+  float *final_norm = nullptr;
+  std::vector<LayerW> layers;
+  // activations [max_batch][...]
+  float *hidden = nullptr, *normed = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *att = nullptr, *proj = nullptr,
+        *gate = nullptr, *up = nullptr, *act = nullptr, *logits = nullptr, *logits_local = nullptr;
+  float *kv = nullptr;        // [max_batch][L][2][max_seq][nkv][hd]
+  float *cs_table = nullptr;  // [max_seq][hd/2 cos | hd/2 sin]
+  int *d_tokens = nullptr;
+  size_t *d_pos = nullptr;
+  void *h_io = nullptr;  // pinned staging for tokens + positions
+  size_t seq_stride = 0;
+};
+
+static int dev_alloc(float **p, size_t n) {
+  LMB_CUDA(cudaMalloc(p, (n ? n : 1) * sizeof(float)));
+  LMB_CUDA(cudaMemset(*p, 0, (n ? n : 1) * sizeof(float)));
+  return LMB_OK;
+}
+
+extern "C" {
+
+int lmb_tp_unique_id(void *id128_out) {
+  LMB_REQUIRE(id128_out, "lmb_tp_unique_id: null argument");
+  if (!nccl().ok) {
+    set_last_error("lmb_tp_unique_id: libnccl.so.2 could not be loaded");
+    return LMB_ERR_STATE;
+  }
+  Nccl::UniqueId id;
+  int rc = nccl().GetUniqueId(&id);
+  if (rc != 0) return nccl_fail(rc, "ncclGetUniqueId");
+  std::memcpy(id128_out, &id, 128);
+  return LMB_OK;
+}
+
+int lmb_tp_init(lmb_ctx *ctx, const void *id128, int rank, int size) {
+  LMB_REQUIRE(ctx && id128 && size >= 1 && rank >= 0 && rank < size, "lmb_tp_init: bad argument");
+  if (!nccl().ok) {
+    set_last_error("lmb_tp_init: libnccl.so.2 could not be loaded");
+    return LMB_ERR_STATE;
+  }
+  LMB_CUDA(cudaSetDevice(ctx->device));
+  Nccl::UniqueId id;
+  std::memcpy(&id, id128, 128);
+  int rc = nccl().CommInitRank(&ctx->comm, size, id, rank);
+  if (rc != 0) return nccl_fail(rc, "ncclCommInitRank");
+  ctx->tp_rank = rank;
+  ctx->tp_size = size;
+  return LMB_OK;
+}
+
+int lmb_tp_destroy(lmb_ctx *ctx) {
+  LMB_REQUIRE(ctx, "lmb_tp_destroy: null context");
+  if (ctx->comm) {
+    cudaStreamSynchronize(ctx->stream);
+    nccl().CommDestroy(ctx->comm);
+    ctx->comm = nullptr;
+  }
+  ctx->tp_rank = 0;
+  ctx->tp_size = 1;
+  return LMB_OK;
+}
+
+int lmb_allreduce_sum(lmb_ctx *ctx, float *d_buf, size_t n) {
+  LMB_REQUIRE(ctx && d_buf, "lmb_allreduce_sum: null argument");
+  if (ctx->tp_size <= 1) return LMB_OK;
+  int rc = nccl().AllReduce(d_buf, d_buf, n, NCCL_FLOAT, NCCL_SUM, ctx->comm, ctx->stream);
+  if (rc != 0) return nccl_fail(rc, "ncclAllReduce");
+  return LMB_OK;
+}
+
+int lmb_allgather(lmb_ctx *ctx, const float *d_send, float *d_recv, size_t n_per_rank) {
+  LMB_REQUIRE(ctx && d_send && d_recv, "lmb_allgather: null argument");
+  if (ctx->tp_size <= 1) {
+    if (d_send != d_recv) LMB_CUDA(cudaMemcpyAsync(d_recv, d_send, n_per_rank * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+    return LMB_OK;
+  }
+  int rc = nccl().AllGather(d_send, d_recv, n_per_rank, NCCL_FLOAT, ctx->comm, ctx->stream);
+  if (rc != 0) return nccl_fail(rc, "ncclAllGather");
+  return LMB_OK;
+}
+
+}  // extern "C"
+
+// ---- model ---------------------------------------------------------------------------------------
+extern "C" {
+
+int lmb_model_create(lmb_ctx *ctx, const lmb_model_config *c, lmb_model **out) {
+  LMB_REQUIRE(ctx && c && out, "lmb_model_create: null argument");
+  *out = nullptr;
+  const int g = c->tp_size > 0 ? c->tp_size : 1;
+  LMB_REQUIRE(c->tp_rank >= 0 && c->tp_rank < g, "lmb_model_create: tp_rank out of range");
+  LMB_REQUIRE(g == 1 || (ctx->comm && ctx->tp_size == g && ctx->tp_rank == c->tp_rank),
+              "lmb_model_create: tensor-parallel model needs lmb_tp_init on its context first");
+  LMB_REQUIRE(c->num_attention_heads % c->num_key_value_heads == 0, "lmb_model_create: heads not divisible by kv heads");
+  LMB_REQUIRE(c->head_dim > 0 && c->head_dim % 2 == 0 && 256 % c->head_dim == 0, "lmb_model_create: head_dim must divide 256");
+  LMB_REQUIRE(c->num_attention_heads % g == 0 && c->num_key_value_heads % g == 0 && c->intermediate_size % g == 0 &&
+                  c->vocab_size % g == 0,
+              "lmb_model_create: heads, kv heads, intermediate and vocab sizes must divide by tp_size");
+  if (g > 1)
+    LMB_REQUIRE((c->num_attention_heads / g * c->head_dim) % 256 == 0 && (c->intermediate_size / g) % 256 == 0,
+                "lmb_model_create: o/down shards must be whole 256-column blocks");
+  LMB_REQUIRE(c->max_batch >= 1 && c->max_seq_len >= 1, "lmb_model_create: max_batch and max_seq_len must be >= 1");
+  LMB_CUDA(cudaSetDevice(ctx->device));
+  lmb_model *m = new (std::nothrow) lmb_model();
+  if (!m) return LMB_ERR_ALLOC;
+  m->ctx = ctx;
+  m->cfg = *c;
+  m->cfg.tp_size = g;
+  m->nh = c->num_attention_heads / g;
+  m->nkv = c->num_key_value_heads / g;
+  m->inter = c->intermediate_size / g;
+  m->vocab_local = c->vocab_size / g;
+  m->layers.resize(c->num_hidden_layers);
+  const size_t B = c->max_batch, h = c->hidden_size, hd = c->head_dim;
+  m->seq_stride = c->num_hidden_layers * 2 * c->max_seq_len * m->nkv * hd;
+  int st = LMB_OK;
+  auto A = [&](float **p, size_t n) { if (st == LMB_OK) st = dev_alloc(p, n); };
+  A(&m->hidden, B * h); A(&m->normed, B * h); A(&m->q, B * m->nh * hd); A(&m->k, B * m->nkv * hd);
+  A(&m->v, B * m->nkv * hd); A(&m->att, B * m->nh * hd); A(&m->proj, B * h); A(&m->gate, B * m->inter);
+  A(&m->up, B * m->inter); A(&m->act, B * m->inter); A(&m->logits, B * c->vocab_size);
+  if (g > 1) A(&m->logits_local, B * m->vocab_local);
+  A(&m->kv, B * m->seq_stride); A(&m->final_norm, h); A(&m->cs_table, c->max_seq_len * hd);
+  for (auto &L : m->layers) { A(&L.in_norm, h); A(&L.post_norm, h); }
+  if (st == LMB_OK) {
+    cudaError_t e = cudaMalloc(&m->d_tokens, B * sizeof(int));
+    if (e == cudaSuccess) e = cudaMalloc(&m->d_pos, B * sizeof(size_t));
+    if (e == cudaSuccess) e = cudaMallocHost(&m->h_io, B * (sizeof(int) + sizeof(size_t)));
+    if (e != cudaSuccess) st = cuda_fail(e, "lmb_model_create");
+  }
+  if (st == LMB_OK) {
+    // cos/sin with the reference's float arithmetic (src/layers/embedding.cpp:45-49):
+    // freq = 1/pow(theta, 2d/head_dim), angle = (position / factor) * freq.
+    const size_t half = hd / 2;
+    std::vector<float> cs(c->max_seq_len * hd);
+    for (size_t pos = 0; pos < c->max_seq_len; ++pos)
+      for (size_t d = 0; d < half; ++d) {
+        const float freq = 1.0f / std::pow(c->rope_theta, (2.0f * d) / hd);
+        const float angle = (pos / c->rope_scaling_factor) * freq;
+        cs[pos * hd + d] = std::cos(angle);
+        cs[pos * hd + half + d] = std::sin(angle);
+      }
+    std::vector<float> ones(h, 1.0f);  // norm weights default to identity (model.hpp:96-104)
+    cudaError_t e = cudaMemcpy(m->cs_table, cs.data(), cs.size() * 4, cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMemcpy(m->final_norm, ones.data(), h * 4, cudaMemcpyHostToDevice);
+    for (auto &L : m->layers) {
+      if (e == cudaSuccess) e = cudaMemcpy(L.in_norm, ones.data(), h * 4, cudaMemcpyHostToDevice);
+      if (e == cudaSuccess) e = cudaMemcpy(L.post_norm, ones.data(), h * 4, cudaMemcpyHostToDevice);
+    }
+    if (e != cudaSuccess) st = cuda_fail(e, "lmb_model_create init");
+  }
+  if (st == LMB_OK) st = configure_decode_ops(ctx);
+  if (st != LMB_OK) {
+    lmb_model_destroy(m);
+    return st;
+  }
+  *out = m;
+  return LMB_OK;
+}
+
+int lmb_model_destroy(lmb_model *m) {
+  if (!m) return LMB_OK;
+  cudaSetDevice(m->ctx->device);
+  cudaStreamSynchronize(m->ctx->stream);
+  float *bufs[] = {m->hidden, m->normed, m->q, m->k, m->v, m->att, m->proj, m->gate, m->up, m->act, m->logits,
+                   m->logits_local, m->kv, m->final_norm, m->cs_table};
+  for (float *b : bufs) if (b) cudaFree(b);
+  for (auto &L : m->layers) {
+    for (auto *w : L.w) lmb_weight_free(w);
+    float *vs[] = {L.in_norm, L.post_norm, L.qb, L.kb, L.vb};
+    for (float *b : vs) if (b) cudaFree(b);
+  }
+  if (m->lm_head && !m->head_tied) lmb_weight_free(m->lm_head);
+  lmb_weight_free(m->embed);
+  if (m->d_tokens) cudaFree(m->d_tokens);
+  if (m->d_pos) cudaFree(m->d_pos);
+  if (m->h_io) cudaFreeHost(m->h_io);
+  delete m;
+  return LMB_OK;
+}
+
+int lmb_model_set_weight(lmb_model *m, int layer, int slot, int kind, int quant_bits, const void *blocks, size_t M, size_t K) {
+  LMB_REQUIRE(m && blocks, "lmb_model_set_weight: null argument");
+  LMB_REQUIRE(slot >= LMB_SLOT_EMBED && slot <= LMB_SLOT_DOWN, "lmb_model_set_weight: unknown slot");
+  const lmb_model_config &c = m->cfg;
+  const size_t g = size_t(c.tp_size), r = size_t(c.tp_rank), bpr = (K + BLK - 1) / BLK;
+  const size_t h = c.hidden_size, hd = c.head_dim;
+  // lut_linear rotates iff 0 < quant_bits <= 2 or the tensor is ternary (lut_gemm_scalar.cpp:92-93)
+  const bool rot = (quant_bits > 0 && quant_bits <= 2) || kind == LMB_TERNARY;
+  lmb_weight **dst = nullptr;
+  size_t r0 = 0, r1 = M, b0 = 0, b1 = bpr, wantM = 0, wantK = 0;
+  if (slot == LMB_SLOT_EMBED) {
+    dst = &m->embed; wantM = c.vocab_size; wantK = h; m->embed_host = blocks;
+  } else if (slot == LMB_SLOT_LM_HEAD) {
+    dst = &m->lm_head; wantM = c.vocab_size; wantK = h; r0 = M * r / g; r1 = M * (r + 1) / g; m->head_rot = rot;
+    if (g == 1 && m->embed && blocks == m->embed_host && kind == m->embed->kind) {  // tied: share the device copy
+      if (m->lm_head && !m->head_tied) lmb_weight_free(m->lm_head);
+      m->lm_head = m->embed;
+      m->head_tied = true;
+      return LMB_OK;
+    }
+  } else {
+    LMB_REQUIRE(layer >= 0 && size_t(layer) < m->layers.size(), "lmb_model_set_weight: layer out of range");
+    LayerW &L = m->layers[size_t(layer)];
+    const int i = slot - LMB_SLOT_Q;
+    dst = &L.w[i];
+    L.rot[i] = rot;
+    const size_t qd = c.num_attention_heads * hd, kvd = c.num_key_value_heads * hd, it = c.intermediate_size;
+    switch (slot) {
+    case LMB_SLOT_Q: wantM = qd; wantK = h; r0 = M * r / g; r1 = M * (r + 1) / g; break;
+    case LMB_SLOT_K: case LMB_SLOT_V: wantM = kvd; wantK = h; r0 = M * r / g; r1 = M * (r + 1) / g; break;
+    case LMB_SLOT_O: wantM = h; wantK = qd; b0 = bpr * r / g; b1 = bpr * (r + 1) / g; break;
+    case LMB_SLOT_GATE: case LMB_SLOT_UP: wantM = it; wantK = h; r0 = M * r / g; r1 = M * (r + 1) / g; break;
+    case LMB_SLOT_DOWN: wantM = h; wantK = it; b0 = bpr * r / g; b1 = bpr * (r + 1) / g; break;
+    }
+  }
+  LMB_REQUIRE(M == wantM && K == wantK, "lmb_model_set_weight: tensor shape does not match the model config");
+  if (*dst && !(slot == LMB_SLOT_LM_HEAD && m->head_tied)) lmb_weight_free(*dst);
+  if (slot == LMB_SLOT_LM_HEAD) m->head_tied = false;
+  *dst = nullptr;
+  return lmb_weight_upload_shard(m->ctx, kind, blocks, M, K, r0, r1, b0, b1, dst);
+}
+
+int lmb_model_set_vector(lmb_model *m, int layer, int which, const float *data, size_t n) {
+  LMB_REQUIRE(m && data, "lmb_model_set_vector: null argument");
+  const lmb_model_config &c = m->cfg;
+  const size_t g = size_t(c.tp_size), r = size_t(c.tp_rank), hd = c.head_dim;
+  float **dst = nullptr;
+  size_t want = c.hidden_size, off = 0, keep = c.hidden_size;
+  if (which == LMB_VEC_FINAL_NORM) dst = &m->final_norm;
+  else {
+    LMB_REQUIRE(layer >= 0 && size_t(layer) < m->layers.size(), "lmb_model_set_vector: layer out of range");
+    LayerW &L = m->layers[size_t(layer)];
+    switch (which) {
+    case LMB_VEC_INPUT_NORM: dst = &L.in_norm; break;
+    case LMB_VEC_POST_NORM: dst = &L.post_norm; break;
+    case LMB_VEC_Q_BIAS: dst = &L.qb; want = c.num_attention_heads * hd; keep = want / g; off = keep * r; break;
+    case LMB_VEC_K_BIAS: dst = &L.kb; want = c.num_key_value_heads * hd; keep = want / g; off = keep * r; break;
+    case LMB_VEC_V_BIAS: dst = &L.vb; want = c.num_key_value_heads * hd; keep = want / g; off = keep * r; break;
+    default: set_last_error("lmb_model_set_vector: unknown vector slot"); return LMB_ERR_ARG;
+    }
+  }
+  LMB_REQUIRE(n == want, "lmb_model_set_vector: length does not match the model config");
+  if (!*dst) LMB_CUDA(cudaMalloc(dst, keep * sizeof(float)));
+  LMB_CUDA(cudaMemcpy(*dst, data + off, keep * sizeof(float), cudaMemcpyHostToDevice));
+  return LMB_OK;
+}
+
+}  // extern "C"
+
+namespace {
+
+int gemv1(lmb_model *m, const lmb_weight *w, bool rot, const float *bias, const float *x, size_t x_len, float *y, size_t batch) {
+  LinearArgs a{w, bias, x, x_len, x_len, y, w->M, batch, rot};
+  return launch_gemv(m->ctx, &a, 1, rot);
+}
+
+// Several projections that read the same input: one launch when kinds and rotation agree.
+int gemv_group(lmb_model *m, int n, lmb_weight *const *ws, const bool *rot, const float *x, size_t x_len, float *const *ys,
+               size_t batch) {
+  bool same = true;
+  for (int i = 1; i < n; ++i) same = same && ws[i]->kind == ws[0]->kind && rot[i] == rot[0];
+  if (same) {
+    LinearArgs a[4];
+    for (int i = 0; i < n; ++i) a[i] = LinearArgs{ws[i], nullptr, x, x_len, x_len, ys[i], ws[i]->M, batch, rot[0]};
+    return launch_gemv(m->ctx, a, n, rot[0]);
+  }
+  for (int i = 0; i < n; ++i) {
+    int st = gemv1(m, ws[i], rot[i], nullptr, x, x_len, ys[i], batch);
+    if (st != LMB_OK) return st;
+  }
+  return LMB_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int lmb_model_forward(lmb_model *m, const int *token_ids, const size_t *positions, size_t batch, float *h_logits) {
+  LMB_REQUIRE(m && token_ids && positions, "lmb_model_forward: null argument");
+  const lmb_model_config &c = m->cfg;
+  LMB_REQUIRE(batch >= 1 && batch <= c.max_batch, "lmb_model_forward: batch exceeds max_batch");
+  LMB_REQUIRE(m->embed && m->lm_head, "lmb_model_forward: embedding or lm_head not set");
+  for (auto &L : m->layers)
+    for (auto *w : L.w) LMB_REQUIRE(w, "lmb_model_forward: a layer weight is not set");
+  for (size_t b = 0; b < batch; ++b)
+    LMB_REQUIRE(positions[b] < c.max_seq_len, "lmb_model_forward: position beyond the KV cache");
+  lmb_ctx *ctx = m->ctx;
+  const size_t h = c.hidden_size, hd = c.head_dim;
+  const RopeDims rd{m->nh, m->nkv, hd, c.max_seq_len, m->seq_stride};
+
+  int *ht = static_cast<int *>(m->h_io);
+  size_t *hp = reinterpret_cast<size_t *>(static_cast<char *>(m->h_io) + c.max_batch * sizeof(int));
+  LMB_CUDA(cudaStreamSynchronize(ctx->stream));  // the staging buffer may still be in use by the previous step
+  std::memcpy(ht, token_ids, batch * sizeof(int));
+  std::memcpy(hp, positions, batch * sizeof(size_t));
+  LMB_CUDA(cudaMemcpyAsync(m->d_tokens, ht, batch * sizeof(int), cudaMemcpyHostToDevice, ctx->stream));
+  LMB_CUDA(cudaMemcpyAsync(m->d_pos, hp, batch * sizeof(size_t), cudaMemcpyHostToDevice, ctx->stream));
+
+  int st = launch_embed_rows(ctx, m->d_tokens, m->embed, c.vocab_size, h, batch, m->hidden);
+  const float *pending = nullptr;  // residual branch not yet added to hidden
+  for (size_t l = 0; l < m->layers.size() && st == LMB_OK; ++l) {
+    LayerW &L = m->layers[l];
+    st = launch_add_rmsnorm(ctx, m->hidden, pending, L.in_norm, m->normed, h, batch, c.rms_norm_eps);
+    if (st != LMB_OK) break;
+    float *qkv[3] = {m->q, m->k, m->v};
+    st = gemv_group(m, 3, &L.w[0], &L.rot[0], m->normed, h, qkv, batch);
+    if (st != LMB_OK) break;
+    st = launch_rope_kv(ctx, m->q, m->k, m->v, L.qb, L.kb, L.vb, m->cs_table, m->d_pos, m->kv, l, rd, batch);
+    if (st != LMB_OK) break;
+    st = launch_decode_attn(ctx, m->q, m->kv, m->d_pos, m->att, l, rd, batch);
+    if (st != LMB_OK) break;
+    st = gemv1(m, L.w[3], L.rot[3], nullptr, m->att, m->nh * hd, m->proj, batch);
+    if (st != LMB_OK) break;
+    if (c.tp_size > 1 && (st = lmb_allreduce_sum(ctx, m->proj, batch * h)) != LMB_OK) break;
+    st = launch_add_rmsnorm(ctx, m->hidden, m->proj, L.post_norm, m->normed, h, batch, c.rms_norm_eps);
+    if (st != LMB_OK) break;
+    float *gu[2] = {m->gate, m->up};
+    st = gemv_group(m, 2, &L.w[4], &L.rot[4], m->normed, h, gu, batch);
+    if (st != LMB_OK) break;
+    st = launch_silu_mul(ctx, m->gate, m->up, m->act, batch * m->inter);
+    if (st != LMB_OK) break;
+    st = gemv1(m, L.w[6], L.rot[6], nullptr, m->act, m->inter, m->proj, batch);
+    if (st != LMB_OK) break;
+    if (c.tp_size > 1 && (st = lmb_allreduce_sum(ctx, m->proj, batch * h)) != LMB_OK) break;
+    pending = m->proj;
+  }
+  if (st != LMB_OK) return st;
+  st = launch_add_rmsnorm(ctx, m->hidden, pending, m->final_norm, m->normed, h, batch, c.rms_norm_eps);
+  if (st != LMB_OK) return st;
+  if (c.tp_size > 1) {
+    st = gemv1(m, m->lm_head, m->head_rot, nullptr, m->normed, h, m->logits_local, batch);
+    for (size_t b = 0; b < batch && st == LMB_OK; ++b)
+      st = lmb_allgather(ctx, m->logits_local + b * m->vocab_local, m->logits + b * c.vocab_size, m->vocab_local);
+  } else {
+    st = gemv1(m, m->lm_head, m->head_rot, nullptr, m->normed, h, m->logits, batch);
+  }
+  if (st != LMB_OK) return st;
+  if (h_logits) {
+    LMB_CUDA(cudaMemcpyAsync(h_logits, m->logits, batch * c.vocab_size * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
+    LMB_CUDA(cudaStreamSynchronize(ctx->stream));
+  }
+  return LMB_OK;
+}
+
+int lmb_model_logits_dev(lmb_model *m, const float **d_logits) {
+  LMB_REQUIRE(m && d_logits, "lmb_model_logits_dev: null argument");
+  *d_logits = m->logits;
+  return LMB_OK;
+}
+
+int lmb_model_reset(lmb_model *m) {
+  LMB_REQUIRE(m, "lmb_model_reset: null model");
+  LMB_CUDA(cudaMemsetAsync(m->kv, 0, m->cfg.max_batch * m->seq_stride * sizeof(float), m->ctx->stream));
+  return LMB_OK;
+}
+
+int lmb_model_kv_export(lmb_model *m, size_t seq, float *h_out) {
+  LMB_REQUIRE(m && h_out && seq < m->cfg.max_batch, "lmb_model_kv_export: bad argument");
+  if (m->cfg.tp_size != 1) {
+    set_last_error("lmb_model_kv_export: only for unsharded models");
+    return LMB_ERR_STATE;
+  }
+  LMB_CUDA(cudaMemcpyAsync(h_out, m->kv + seq * m->seq_stride, m->seq_stride * sizeof(float), cudaMemcpyDeviceToHost, m->ctx->stream));
+  LMB_CUDA(cudaStreamSynchronize(m->ctx->stream));
+  return LMB_OK;
+}
+
+int lmb_model_kv_import(lmb_model *m, size_t seq, const float *h_in) {
+  LMB_REQUIRE(m && h_in && seq < m->cfg.max_batch, "lmb_model_kv_import: bad argument");
+  if (m->cfg.tp_size != 1) {
+    set_last_error("lmb_model_kv_import: only for unsharded models");
+    return LMB_ERR_STATE;
+  }
+  LMB_CUDA(cudaMemcpyAsync(m->kv + seq * m->seq_stride, h_in, m->seq_stride * sizeof(float), cudaMemcpyHostToDevice, m->ctx->stream));
+  LMB_CUDA(cudaStreamSynchronize(m->ctx->stream));
+  return LMB_OK;
+}
+
+int lmb_model_step_bytes(lmb_model *m, size_t position, uint64_t *bytes_out) {
+  LMB_REQUIRE(m && bytes_out, "lmb_model_step_bytes: null argument");
+  auto wb = [](const lmb_weight *w) -> uint64_t {
+    return w ? uint64_t(w->M) * w->bpr * kind_info(w->kind).ref_bytes + 4 * w->bpr * BLK + 4 * w->M : 0;
+  };
+  uint64_t n = wb(m->lm_head) + 4 * m->cfg.hidden_size;
+  for (auto &L : m->layers)
+    for (auto *w : L.w) n += wb(w);
+  n += uint64_t(2) * m->layers.size() * (position + 1) * m->nkv * m->cfg.head_dim * 4;
+  *bytes_out = n;
+  return LMB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,115 @@
+"""CPU: the C-ABI library loads and exports every symbol include/lutmac_b200.h declares, the
+host-side re-tiling is a bit-exact bijection, and the host logic (block structs, synthetic
+generators, byte accounting, tensor-parallel sharding) behaves.  No compute call needs a GPU."""
+import os
+import re
+
+import numpy as np
+import pytest
+
+from lutmac_b200 import _lib, api, synth, tp
+from lutmac_b200.blocks import (BINARY, BLOCK_BYTES, BLOCK_DTYPES, INT2, INT3, INT4, INT5, INT6, INT8, KIND_NAMES,
+                                TERNARY, PackedTensor, algorithmic_bytes, blocks_per_row)
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ALL_KINDS = (TERNARY, BINARY, INT2, INT3, INT4, INT5, INT6, INT8)
+
+
+def test_library_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, "include", "lutmac_b200.h")).read()
+    declared = set(re.findall(r"\b(lmb_[a-z0-9_]+)\s*\(", header))
+    declared -= {"lmb_allreduce_fn", "lmb_allgather_fn"}
+    assert len(declared) > 40
+    L = _lib.lib()
+    for name in sorted(declared):
+        assert hasattr(L, name), f"{name} declared in the header but not exported"
+    assert declared == set(_lib.SIGNATURES), declared ^ set(_lib.SIGNATURES)
+
+
+def test_block_sizes_match_the_reference_structs():
+    L = _lib.lib()
+    for kind in ALL_KINDS:
+        assert L.lmb_block_bytes(kind) == BLOCK_BYTES[kind] == BLOCK_DTYPES[kind].itemsize
+    assert L.lmb_block_bytes(7) == 0
+
+
+def test_status_strings_and_argument_errors():
+    L = _lib.lib()
+    assert L.lmb_strerror(0) == b"ok"
+    assert L.lmb_retile_host(77, None, 1, 1, None) == _lib.ERR_ARG
+    assert b"unknown block kind" in L.lmb_last_error()
+    with pytest.raises(_lib.LutmacError):
+        _lib.check(L.lmb_retile_host(TERNARY, None, 4, 256, None))
+
+
+@pytest.mark.parametrize("kind", ALL_KINDS)
+def test_retile_roundtrip_is_bit_exact(kind):
+    rng = np.random.default_rng(kind)
+    for (M, K) in ((1, 4), (33, 300), (64, 512), (100, 1024)):
+        t = synth.tensor(rng, kind, M, K)
+        tiled = api.retile_host(t)
+        assert tiled.size == (M + 31) // 32 * blocks_per_row(K) * 32 * BLOCK_BYTES[kind]
+        back = api.untile_host(kind, tiled, M, K)
+        for f in BLOCK_DTYPES[kind].names:
+            assert np.array_equal(back[f], t.blocks[f]), (KIND_NAMES[kind], M, K, f)
+
+
+def test_ternary_tiles_hold_the_reference_lut_indices(oracle):
+    """The device layout stores P = ~zero & ~sign and N = ~zero & sign: their nibbles are
+    exactly extract_indices' (pos, neg)."""
+    rng = np.random.default_rng(0)
+    t = synth.ternary_tensor(rng, 40, 512)
+    tiled = api.retile_host(t)
+    bpr = 2
+    for r in (0, 17, 39):
+        for b in range(bpr):
+            tile = tiled[((r // 32) * bpr + b) * 32 * 68:][:32 * 68]
+            blk = t.blocks[r * bpr + b]
+            for g in range(64):
+                byte, c, j, lane = g // 2, (g // 2) // 8, (g // 2) % 8, r % 32
+                p, n = tile[(c * 32 + lane) * 16 + j], tile[(c * 32 + lane) * 16 + 8 + j]
+                got = ((p >> 4, n >> 4) if g % 2 == 0 else (p & 15, n & 15))
+                assert got == oracle.extract_indices(blk["sign_plane"], blk["zero_plane"], g)
+
+
+def test_algorithmic_bytes_worked_numbers():
+    assert algorithmic_bytes(TERNARY, 2048, 2048) == 1130496            # config 1
+    assert algorithmic_bytes(INT4, 2048, 2048) == 2162688 + 8192 + 8192
+    assert algorithmic_bytes(INT4, 8192, 2048) == 8650752 + 8192 + 32768
+    assert algorithmic_bytes(INT8, 128256, 2048) == 128256 * 8 * 260 + 8192 + 4 * 128256
+
+
+def test_synthetic_generators_are_seeded_and_well_formed():
+    a = synth.config1(0)
+    b = synth.config1(0)
+    assert np.array_equal(a[0].blocks, b[0].blocks) and np.array_equal(a[1], b[1])
+    t, x = a
+    assert t.kind == TERNARY and (t.M, t.K) == (2048, 2048) and t.needs_rotation()
+    assert not (t.blocks["sign_plane"] & t.blocks["zero_plane"]).any()  # canonical: no sign under zero
+    frac = np.unpackbits(t.blocks["zero_plane"]).mean()
+    assert 0.32 < frac < 0.35
+    assert 0.005 < (np.abs(x) > 6).mean() < 0.02  # ~1 % outliers x10
+    assert np.all(t.blocks["scale"].reshape(2048, 8) == t.blocks["scale"].reshape(2048, 8)[:, :1])  # per-row scale
+    layer = synth.config2_layer(np.random.default_rng(0))
+    assert [(v.M, v.K) for v in layer.values()] == [(M, K) for _, M, K in synth.LLAMA32_1B_SHAPES]
+    assert not synth.int4_tensor(np.random.default_rng(0), 4, 256).needs_rotation()
+
+
+def test_padding_columns_carry_zero_weights(oracle):
+    rng = np.random.default_rng(3)
+    for kind in (TERNARY, INT4, INT8):
+        t = synth.tensor(rng, kind, 5, 300)
+        for r in range(5):
+            for c in range(300, 512):
+                assert oracle.block_get(kind, t.blocks, r * 2 + c // 256, c % 256) == 0.0
+
+
+def test_tp_sharding_reassembles(oracle):
+    rng = np.random.default_rng(9)
+    t = synth.ternary_tensor(rng, 64, 1024)
+    x = oracle.apply_hadamard_rotation(synth.activations(rng, 1024))
+    full = oracle.gemv(TERNARY, t.blocks, x, 64, 1024)
+    rows = np.concatenate([oracle.gemv(TERNARY, tp.shard_rows(t, r, 4).blocks, x, 16, 1024) for r in range(4)])
+    assert np.array_equal(rows, full)
+    parts = [oracle.gemv(TERNARY, tp.shard_blocks(t, r, 2).blocks, x[r * 512:(r + 1) * 512], 64, 512) for r in range(2)]
+    assert np.allclose(parts[0] + parts[1], full, rtol=1e-5, atol=1e-6)

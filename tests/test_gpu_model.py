@@ -1,0 +1,76 @@
+"""GPU parity of one decode step (Model::forward) against the reference fixtures and the oracle:
+logits within 1e-5 relative L2 (fp32 accumulation), single sequence and batched."""
+import os
+
+import numpy as np
+import pytest
+
+from lutmac_b200 import synth
+from lutmac_b200.blocks import INT2, INT4, INT8, TERNARY
+from lutmac_b200.model import Model
+from tests.conftest import rel_l2
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-5
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+CASES = [("int4", INT4, {}), ("ternary", TERNARY, {}), ("int2_bias", INT2, {"qkv_bias": True}),
+         ("int8", INT8, {"n_kv_heads": 1})]
+
+
+@pytest.mark.parametrize("name,kind,over", CASES)
+def test_forward_matches_reference_fixtures(ctx, name, kind, over):
+    g = np.load(os.path.join(GOLD, "model.npz"))
+    spec = synth.model_spec(synth.tiny_model_shape(**over), kind, seed=11, max_seq=2048)
+    m = Model(spec, ctx)
+    for p, t in enumerate(g["tokens"]):
+        logits = m.forward(int(t), p)
+        assert rel_l2(logits, g[name + "_logits"][p]) < TOL, (name, p)
+    m.close()
+
+
+def test_forward_vs_oracle_longer_context_and_kv(ctx, oracle):
+    from oracle.oracle import OracleModel
+    spec = synth.model_spec(synth.tiny_model_shape(n_layers=3, hidden=512, inter=768, n_heads=8, n_kv_heads=2), INT4,
+                            seed=3, max_seq=64)
+    m = Model(spec, ctx)
+    o = OracleModel(oracle, spec)
+    rng = np.random.default_rng(0)
+    toks = rng.integers(0, spec.cfg["vocab"], size=40)
+    for p, t in enumerate(toks):
+        want = o.forward(int(t), p)
+        got = m.forward(int(t), p)
+        if p % 13 == 0 or p == len(toks) - 1:
+            assert rel_l2(got, want) < TOL, p
+    assert rel_l2(m.kv_export(), o.kv) < TOL
+    # KV hand-off: a fresh model that imports the oracle's cache continues identically
+    m2 = Model(spec, ctx)
+    m2.kv_import(o.kv)
+    want = o.forward(5, len(toks))
+    assert rel_l2(m2.forward(5, len(toks)), want) < TOL
+    m.close()
+    m2.close()
+
+
+def test_batched_decode_equals_independent_sequences(ctx, oracle):
+    from oracle.oracle import OracleModel
+    spec = synth.model_spec(synth.tiny_model_shape(qkv_bias=True), INT2, seed=5, max_seq=32)
+    B = 3
+    m = Model(spec, ctx, max_batch=B)
+    oracles = [OracleModel(oracle, spec) for _ in range(B)]
+    rng = np.random.default_rng(1)
+    for p in range(6):
+        toks = rng.integers(0, spec.cfg["vocab"], size=B)
+        got = m.forward(toks, [p] * B)
+        for b in range(B):
+            assert rel_l2(got[b], oracles[b].forward(int(toks[b]), p)) < TOL, (p, b)
+    m.close()
+
+
+def test_model_errors(ctx):
+    from lutmac_b200._lib import LutmacError
+    spec = synth.model_spec(synth.tiny_model_shape(), INT4, seed=1, max_seq=8)
+    m = Model(spec, ctx)
+    with pytest.raises(LutmacError):
+        m.forward(1, 8)  # beyond the KV cache
+    m.close()
