@@ -198,18 +198,20 @@ def run_ours(args):
     from lutmac_b200.api import Group
     flat = [e for row in dev for e in row]
     group = Group(ctx, [e[0] for e in flat], [e[1] for e in flat], [e[2] for e in flat], flags=0)
-    issue_suite()  # sizes the split-K scratch before capture
-    ctx.sync()
-    ctx.graph_begin()
-    issue_suite()
-    chain = ctx.graph_end()
-    for _ in range(3):
-        chain.launch()
-    ctx.sync()
-    ctx.timer_start()
-    for _ in range(10):
-        chain.launch()
-    chain_ms = ctx.timer_stop() / 10
+    chain_ms = None
+    if not args.no_chain:
+        issue_suite()  # sizes the split-K scratch before capture
+        ctx.sync()
+        ctx.graph_begin()
+        issue_suite()
+        chain = ctx.graph_end()
+        for _ in range(3):
+            chain.launch()
+        ctx.sync()
+        ctx.timer_start()
+        for _ in range(10):
+            chain.launch()
+        chain_ms = ctx.timer_stop() / 10
 
     class graph:  # the timed step
         launch = staticmethod(group.launch)
@@ -247,28 +249,30 @@ def run_ours(args):
     value = world * step_bytes * args.steps / (ms * 1e-3) / 1e9
 
     # end to end: host buffers through the layer API, one call per layer (7 lut_linear each)
-    host_in = [[np.ascontiguousarray(acts[li][n]) for n, _, _ in synth.LLAMA32_1B_SHAPES] for li in range(N_LAYERS)]
-    tensors = [[layers[li][n] for n, _, _ in synth.LLAMA32_1B_SHAPES] for li in range(N_LAYERS)]
-    for li in range(N_LAYERS):
-        for t_, (w, _, _, _) in zip(tensors[li], dev[li]):
-            t_._device = w
-    e2e_steps = max(1, min(args.steps, 5))
-    for li in range(N_LAYERS):
-        lut_linear_multi(tensors[li], host_in[li], ctx=ctx)
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        for li in range(N_LAYERS):
-            lut_linear_multi(tensors[li], host_in[li], ctx=ctx)
-    e2e_s = time.perf_counter() - t0
-    if dist is not None:
-        import torch
-        t = torch.tensor([e2e_s], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t.item())
-    e2e_val = world * step_bytes * e2e_steps / e2e_s / 1e9
     h2d = N_LAYERS * sum(4 * K for _, _, K in synth.LLAMA32_1B_SHAPES)
     d2h = N_LAYERS * sum(4 * M for _, M, _ in synth.LLAMA32_1B_SHAPES)
+    e2e_val = None
+    if not args.no_e2e:
+        host_in = [[np.ascontiguousarray(acts[li][n]) for n, _, _ in synth.LLAMA32_1B_SHAPES] for li in range(N_LAYERS)]
+        tensors = [[layers[li][n] for n, _, _ in synth.LLAMA32_1B_SHAPES] for li in range(N_LAYERS)]
+        for li in range(N_LAYERS):
+            for t_, (w, _, _, _) in zip(tensors[li], dev[li]):
+                t_._device = w
+        e2e_steps = max(1, min(args.steps, 5))
+        for li in range(N_LAYERS):
+            lut_linear_multi(tensors[li], host_in[li], ctx=ctx)
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            for li in range(N_LAYERS):
+                lut_linear_multi(tensors[li], host_in[li], ctx=ctx)
+        e2e_s = time.perf_counter() - t0
+        if dist is not None:
+            import torch
+            t = torch.tensor([e2e_s], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e2e_s = float(t.item())
+        e2e_val = world * step_bytes * e2e_steps / e2e_s / 1e9
 
     if rank != 0:
         return
@@ -280,7 +284,7 @@ def run_ours(args):
             "dtype": "f32", "data": "synthetic",
             "config": {"workload": WORKLOAD, "l2_policy": "inputs larger than L2 (501.7 MB of weights per step)",
                        "launch": "112 GEMVs per step as one prepared group launch (lmb_group_launch)",
-                       "chain_of_112_single_launches_gbs": step_bytes / (chain_ms * 1e-3) / 1e9},
+                       "chain_of_112_single_launches_gbs": (step_bytes / (chain_ms * 1e-3) / 1e9) if chain_ms else None},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,
                          "peak_source": peak_src, "kernel": "k_gemv<int4>",
                          "algorithmic_bytes_per_launch": per_launch_bytes, "traffic": load_traffic()},
@@ -302,6 +306,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-chain", action="store_true", help="skip the chain-of-single-launches side measurement")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
