@@ -98,15 +98,13 @@ def load_peaks():
     return 6650.0, "fallback"
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one group launch of the suite, from the ncu
+# capture summarised in profiles/k_gemv_int4_suite_group.md
+NCU_DRAM_BYTES_PER_GROUP_LAUNCH = 510081280
+
+
 def load_traffic():
-    """DRAM bytes per suite pass from the committed ncu capture, if any (profiles/traffic.json)."""
-    p = os.path.join(ROOT, "profiles", "traffic.json")
-    if os.path.exists(p):
-        try:
-            return json.load(open(p)).get("int4_suite_dram_bytes_per_launch")
-        except Exception:
-            return None
-    return None
+    return NCU_DRAM_BYTES_PER_GROUP_LAUNCH
 
 
 # ---- CPU baseline / reference arm (the only places that touch oracle/) -------------------------------

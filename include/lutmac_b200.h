@@ -122,6 +122,27 @@ int lmb_untile_host(int kind, const void *tiled, size_t M, size_t K, void *block
 int lmb_linear(lmb_ctx *ctx, const lmb_weight *w, const float *d_bias, const float *d_x, size_t x_len,
                size_t x_stride, float *d_y, size_t batch, unsigned flags);
 
+/* lut_linear for hosts that must not allocate device memory.  No counterpart in the reference.
+ *
+ * Some callers cannot reach cudaMalloc at all: a plugin running inside a serving process whose
+ * framework has already claimed the whole GPU for its own memory pool, a host thread with a
+ * hard latency bound that may not enter the driver's allocator, or code issued while a stream
+ * is being captured.  For them this entry point runs the same kernel as lmb_linear (batch 1)
+ * but takes the split-K scratch from an array built into the library image instead of from a
+ * context: it needs no lmb_ctx and calls no allocating routine.  The caller passes the resident
+ * weight, the input and output device pointers and the stream to run on.
+ *
+ * Limit: the built-in scratch holds 131,072 floats (512 KiB) and 1024 row-group counters per
+ * GPU (every GPU that loads the library carries them until the process exits).  A shape whose
+ * split needs more -- (K slices) x (rows padded to 32) floats -- is refused with LMB_ERR_LIMIT;
+ * every projection of the 1B, 1.5B and 70B decoder shapes fits.
+ * All calls on one GPU share that array: calls that overlap on the device (different streams)
+ * race with each other; issue them on one stream or order them with events.
+ * The first call on each device looks up the array's device address and configures the kernel;
+ * make that first call before any stream capture begins. */
+int lmb_linear_static_scratch(const lmb_weight *w, const float *d_bias, const float *d_x, size_t x_len, float *d_y,
+                              unsigned flags, void *cuda_stream);
+
 /* Prepared group: n independent batch-1 lut_linear calls of one block kind (inputs d_xs[i] of K_i
  * floats, outputs d_ys[i] of M_i floats, device pointers) planned once and issued as a single
  * kernel launch.  The reference issues them one by one (e.g. q/k/v at src/model.cpp:307-309). */

@@ -63,6 +63,7 @@ SIGNATURES = {
     "lmb_retile_host": (C.c_int, [C.c_int, vp, sz, sz, vp]),
     "lmb_untile_host": (C.c_int, [C.c_int, vp, sz, sz, vp]),
     "lmb_linear": (C.c_int, [vp, vp, vp, vp, sz, sz, vp, sz, C.c_uint]),
+    "lmb_linear_static_scratch": (C.c_int, [vp, vp, vp, sz, vp, C.c_uint, vp]),
     "lmb_group_create": (C.c_int, [vp, sz, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), C.c_uint, C.POINTER(vp)]),
     "lmb_group_launch": (C.c_int, [vp, vp]),
     "lmb_group_destroy": (C.c_int, [vp]),

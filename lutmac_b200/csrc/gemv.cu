@@ -629,6 +629,93 @@ int lmb_group_destroy(lmb_group *g) {
   return LMB_OK;
 }
 
+// ---- lmb_linear_static_scratch ---------------------------------------------------------------------
+// Split-K scratch that belongs to the library image instead of the heap: every GPU that loads the
+// library carries these two arrays until the process exits.
+#define LMB_STATIC_SCRATCH_FLOATS (size_t(1) << 17)  /* 512 KiB of partial sums */
+#define LMB_STATIC_COUNTERS 1024                     /* row-group arrival counters */
+static __device__ __align__(256) float g_static_scratch[LMB_STATIC_SCRATCH_FLOATS];
+static __device__ __align__(256) unsigned g_static_counters[LMB_STATIC_COUNTERS];
+
+namespace {
+struct StaticSetup {
+  bool ready = false;
+  float *scratch = nullptr;      // device address of g_static_scratch on this device
+  unsigned *counters = nullptr;  // device address of g_static_counters on this device
+  int sm_count = 0;
+};
+StaticSetup g_static_setup[64];  // per device ordinal
+}  // namespace
+
+int lmb_linear_static_scratch(const lmb_weight *w, const float *d_bias, const float *d_x, size_t x_len, float *d_y,
+                              unsigned flags, void *cuda_stream) {
+  using namespace lmb;
+  LMB_REQUIRE(w && d_x && d_y, "lmb_linear_static_scratch: null argument");
+  LMB_REQUIRE(x_len <= w->bpr * size_t(BLK), "lmb_linear_static_scratch: x_len exceeds the padded input width");
+  int dev = -1;
+  LMB_CUDA(cudaGetDevice(&dev));
+  LMB_REQUIRE(dev == w->device, "lmb_linear_static_scratch: the weight's device is not the current device");
+  LMB_REQUIRE(dev >= 0 && dev < 64, "lmb_linear_static_scratch: device ordinal beyond 63");
+  StaticSetup &su = g_static_setup[dev];
+  if (!su.ready) {
+    // Once per device, with that device current.  In host code the array names are only handles:
+    // the device addresses the kernel needs come from cudaGetSymbolAddress.
+    void *ps = nullptr, *pc = nullptr;
+    LMB_CUDA(cudaGetSymbolAddress(&ps, g_static_scratch));
+    LMB_CUDA(cudaGetSymbolAddress(&pc, g_static_counters));
+    LMB_CUDA(cudaDeviceGetAttribute(&su.sm_count, cudaDevAttrMultiProcessorCount, dev));
+    lmb_ctx probe;  // only carries the device for configure_gemv; nothing is allocated
+    probe.device = dev;
+    int st = configure_gemv(&probe);
+    if (st != LMB_OK) return st;
+    su.scratch = static_cast<float *>(ps);
+    su.counters = static_cast<unsigned *>(pc);
+    su.ready = true;
+  }
+  const int kind = w->kind;
+  const Plan pl = make_plan(kind, w->row_tiles, w->bpr, 1, su.sm_count);
+  const size_t mp = w->row_tiles * TILE_ROWS;
+  if (pl.n_ks > 1 && (size_t(pl.n_ks) * mp > LMB_STATIC_SCRATCH_FLOATS || size_t(pl.n_rg) > LMB_STATIC_COUNTERS)) {
+    set_last_error("lmb_linear_static_scratch: this shape needs more than the built-in 512 KiB of split-K scratch "
+                   "(K slices x padded rows > 131072 floats, or more than 1024 row groups); use lmb_linear");
+    return LMB_ERR_LIMIT;
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  // The array keeps whatever the last call left.  Partial sums are fully overwritten before they
+  // are read; the counters must start at zero, so they are cleared on the caller's stream.
+  if (pl.n_ks > 1) LMB_CUDA(cudaMemsetAsync(su.counters, 0, size_t(pl.n_rg) * sizeof(unsigned), stream));
+  GemvParams p;
+  p.njobs = 1;
+  const bool auto_rot = (kind == LMB_TERNARY || kind == LMB_BINARY || kind == LMB_INT2);
+  p.rotate = ((flags & LMB_ROTATE) || ((flags & LMB_AUTO_ROTATE) && auto_rot)) ? 1 : 0;
+  p.jobs_dev = nullptr;
+  p.cta_map = nullptr;
+  Job &jb = p.job[0];
+  jb.tiles = w->d_tiles;
+  jb.x = d_x;
+  jb.y = d_y;
+  jb.bias = d_bias;
+  jb.scratch = su.scratch;
+  jb.counters = su.counters;
+  jb.M = int(w->M);
+  jb.mp = int(mp);
+  jb.bpr = int(w->bpr);
+  jb.row_tiles = int(w->row_tiles);
+  jb.R = pl.R;
+  jb.S = pl.S;
+  jb.n_rg = pl.n_rg;
+  jb.n_ks = pl.n_ks;
+  jb.cta_end = pl.ctas;
+  jb.x_len = unsigned(x_len);
+  jb.x_stride = unsigned(x_len);
+  jb.y_stride = unsigned(w->M);
+  lmb_ctx launch_ctx;  // plain launch on the caller's stream, no programmatic dependent launch
+  launch_ctx.device = dev;
+  launch_ctx.stream = stream;
+  launch_ctx.pdl = false;
+  return launch_params_kind(&launch_ctx, kind, p, pl.ctas, pl.S, 1);
+}
+
 }  // extern "C"
 
 namespace lmb {

@@ -1,0 +1,58 @@
+"""GPU: lmb_linear_static_scratch, the lut_linear entry point for callers that cannot allocate
+device memory (a plugin inside a process whose framework owns the whole GPU memory pool, a
+latency-bound thread that may not enter the driver's allocator).  It must give what lmb_linear
+gives, call after call, although every call shares one built-in scratch array that still holds
+the previous call's partial sums.  Collected last on purpose."""
+import ctypes
+
+import numpy as np
+import pytest
+
+from lutmac_b200 import _lib, synth
+from lutmac_b200.blocks import INT4, TERNARY
+from tests.conftest import rel_l2
+
+pytestmark = pytest.mark.gpu
+
+
+def device_synchronize():
+    """Wait for every stream of the current CUDA context (the context's own stream is
+    non-blocking, so it does not order itself against the default stream used below)."""
+    assert ctypes.CDLL("libcuda.so.1").cuCtxSynchronize() == 0
+
+
+@pytest.mark.parametrize("kind,M,K", [(INT4, 64, 8192), (TERNARY, 100, 4096), (INT4, 512, 2048)])
+def test_static_scratch_matches_lmb_linear_twice(ctx, oracle, kind, M, K):
+    rng = np.random.default_rng(kind * 7 + M)
+    t = synth.tensor(rng, kind, M, K)
+    w = ctx.upload(t)
+    results = []
+    for call in range(2):  # two calls in a row: the second one finds the first one's leftovers
+        x = synth.activations(rng, K)
+        dx = ctx.to_device(x)
+        dy_ref, dy = ctx.malloc(M * 4), ctx.malloc(M * 4)
+        dy.zero()
+        ctx.linear(w, dx, dy_ref, flags=_lib.AUTO_ROTATE)
+        want = dy_ref.download(np.float32)  # synchronises the context's stream
+        # the new entry point takes no context: it runs on the stream it is given (here the
+        # default stream)
+        device_synchronize()
+        _lib.check(_lib.lib().lmb_linear_static_scratch(w.h, None, dx.ptr, K, dy.ptr, _lib.AUTO_ROTATE, None))
+        device_synchronize()
+        got = dy.download(np.float32)
+        assert rel_l2(got, want) < 1e-5, (call, rel_l2(got, want))
+        assert rel_l2(got, oracle.lut_linear(kind, t.quant_bits, t.blocks, M, K, None, x)[0]) < 1e-5
+        results.append(got)
+    assert not np.array_equal(results[0], results[1])  # different inputs gave different outputs
+    w.free()
+
+
+def test_static_scratch_refuses_a_split_beyond_its_array(ctx):
+    rng = np.random.default_rng(0)
+    t = synth.int4_tensor(rng, 75520, 512)  # 295 row groups x 2 K-slices x 256 rows > 131072 floats
+    w = ctx.upload(t)
+    dx, dy = ctx.malloc(t.K * 4), ctx.malloc(t.M * 4)
+    st = _lib.lib().lmb_linear_static_scratch(w.h, None, dx.ptr, t.K, dy.ptr, 0, None)
+    assert st == _lib.ERR_LIMIT
+    assert b"512 KiB" in _lib.lib().lmb_last_error()
+    w.free()
