@@ -37,7 +37,10 @@ constexpr int SM_COUNT_HINT = 148;
 //            bits of the interleaved (b1,b2) pairs split into two MSB-first bit planes.
 //   INT3     6 chunks; chunk 3j+p = Q_{2-p}[16j..16j+15] (j < 2): bit planes of the 3-bit
 //            code, most significant plane first.
-//   INT4     8 chunks; chunk c = data[16c..16c+15] unchanged (weight 2i in the high nibble).
+//   INT4     8 chunks in the operand order of the 8-bit integer MMA instead of one row per lane:
+//            chunk h*4+q of lane (g = lane/4, tid = lane%4) = four words {row 16h+g: k-steps 2q,
+//            2q+1; row 16h+g+8: k-steps 2q, 2q+1}; byte j of the word of k-step s holds column
+//            32s+4tid+j in its low nibble and column 32s+16+4tid+j in its high nibble.
 //   INT5     10 chunks; 0..7 = low nibbles packed like INT4, 8..9 = bit-4 plane.
 //   INT6     12 chunks; 0..7 = low nibbles, 8..9 = bit-4 plane, 10..11 = bit-5 plane.
 //   INT8     16 chunks; chunk c = data[16c..16c+15] unchanged.

@@ -20,9 +20,11 @@ __device__ float tile_elem(int kind, const uint8_t *tiles, size_t bpr, size_t ro
   const unsigned bit = 7u - unsigned(j % 8);
   switch (kind) {
   case LMB_INT8: return float(int8_t(pay(j / 16, j % 16))) * s0;
-  case LMB_INT4: {
-    const uint8_t byte = pay((j / 2) / 16, (j / 2) % 16);
-    const int nib = (j % 2 == 0) ? (byte >> 4) : (byte & 15);
+  case LMB_INT4: {  // MMA operand order, see common.cuh
+    const size_t h = l / 16, g = l % 8, hi8 = (l % 16) / 8, s = j / 32, kk = j % 32, tid = (kk % 16) / 4;
+    const size_t lane = g * 4 + tid, chunk = h * 4 + s / 2, word = hi8 * 2 + s % 2;
+    const uint8_t byte = tile[(chunk * TILE_ROWS + lane) * 16 + word * 4 + kk % 4];
+    const int nib = (kk >= 16) ? (byte >> 4) : (byte & 15);
     return float(nib - 8) * s0;
   }
   case LMB_TERNARY: {

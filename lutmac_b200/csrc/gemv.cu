@@ -122,8 +122,15 @@ template <int KIND> struct LutUnit {
     for (int s = 0; s < NS; ++s) sc[s] = ld_stream_f32(tile + size_t(C) * TILE_ROWS * 16 + (size_t(s) * TILE_ROWS + lane) * 4);
   }
 
+  using Acc = float;  // one row per lane
+  static __device__ __forceinline__ void acc_init(Acc &a) { a = 0.0f; }
+  static __device__ __forceinline__ float acc_row(const Acc &a, int) { return a; }
+  __device__ __forceinline__ void eval(const float *blk, float xsum, const int *, Acc &acc) const {
+    acc += value(blk, xsum);
+  }
+
   // scale * sum_i w_i x_i of this row-block
-  __device__ __forceinline__ float eval(const float *blk, float xsum) const {
+  __device__ __forceinline__ float value(const float *blk, float xsum) const {
     const uint32_t tb = smem_u32(blk);
     if constexpr (KIND == LMB_TERNARY) {
       const float p = (lut_8bytes<0>(v[0].x, v[0].y, tb) + lut_8bytes<16>(v[1].x, v[1].y, tb)) +
@@ -154,7 +161,7 @@ template <int KIND> struct LutUnit {
   // across the warp (no bank conflicts).  Addition order per entry is the reference's
   // (a0, a1, a2, a3 left to right, lut_gemm.hpp:30-44).
   static __device__ __forceinline__ void prologue(const float *x, size_t x_len, size_t b, bool rotate, int lane,
-                                                  float *blk, float *xsum) {
+                                                  float *blk, float *xsum, int *) {
     float v[8];
     load_x8(x, x_len, b, lane, v);
     if (rotate) fwht256_warp(v, lane);
@@ -197,30 +204,7 @@ template <> struct Unit<LMB_INT3> : LutUnit<LMB_INT3> {};
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ float as_f(uint32_t u) { return __uint_as_float(u); }
 constexpr uint32_t MAGIC = 0x4B000000u;  // 2^23
-__device__ __forceinline__ constexpr float nib_bias(int p) { return -(8388608.0f + 8.0f * float(1 << p)); }
 
-// 8 weights of one word of 4-bit codes (byte j: weight 2j in the high nibble, 2j+1 in the low
-// nibble, types.hpp:184-190) times 8 activations {xa, xb}.
-__device__ __forceinline__ void int4_word(uint32_t w, const float4 xa, const float4 xb, float2 acc[4]) {
-  const uint32_t h = w >> 12;  // brings bits 20..31 down to 8..19
-  float2 g;
-  g = add2(make_float2(as_f((w & 0x000000F0u) | MAGIC), as_f((w & 0x0000000Fu) | MAGIC)), make_float2(nib_bias(4), nib_bias(0)));
-  fma2(acc[0], g, make_float2(xa.x, xa.y));
-  g = add2(make_float2(as_f((w & 0x0000F000u) | MAGIC), as_f((w & 0x00000F00u) | MAGIC)), make_float2(nib_bias(12), nib_bias(8)));
-  fma2(acc[1], g, make_float2(xa.z, xa.w));
-  g = add2(make_float2(as_f((h & 0x00000F00u) | MAGIC), as_f((w & 0x000F0000u) | MAGIC)), make_float2(nib_bias(8), nib_bias(16)));
-  fma2(acc[2], g, make_float2(xb.x, xb.y));
-  g = add2(make_float2(as_f((h & 0x000F0000u) | MAGIC), as_f((h & 0x0000F000u) | MAGIC)), make_float2(nib_bias(16), nib_bias(12)));
-  fma2(acc[3], g, make_float2(xb.z, xb.w));
-}
-__device__ __forceinline__ float int4_finish(const float2 acc[4]) {
-  // slot scalings: acc0 (2^4, 1), acc1 (2^12, 2^8), acc2 (2^8, 2^16), acc3 (2^16, 2^12)
-  const float s0 = acc[0].y + acc[0].x * 0.0625f;
-  const float s8 = (acc[1].y + acc[2].x) * (1.0f / 256.0f);
-  const float s12 = (acc[1].x + acc[3].y) * (1.0f / 4096.0f);
-  const float s16 = (acc[2].y + acc[3].x) * (1.0f / 65536.0f);
-  return (s0 + s8) + (s12 + s16);
-}
 // 4 weights of one word of int8 codes times 4 activations.
 __device__ __forceinline__ void int8_word(uint32_t w, const float4 xv, float2 acc[2]) {
   const uint32_t u = w ^ 0x80808080u;  // q + 128 in every byte
@@ -241,30 +225,117 @@ __device__ __forceinline__ void dq_prologue(const float *x, size_t x_len, size_t
   reinterpret_cast<float4 *>(blk)[2 * lane + 1] = make_float4(v[4], v[5], v[6], v[7]);
 }
 
+// ---------------------------------------------------------------------------------------------
+// 4-bit kind on the integer tensor-core path.  The dequantise+FMA form above costs about four
+// issue slots per weight and is bound by instruction issue at 0.3 of HBM bandwidth (ncu), so
+// the 4-bit codes are fed to the 8-bit integer MMA as they are (two masks per 8 codes) and the
+// activations are turned, once per 256-block, into 32-bit fixed point with a shared exponent,
+// split into four signed base-256 digits (the MMA's 8 output columns hold the digits).  All
+// products and sums are exact integers; the only rounding is the fixed-point conversion of x
+// (absolute error <= 2^-31 of the block's largest |x|) and two int->float conversions per row
+// and block.  The zero point 8 is removed in integers with the per-block digit sums.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
 template <> struct Unit<LMB_INT4> {
-  static constexpr int FPB = 256;
+  static constexpr int FPB = 256;  // 1 KiB per block: 256 activations x 4 digit bytes, in B-operand order
   uint4 v[8];
   float sc;
+  struct Acc { float r[4]; };  // rows g, g+8, g+16, g+24 of the tile; meaningful on lanes with lane%4 == 0
+  static __device__ __forceinline__ void acc_init(Acc &a) { a.r[0] = a.r[1] = a.r[2] = a.r[3] = 0.0f; }
+  static __device__ __forceinline__ float acc_row(const Acc &a, int lane) {
+    const int src = 4 * (lane & 7);
+    const float r0 = __shfl_sync(0xffffffffu, a.r[0], src), r1 = __shfl_sync(0xffffffffu, a.r[1], src);
+    const float r2 = __shfl_sync(0xffffffffu, a.r[2], src), r3 = __shfl_sync(0xffffffffu, a.r[3], src);
+    const int k = lane >> 3;
+    return k == 0 ? r0 : (k == 1 ? r1 : (k == 2 ? r2 : r3));
+  }
   __device__ __forceinline__ void load(const uint8_t *tile, int lane) {
 #pragma unroll
     for (int c = 0; c < 8; ++c) v[c] = ld_stream_v4(tile + (size_t(c) * TILE_ROWS + lane) * 16);
     sc = ld_stream_f32(tile + size_t(8) * TILE_ROWS * 16 + size_t(lane) * 4);
   }
-  __device__ __forceinline__ float eval(const float *blk, float) const {
-    const float4 *x4 = reinterpret_cast<const float4 *>(blk);
-    float2 acc[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
+  __device__ __forceinline__ void eval(const float *blk, float blockscale, const int *dsum, Acc &acc) const {
+    const int lane = threadIdx.x & 31, g = lane >> 2, tid = lane & 3;
+    const uint4 *dig = reinterpret_cast<const uint4 *>(blk);
+    uint4 bq[4];
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
-      int4_word(v[c].x, x4[8 * c + 0], x4[8 * c + 1], acc);
-      int4_word(v[c].y, x4[8 * c + 2], x4[8 * c + 3], acc);
-      int4_word(v[c].z, x4[8 * c + 4], x4[8 * c + 5], acc);
-      int4_word(v[c].w, x4[8 * c + 6], x4[8 * c + 7], acc);
+    for (int q = 0; q < 4; ++q) bq[q] = (g < 4) ? dig[(q * 4 + g) * 4 + tid] : make_uint4(0u, 0u, 0u, 0u);
+    const int d_lo = (tid < 2) ? dsum[2 * tid] : 0, d_hi = (tid < 2) ? dsum[2 * tid + 1] : 0;
+    constexpr uint32_t M4 = 0x0F0F0F0Fu;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      int c[4] = {0, 0, 0, 0};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint4 w = v[h * 4 + q];  // {row g: k-steps 2q, 2q+1; row g+8: k-steps 2q, 2q+1}
+        mma_u8s8(c, w.x & M4, w.z & M4, (w.x >> 4) & M4, (w.z >> 4) & M4, bq[q].x, bq[q].y);
+        mma_u8s8(c, w.y & M4, w.w & M4, (w.y >> 4) & M4, (w.w >> 4) & M4, bq[q].z, bq[q].w);
+      }
+      // columns = digits: this lane holds digits 2tid, 2tid+1 of rows g (c0,c1) and g+8 (c2,c3)
+      const float f0 = float((c[0] - 8 * d_lo) + 256 * (c[1] - 8 * d_hi));
+      const float f1 = float((c[2] - 8 * d_lo) + 256 * (c[3] - 8 * d_hi));
+      const float t0 = f0 + 65536.0f * __shfl_down_sync(0xffffffffu, f0, 1);
+      const float t1 = f1 + 65536.0f * __shfl_down_sync(0xffffffffu, f1, 1);
+      const float s0 = __shfl_sync(0xffffffffu, sc, 16 * h + g), s1 = __shfl_sync(0xffffffffu, sc, 16 * h + g + 8);
+      acc.r[2 * h] += t0 * (blockscale * s0);
+      acc.r[2 * h + 1] += t1 * (blockscale * s1);
     }
-    return int4_finish(acc) * sc;
   }
+  // One warp per 256-block: load (zero padded), optionally rotate, convert to fixed point with
+  // the block's exponent, split into signed base-256 digits and store them in B-operand order;
+  // *bscale = 2^(E-30), dsum[d] = sum of digit d over the block.
   static __device__ __forceinline__ void prologue(const float *x, size_t x_len, size_t b, bool rotate, int lane,
-                                                  float *blk, float *) {
-    dq_prologue(x, x_len, b, rotate, lane, blk);
+                                                  float *blk, float *bscale, int *dsum) {
+    float v[8];
+    load_x8(x, x_len, b, lane, v);
+    if (rotate) fwht256_warp(v, lane);
+    float amax = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
+    int e = 0;
+    frexpf(amax, &e);          // amax < 2^e
+    e = max(e, -90);           // keeps 2^(30-e) finite for vanishing blocks
+    const float inv = ldexpf(1.0f, 30 - e);
+    uint32_t words[4][2] = {{0u, 0u}, {0u, 0u}, {0u, 0u}, {0u, 0u}};
+    int ds[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      int q = __float2int_rn(v[j] * inv);  // |q| <= 2^30
+#pragma unroll
+      for (int d = 0; d < 4; ++d) {
+        const int dig = (d < 3) ? int(int8_t(q & 0xFF)) : q;
+        q = (q - dig) >> 8;
+        ds[d] += dig;
+        words[d][j >> 2] |= uint32_t(dig & 0xFF) << (8 * (j & 3));
+      }
+    }
+    // element j of lane l is column 8l+j: k-step s = l/4, position kk = 8(l%4)+j inside it
+    const int s = lane >> 2, reg = (lane & 3) >> 1, tidb = 2 * (lane & 1);
+    uint32_t *dst = reinterpret_cast<uint32_t *>(blk);
+#pragma unroll
+    for (int d = 0; d < 4; ++d) {
+      const int base = (((s >> 1) * 4 + d) * 4 + tidb) * 4 + (s & 1) * 2 + reg;
+      dst[base] = words[d][0];
+      dst[base + 4] = words[d][1];
+    }
+#pragma unroll
+    for (int d = 0; d < 4; ++d) {
+#pragma unroll
+      for (int m = 16; m > 0; m >>= 1) ds[d] += __shfl_xor_sync(0xffffffffu, ds[d], m);
+    }
+    if (lane == 0) {
+      *bscale = (amax > 0.0f) ? ldexpf(1.0f, e - 30) : 0.0f;
+      dsum[0] = ds[0]; dsum[1] = ds[1]; dsum[2] = ds[2]; dsum[3] = ds[3];
+    }
   }
 };
 
@@ -277,7 +348,10 @@ template <> struct Unit<LMB_INT8> {
     for (int c = 0; c < 16; ++c) v[c] = ld_stream_v4(tile + (size_t(c) * TILE_ROWS + lane) * 16);
     sc = ld_stream_f32(tile + size_t(16) * TILE_ROWS * 16 + size_t(lane) * 4);
   }
-  __device__ __forceinline__ float eval(const float *blk, float) const {
+  using Acc = float;
+  static __device__ __forceinline__ void acc_init(Acc &a) { a = 0.0f; }
+  static __device__ __forceinline__ float acc_row(const Acc &a, int) { return a; }
+  __device__ __forceinline__ void eval(const float *blk, float, const int *, Acc &out) const {
     const float4 *x4 = reinterpret_cast<const float4 *>(blk);
     float2 acc[2] = {{0.f, 0.f}, {0.f, 0.f}};
 #pragma unroll
@@ -287,10 +361,10 @@ template <> struct Unit<LMB_INT8> {
       int8_word(v[c].z, x4[4 * c + 2], acc);
       int8_word(v[c].w, x4[4 * c + 3], acc);
     }
-    return ((acc[0].x + acc[0].y) + (acc[1].x + acc[1].y)) * sc;
+    out += ((acc[0].x + acc[0].y) + (acc[1].x + acc[1].y)) * sc;
   }
   static __device__ __forceinline__ void prologue(const float *x, size_t x_len, size_t b, bool rotate, int lane,
-                                                  float *blk, float *) {
+                                                  float *blk, float *, int *) {
     dq_prologue(x, x_len, b, rotate, lane, blk);
   }
 };
@@ -307,6 +381,7 @@ __global__ void __launch_bounds__(THREADS) k_gemv(const __grid_constant__ GemvPa
   extern __shared__ __align__(1024) float smem[];
   __shared__ float part[THREADS];
   __shared__ float xsum[64];
+  __shared__ int xaux[64 * 4];
   __shared__ int is_last;
 
   pdl_launch_dependents();
@@ -343,24 +418,26 @@ __global__ void __launch_bounds__(THREADS) k_gemv(const __grid_constant__ GemvPa
 
   const float *x = job.x + size_t(batch) * job.x_stride;
   for (int bl = warp; bl < ns; bl += WARPS)
-    U::prologue(x, job.x_len, size_t(b0 + bl), p.rotate != 0, lane, smem + size_t(bl) * FPB, xsum + bl);
+    U::prologue(x, job.x_len, size_t(b0 + bl), p.rotate != 0, lane, smem + size_t(bl) * FPB, xsum + bl, xaux + 4 * bl);
   __syncthreads();
 
-  float acc = 0.0f;
+  typename U::Acc accs;
+  U::acc_init(accs);
   if (active) {
     for (int bl = sub; bl < ns; bl += wpr) {
       const bool more = bl + wpr < ns;
       if constexpr (PREFETCH) {
         U nxt;
         if (more) nxt.load(row_tiles + size_t(bl + wpr) * TB, lane);
-        acc += cur.eval(smem + size_t(bl) * FPB, xsum[bl]);
+        cur.eval(smem + size_t(bl) * FPB, xsum[bl], xaux + 4 * bl, accs);
         if (more) cur = nxt;
       } else {
-        acc += cur.eval(smem + size_t(bl) * FPB, xsum[bl]);
+        cur.eval(smem + size_t(bl) * FPB, xsum[bl], xaux + 4 * bl, accs);
         if (more) cur.load(row_tiles + size_t(bl + wpr) * TB, lane);
       }
     }
   }
+  const float acc = U::acc_row(accs, lane);  // warp-uniform control flow: every lane takes part
 
   // combine the warps that share a row-tile, in warp order: thread t ends up with row rt0*32 + t
   part[threadIdx.x] = acc;
@@ -406,7 +483,7 @@ __global__ void k_debug_luts(const float *x, size_t x_len, int nblocks, int rota
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int b = blockIdx.x * WARPS + warp;
   if (b < nblocks) {
-    LutUnit<LMB_TERNARY>::prologue(x, x_len, size_t(b), rotate != 0, lane, tab[warp], &xs[warp]);
+    LutUnit<LMB_TERNARY>::prologue(x, x_len, size_t(b), rotate != 0, lane, tab[warp], &xs[warp], nullptr);
     __syncwarp();
     for (int i = lane; i < 1024; i += 32) out[size_t(b) * 1024 + i] = tab[warp][i];
   }

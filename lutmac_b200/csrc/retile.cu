@@ -173,6 +173,52 @@ void lane_to_block(int kind, const uint8_t *pay, const float *sc, uint8_t *blk) 
   }
 }
 
+// INT4 tiles are stored in the operand order of the 8-bit integer MMA (m16n8k32): chunk h*4+q of
+// lane (g, tid) holds four words {row 16h+g: k-steps 2q, 2q+1; row 16h+g+8: k-steps 2q, 2q+1};
+// byte j of the word of k-step s carries column 32s+4tid+j in its low nibble and column
+// 32s+16+4tid+j in its high nibble, so that `w & 0x0F0F0F0F` and `(w >> 4) & 0x0F0F0F0F` are the
+// two A-operand registers of a row without any further shuffling.  A pure permutation of the
+// nibbles of the 32 row-blocks of a tile.
+inline unsigned int4_code(const uint8_t *rowmajor, size_t row, size_t col) {
+  const size_t jb = col / 2;
+  const uint8_t byte = rowmajor[(jb / 16) * 512 + row * 16 + jb % 16];
+  return (col % 2 == 0) ? (byte >> 4) : (byte & 15u);
+}
+inline void int4_set(uint8_t *rowmajor, size_t row, size_t col, unsigned code) {
+  const size_t jb = col / 2;
+  uint8_t &byte = rowmajor[(jb / 16) * 512 + row * 16 + jb % 16];
+  byte = (col % 2 == 0) ? uint8_t((byte & 0x0F) | (code << 4)) : uint8_t((byte & 0xF0) | code);
+}
+template <class Fn> inline void int4_fragment_walk(Fn &&fn) {
+  for (size_t h = 0; h < 2; ++h)
+    for (size_t q = 0; q < 4; ++q)
+      for (size_t g = 0; g < 8; ++g)
+        for (size_t tid = 0; tid < 4; ++tid)
+          for (size_t hi8 = 0; hi8 < 2; ++hi8)
+            for (size_t so = 0; so < 2; ++so)
+              for (size_t j = 0; j < 4; ++j) {
+                const size_t row = 16 * h + g + 8 * hi8, s = 2 * q + so;
+                const size_t idx = ((h * 4 + q) * 32 + g * 4 + tid) * 16 + (hi8 * 2 + so) * 4 + j;
+                fn(idx, row, 32 * s + 4 * tid + j, 32 * s + 16 + 4 * tid + j);
+              }
+}
+void int4_to_fragments(uint8_t *payload) {  // 4096 bytes, in place
+  uint8_t src[4096];
+  std::memcpy(src, payload, 4096);
+  int4_fragment_walk([&](size_t idx, size_t row, size_t col_lo, size_t col_hi) {
+    payload[idx] = uint8_t((int4_code(src, row, col_hi) << 4) | int4_code(src, row, col_lo));
+  });
+}
+void int4_from_fragments(uint8_t *payload) {
+  uint8_t src[4096];
+  std::memcpy(src, payload, 4096);
+  std::memset(payload, 0, 4096);
+  int4_fragment_walk([&](size_t idx, size_t row, size_t col_lo, size_t col_hi) {
+    int4_set(payload, row, col_lo, src[idx] & 15u);
+    int4_set(payload, row, col_hi, src[idx] >> 4);
+  });
+}
+
 template <class F> void parallel_tiles(size_t n, F &&f) {
   unsigned hw = std::max(1u, std::thread::hardware_concurrency());
   size_t nt = std::min<size_t>(hw, std::max<size_t>(1, n / 64));
@@ -213,6 +259,7 @@ void retile(int kind, const uint8_t *blocks, size_t src_bpr, size_t row0, size_t
         float *ts = reinterpret_cast<float *>(tile + size_t(ki.chunks) * TILE_ROWS * 16);
         for (int s = 0; s < ki.nscales; ++s) ts[size_t(s) * TILE_ROWS + l] = sc[s];
       }
+      if (kind == LMB_INT4) int4_to_fragments(tile);
     }
   });
 }
@@ -225,10 +272,16 @@ void untile(int kind, const uint8_t *tiled, size_t M, size_t bpr, uint8_t *block
     float sc[2];
     for (size_t b = 0; b < bpr; ++b) {
       const uint8_t *tile = tiled + (rt * bpr + b) * tb;
+      uint8_t rowmajor[4096];
+      if (kind == LMB_INT4) {
+        std::memcpy(rowmajor, tile, 4096);
+        int4_from_fragments(rowmajor);
+      }
+      const uint8_t *paysrc = (kind == LMB_INT4) ? rowmajor : tile;
       for (size_t l = 0; l < TILE_ROWS; ++l) {
         size_t r = rt * TILE_ROWS + l;
         if (r >= M) break;
-        for (int c = 0; c < ki.chunks; ++c) std::memcpy(pay.data() + 16 * c, tile + (size_t(c) * TILE_ROWS + l) * 16, 16);
+        for (int c = 0; c < ki.chunks; ++c) std::memcpy(pay.data() + 16 * c, paysrc + (size_t(c) * TILE_ROWS + l) * 16, 16);
         const float *ts = reinterpret_cast<const float *>(tile + size_t(ki.chunks) * TILE_ROWS * 16);
         for (int s = 0; s < ki.nscales; ++s) sc[s] = ts[size_t(s) * TILE_ROWS + l];
         lane_to_block(kind, pay.data(), sc, blocks + (r * bpr + b) * size_t(ki.ref_bytes));
