@@ -460,13 +460,15 @@ __global__ void __launch_bounds__(THREADS) k_gemv(const __grid_constant__ GemvPa
   // split K: publish the partial sums, the last slice to arrive adds them in slice order
   float *scr = job.scratch + size_t(batch) * job.n_ks * job.mp;
   if (owns_row) scr[size_t(ks) * job.mp + row] = s;
-  __threadfence();
   __syncthreads();
   unsigned *ctr = job.counters + size_t(batch) * job.n_rg + rg;
-  if (t == 0) is_last = (atomicAdd(ctr, 1u) == unsigned(job.n_ks - 1));
+  if (t == 0) {
+    __threadfence();  // cumulative: publishes the CTA's partial sums (ordered before it by the barrier)
+    is_last = (atomicAdd(ctr, 1u) == unsigned(job.n_ks - 1));
+    __threadfence();
+  }
   __syncthreads();
   if (!is_last) return;
-  __threadfence();
   if (owns_row && row < job.M) {
     float tot = 0.0f;
     for (int k = 0; k < job.n_ks; ++k) tot += __ldcg(scr + size_t(k) * job.mp + row);
@@ -493,18 +495,39 @@ struct Plan {
   int R, S, n_rg, n_ks, ctas;
 };
 
-Plan make_plan(int kind, size_t row_tiles, size_t bpr, size_t batch, int sm_count) {
+// Resident CTAs per SM of k_gemv<kind> (register limited), used to count waves.
+int ctas_per_sm(int kind) { return kind_info(kind).lut ? 3 : 2; }
+
+// R row-tiles per CTA (as many as there are, up to 8) and the K split.  The split minimises a
+// makespan estimate: waves of CTAs x (blocks per warp + a fixed per-CTA cost of about two
+// blocks for prologue, barriers and the split-K hand-off); `other_ctas` are CTAs that other
+// jobs of the same launch bring along (with plenty of those, K is not split at all).
+Plan make_plan(int kind, size_t row_tiles, size_t bpr, size_t batch, int sm_count, size_t other_ctas = 0) {
   Plan pl;
   int R = 8;
   while (R > 1 && size_t(R) > row_tiles) R >>= 1;
   pl.R = R;
   pl.n_rg = int((row_tiles + R - 1) / R);
-  const int s_cap = kind_info(kind).lut ? 12 : 48;  // 48 KiB of tables / activations per CTA
-  const size_t target = size_t(2) * sm_count;  // split K only while the row groups alone leave SMs idle
-  size_t n_ks = (target + pl.n_rg * batch - 1) / (pl.n_rg * batch);
-  n_ks = n_ks < 1 ? 1 : (n_ks > bpr ? bpr : n_ks);
-  size_t S = (bpr + n_ks - 1) / n_ks;
-  if (S > size_t(s_cap)) S = s_cap;
+  const size_t s_cap = kind_info(kind).lut ? 12 : 48;  // 48 KiB of tables / activations per CTA
+  const size_t slots = size_t(sm_count) * ctas_per_sm(kind);
+  const size_t wpr = size_t(8 / R);
+  size_t best_ks = 0, best_cost = ~size_t(0);
+  for (size_t n_ks = 1; n_ks <= bpr; ++n_ks) {
+    const size_t S = (bpr + n_ks - 1) / n_ks;
+    if (S > s_cap) continue;
+    if ((bpr + S - 1) / S != n_ks) continue;  // not a distinct split
+    const size_t ctas = size_t(pl.n_rg) * n_ks * batch + other_ctas;
+    const size_t waves = (ctas + slots - 1) / slots;
+    const size_t per_warp = (S + wpr - 1) / wpr;
+    const size_t cost = waves * (per_warp + 2) * 16 + n_ks;  // ties: fewer slices
+    if (cost < best_cost) {
+      best_cost = cost;
+      best_ks = n_ks;
+    }
+    if (other_ctas >= 3 * slots) break;  // enough parallelism without splitting K
+  }
+  if (best_ks == 0) best_ks = (bpr + s_cap - 1) / s_cap;
+  size_t S = (bpr + best_ks - 1) / best_ks;
   pl.S = int(S);
   pl.n_ks = int((bpr + S - 1) / S);
   pl.ctas = pl.n_rg * pl.n_ks;
@@ -518,9 +541,12 @@ int prepare_jobs(lmb_ctx *ctx, int kind, const LinearArgs *args, int njobs, Job 
   const size_t batch = args[0].batch;
   std::vector<Plan> plans(static_cast<size_t>(njobs));
   size_t scratch_need = 0, counter_need = 0;
+  size_t total_rg = 0;
+  for (int j = 0; j < njobs; ++j) total_rg += (args[j].w->row_tiles + 7) / 8 * batch;
   for (int j = 0; j < njobs; ++j) {
     const lmb_weight *w = args[j].w;
-    plans[size_t(j)] = make_plan(kind, w->row_tiles, w->bpr, batch, ctx->sm_count);
+    const size_t others = total_rg - (w->row_tiles + 7) / 8 * batch;
+    plans[size_t(j)] = make_plan(kind, w->row_tiles, w->bpr, batch, ctx->sm_count, others);
     if (plans[size_t(j)].n_ks > 1) {
       scratch_need += batch * plans[size_t(j)].n_ks * w->row_tiles * TILE_ROWS;
       counter_need += batch * plans[size_t(j)].n_rg;

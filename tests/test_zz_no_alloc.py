@@ -49,7 +49,9 @@ def test_static_scratch_matches_lmb_linear_twice(ctx, oracle, kind, M, K):
 
 def test_static_scratch_refuses_a_split_beyond_its_array(ctx):
     rng = np.random.default_rng(0)
-    t = synth.int4_tensor(rng, 75520, 512)  # 295 row groups x 2 K-slices x 256 rows > 131072 floats
+    # 13 blocks per row exceed one CTA's table budget, so K is split at least in two:
+    # >= 2 slices x 66016 padded rows > 131072 floats
+    t = synth.ternary_tensor(rng, 66000, 3328)
     w = ctx.upload(t)
     dx, dy = ctx.malloc(t.K * 4), ctx.malloc(t.M * 4)
     st = _lib.lib().lmb_linear_static_scratch(w.h, None, dx.ptr, t.K, dy.ptr, 0, None)
