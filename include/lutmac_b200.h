@@ -150,6 +150,11 @@ typedef struct lmb_group lmb_group;
 int lmb_group_create(lmb_ctx *ctx, size_t n, const lmb_weight *const *ws, const float *const *d_xs, float *const *d_ys,
                      unsigned flags, lmb_group **out);
 int lmb_group_launch(lmb_ctx *ctx, lmb_group *g);
+/* Host-buffer form: the group owns its device and pinned staging buffers; one call copies all
+ * inputs in (inputs[i] = K_i floats), runs the single launch and copies all outputs back
+ * (outputs[i] = M_i floats). */
+int lmb_group_create_host(lmb_ctx *ctx, size_t n, const lmb_weight *const *ws, unsigned flags, lmb_group **out);
+int lmb_group_run_host(lmb_ctx *ctx, lmb_group *g, const float *const *inputs, float *const *outputs);
 int lmb_group_destroy(lmb_group *g);
 
 /* ---- kernel API on host pointers: replaces the dispatchers lut_gemv, lut_gemv_binary,

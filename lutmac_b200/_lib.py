@@ -66,6 +66,8 @@ SIGNATURES = {
     "lmb_linear_static_scratch": (C.c_int, [vp, vp, vp, sz, vp, C.c_uint, vp]),
     "lmb_group_create": (C.c_int, [vp, sz, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), C.c_uint, C.POINTER(vp)]),
     "lmb_group_launch": (C.c_int, [vp, vp]),
+    "lmb_group_create_host": (C.c_int, [vp, sz, C.POINTER(vp), C.c_uint, C.POINTER(vp)]),
+    "lmb_group_run_host": (C.c_int, [vp, vp, C.POINTER(vp), C.POINTER(vp)]),
     "lmb_group_destroy": (C.c_int, [vp]),
     "lmb_gemv_host": (C.c_int, [C.c_int, vp, sz, vp, vp, sz, sz]),
     "lmb_linear_host": (C.c_int, [vp, vp, vp, vp, vp, sz, C.c_uint]),

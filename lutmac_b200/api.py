@@ -146,6 +146,34 @@ class Group:
             pass
 
 
+class HostGroup:
+    """The host-buffer form of Group: numpy inputs in, numpy outputs out, one launch."""
+
+    def __init__(self, ctx: Context, weights, flags: int = _lib.AUTO_ROTATE):
+        n = len(weights)
+        self.ctx, self.weights = ctx, list(weights)
+        W = (C.c_void_p * n)(*[w.h for w in weights])
+        h = C.c_void_p()
+        check(lib().lmb_group_create_host(ctx.h, n, W, flags, C.byref(h)))
+        self.h = h
+        self.outs = [np.empty(w.M, np.float32) for w in weights]
+        self._Y = (C.c_void_p * n)(*[y.ctypes.data for y in self.outs])
+
+    def run(self, inputs):
+        xs = [np.ascontiguousarray(x, np.float32) for x in inputs]
+        X = (C.c_void_p * len(xs))(*[x.ctypes.data for x in xs])
+        check(lib().lmb_group_run_host(self.ctx.h, self.h, X, self._Y))
+        return self.outs
+
+    def __del__(self):
+        try:
+            if self.h:
+                lib().lmb_group_destroy(self.h)
+                self.h = None
+        except Exception:
+            pass
+
+
 class DeviceBuffer:
     def __init__(self, ctx: Context, nbytes: int):
         self.ctx = ctx

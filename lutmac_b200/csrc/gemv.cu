@@ -24,6 +24,7 @@
 // Programmatic dependent launch: a kernel lets its successor start at once, the successor
 // prefetches its first weight tiles (weights never depend on a predecessor) and only then
 // waits for the predecessor's results before touching activations or writing anything.
+#include <cstring>
 #include <new>
 #include <vector>
 
@@ -673,6 +674,11 @@ struct lmb_group {
   bool rotate = false;
   lmb::Job *d_jobs = nullptr;
   int2 *d_map = nullptr;
+  // host-buffer form (lmb_group_create_host): the group owns contiguous device and pinned
+  // host buffers for all inputs and all outputs
+  float *d_io = nullptr, *h_io = nullptr;
+  size_t in_floats = 0, out_floats = 0;
+  std::vector<size_t> in_off, out_off, in_len, out_len;
 };
 
 extern "C" {
@@ -728,7 +734,73 @@ int lmb_group_destroy(lmb_group *g) {
   if (!g) return LMB_OK;
   if (g->d_jobs) cudaFree(g->d_jobs);
   if (g->d_map) cudaFree(g->d_map);
+  if (g->d_io) cudaFree(g->d_io);
+  if (g->h_io) cudaFreeHost(g->h_io);
   delete g;
+  return LMB_OK;
+}
+
+int lmb_group_create_host(lmb_ctx *ctx, size_t n, const lmb_weight *const *ws, unsigned flags, lmb_group **out) {
+  using namespace lmb;
+  LMB_REQUIRE(ctx && ws && out && n > 0, "lmb_group_create_host: null argument");
+  *out = nullptr;
+  std::vector<size_t> in_off(n), out_off(n), in_len(n), out_len(n);
+  size_t in_f = 0, out_f = 0;
+  for (size_t i = 0; i < n; ++i) {
+    LMB_REQUIRE(ws[i], "lmb_group_create_host: null entry");
+    in_off[i] = in_f;
+    in_len[i] = ws[i]->K;
+    in_f += (ws[i]->K + 3) / 4 * 4;  // keeps every input 16-byte aligned
+  }
+  for (size_t i = 0; i < n; ++i) {
+    out_off[i] = in_f + out_f;
+    out_len[i] = ws[i]->M;
+    out_f += (ws[i]->M + 3) / 4 * 4;
+  }
+  float *d_io = nullptr, *h_io = nullptr;
+  LMB_CUDA(cudaMalloc(&d_io, (in_f + out_f) * sizeof(float)));
+  cudaError_t e = cudaMallocHost(&h_io, (in_f + out_f) * sizeof(float));
+  if (e != cudaSuccess) {
+    cudaFree(d_io);
+    return cuda_fail(e, "lmb_group_create_host");
+  }
+  std::vector<const float *> xs(n);
+  std::vector<float *> ys(n);
+  for (size_t i = 0; i < n; ++i) {
+    xs[i] = d_io + in_off[i];
+    ys[i] = d_io + out_off[i];
+  }
+  int st = lmb_group_create(ctx, n, ws, xs.data(), ys.data(), flags, out);
+  if (st != LMB_OK) {
+    cudaFree(d_io);
+    cudaFreeHost(h_io);
+    return st;
+  }
+  lmb_group *g = *out;
+  g->d_io = d_io;
+  g->h_io = h_io;
+  g->in_floats = in_f;
+  g->out_floats = out_f;
+  g->in_off = in_off;
+  g->out_off = out_off;
+  g->in_len = in_len;
+  g->out_len = out_len;
+  return LMB_OK;
+}
+
+int lmb_group_run_host(lmb_ctx *ctx, lmb_group *g, const float *const *inputs, float *const *outputs) {
+  using namespace lmb;
+  LMB_REQUIRE(ctx && g && inputs && outputs, "lmb_group_run_host: null argument");
+  LMB_REQUIRE(g->d_io, "lmb_group_run_host: the group was not made by lmb_group_create_host");
+  const size_t n = size_t(g->njobs);
+  for (size_t i = 0; i < n; ++i) std::memcpy(g->h_io + g->in_off[i], inputs[i], g->in_len[i] * sizeof(float));
+  LMB_CUDA(cudaMemcpyAsync(g->d_io, g->h_io, g->in_floats * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+  int st = lmb_group_launch(ctx, g);
+  if (st != LMB_OK) return st;
+  LMB_CUDA(cudaMemcpyAsync(g->h_io + g->in_floats, g->d_io + g->in_floats, g->out_floats * sizeof(float),
+                           cudaMemcpyDeviceToHost, ctx->stream));
+  LMB_CUDA(cudaStreamSynchronize(ctx->stream));
+  for (size_t i = 0; i < n; ++i) std::memcpy(outputs[i], g->h_io + g->out_off[i], g->out_len[i] * sizeof(float));
   return LMB_OK;
 }
 

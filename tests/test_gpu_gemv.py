@@ -208,3 +208,16 @@ def test_split_k_is_deterministic(ctx):
     x = synth.activations(rng, 8192)
     ys = [run_linear(ctx, t, x)[0] for _ in range(3)]
     assert np.array_equal(ys[0], ys[1]) and np.array_equal(ys[0], ys[2])
+
+
+def test_host_group_matches_oracle(ctx, oracle):
+    rng = np.random.default_rng(77)
+    shapes = [(256, 512), (64, 512), (1024, 512), (512, 1024), (33, 300)]
+    ts = [synth.int4_tensor(rng, M, K) for M, K in shapes]
+    ws = [ctx.upload(t) for t in ts]
+    hg = api.HostGroup(ctx, ws)
+    for _ in range(2):
+        xs = [synth.activations(rng, K) for _, K in shapes]
+        outs = hg.run(xs)
+        for t, x, y in zip(ts, xs, outs):
+            assert rel_l2(y, oracle.lut_linear(INT4, 4, t.blocks, t.M, t.K, None, x)[0]) < TOL
