@@ -66,6 +66,12 @@ int lmb_ctx_destroy(lmb_ctx *ctx);
  * pointer); NULL returns to the context's own stream. */
 int lmb_ctx_set_stream(lmb_ctx *ctx, void *cuda_stream);
 int lmb_ctx_sync(lmb_ctx *ctx);
+/* Options.  LMB_OPT_TERNARY_LUT = 1: ternary weights uploaded afterwards use the table-lookup
+ * kernel (16-entry group tables, the reference's LUT formulation) instead of the default integer
+ * tensor-core kernel.  LMB_OPT_PDL = 0: plain stream order instead of programmatic dependent
+ * launch between consecutive kernels. */
+enum { LMB_OPT_TERNARY_LUT = 1, LMB_OPT_PDL = 2 };
+int lmb_ctx_set_option(lmb_ctx *ctx, int option, int value);
 int lmb_device_count(int *out);
 /* Number of kernels this library has launched on the context since creation. */
 int lmb_ctx_launch_count(lmb_ctx *ctx, uint64_t *out);

@@ -17,6 +17,8 @@ ERR_ARG, ERR_CUDA, ERR_ALLOC, ERR_TIMEOUT, ERR_FORMAT, ERR_LIMIT, ERR_STATE = 1,
 
 ROTATE = 1
 AUTO_ROTATE = 2
+OPT_TERNARY_LUT = 1
+OPT_PDL = 2
 
 f32p = C.POINTER(C.c_float)
 vp = C.c_void_p
@@ -39,6 +41,7 @@ SIGNATURES = {
     "lmb_ctx_destroy": (C.c_int, [vp]),
     "lmb_ctx_set_stream": (C.c_int, [vp, vp]),
     "lmb_ctx_sync": (C.c_int, [vp]),
+    "lmb_ctx_set_option": (C.c_int, [vp, C.c_int, C.c_int]),
     "lmb_device_count": (C.c_int, [C.POINTER(C.c_int)]),
     "lmb_ctx_launch_count": (C.c_int, [vp, C.POINTER(C.c_uint64)]),
     "lmb_malloc": (C.c_int, [vp, sz, C.POINTER(vp)]),

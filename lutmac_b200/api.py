@@ -45,6 +45,9 @@ class Context:
     def sync(self):
         check(lib().lmb_ctx_sync(self.h))
 
+    def set_option(self, option: int, value: int):
+        check(lib().lmb_ctx_set_option(self.h, option, value))
+
     def set_stream(self, cuda_stream: Optional[int]):
         check(lib().lmb_ctx_set_stream(self.h, C.c_void_p(cuda_stream or 0)))
 

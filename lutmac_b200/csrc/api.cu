@@ -101,7 +101,7 @@ static int linear_impl(lmb_ctx *ctx, const lmb_weight *w, const float *d_bias, c
   a.batch = batch;
   // lut_linear rotates iff 0 < quant_bits <= 2 or the ternary block vector is non-empty
   // (lut_gemm_scalar.cpp:92-93): ternary, binary and 2-bit tensors.
-  const bool auto_rot = (w->kind == LMB_TERNARY || w->kind == LMB_BINARY || w->kind == LMB_INT2);
+  const bool auto_rot = (w->ref_kind == LMB_TERNARY || w->ref_kind == LMB_BINARY || w->ref_kind == LMB_INT2);
   a.rotate = (flags & LMB_ROTATE) || ((flags & LMB_AUTO_ROTATE) && auto_rot);
   return launch_gemv(ctx, &a, 1, a.rotate);
 }
@@ -208,6 +208,15 @@ int lmb_ctx_set_stream(lmb_ctx *ctx, void *cuda_stream) {
   LMB_REQUIRE(ctx, "lmb_ctx_set_stream: null context");
   ctx->stream = cuda_stream ? static_cast<cudaStream_t>(cuda_stream) : ctx->own_stream;
   return LMB_OK;
+}
+
+int lmb_ctx_set_option(lmb_ctx *ctx, int option, int value) {
+  LMB_REQUIRE(ctx, "lmb_ctx_set_option: null context");
+  switch (option) {
+  case LMB_OPT_TERNARY_LUT: ctx->ternary_lut = value != 0; return LMB_OK;
+  case LMB_OPT_PDL: ctx->pdl = value != 0; return LMB_OK;
+  default: set_last_error("lmb_ctx_set_option: unknown option"); return LMB_ERR_ARG;
+  }
 }
 
 int lmb_ctx_sync(lmb_ctx *ctx) {
@@ -345,7 +354,8 @@ int lmb_weight_upload_shard(lmb_ctx *ctx, int kind, const void *blocks, size_t M
   *out = nullptr;
   lmb_weight *w = new (std::nothrow) lmb_weight();
   if (!w) return LMB_ERR_ALLOC;
-  w->kind = kind;
+  w->ref_kind = kind;
+  w->kind = (kind == LMB_TERNARY && !ctx->ternary_lut) ? DK_TERNARY_MMA : kind;
   w->device = ctx->device;
   w->M = row1 - row0;
   w->bpr = blk1 - blk0;
@@ -353,14 +363,14 @@ int lmb_weight_upload_shard(lmb_ctx *ctx, int kind, const void *blocks, size_t M
   // except when it includes that last column.
   w->K = (blk1 == src_bpr) ? (K - blk0 * BLK) : (w->bpr * BLK);
   w->row_tiles = (w->M + TILE_ROWS - 1) / TILE_ROWS;
-  w->bytes = w->row_tiles * w->bpr * tile_bytes(kind);
+  w->bytes = w->row_tiles * w->bpr * tile_bytes(w->kind);
   void *h = nullptr;
   cudaError_t e = cudaMallocHost(&h, w->bytes);
   if (e != cudaSuccess) {
     delete w;
     return cuda_fail(e, "cudaMallocHost(weight staging)");
   }
-  retile(kind, static_cast<const uint8_t *>(blocks), src_bpr, row0, row1, blk0, blk1, static_cast<uint8_t *>(h));
+  retile(w->kind, static_cast<const uint8_t *>(blocks), src_bpr, row0, row1, blk0, blk1, static_cast<uint8_t *>(h));
   e = cudaSetDevice(ctx->device);
   if (e == cudaSuccess) e = cudaMalloc(&w->d_tiles, w->bytes);
   if (e == cudaSuccess) e = cudaMemcpyAsync(w->d_tiles, h, w->bytes, cudaMemcpyHostToDevice, ctx->stream);
@@ -389,7 +399,7 @@ int lmb_weight_free(lmb_weight *w) {
 
 int lmb_weight_info(const lmb_weight *w, int *kind, size_t *M, size_t *K, size_t *device_bytes) {
   LMB_REQUIRE(w, "lmb_weight_info: null weight");
-  if (kind) *kind = w->kind;
+  if (kind) *kind = w->ref_kind;
   if (M) *M = w->M;
   if (K) *K = w->K;
   if (device_bytes) *device_bytes = w->bytes;
@@ -527,7 +537,8 @@ int lmb_debug_luts(lmb_ctx *ctx, const float *d_x, size_t x_len, unsigned flags,
 
 int lmb_debug_ternary_indices(lmb_ctx *ctx, const lmb_weight *w, uint8_t *h_out) {
   LMB_REQUIRE(ctx && w && h_out, "lmb_debug_ternary_indices: null argument");
-  LMB_REQUIRE(w->kind == LMB_TERNARY, "lmb_debug_ternary_indices: ternary weights only");
+  LMB_REQUIRE(w->kind == LMB_TERNARY,
+              "lmb_debug_ternary_indices: only for ternary weights uploaded in the table-lookup layout (LMB_OPT_TERNARY_LUT)");
   // The kernel's LUT indices are the nibbles of the P / N planes held in the device tiles.
   std::vector<uint8_t> h(w->bytes);
   LMB_CUDA(cudaMemcpyAsync(h.data(), w->d_tiles, w->bytes, cudaMemcpyDeviceToHost, ctx->stream));

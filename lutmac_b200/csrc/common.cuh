@@ -29,7 +29,8 @@ constexpr int SM_COUNT_HINT = 148;
 // exactly the reference's bytes.  Rows beyond M are padded with zero-weight blocks.
 //
 // What a lane's chunks hold, per kind (256 weights w0..w255 of one reference block):
-//   TERNARY  4 chunks; chunk c = { P[8c..8c+7], N[8c..8c+7] } where P = ~zero & ~sign and
+//   TERNARY  (table-lookup layout; the default device layout of ternary weights is
+//            DK_TERNARY_MMA below) 4 chunks; chunk c = { P[8c..8c+7], N[8c..8c+7] } where P = ~zero & ~sign and
 //            N = ~zero & sign are the positive / negative masks of extract_indices
 //            (lut_gemm.hpp:79-99), same byte order and MSB-first bit order as the planes.
 //   BINARY   2 chunks; chunk c = data[16c..16c+15] unchanged.
@@ -44,7 +45,16 @@ constexpr int SM_COUNT_HINT = 148;
 //   INT5     10 chunks; 0..7 = low nibbles packed like INT4, 8..9 = bit-4 plane.
 //   INT6     12 chunks; 0..7 = low nibbles, 8..9 = bit-4 plane, 10..11 = bit-5 plane.
 //   INT8     16 chunks; chunk c = data[16c..16c+15] unchanged.
+//   DK_TERNARY_MMA  4 chunks of 2-bit codes t+1 in MMA operand order: chunk h*2+qq of lane
+//            (g, tid) = four words {row 16h+g: k-steps 4qq..4qq+1, 4qq+2..4qq+3; row 16h+g+8:
+//            the same}; byte j of a word holds four 2-bit fields p = 0..3: field p is column
+//            32(s0 + p/2) + 16(p%2) + 4tid + j with s0 the word's first k-step.
 // ---------------------------------------------------------------------------------------------
+// Device-only layout kind: ternary weights as 2-bit codes (t+1) in the operand order of the
+// 8-bit integer MMA.  lmb_weight::kind holds the device layout, lmb_weight::ref_kind the
+// reference block kind it was made from.
+constexpr int DK_TERNARY_MMA = 16;
+
 struct KindInfo {
   int ref_bytes;   // sizeof the reference block struct
   int chunks;      // 16-byte payload chunks per row-block
@@ -61,6 +71,7 @@ __host__ __device__ constexpr KindInfo kind_info(int kind) {
        : kind == LMB_INT5    ? KindInfo{164, 10, 1, false}
        : kind == LMB_INT6    ? KindInfo{196, 12, 1, false}
        : kind == LMB_INT8    ? KindInfo{260, 16, 1, false}
+       : kind == DK_TERNARY_MMA ? KindInfo{68, 4, 1, false}
                              : KindInfo{0, 0, 0, false};
 }
 
@@ -104,7 +115,8 @@ struct lmb_ctx {
   uint64_t capture_base = 0;
   void *comm = nullptr;  // NCCL communicator (tensor parallelism)
   int tp_rank = 0, tp_size = 1;
-  bool pdl = true;  // programmatic dependent launch between consecutive kernels
+  bool pdl = true;
+  bool ternary_lut = false;  // upload ternary weights for the table-lookup kernel instead of the MMA kernel  // programmatic dependent launch between consecutive kernels
   // scratch for split-K partial sums and its arrival counters (grown on demand)
   float *scratch = nullptr;
   size_t scratch_floats = 0;
@@ -118,7 +130,8 @@ struct lmb_ctx {
 };
 
 struct lmb_weight {
-  int kind = 0;
+  int kind = 0;      // device layout kind (a reference kind, or DK_TERNARY_MMA)
+  int ref_kind = 0;  // reference block kind
   int device = 0;
   size_t M = 0, K = 0;   // logical shape (of the shard, if sharded)
   size_t bpr = 0;        // block-columns

@@ -244,6 +244,9 @@ __device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, 
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+__device__ __forceinline__ void mma_prologue(const float *x, size_t x_len, size_t b, bool rotate, int lane, float *blk,
+                                             float *bscale, int *dsum);
+
 template <> struct Unit<LMB_INT4> {
   static constexpr int FPB = 256;  // 1 KiB per block: 256 activations x 4 digit bytes, in B-operand order
   uint4 v[8];
@@ -294,6 +297,14 @@ template <> struct Unit<LMB_INT4> {
   // *bscale = 2^(E-30), dsum[d] = sum of digit d over the block.
   static __device__ __forceinline__ void prologue(const float *x, size_t x_len, size_t b, bool rotate, int lane,
                                                   float *blk, float *bscale, int *dsum) {
+    mma_prologue(x, x_len, b, rotate, lane, blk, bscale, dsum);
+  }
+};
+
+// (definition of the shared MMA prologue)
+__device__ __forceinline__ void mma_prologue(const float *x, size_t x_len, size_t b, bool rotate, int lane, float *blk,
+                                             float *bscale, int *dsum) {
+  {
     float v[8];
     load_x8(x, x_len, b, lane, v);
     if (rotate) fwht256_warp(v, lane);
@@ -337,6 +348,54 @@ template <> struct Unit<LMB_INT4> {
       *bscale = (amax > 0.0f) ? ldexpf(1.0f, e - 30) : 0.0f;
       dsum[0] = ds[0]; dsum[1] = ds[1]; dsum[2] = ds[2]; dsum[3] = ds[3];
     }
+  }
+}
+
+// Ternary weights as 2-bit codes t+1 on the same integer MMA path (zero point 1): one word
+// yields the four A-operand registers of a row for two k-steps by shift-and-mask.
+template <> struct Unit<DK_TERNARY_MMA> {
+  static constexpr int FPB = 256;
+  uint4 v[4];
+  float sc;
+  using Acc = Unit<LMB_INT4>::Acc;
+  static __device__ __forceinline__ void acc_init(Acc &a) { Unit<LMB_INT4>::acc_init(a); }
+  static __device__ __forceinline__ float acc_row(const Acc &a, int lane) { return Unit<LMB_INT4>::acc_row(a, lane); }
+  __device__ __forceinline__ void load(const uint8_t *tile, int lane) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) v[c] = ld_stream_v4(tile + (size_t(c) * TILE_ROWS + lane) * 16);
+    sc = ld_stream_f32(tile + size_t(4) * TILE_ROWS * 16 + size_t(lane) * 4);
+  }
+  __device__ __forceinline__ void eval(const float *blk, float blockscale, const int *dsum, Acc &acc) const {
+    const int lane = threadIdx.x & 31, g = lane >> 2, tid = lane & 3;
+    const uint4 *dig = reinterpret_cast<const uint4 *>(blk);
+    uint4 bq[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) bq[q] = (g < 4) ? dig[(q * 4 + g) * 4 + tid] : make_uint4(0u, 0u, 0u, 0u);
+    const int d_lo = (tid < 2) ? dsum[2 * tid] : 0, d_hi = (tid < 2) ? dsum[2 * tid + 1] : 0;
+    constexpr uint32_t M2 = 0x03030303u;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      int c[4] = {0, 0, 0, 0};
+#pragma unroll
+      for (int qq = 0; qq < 2; ++qq) {
+        const uint4 w = v[h * 2 + qq];  // {row g: k-steps 4qq..+1, 4qq+2..+3; row g+8: the same}
+        mma_u8s8(c, w.x & M2, w.z & M2, (w.x >> 2) & M2, (w.z >> 2) & M2, bq[2 * qq].x, bq[2 * qq].y);
+        mma_u8s8(c, (w.x >> 4) & M2, (w.z >> 4) & M2, (w.x >> 6) & M2, (w.z >> 6) & M2, bq[2 * qq].z, bq[2 * qq].w);
+        mma_u8s8(c, w.y & M2, w.w & M2, (w.y >> 2) & M2, (w.w >> 2) & M2, bq[2 * qq + 1].x, bq[2 * qq + 1].y);
+        mma_u8s8(c, (w.y >> 4) & M2, (w.w >> 4) & M2, (w.y >> 6) & M2, (w.w >> 6) & M2, bq[2 * qq + 1].z, bq[2 * qq + 1].w);
+      }
+      const float f0 = float((c[0] - d_lo) + 256 * (c[1] - d_hi));
+      const float f1 = float((c[2] - d_lo) + 256 * (c[3] - d_hi));
+      const float t0 = f0 + 65536.0f * __shfl_down_sync(0xffffffffu, f0, 1);
+      const float t1 = f1 + 65536.0f * __shfl_down_sync(0xffffffffu, f1, 1);
+      const float s0 = __shfl_sync(0xffffffffu, sc, 16 * h + g), s1 = __shfl_sync(0xffffffffu, sc, 16 * h + g + 8);
+      acc.r[2 * h] += t0 * (blockscale * s0);
+      acc.r[2 * h + 1] += t1 * (blockscale * s1);
+    }
+  }
+  static __device__ __forceinline__ void prologue(const float *x, size_t x_len, size_t b, bool rotate, int lane,
+                                                  float *blk, float *bscale, int *dsum) {
+    mma_prologue(x, x_len, b, rotate, lane, blk, bscale, dsum);
   }
 };
 
@@ -626,6 +685,7 @@ int launch_params_kind(lmb_ctx *ctx, int kind, const GemvParams &p, int ctas, in
   case LMB_INT3: return launch_params<LMB_INT3>(ctx, p, ctas, s_max, batch);
   case LMB_INT4: return launch_params<LMB_INT4>(ctx, p, ctas, s_max, batch);
   case LMB_INT8: return launch_params<LMB_INT8>(ctx, p, ctas, s_max, batch);
+  case DK_TERNARY_MMA: return launch_params<DK_TERNARY_MMA>(ctx, p, ctas, s_max, batch);
   default: set_last_error("launch_gemv: kind has no device kernel"); return LMB_ERR_ARG;
   }
 }
@@ -640,6 +700,7 @@ int configure_gemv(lmb_ctx *ctx) {
   LMB_CUDA(cudaFuncSetAttribute(k_gemv<LMB_INT3>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
   LMB_CUDA(cudaFuncSetAttribute(k_gemv<LMB_INT4>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
   LMB_CUDA(cudaFuncSetAttribute(k_gemv<LMB_INT8>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  LMB_CUDA(cudaFuncSetAttribute(k_gemv<DK_TERNARY_MMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
   return LMB_OK;
 }
 
@@ -695,7 +756,7 @@ int lmb_group_create(lmb_ctx *ctx, size_t n, const lmb_weight *const *ws, const 
     args[i] = LinearArgs{ws[i], nullptr, d_xs[i], ws[i]->K, ws[i]->K, d_ys[i], ws[i]->M, 1, false};
   }
   const int kind = ws[0]->kind;
-  const bool auto_rot = (kind == LMB_TERNARY || kind == LMB_BINARY || kind == LMB_INT2);
+  const bool auto_rot = (kind == LMB_TERNARY || kind == DK_TERNARY_MMA || kind == LMB_BINARY || kind == LMB_INT2);
   std::vector<Job> jobs(n);
   std::vector<int2> map;
   lmb_group *g = new (std::nothrow) lmb_group();
@@ -861,7 +922,7 @@ int lmb_linear_static_scratch(const lmb_weight *w, const float *d_bias, const fl
   if (pl.n_ks > 1) LMB_CUDA(cudaMemsetAsync(su.counters, 0, size_t(pl.n_rg) * sizeof(unsigned), stream));
   GemvParams p;
   p.njobs = 1;
-  const bool auto_rot = (kind == LMB_TERNARY || kind == LMB_BINARY || kind == LMB_INT2);
+  const bool auto_rot = (kind == LMB_TERNARY || kind == DK_TERNARY_MMA || kind == LMB_BINARY || kind == LMB_INT2);
   p.rotate = ((flags & LMB_ROTATE) || ((flags & LMB_AUTO_ROTATE) && auto_rot)) ? 1 : 0;
   p.jobs_dev = nullptr;
   p.cta_map = nullptr;

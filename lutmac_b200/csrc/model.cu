@@ -264,7 +264,7 @@ int lmb_model_set_weight(lmb_model *m, int layer, int slot, int kind, int quant_
     dst = &m->embed; wantM = c.vocab_size; wantK = h; m->embed_host = blocks;
   } else if (slot == LMB_SLOT_LM_HEAD) {
     dst = &m->lm_head; wantM = c.vocab_size; wantK = h; r0 = M * r / g; r1 = M * (r + 1) / g; m->head_rot = rot;
-    if (g == 1 && m->embed && blocks == m->embed_host && kind == m->embed->kind) {  // tied: share the device copy
+    if (g == 1 && m->embed && blocks == m->embed_host && kind == m->embed->ref_kind) {  // tied: share the device copy
       if (m->lm_head && !m->head_tied) lmb_weight_free(m->lm_head);
       m->lm_head = m->embed;
       m->head_tied = true;

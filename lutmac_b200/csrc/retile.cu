@@ -51,6 +51,17 @@ void block_to_lane(int kind, const uint8_t *blk, uint8_t *pay, float *sc) {
     std::memcpy(sc, blk + 64, 4);
     break;
   }
+  case DK_TERNARY_MMA: {  // row-major 2-bit codes t+1 (column c in byte c/4, bits 2(c%4)); permuted per tile later
+    const uint8_t *sign = blk, *zero = blk + 32;
+    std::memset(pay, 0, 64);
+    for (size_t i = 0; i < 256; ++i) {
+      const unsigned z = plane_get(zero, i), sg = plane_get(sign, i);
+      const unsigned code = z ? 1u : (sg ? 0u : 2u);
+      pay[i / 4] |= uint8_t(code << (2 * (i % 4)));
+    }
+    std::memcpy(sc, blk + 64, 4);
+    break;
+  }
   case LMB_BINARY:
     std::memcpy(pay, blk, 32);
     std::memcpy(sc, blk + 32, 4);
@@ -118,6 +129,16 @@ void lane_to_block(int kind, const uint8_t *pay, const float *sc, uint8_t *blk) 
       }
     std::memcpy(blk + 64, sc, 4);
     break;
+  case DK_TERNARY_MMA: {
+    std::memset(blk, 0, 64);
+    for (size_t i = 0; i < 256; ++i) {
+      const unsigned code = (pay[i / 4] >> (2 * (i % 4))) & 3u;
+      if (code == 0) plane_set(blk, i, 1);       // sign plane
+      if (code == 1) plane_set(blk + 32, i, 1);  // zero plane
+    }
+    std::memcpy(blk + 64, sc, 4);
+    break;
+  }
   case LMB_BINARY:
     std::memcpy(blk, pay, 32);
     std::memcpy(blk + 32, sc, 4);
@@ -219,6 +240,45 @@ void int4_from_fragments(uint8_t *payload) {
   });
 }
 
+// DK_TERNARY_MMA: the same idea for 2-bit codes (2048 payload bytes per tile).
+template <class Fn> inline void tern_fragment_walk(Fn &&fn) {
+  for (size_t h = 0; h < 2; ++h)
+    for (size_t qq = 0; qq < 2; ++qq)
+      for (size_t g = 0; g < 8; ++g)
+        for (size_t tid = 0; tid < 4; ++tid)
+          for (size_t hi8 = 0; hi8 < 2; ++hi8)
+            for (size_t pair = 0; pair < 2; ++pair)
+              for (size_t j = 0; j < 4; ++j)
+                for (size_t pf = 0; pf < 4; ++pf) {
+                  const size_t row = 16 * h + g + 8 * hi8, s = 4 * qq + 2 * pair + pf / 2;
+                  const size_t col = 32 * s + 16 * (pf % 2) + 4 * tid + j;
+                  const size_t idx = ((h * 2 + qq) * 32 + g * 4 + tid) * 16 + (hi8 * 2 + pair) * 4 + j;
+                  fn(idx, 2 * pf, row, col);
+                }
+}
+inline unsigned tern_code(const uint8_t *rowmajor, size_t row, size_t col) {
+  const size_t jb = col / 4;
+  return (rowmajor[(jb / 16) * 512 + row * 16 + jb % 16] >> (2 * (col % 4))) & 3u;
+}
+void tern_to_fragments(uint8_t *payload) {  // 2048 bytes, in place
+  uint8_t src[2048];
+  std::memcpy(src, payload, 2048);
+  std::memset(payload, 0, 2048);
+  tern_fragment_walk([&](size_t idx, size_t shift, size_t row, size_t col) {
+    payload[idx] |= uint8_t(tern_code(src, row, col) << shift);
+  });
+}
+void tern_from_fragments(uint8_t *payload) {
+  uint8_t src[2048];
+  std::memcpy(src, payload, 2048);
+  std::memset(payload, 0, 2048);
+  tern_fragment_walk([&](size_t idx, size_t shift, size_t row, size_t col) {
+    const unsigned code = (src[idx] >> shift) & 3u;
+    const size_t jb = col / 4;
+    payload[(jb / 16) * 512 + row * 16 + jb % 16] |= uint8_t(code << (2 * (col % 4)));
+  });
+}
+
 template <class F> void parallel_tiles(size_t n, F &&f) {
   unsigned hw = std::max(1u, std::thread::hardware_concurrency());
   size_t nt = std::min<size_t>(hw, std::max<size_t>(1, n / 64));
@@ -260,6 +320,7 @@ void retile(int kind, const uint8_t *blocks, size_t src_bpr, size_t row0, size_t
         for (int s = 0; s < ki.nscales; ++s) ts[size_t(s) * TILE_ROWS + l] = sc[s];
       }
       if (kind == LMB_INT4) int4_to_fragments(tile);
+      if (kind == DK_TERNARY_MMA) tern_to_fragments(tile);
     }
   });
 }
@@ -276,8 +337,11 @@ void untile(int kind, const uint8_t *tiled, size_t M, size_t bpr, uint8_t *block
       if (kind == LMB_INT4) {
         std::memcpy(rowmajor, tile, 4096);
         int4_from_fragments(rowmajor);
+      } else if (kind == DK_TERNARY_MMA) {
+        std::memcpy(rowmajor, tile, 2048);
+        tern_from_fragments(rowmajor);
       }
-      const uint8_t *paysrc = (kind == LMB_INT4) ? rowmajor : tile;
+      const uint8_t *paysrc = (kind == LMB_INT4 || kind == DK_TERNARY_MMA) ? rowmajor : tile;
       for (size_t l = 0; l < TILE_ROWS; ++l) {
         size_t r = rt * TILE_ROWS + l;
         if (r >= M) break;

@@ -45,3 +45,14 @@ def reference():
 def ctx():
     from lutmac_b200.api import Context
     return Context(0)
+
+
+@pytest.fixture(scope="session")
+def ctx_lut():
+    """A context whose ternary weights use the table-lookup kernel (the reference's LUT
+    formulation) instead of the default integer tensor-core kernel."""
+    from lutmac_b200 import _lib
+    from lutmac_b200.api import Context
+    c = Context(0)
+    c.set_option(_lib.OPT_TERNARY_LUT, 1)
+    return c

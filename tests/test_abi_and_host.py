@@ -54,6 +54,20 @@ def test_retile_roundtrip_is_bit_exact(kind):
             assert np.array_equal(back[f], t.blocks[f]), (KIND_NAMES[kind], M, K, f)
 
 
+def test_ternary_mma_layout_roundtrip_is_bit_exact():
+    """Device-only layout 16: ternary as 2-bit codes in integer-MMA operand order."""
+    rng = np.random.default_rng(16)
+    L = _lib.lib()
+    for (M, K) in ((33, 300), (64, 512), (100, 1024)):
+        t = synth.ternary_tensor(rng, M, K)
+        tiled = np.zeros(L.lmb_tiled_bytes(16, M, K), np.uint8)
+        _lib.check(L.lmb_retile_host(16, t.blocks.ctypes.data, M, K, tiled.ctypes.data))
+        back = np.zeros(M * blocks_per_row(K), BLOCK_DTYPES[TERNARY])
+        _lib.check(L.lmb_untile_host(16, tiled.ctypes.data, M, K, back.ctypes.data))
+        for f in BLOCK_DTYPES[TERNARY].names:
+            assert np.array_equal(back[f], t.blocks[f]), (M, K, f)
+
+
 def test_ternary_tiles_hold_the_reference_lut_indices(oracle):
     """The device layout stores P = ~zero & ~sign and N = ~zero & sign: their nibbles are
     exactly extract_indices' (pos, neg)."""

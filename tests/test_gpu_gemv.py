@@ -145,7 +145,8 @@ def test_device_weight_roundtrip_bit_exact(ctx, kind):
         w.free()
 
 
-def test_ternary_lut_indices_bit_exact(ctx, oracle):
+def test_ternary_lut_indices_bit_exact(ctx_lut, oracle):
+    ctx = ctx_lut
     rng = np.random.default_rng(5)
     t = synth.ternary_tensor(rng, 40, 512)
     w = ctx.upload(t)
@@ -221,3 +222,42 @@ def test_host_group_matches_oracle(ctx, oracle):
         outs = hg.run(xs)
         for t, x, y in zip(ts, xs, outs):
             assert rel_l2(y, oracle.lut_linear(INT4, 4, t.blocks, t.M, t.K, None, x)[0]) < TOL
+
+
+@pytest.mark.parametrize("which", ["mma", "lut"])
+def test_ternary_both_device_layouts(ctx, ctx_lut, oracle, which):
+    """Ternary weights run on the integer tensor-core kernel by default and on the table-lookup
+    kernel on request; both must match the oracle, with and without rotation, and round-trip."""
+    c = ctx if which == "mma" else ctx_lut
+    rng = np.random.default_rng(21)
+    for (M, K) in EDGE_SHAPES + [(2048, 2048), (1024, 8192)]:
+        t = synth.ternary_tensor(rng, M, K)
+        x = synth.activations(rng, K)
+        for flags in (0, _lib.AUTO_ROTATE):
+            y = run_linear(c, t, x, flags=flags)[0]
+            want = (oracle.lut_linear(TERNARY, 2, t.blocks, M, K, None, x)[0] if flags
+                    else oracle.gemv(TERNARY, t.blocks, np.pad(x, (0, blocks_per_row(K) * 256 - K)), M, K))
+            err = rel_l2(y, want)
+            assert err < TOL or np.max(np.abs(y - want)) < 1e-6, (which, M, K, flags, err)
+    t = synth.ternary_tensor(rng, 70, 768)
+    w = c.upload(t)
+    back = w.download()
+    for f in BLOCK_DTYPES[TERNARY].names:
+        assert np.array_equal(back[f], t.blocks[f]), f
+    w.free()
+
+
+def test_extreme_activation_ranges(ctx, oracle):
+    """The integer tensor-core kernels quantise x per 256-block with a shared exponent: blocks
+    of very different magnitude, tiny values, and an all-zero block must still match."""
+    rng = np.random.default_rng(31)
+    for kind in (INT4, TERNARY):
+        t = synth.tensor(rng, kind, 96, 1024)
+        x = synth.activations(rng, 1024)
+        x[:256] *= 1e-20
+        x[256:512] *= 1e12
+        x[512:768] = 0.0
+        x[768] = 1e4
+        y = run_linear(ctx, t, x)[0]
+        want = oracle.gemv_f64(kind, t.blocks, x, 96, 1024)
+        assert rel_l2(y, want) < TOL, KIND_NAMES[kind]

@@ -47,7 +47,8 @@ def test_static_scratch_matches_lmb_linear_twice(ctx, oracle, kind, M, K):
     w.free()
 
 
-def test_static_scratch_refuses_a_split_beyond_its_array(ctx):
+def test_static_scratch_refuses_a_split_beyond_its_array(ctx_lut):
+    ctx = ctx_lut  # table-lookup layout: at most 12 blocks of tables per CTA
     rng = np.random.default_rng(0)
     # 13 blocks per row exceed one CTA's table budget, so K is split at least in two:
     # >= 2 slices x 66016 padded rows > 131072 floats
