@@ -57,6 +57,7 @@ __device__ float tile_elem(int kind, const uint8_t *tiles, size_t bpr, size_t ro
 
 __global__ void k_embed_rows(const int *tokens, int kind, const uint8_t *tiles, size_t bpr, size_t vocab, size_t h,
                              float *hidden) {
+  asm volatile("griddepcontrol.launch_dependents;");  // a following GEMV may prefetch its weights
   const size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= h) return;
   const int tok = tokens[blockIdx.y];
@@ -93,6 +94,7 @@ __device__ __forceinline__ float block_max(float v, float *red) {
 // hidden += add (if given); out = hidden * rsqrt(mean(hidden^2) + eps) * w.  One CTA per sequence.
 __global__ void __launch_bounds__(1024) k_add_rmsnorm(float *hidden, const float *add, const float *w, float *out,
                                                       size_t h, float eps) {
+  asm volatile("griddepcontrol.launch_dependents;");  // a following GEMV may prefetch its weights
   __shared__ float red[32];
   float *x = hidden + size_t(blockIdx.x) * h;
   const float *a = add ? add + size_t(blockIdx.x) * h : nullptr;
@@ -114,6 +116,7 @@ __global__ void __launch_bounds__(1024) k_add_rmsnorm(float *hidden, const float
 // q/k/v bias, rotary embedding of q and k (pairs d, d + hd/2), K/V written into the cache.
 __global__ void k_rope_kv(float *q, float *k, const float *v, const float *qb, const float *kb, const float *vb,
                           const float *cs_table, const size_t *positions, float *kv, size_t layer, RopeDims d) {
+  asm volatile("griddepcontrol.launch_dependents;");  // a following GEMV may prefetch its weights
   const size_t b = blockIdx.x, pos = positions[b], half = d.hd / 2;
   const float *cs = cs_table + pos * d.hd;  // [half cos | half sin]
   float *qs = q + b * d.nh * d.hd, *ks = k + b * d.nkv * d.hd;
@@ -153,58 +156,132 @@ __global__ void k_rope_kv(float *q, float *k, const float *v, const float *qb, c
   }
 }
 
-// One CTA per (head, sequence): scores over the cached keys, softmax, weighted sum of values.
-__global__ void __launch_bounds__(256) k_decode_attn(const float *q, const float *kv, const size_t *positions, float *out,
-                                                     size_t layer, RopeDims d) {
+// Split-KV decode attention.  One CTA per (query head, KV split, sequence): scores of its slice
+// of cached keys (four timesteps in flight per warp), a local softmax, the weighted sum of its
+// values; partial (max, sum, vector) go to scratch and the last split to arrive for a head
+// merges them in split order and normalises (model.cpp:338-372, attention.cpp:23-42).
+constexpr int ATT_THREADS = 128;
+constexpr int ATT_MAX_SPLIT_LEN = 2048;
+
+__global__ void __launch_bounds__(ATT_THREADS) k_decode_attn(const float *q, const float *kv, const size_t *positions,
+                                                             float *out, float *partial, unsigned *counters, int n_splits,
+                                                             size_t layer, RopeDims d) {
+  asm volatile("griddepcontrol.launch_dependents;");  // a following GEMV may prefetch its weights
   extern __shared__ float sm[];
-  float *sc = sm;                 // [max_seq]
-  float *qs = sc + d.max_seq;     // [hd]
-  float *acc = qs + d.hd;         // [groups][hd]
-  __shared__ float red[32];
-  const size_t head = blockIdx.x, b = blockIdx.y, seq = positions[b] + 1;
+  float *sc = sm;                    // [split_len]
+  float *qs = sc + d.split_len;      // [hd]
+  float *red = qs + d.hd;            // [32]
+  float *acc = red + 32;             // [ATT_THREADS]
+  __shared__ int is_last;
+  const size_t head = blockIdx.x, split = blockIdx.y, b = blockIdx.z, seq = positions[b] + 1;
   const size_t kvh = head / (d.nh / d.nkv), kv_dim = d.nkv * d.hd;
   const float *kc = kv + b * d.seq_stride + (layer * 2) * d.max_seq * kv_dim + kvh * d.hd;
   const float *vc = kc + d.max_seq * kv_dim;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-  for (size_t i = threadIdx.x; i < d.hd; i += blockDim.x) qs[i] = q[(b * d.nh + head) * d.hd + i];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = ATT_THREADS / 32;
+  // slice of this split: equal slices rounded up to 16 timesteps
+  size_t len = (seq + n_splits - 1) / n_splits;
+  len = (len + 15) / 16 * 16;
+  const size_t t0 = min(split * len, seq), t1 = min(t0 + len, seq), n = t1 - t0;
+  for (size_t i = threadIdx.x; i < d.hd; i += ATT_THREADS) qs[i] = q[(b * d.nh + head) * d.hd + i];
   __syncthreads();
   const float scale = 1.0f / sqrtf(float(d.hd));
-  for (size_t t = warp; t < seq; t += nw) {
-    const float *kt = kc + t * kv_dim;
-    float s = 0.0f;
-    for (size_t i = lane; i < d.hd; i += 32) s += qs[i] * kt[i];
+  const size_t per = d.hd / 32;  // 2 or 4 (head_dim 64 or 128); other head dims take the generic loop
+  for (size_t tb = warp * 4; tb < n; tb += nw * 4) {
+    float s[4] = {0.f, 0.f, 0.f, 0.f};
+    if (per == 4) {
+      float4 kk[4];
+      const float4 qv = reinterpret_cast<const float4 *>(qs)[lane];
 #pragma unroll
-    for (int m = 16; m > 0; m >>= 1) s += __shfl_xor_sync(0xffffffffu, s, m);
-    if (lane == 0) sc[t] = s * scale;
+      for (int i = 0; i < 4; ++i)
+        kk[i] = (tb + i < n) ? reinterpret_cast<const float4 *>(kc + (t0 + tb + i) * kv_dim)[lane] : make_float4(0, 0, 0, 0);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) s[i] = qv.x * kk[i].x + qv.y * kk[i].y + qv.z * kk[i].z + qv.w * kk[i].w;
+    } else if (per == 2) {
+      float2 kk[4];
+      const float2 qv = reinterpret_cast<const float2 *>(qs)[lane];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        kk[i] = (tb + i < n) ? reinterpret_cast<const float2 *>(kc + (t0 + tb + i) * kv_dim)[lane] : make_float2(0, 0);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) s[i] = qv.x * kk[i].x + qv.y * kk[i].y;
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (tb + i < n)
+          for (size_t c = lane; c < d.hd; c += 32) s[i] += qs[c] * kc[(t0 + tb + i) * kv_dim + c];
+    }
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) s[i] += __shfl_xor_sync(0xffffffffu, s[i], m);
+    }
+    if (lane < 4 && tb + lane < n) sc[tb + lane] = (lane == 0 ? s[0] : lane == 1 ? s[1] : lane == 2 ? s[2] : s[3]) * scale;
   }
   __syncthreads();
   float mx = -INFINITY;
-  for (size_t t = threadIdx.x; t < seq; t += blockDim.x) mx = fmaxf(mx, sc[t]);
+  for (size_t t = threadIdx.x; t < n; t += ATT_THREADS) mx = fmaxf(mx, sc[t]);
   mx = block_max(mx, red);
   float sum = 0.0f;
-  for (size_t t = threadIdx.x; t < seq; t += blockDim.x) {
+  for (size_t t = threadIdx.x; t < n; t += ATT_THREADS) {
     const float e = expf(sc[t] - mx);
     sc[t] = e;
     sum += e;
   }
   sum = block_sum(sum, red);
-  const float inv = 1.0f / sum;
   __syncthreads();
-  const size_t groups = blockDim.x / d.hd, g = threadIdx.x / d.hd, dd = threadIdx.x % d.hd;
+  // weighted values: thread = (group, dim); groups stride over timesteps, 4 loads in flight
+  const size_t groups = ATT_THREADS / d.hd, g = threadIdx.x / d.hd, dd = threadIdx.x % d.hd;
+  float a = 0.0f;
   if (g < groups) {
-    float a = 0.0f;
-    for (size_t t = g; t < seq; t += groups) a += (sc[t] * inv) * vc[t * kv_dim + dd];
-    acc[g * d.hd + dd] = a;
+    size_t t = g;
+    for (; t + 3 * groups < n; t += 4 * groups) {
+      const float v0 = vc[(t0 + t) * kv_dim + dd], v1 = vc[(t0 + t + groups) * kv_dim + dd];
+      const float v2 = vc[(t0 + t + 2 * groups) * kv_dim + dd], v3 = vc[(t0 + t + 3 * groups) * kv_dim + dd];
+      a += sc[t] * v0 + sc[t + groups] * v1 + sc[t + 2 * groups] * v2 + sc[t + 3 * groups] * v3;
+    }
+    for (; t < n; t += groups) a += sc[t] * vc[(t0 + t) * kv_dim + dd];
+  }
+  acc[threadIdx.x] = a;
+  __syncthreads();
+  // partial record of this split: [hd values | max | sum]
+  const size_t rec = d.hd + 2;
+  float *prt = partial + ((b * d.nh + head) * n_splits + split) * rec;
+  if (threadIdx.x < d.hd) {
+    float v = 0.0f;
+    for (size_t k2 = 0; k2 < groups; ++k2) v += acc[k2 * d.hd + threadIdx.x];
+    prt[threadIdx.x] = v;
+  }
+  if (threadIdx.x == 0) {
+    prt[d.hd] = mx;
+    prt[d.hd + 1] = sum;
   }
   __syncthreads();
-  if (threadIdx.x < d.hd) {
-    float a = 0.0f;
-    for (size_t k2 = 0; k2 < groups; ++k2) a += acc[k2 * d.hd + threadIdx.x];
-    out[(b * d.nh + head) * d.hd + threadIdx.x] = a;
+  unsigned *ctr = counters + b * d.nh + head;
+  if (threadIdx.x == 0) {
+    __threadfence();
+    is_last = (atomicAdd(ctr, 1u) == unsigned(n_splits - 1));
+    __threadfence();
   }
+  __syncthreads();
+  if (!is_last) return;
+  const float *all = partial + ((b * d.nh + head) * n_splits) * rec;
+  float gmx = -INFINITY;
+  for (int k2 = 0; k2 < n_splits; ++k2) gmx = fmaxf(gmx, __ldcg(all + k2 * rec + d.hd));
+  if (threadIdx.x < d.hd) {
+    float tot = 0.0f, den = 0.0f;
+    for (int k2 = 0; k2 < n_splits; ++k2) {
+      const float m2 = __ldcg(all + k2 * rec + d.hd), l2 = __ldcg(all + k2 * rec + d.hd + 1);
+      const float w = (l2 > 0.0f) ? expf(m2 - gmx) : 0.0f;
+      tot += w * __ldcg(all + k2 * rec + threadIdx.x);
+      den += w * l2;
+    }
+    out[(b * d.nh + head) * d.hd + threadIdx.x] = tot * (1.0f / den);
+  }
+  if (threadIdx.x == 0) *ctr = 0u;
 }
 
 __global__ void k_silu_mul(const float *gate, const float *up, float *out, size_t n) {
+  asm volatile("griddepcontrol.launch_dependents;");  // a following GEMV may prefetch its weights
   const size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i < n) {
     const float g = gate[i];
@@ -240,15 +317,25 @@ int launch_rope_kv(lmb_ctx *ctx, float *q, float *k, const float *v, const float
   return LMB_OK;
 }
 
-int launch_decode_attn(lmb_ctx *ctx, const float *q, const float *kv, const size_t *positions, float *out, size_t layer,
-                       const RopeDims &d, size_t batch) {
-  if (d.hd > 256 || d.hd == 0 || 256 % d.hd != 0) {
-    set_last_error("decode attention: head_dim must divide 256");
+int decode_attn_splits(const lmb_ctx *ctx, size_t nh, size_t batch, size_t max_seq) {
+  size_t n = (size_t(2) * ctx->sm_count + nh * batch - 1) / (nh * batch);
+  const size_t most = (max_seq + 63) / 64;  // no slice shorter than 64 timesteps at full context
+  n = n < 1 ? 1 : (n > 32 ? 32 : n);
+  return int(n > most ? most : n);
+}
+
+int launch_decode_attn(lmb_ctx *ctx, const float *q, const float *kv, const size_t *positions, float *out, float *partial,
+                       unsigned *counters, int n_splits, size_t layer, const RopeDims &d0, size_t batch) {
+  RopeDims d = d0;
+  if (d.hd > ATT_THREADS || d.hd == 0 || ATT_THREADS % d.hd != 0) {
+    set_last_error("decode attention: head_dim must divide 128");
     return LMB_ERR_ARG;
   }
-  const size_t smem = (d.max_seq + d.hd + 256) * sizeof(float);
-  dim3 grid(unsigned(d.nh), unsigned(batch));
-  k_decode_attn<<<grid, 256, smem, ctx->stream>>>(q, kv, positions, out, layer, d);
+  size_t len = (d.max_seq + n_splits - 1) / n_splits;
+  d.split_len = (len + 15) / 16 * 16;
+  const size_t smem = (d.split_len + d.hd + 32 + ATT_THREADS) * sizeof(float);
+  dim3 grid(unsigned(d.nh), unsigned(n_splits), unsigned(batch));
+  k_decode_attn<<<grid, ATT_THREADS, smem, ctx->stream>>>(q, kv, positions, out, partial, counters, n_splits, layer, d);
   ctx->launches++;
   LMB_CUDA(cudaGetLastError());
   return LMB_OK;

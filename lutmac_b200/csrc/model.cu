@@ -7,6 +7,7 @@
 #include <dlfcn.h>
 
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <vector>
@@ -75,12 +76,19 @@ struct lmb_model {
   // activations [max_batch][...]
   float *hidden = nullptr, *normed = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *att = nullptr, *proj = nullptr,
         *gate = nullptr, *up = nullptr, *act = nullptr, *logits = nullptr, *logits_local = nullptr;
+  float *att_partial = nullptr;      // [max_batch][nh][32 splits][hd + 2]
+  unsigned *att_counters = nullptr;  // [max_batch][nh]
   float *kv = nullptr;        // [max_batch][L][2][max_seq][nkv][hd]
   float *cs_table = nullptr;  // [max_seq][hd/2 cos | hd/2 sin]
   int *d_tokens = nullptr;
   size_t *d_pos = nullptr;
   void *h_io = nullptr;  // pinned staging for tokens + positions
   size_t seq_stride = 0;
+  // one instantiated CUDA graph of the whole step per batch size (token ids and positions are
+  // read from device buffers, so the graph never changes)
+  bool use_graph = true, capturing = false;
+  std::vector<cudaGraphExec_t> graphs;      // index = batch
+  std::vector<uint64_t> graph_launches;
 };
 
 static int dev_alloc(float **p, size_t n) {
@@ -164,7 +172,7 @@ int lmb_model_create(lmb_ctx *ctx, const lmb_model_config *c, lmb_model **out) {
   LMB_REQUIRE(g == 1 || (ctx->comm && ctx->tp_size == g && ctx->tp_rank == c->tp_rank),
               "lmb_model_create: tensor-parallel model needs lmb_tp_init on its context first");
   LMB_REQUIRE(c->num_attention_heads % c->num_key_value_heads == 0, "lmb_model_create: heads not divisible by kv heads");
-  LMB_REQUIRE(c->head_dim > 0 && c->head_dim % 2 == 0 && 256 % c->head_dim == 0, "lmb_model_create: head_dim must divide 256");
+  LMB_REQUIRE(c->head_dim > 0 && c->head_dim % 2 == 0 && 128 % c->head_dim == 0, "lmb_model_create: head_dim must divide 128");
   LMB_REQUIRE(c->num_attention_heads % g == 0 && c->num_key_value_heads % g == 0 && c->intermediate_size % g == 0 &&
                   c->vocab_size % g == 0,
               "lmb_model_create: heads, kv heads, intermediate and vocab sizes must divide by tp_size");
@@ -183,6 +191,10 @@ int lmb_model_create(lmb_ctx *ctx, const lmb_model_config *c, lmb_model **out) {
   m->inter = c->intermediate_size / g;
   m->vocab_local = c->vocab_size / g;
   m->layers.resize(c->num_hidden_layers);
+  {
+    const char *gv = getenv("LMB_MODEL_GRAPH");
+    m->use_graph = !(gv && gv[0] == '0');
+  }
   const size_t B = c->max_batch, h = c->hidden_size, hd = c->head_dim;
   m->seq_stride = c->num_hidden_layers * 2 * c->max_seq_len * m->nkv * hd;
   int st = LMB_OK;
@@ -191,6 +203,8 @@ int lmb_model_create(lmb_ctx *ctx, const lmb_model_config *c, lmb_model **out) {
   A(&m->v, B * m->nkv * hd); A(&m->att, B * m->nh * hd); A(&m->proj, B * h); A(&m->gate, B * m->inter);
   A(&m->up, B * m->inter); A(&m->act, B * m->inter); A(&m->logits, B * c->vocab_size);
   if (g > 1) A(&m->logits_local, B * m->vocab_local);
+  A(&m->att_partial, B * m->nh * 32 * (hd + 2));
+  A(reinterpret_cast<float **>(&m->att_counters), B * m->nh);
   A(&m->kv, B * m->seq_stride); A(&m->final_norm, h); A(&m->cs_table, c->max_seq_len * hd);
   for (auto &L : m->layers) { A(&L.in_norm, h); A(&L.post_norm, h); }
   if (st == LMB_OK) {
@@ -234,7 +248,8 @@ int lmb_model_destroy(lmb_model *m) {
   cudaSetDevice(m->ctx->device);
   cudaStreamSynchronize(m->ctx->stream);
   float *bufs[] = {m->hidden, m->normed, m->q, m->k, m->v, m->att, m->proj, m->gate, m->up, m->act, m->logits,
-                   m->logits_local, m->kv, m->final_norm, m->cs_table};
+                   m->logits_local, m->kv, m->final_norm, m->cs_table, m->att_partial,
+                   reinterpret_cast<float *>(m->att_counters)};
   for (float *b : bufs) if (b) cudaFree(b);
   for (auto &L : m->layers) {
     for (auto *w : L.w) lmb_weight_free(w);
@@ -243,6 +258,7 @@ int lmb_model_destroy(lmb_model *m) {
   }
   if (m->lm_head && !m->head_tied) lmb_weight_free(m->lm_head);
   lmb_weight_free(m->embed);
+  for (auto g : m->graphs) if (g) cudaGraphExecDestroy(g);
   if (m->d_tokens) cudaFree(m->d_tokens);
   if (m->d_pos) cudaFree(m->d_pos);
   if (m->h_io) cudaFreeHost(m->h_io);
@@ -253,6 +269,10 @@ int lmb_model_destroy(lmb_model *m) {
 int lmb_model_set_weight(lmb_model *m, int layer, int slot, int kind, int quant_bits, const void *blocks, size_t M, size_t K) {
   LMB_REQUIRE(m && blocks, "lmb_model_set_weight: null argument");
   LMB_REQUIRE(slot >= LMB_SLOT_EMBED && slot <= LMB_SLOT_DOWN, "lmb_model_set_weight: unknown slot");
+  for (auto &g : m->graphs) {  // captured steps hold the old pointers
+    if (g) cudaGraphExecDestroy(g);
+    g = nullptr;
+  }
   const lmb_model_config &c = m->cfg;
   const size_t g = size_t(c.tp_size), r = size_t(c.tp_rank), bpr = (K + BLK - 1) / BLK;
   const size_t h = c.hidden_size, hd = c.head_dim;
@@ -358,17 +378,64 @@ int lmb_model_forward(lmb_model *m, const int *token_ids, const size_t *position
     LMB_REQUIRE(positions[b] < c.max_seq_len, "lmb_model_forward: position beyond the KV cache");
   lmb_ctx *ctx = m->ctx;
   const size_t h = c.hidden_size, hd = c.head_dim;
-  const RopeDims rd{m->nh, m->nkv, hd, c.max_seq_len, m->seq_stride};
+  const RopeDims rd{m->nh, m->nkv, hd, c.max_seq_len, m->seq_stride, 0};
+  const int n_splits = decode_attn_splits(ctx, m->nh, batch, c.max_seq_len);
 
   int *ht = static_cast<int *>(m->h_io);
   size_t *hp = reinterpret_cast<size_t *>(static_cast<char *>(m->h_io) + c.max_batch * sizeof(int));
-  LMB_CUDA(cudaStreamSynchronize(ctx->stream));  // the staging buffer may still be in use by the previous step
-  std::memcpy(ht, token_ids, batch * sizeof(int));
-  std::memcpy(hp, positions, batch * sizeof(size_t));
-  LMB_CUDA(cudaMemcpyAsync(m->d_tokens, ht, batch * sizeof(int), cudaMemcpyHostToDevice, ctx->stream));
-  LMB_CUDA(cudaMemcpyAsync(m->d_pos, hp, batch * sizeof(size_t), cudaMemcpyHostToDevice, ctx->stream));
+  if (!m->capturing) {
+    LMB_CUDA(cudaStreamSynchronize(ctx->stream));  // the staging buffer may still be in use by the previous step
+    std::memcpy(ht, token_ids, batch * sizeof(int));
+    std::memcpy(hp, positions, batch * sizeof(size_t));
+    LMB_CUDA(cudaMemcpyAsync(m->d_tokens, ht, batch * sizeof(int), cudaMemcpyHostToDevice, ctx->stream));
+    LMB_CUDA(cudaMemcpyAsync(m->d_pos, hp, batch * sizeof(size_t), cudaMemcpyHostToDevice, ctx->stream));
+  }
 
-  int st = launch_embed_rows(ctx, m->d_tokens, m->embed, c.vocab_size, h, batch, m->hidden);
+  int st = LMB_OK;
+  const bool graphed = m->use_graph;
+  if (graphed) {
+    if (m->graphs.size() <= batch) {
+      m->graphs.resize(batch + 1, nullptr);
+      m->graph_launches.resize(batch + 1, 0);
+    }
+    if (m->graphs[batch]) {
+      LMB_CUDA(cudaGraphLaunch(m->graphs[batch], ctx->stream));
+      ctx->launches += m->graph_launches[batch];
+      goto fetch;
+    }
+    {
+      // size the split-K scratch outside capture: one eager step first (it also is this step)
+      const uint64_t before = ctx->launches;
+      m->use_graph = false;
+      st = lmb_model_forward(m, token_ids, positions, batch, nullptr);
+      m->use_graph = true;
+      if (st != LMB_OK) return st;
+      // capture the same step (it rewrites the same KV slots with the same values)
+      const uint64_t base = ctx->launches;
+      LMB_CUDA(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+      m->use_graph = false;
+      m->capturing = true;
+      st = lmb_model_forward(m, token_ids, positions, batch, nullptr);
+      m->capturing = false;
+      m->use_graph = true;
+      cudaGraph_t g = nullptr;
+      cudaError_t e = cudaStreamEndCapture(ctx->stream, &g);
+      if (st != LMB_OK) {
+        if (g) cudaGraphDestroy(g);
+        return st;
+      }
+      if (e != cudaSuccess) return cuda_fail(e, "cudaStreamEndCapture(decode step)");
+      e = cudaGraphInstantiate(&m->graphs[batch], g, 0);
+      cudaGraphDestroy(g);
+      if (e != cudaSuccess) return cuda_fail(e, "cudaGraphInstantiate(decode step)");
+      m->graph_launches[batch] = ctx->launches - base;
+      ctx->launches = base;
+      (void)before;
+      goto fetch;
+    }
+  }
+  st = launch_embed_rows(ctx, m->d_tokens, m->embed, c.vocab_size, h, batch, m->hidden);
+  {
   const float *pending = nullptr;  // residual branch not yet added to hidden
   for (size_t l = 0; l < m->layers.size() && st == LMB_OK; ++l) {
     LayerW &L = m->layers[l];
@@ -379,7 +446,7 @@ int lmb_model_forward(lmb_model *m, const int *token_ids, const size_t *position
     if (st != LMB_OK) break;
     st = launch_rope_kv(ctx, m->q, m->k, m->v, L.qb, L.kb, L.vb, m->cs_table, m->d_pos, m->kv, l, rd, batch);
     if (st != LMB_OK) break;
-    st = launch_decode_attn(ctx, m->q, m->kv, m->d_pos, m->att, l, rd, batch);
+    st = launch_decode_attn(ctx, m->q, m->kv, m->d_pos, m->att, m->att_partial, m->att_counters, n_splits, l, rd, batch);
     if (st != LMB_OK) break;
     st = gemv1(m, L.w[3], L.rot[3], nullptr, m->att, m->nh * hd, m->proj, batch);
     if (st != LMB_OK) break;
@@ -407,6 +474,8 @@ int lmb_model_forward(lmb_model *m, const int *token_ids, const size_t *position
     st = gemv1(m, m->lm_head, m->head_rot, nullptr, m->normed, h, m->logits, batch);
   }
   if (st != LMB_OK) return st;
+  }
+fetch:
   if (h_logits) {
     LMB_CUDA(cudaMemcpyAsync(h_logits, m->logits, batch * c.vocab_size * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
     LMB_CUDA(cudaStreamSynchronize(ctx->stream));
