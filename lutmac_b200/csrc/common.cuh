@@ -152,9 +152,13 @@ struct LinearArgs {
   size_t y_stride;
   size_t batch;
   bool rotate;
+  const float *x2 = nullptr;        // norm weight (XMODE_RMSNORM) or the vector multiplied in (XMODE_SILU_MUL)
+  const float *residual = nullptr;  // added to the output (same layout as y; may alias y)
 };
+// How the GEMV prologue forms its activations from x.
+enum { XMODE_PLAIN = 0, XMODE_RMSNORM = 1, XMODE_SILU_MUL = 2 };
 int configure_gemv(lmb_ctx *ctx);
-int launch_gemv(lmb_ctx *ctx, const LinearArgs *args, int njobs, bool rotate);
+int launch_gemv(lmb_ctx *ctx, const LinearArgs *args, int njobs, bool rotate, int xmode = XMODE_PLAIN, float eps = 0.0f);
 int launch_fwht256(lmb_ctx *ctx, float *d_x, size_t n);
 int launch_debug_luts(lmb_ctx *ctx, const float *d_x, size_t x_len, bool rotate, float *d_out);
 

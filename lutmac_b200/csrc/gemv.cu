@@ -44,6 +44,8 @@ struct Job {
   const float *x;
   float *y;
   const float *bias;
+  const float *x2;        // second prologue operand: norm weight (XMODE_RMSNORM) or up vector (XMODE_SILU_MUL)
+  const float *residual;  // added to the output, laid out like y (may alias y); null for none
   float *scratch;       // [batch][n_ks][mp] partial sums (n_ks > 1 only)
   unsigned *counters;   // [batch][n_rg] arrival counters (n_ks > 1 only)
   int M, mp, bpr, row_tiles;
@@ -56,6 +58,8 @@ struct GemvParams {
   Job job[MAX_JOBS];
   int njobs;
   int rotate;
+  int xmode;   // how the activations are formed in the prologue (XMODE_*)
+  float eps;   // XMODE_RMSNORM
   // a prepared group of any number of jobs: job table and per-CTA (job, first CTA of the job)
   // pairs in device memory; null for ordinary launches
   const Job *jobs_dev;
@@ -161,11 +165,7 @@ template <int KIND> struct LutUnit {
   // quarter-table) pair per lane and pass, so that the 128-bit table stores are contiguous
   // across the warp (no bank conflicts).  Addition order per entry is the reference's
   // (a0, a1, a2, a3 left to right, lut_gemm.hpp:30-44).
-  static __device__ __forceinline__ void prologue(const float *x, size_t x_len, size_t b, bool rotate, int lane,
-                                                  float *blk, float *xsum, int *) {
-    float v[8];
-    load_x8(x, x_len, b, lane, v);
-    if (rotate) fwht256_warp(v, lane);
+  static __device__ __forceinline__ void prologue(const float (&v)[8], int lane, float *blk, float *xsum, int *) {
     float s = (((v[0] + v[1]) + v[2]) + v[3]) + (((v[4] + v[5]) + v[6]) + v[7]);
 #pragma unroll
     for (int m = 16; m > 0; m >>= 1) s += __shfl_xor_sync(0xffffffffu, s, m);
@@ -218,10 +218,7 @@ __device__ __forceinline__ void int8_word(uint32_t w, const float4 xv, float2 ac
 }
 
 // Shared prologue of the dequantise kinds: the (padded, optionally rotated) block itself.
-__device__ __forceinline__ void dq_prologue(const float *x, size_t x_len, size_t b, bool rotate, int lane, float *blk) {
-  float v[8];
-  load_x8(x, x_len, b, lane, v);
-  if (rotate) fwht256_warp(v, lane);
+__device__ __forceinline__ void dq_prologue(const float (&v)[8], int lane, float *blk) {
   reinterpret_cast<float4 *>(blk)[2 * lane] = make_float4(v[0], v[1], v[2], v[3]);
   reinterpret_cast<float4 *>(blk)[2 * lane + 1] = make_float4(v[4], v[5], v[6], v[7]);
 }
@@ -244,8 +241,7 @@ __device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, 
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ void mma_prologue(const float *x, size_t x_len, size_t b, bool rotate, int lane, float *blk,
-                                             float *bscale, int *dsum);
+__device__ __forceinline__ void mma_prologue(const float (&v)[8], int lane, float *blk, float *bscale, int *dsum);
 
 template <> struct Unit<LMB_INT4> {
   static constexpr int FPB = 256;  // 1 KiB per block: 256 activations x 4 digit bytes, in B-operand order
@@ -295,19 +291,14 @@ template <> struct Unit<LMB_INT4> {
   // One warp per 256-block: load (zero padded), optionally rotate, convert to fixed point with
   // the block's exponent, split into signed base-256 digits and store them in B-operand order;
   // *bscale = 2^(E-30), dsum[d] = sum of digit d over the block.
-  static __device__ __forceinline__ void prologue(const float *x, size_t x_len, size_t b, bool rotate, int lane,
-                                                  float *blk, float *bscale, int *dsum) {
-    mma_prologue(x, x_len, b, rotate, lane, blk, bscale, dsum);
+  static __device__ __forceinline__ void prologue(const float (&v)[8], int lane, float *blk, float *bscale, int *dsum) {
+    mma_prologue(v, lane, blk, bscale, dsum);
   }
 };
 
 // (definition of the shared MMA prologue)
-__device__ __forceinline__ void mma_prologue(const float *x, size_t x_len, size_t b, bool rotate, int lane, float *blk,
-                                             float *bscale, int *dsum) {
+__device__ __forceinline__ void mma_prologue(const float (&v)[8], int lane, float *blk, float *bscale, int *dsum) {
   {
-    float v[8];
-    load_x8(x, x_len, b, lane, v);
-    if (rotate) fwht256_warp(v, lane);
     float amax = 0.0f;
 #pragma unroll
     for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
@@ -393,9 +384,8 @@ template <> struct Unit<DK_TERNARY_MMA> {
       acc.r[2 * h + 1] += t1 * (blockscale * s1);
     }
   }
-  static __device__ __forceinline__ void prologue(const float *x, size_t x_len, size_t b, bool rotate, int lane,
-                                                  float *blk, float *bscale, int *dsum) {
-    mma_prologue(x, x_len, b, rotate, lane, blk, bscale, dsum);
+  static __device__ __forceinline__ void prologue(const float (&v)[8], int lane, float *blk, float *bscale, int *dsum) {
+    mma_prologue(v, lane, blk, bscale, dsum);
   }
 };
 
@@ -423,9 +413,8 @@ template <> struct Unit<LMB_INT8> {
     }
     out += ((acc[0].x + acc[0].y) + (acc[1].x + acc[1].y)) * sc;
   }
-  static __device__ __forceinline__ void prologue(const float *x, size_t x_len, size_t b, bool rotate, int lane,
-                                                  float *blk, float *, int *) {
-    dq_prologue(x, x_len, b, rotate, lane, blk);
+  static __device__ __forceinline__ void prologue(const float (&v)[8], int lane, float *blk, float *, int *) {
+    dq_prologue(v, lane, blk);
   }
 };
 
@@ -477,8 +466,41 @@ __global__ void __launch_bounds__(THREADS) k_gemv(const __grid_constant__ GemvPa
   pdl_wait();
 
   const float *x = job.x + size_t(batch) * job.x_stride;
-  for (int bl = warp; bl < ns; bl += WARPS)
-    U::prologue(x, job.x_len, size_t(b0 + bl), p.rotate != 0, lane, smem + size_t(bl) * FPB, xsum + bl, xaux + 4 * bl);
+  float inv_rms = 1.0f;
+  if (p.xmode == XMODE_RMSNORM) {
+    // RMSNorm of the whole input vector (src/layers/norm.cpp:18-34), recomputed by every CTA
+    float ss = 0.0f;
+    for (unsigned i = threadIdx.x; i < job.x_len; i += THREADS) {
+      const float v = x[i];
+      ss += v * v;
+    }
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
+    if (lane == 0) part[warp] = ss;
+    __syncthreads();
+    ss = 0.0f;
+#pragma unroll
+    for (int k = 0; k < WARPS; ++k) ss += part[k];
+    inv_rms = 1.0f / sqrtf(ss / float(job.x_len) + p.eps);
+    __syncthreads();  // part[] is reused below
+  }
+  for (int bl = warp; bl < ns; bl += WARPS) {
+    float v[8];
+    load_x8(x, job.x_len, size_t(b0 + bl), lane, v);
+    if (p.xmode == XMODE_RMSNORM) {
+      float w8[8];
+      load_x8(job.x2, job.x_len, size_t(b0 + bl), lane, w8);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = v[j] * inv_rms * w8[j];
+    } else if (p.xmode == XMODE_SILU_MUL) {
+      float u8[8];  // silu(gate) * up, model.cpp:36,414-416
+      load_x8(job.x2 + size_t(batch) * job.x_stride, job.x_len, size_t(b0 + bl), lane, u8);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = (v[j] / (1.0f + expf(-v[j]))) * u8[j];
+    }
+    if (p.rotate) fwht256_warp(v, lane);
+    U::prologue(v, lane, smem + size_t(bl) * FPB, xsum + bl, xaux + 4 * bl);
+  }
   __syncthreads();
 
   typename U::Acc accs;
@@ -513,6 +535,7 @@ __global__ void __launch_bounds__(THREADS) k_gemv(const __grid_constant__ GemvPa
   if (job.n_ks == 1) {
     if (owns_row && row < job.M) {
       if (job.bias) s += job.bias[row];
+      if (job.residual) s += job.residual[size_t(batch) * job.y_stride + row];
       job.y[size_t(batch) * job.y_stride + row] = s;
     }
     return;
@@ -533,6 +556,7 @@ __global__ void __launch_bounds__(THREADS) k_gemv(const __grid_constant__ GemvPa
     float tot = 0.0f;
     for (int k = 0; k < job.n_ks; ++k) tot += __ldcg(scr + size_t(k) * job.mp + row);
     if (job.bias) tot += job.bias[row];
+    if (job.residual) tot += job.residual[size_t(batch) * job.y_stride + row];
     job.y[size_t(batch) * job.y_stride + row] = tot;
   }
   if (t == 0) *ctr = 0u;  // ready for the next launch
@@ -545,7 +569,10 @@ __global__ void k_debug_luts(const float *x, size_t x_len, int nblocks, int rota
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int b = blockIdx.x * WARPS + warp;
   if (b < nblocks) {
-    LutUnit<LMB_TERNARY>::prologue(x, x_len, size_t(b), rotate != 0, lane, tab[warp], &xs[warp], nullptr);
+    float v[8];
+    load_x8(x, x_len, size_t(b), lane, v);
+    if (rotate) fwht256_warp(v, lane);
+    LutUnit<LMB_TERNARY>::prologue(v, lane, tab[warp], &xs[warp], nullptr);
     __syncwarp();
     for (int i = lane; i < 1024; i += 32) out[size_t(b) * 1024 + i] = tab[warp][i];
   }
@@ -633,6 +660,8 @@ int prepare_jobs(lmb_ctx *ctx, int kind, const LinearArgs *args, int njobs, Job 
     jb.x = args[j].x;
     jb.y = args[j].y;
     jb.bias = args[j].bias;
+    jb.x2 = args[j].x2;
+    jb.residual = args[j].residual;
     jb.M = int(w->M);
     jb.mp = int(w->row_tiles * TILE_ROWS);
     jb.bpr = int(w->bpr);
@@ -705,7 +734,7 @@ int configure_gemv(lmb_ctx *ctx) {
 }
 
 // Up to MAX_JOBS independent GEMVs of one kind and one batch size in a single launch.
-int launch_gemv(lmb_ctx *ctx, const LinearArgs *args, int njobs, bool rotate) {
+int launch_gemv(lmb_ctx *ctx, const LinearArgs *args, int njobs, bool rotate, int xmode, float eps) {
   if (njobs < 1 || njobs > MAX_JOBS) {
     set_last_error("launch_gemv: between 1 and 4 jobs per launch");
     return LMB_ERR_ARG;
@@ -719,6 +748,8 @@ int launch_gemv(lmb_ctx *ctx, const LinearArgs *args, int njobs, bool rotate) {
   GemvParams p;
   p.njobs = njobs;
   p.rotate = rotate ? 1 : 0;
+  p.xmode = xmode;
+  p.eps = eps;
   p.jobs_dev = nullptr;
   p.cta_map = nullptr;
   int ctas = 0, s_max = 1;
@@ -753,7 +784,7 @@ int lmb_group_create(lmb_ctx *ctx, size_t n, const lmb_weight *const *ws, const 
   for (size_t i = 0; i < n; ++i) {
     LMB_REQUIRE(ws[i] && d_xs[i] && d_ys[i], "lmb_group_create: null entry");
     LMB_REQUIRE(ws[i]->kind == ws[0]->kind, "lmb_group_create: all weights of a group must share a block kind");
-    args[i] = LinearArgs{ws[i], nullptr, d_xs[i], ws[i]->K, ws[i]->K, d_ys[i], ws[i]->M, 1, false};
+    args[i] = LinearArgs{ws[i], nullptr, d_xs[i], ws[i]->K, ws[i]->K, d_ys[i], ws[i]->M, 1, false, nullptr, nullptr};
   }
   const int kind = ws[0]->kind;
   const bool auto_rot = (kind == LMB_TERNARY || kind == DK_TERNARY_MMA || kind == LMB_BINARY || kind == LMB_INT2);
@@ -786,6 +817,8 @@ int lmb_group_launch(lmb_ctx *ctx, lmb_group *g) {
   GemvParams p;
   p.njobs = g->njobs;
   p.rotate = g->rotate ? 1 : 0;
+  p.xmode = XMODE_PLAIN;
+  p.eps = 0.0f;
   p.jobs_dev = g->d_jobs;
   p.cta_map = g->d_map;
   return launch_params_kind(ctx, g->kind, p, g->ctas, g->s_max, 1);
@@ -922,6 +955,8 @@ int lmb_linear_static_scratch(const lmb_weight *w, const float *d_bias, const fl
   if (pl.n_ks > 1) LMB_CUDA(cudaMemsetAsync(su.counters, 0, size_t(pl.n_rg) * sizeof(unsigned), stream));
   GemvParams p;
   p.njobs = 1;
+  p.xmode = XMODE_PLAIN;
+  p.eps = 0.0f;
   const bool auto_rot = (kind == LMB_TERNARY || kind == DK_TERNARY_MMA || kind == LMB_BINARY || kind == LMB_INT2);
   p.rotate = ((flags & LMB_ROTATE) || ((flags & LMB_AUTO_ROTATE) && auto_rot)) ? 1 : 0;
   p.jobs_dev = nullptr;
@@ -931,6 +966,8 @@ int lmb_linear_static_scratch(const lmb_weight *w, const float *d_bias, const fl
   jb.x = d_x;
   jb.y = d_y;
   jb.bias = d_bias;
+  jb.x2 = nullptr;
+  jb.residual = nullptr;
   jb.scratch = su.scratch;
   jb.counters = su.counters;
   jb.M = int(w->M);

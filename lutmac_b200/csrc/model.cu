@@ -87,6 +87,7 @@ struct lmb_model {
   // one instantiated CUDA graph of the whole step per batch size (token ids and positions are
   // read from device buffers, so the graph never changes)
   bool use_graph = true, capturing = false;
+  bool fused = true;  // norm / activation / residual fused into the GEMV launches (unsharded models)
   std::vector<cudaGraphExec_t> graphs;      // index = batch
   std::vector<uint64_t> graph_launches;
 };
@@ -194,6 +195,8 @@ int lmb_model_create(lmb_ctx *ctx, const lmb_model_config *c, lmb_model **out) {
   {
     const char *gv = getenv("LMB_MODEL_GRAPH");
     m->use_graph = !(gv && gv[0] == '0');
+    const char *fv = getenv("LMB_MODEL_FUSED");
+    m->fused = !(fv && fv[0] == '0');
   }
   const size_t B = c->max_batch, h = c->hidden_size, hd = c->head_dim;
   m->seq_stride = c->num_hidden_layers * 2 * c->max_seq_len * m->nkv * hd;
@@ -341,23 +344,30 @@ int lmb_model_set_vector(lmb_model *m, int layer, int which, const float *data, 
 
 namespace {
 
-int gemv1(lmb_model *m, const lmb_weight *w, bool rot, const float *bias, const float *x, size_t x_len, float *y, size_t batch) {
-  LinearArgs a{w, bias, x, x_len, x_len, y, w->M, batch, rot};
-  return launch_gemv(m->ctx, &a, 1, rot);
+struct Fuse {
+  int xmode = XMODE_PLAIN;
+  const float *x2 = nullptr;        // norm weight / multiplied-in vector
+  const float *residual = nullptr;  // added to the output
+};
+
+int gemv1(lmb_model *m, const lmb_weight *w, bool rot, const float *x, size_t x_len, float *y, size_t batch,
+          const Fuse &f = Fuse()) {
+  LinearArgs a{w, nullptr, x, x_len, x_len, y, w->M, batch, rot, f.x2, f.residual};
+  return launch_gemv(m->ctx, &a, 1, rot, f.xmode, m->cfg.rms_norm_eps);
 }
 
 // Several projections that read the same input: one launch when kinds and rotation agree.
 int gemv_group(lmb_model *m, int n, lmb_weight *const *ws, const bool *rot, const float *x, size_t x_len, float *const *ys,
-               size_t batch) {
+               size_t batch, const Fuse &f = Fuse()) {
   bool same = true;
   for (int i = 1; i < n; ++i) same = same && ws[i]->kind == ws[0]->kind && rot[i] == rot[0];
   if (same) {
     LinearArgs a[4];
-    for (int i = 0; i < n; ++i) a[i] = LinearArgs{ws[i], nullptr, x, x_len, x_len, ys[i], ws[i]->M, batch, rot[0]};
-    return launch_gemv(m->ctx, a, n, rot[0]);
+    for (int i = 0; i < n; ++i) a[i] = LinearArgs{ws[i], nullptr, x, x_len, x_len, ys[i], ws[i]->M, batch, rot[0], f.x2, nullptr};
+    return launch_gemv(m->ctx, a, n, rot[0], f.xmode, m->cfg.rms_norm_eps);
   }
   for (int i = 0; i < n; ++i) {
-    int st = gemv1(m, ws[i], rot[i], nullptr, x, x_len, ys[i], batch);
+    int st = gemv1(m, ws[i], rot[i], x, x_len, ys[i], batch, f);
     if (st != LMB_OK) return st;
   }
   return LMB_OK;
@@ -436,6 +446,37 @@ int lmb_model_forward(lmb_model *m, const int *token_ids, const size_t *position
   }
   st = launch_embed_rows(ctx, m->d_tokens, m->embed, c.vocab_size, h, batch, m->hidden);
   {
+  if (c.tp_size == 1 && m->fused) {
+    // Fused form: RMSNorm rides in the prologue of the projections that consume it, SiLU*up in
+    // the prologue of down_proj, the residual adds in the epilogues of o_proj and down_proj
+    // (which write the hidden state in place): 6 launches per layer instead of 9.
+    for (size_t l = 0; l < m->layers.size() && st == LMB_OK; ++l) {
+      LayerW &L = m->layers[l];
+      Fuse norm1, norm2, res, act;
+      norm1.xmode = XMODE_RMSNORM; norm1.x2 = L.in_norm;
+      norm2.xmode = XMODE_RMSNORM; norm2.x2 = L.post_norm;
+      res.residual = m->hidden;
+      act.xmode = XMODE_SILU_MUL; act.x2 = m->up; act.residual = m->hidden;
+      float *qkv[3] = {m->q, m->k, m->v};
+      st = gemv_group(m, 3, &L.w[0], &L.rot[0], m->hidden, h, qkv, batch, norm1);
+      if (st != LMB_OK) break;
+      st = launch_rope_kv(ctx, m->q, m->k, m->v, L.qb, L.kb, L.vb, m->cs_table, m->d_pos, m->kv, l, rd, batch);
+      if (st != LMB_OK) break;
+      st = launch_decode_attn(ctx, m->q, m->kv, m->d_pos, m->att, m->att_partial, m->att_counters, n_splits, l, rd, batch);
+      if (st != LMB_OK) break;
+      st = gemv1(m, L.w[3], L.rot[3], m->att, m->nh * hd, m->hidden, batch, res);
+      if (st != LMB_OK) break;
+      float *gu[2] = {m->gate, m->up};
+      st = gemv_group(m, 2, &L.w[4], &L.rot[4], m->hidden, h, gu, batch, norm2);
+      if (st != LMB_OK) break;
+      st = gemv1(m, L.w[6], L.rot[6], m->gate, m->inter, m->hidden, batch, act);
+    }
+    if (st != LMB_OK) return st;
+    Fuse fin;
+    fin.xmode = XMODE_RMSNORM; fin.x2 = m->final_norm;
+    st = gemv1(m, m->lm_head, m->head_rot, m->hidden, h, m->logits, batch, fin);
+    if (st != LMB_OK) return st;
+  } else {
   const float *pending = nullptr;  // residual branch not yet added to hidden
   for (size_t l = 0; l < m->layers.size() && st == LMB_OK; ++l) {
     LayerW &L = m->layers[l];
@@ -448,7 +489,7 @@ int lmb_model_forward(lmb_model *m, const int *token_ids, const size_t *position
     if (st != LMB_OK) break;
     st = launch_decode_attn(ctx, m->q, m->kv, m->d_pos, m->att, m->att_partial, m->att_counters, n_splits, l, rd, batch);
     if (st != LMB_OK) break;
-    st = gemv1(m, L.w[3], L.rot[3], nullptr, m->att, m->nh * hd, m->proj, batch);
+    st = gemv1(m, L.w[3], L.rot[3], m->att, m->nh * hd, m->proj, batch);
     if (st != LMB_OK) break;
     if (c.tp_size > 1 && (st = lmb_allreduce_sum(ctx, m->proj, batch * h)) != LMB_OK) break;
     st = launch_add_rmsnorm(ctx, m->hidden, m->proj, L.post_norm, m->normed, h, batch, c.rms_norm_eps);
@@ -458,7 +499,7 @@ int lmb_model_forward(lmb_model *m, const int *token_ids, const size_t *position
     if (st != LMB_OK) break;
     st = launch_silu_mul(ctx, m->gate, m->up, m->act, batch * m->inter);
     if (st != LMB_OK) break;
-    st = gemv1(m, L.w[6], L.rot[6], nullptr, m->act, m->inter, m->proj, batch);
+    st = gemv1(m, L.w[6], L.rot[6], m->act, m->inter, m->proj, batch);
     if (st != LMB_OK) break;
     if (c.tp_size > 1 && (st = lmb_allreduce_sum(ctx, m->proj, batch * h)) != LMB_OK) break;
     pending = m->proj;
@@ -467,13 +508,14 @@ int lmb_model_forward(lmb_model *m, const int *token_ids, const size_t *position
   st = launch_add_rmsnorm(ctx, m->hidden, pending, m->final_norm, m->normed, h, batch, c.rms_norm_eps);
   if (st != LMB_OK) return st;
   if (c.tp_size > 1) {
-    st = gemv1(m, m->lm_head, m->head_rot, nullptr, m->normed, h, m->logits_local, batch);
+    st = gemv1(m, m->lm_head, m->head_rot, m->normed, h, m->logits_local, batch);
     for (size_t b = 0; b < batch && st == LMB_OK; ++b)
       st = lmb_allgather(ctx, m->logits_local + b * m->vocab_local, m->logits + b * c.vocab_size, m->vocab_local);
   } else {
-    st = gemv1(m, m->lm_head, m->head_rot, nullptr, m->normed, h, m->logits, batch);
+    st = gemv1(m, m->lm_head, m->head_rot, m->normed, h, m->logits, batch);
   }
   if (st != LMB_OK) return st;
+  }
   }
 fetch:
   if (h_logits) {
