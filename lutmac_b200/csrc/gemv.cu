@@ -585,40 +585,45 @@ struct Plan {
 // Resident CTAs per SM of k_gemv<kind> (register limited), used to count waves.
 int ctas_per_sm(int kind) { return kind_info(kind).lut ? 3 : 2; }
 
-// R row-tiles per CTA (as many as there are, up to 8) and the K split.  The split minimises a
-// makespan estimate: waves of CTAs x (blocks per warp + a fixed per-CTA cost of about two
-// blocks for prologue, barriers and the split-K hand-off); `other_ctas` are CTAs that other
-// jobs of the same launch bring along (with plenty of those, K is not split at all).
+// Chooses R (row-tiles per CTA: 8, 4, 2 or 1; the 8 warps of a CTA then share a row-tile
+// 1, 2, 4 or 8 ways along K, which costs only a shared-memory reduction) and the K split over
+// CTAs (which costs a trip through global scratch) by minimising a makespan estimate in units
+// of "one warp evaluates one 256-column block":
+//     waves of CTAs x (blocks per warp + prologue share + fixed CTA cost [+ split-K hand-off]).
+// `other_ctas` are CTAs that other jobs of the same launch bring along.
 Plan make_plan(int kind, size_t row_tiles, size_t bpr, size_t batch, int sm_count, size_t other_ctas = 0) {
-  Plan pl;
-  int R = 8;
-  while (R > 1 && size_t(R) > row_tiles) R >>= 1;
-  pl.R = R;
-  pl.n_rg = int((row_tiles + R - 1) / R);
-  const size_t s_cap = kind_info(kind).lut ? 12 : 48;  // 48 KiB of tables / activations per CTA
+  const bool lut = kind_info(kind).lut;
+  const size_t s_cap = lut ? 12 : 48;  // 48 KiB of tables / activations per CTA
   const size_t slots = size_t(sm_count) * ctas_per_sm(kind);
-  const size_t wpr = size_t(8 / R);
-  size_t best_ks = 0, best_cost = ~size_t(0);
-  for (size_t n_ks = 1; n_ks <= bpr; ++n_ks) {
-    const size_t S = (bpr + n_ks - 1) / n_ks;
-    if (S > s_cap) continue;
-    if ((bpr + S - 1) / S != n_ks) continue;  // not a distinct split
-    const size_t ctas = size_t(pl.n_rg) * n_ks * batch + other_ctas;
-    const size_t waves = (ctas + slots - 1) / slots;
-    const size_t per_warp = (S + wpr - 1) / wpr;
-    const size_t cost = waves * (per_warp + 2) * 16 + n_ks;  // ties: fewer slices
-    if (cost < best_cost) {
-      best_cost = cost;
-      best_ks = n_ks;
+  const double prologue_per_block = lut ? 1.0 : 0.5, fixed = 1.5, split_cost = 2.5;
+  Plan best{};
+  double best_cost = 1e30;
+  for (int R = 8; R >= 1; R >>= 1) {
+    if (size_t(R) > row_tiles && R > 1) continue;
+    const size_t n_rg = (row_tiles + R - 1) / R, wpr = size_t(8 / R);
+    for (size_t n_ks = 1; n_ks <= bpr; ++n_ks) {
+      const size_t S = (bpr + n_ks - 1) / n_ks;
+      if (S > s_cap) continue;
+      if ((bpr + S - 1) / S != n_ks) continue;  // not a distinct split
+      const size_t own = n_rg * n_ks * batch;
+      const double per_warp = double((S + wpr - 1) / wpr);
+      const double cta_time = per_warp + prologue_per_block * double((S + 7) / 8) + fixed + (n_ks > 1 ? split_cost : 0.0);
+      // with plenty of CTAs from other jobs the GPU is busy anyway: minimise this job's total
+      // CTA time; otherwise minimise the time until its last CTA finishes
+      const double cost = (other_ctas >= 2 * slots ? double(own) * cta_time / double(slots)
+                                                   : double((own + other_ctas + slots - 1) / slots) * cta_time) +
+                          1e-3 * double(n_ks) + 1e-4 * double(8 / R);
+      if (cost < best_cost) {
+        best_cost = cost;
+        best.R = R;
+        best.S = int(S);
+        best.n_rg = int(n_rg);
+        best.n_ks = int(n_ks);
+      }
     }
-    if (other_ctas >= 3 * slots) break;  // enough parallelism without splitting K
   }
-  if (best_ks == 0) best_ks = (bpr + s_cap - 1) / s_cap;
-  size_t S = (bpr + best_ks - 1) / best_ks;
-  pl.S = int(S);
-  pl.n_ks = int((bpr + S - 1) / S);
-  pl.ctas = pl.n_rg * pl.n_ks;
-  return pl;
+  best.ctas = best.n_rg * best.n_ks;
+  return best;
 }
 
 // Plans every job of a launch and fills the job descriptors (scratch regions are carved out of
