@@ -1,8 +1,7 @@
 // Glue kernels of one decode step, all fp32 like the reference: embedding-row dequantisation
 // (src/model.cpp:58-252), RMSNorm with fused residual add (src/layers/norm.cpp:18-34,
-// model.cpp:385-399), bias + RoPE + KV-cache write (model.cpp:312-335,
-// src/layers/embedding.cpp:36-75), GQA decode attention (model.cpp:338-372,
-// src/layers/attention.cpp:23-42) and SiLU(gate)*up (model.cpp:36,414-416).
+// model.cpp:385-399), GQA decode attention with bias + RoPE + KV-cache write folded in
+// (model.cpp:312-372, src/layers/embedding.cpp:36-75, src/layers/attention.cpp:23-42) and SiLU(gate)*up (model.cpp:36,414-416).
 #include "decode_ops.cuh"
 
 namespace lmb {
@@ -113,102 +112,123 @@ __global__ void __launch_bounds__(1024) k_add_rmsnorm(float *hidden, const float
   for (size_t i = threadIdx.x; i < h; i += blockDim.x) o[i] = x[i] * inv * w[i];
 }
 
-// q/k/v bias, rotary embedding of q and k (pairs d, d + hd/2), K/V written into the cache.
-__global__ void k_rope_kv(float *q, float *k, const float *v, const float *qb, const float *kb, const float *vb,
-                          const float *cs_table, const size_t *positions, float *kv, size_t layer, RopeDims d) {
-  asm volatile("griddepcontrol.launch_dependents;");  // a following GEMV may prefetch its weights
-  const size_t b = blockIdx.x, pos = positions[b], half = d.hd / 2;
-  const float *cs = cs_table + pos * d.hd;  // [half cos | half sin]
-  float *qs = q + b * d.nh * d.hd, *ks = k + b * d.nkv * d.hd;
-  const float *vs = v + b * d.nkv * d.hd;
-  const size_t kv_dim = d.nkv * d.hd;
-  float *kc = kv + b * d.seq_stride + (layer * 2) * d.max_seq * kv_dim + pos * kv_dim;
-  float *vc = kc + d.max_seq * kv_dim;
-  for (size_t i = threadIdx.x; i < d.nh * half; i += blockDim.x) {
-    const size_t hh = i / half, dd = i % half, i0 = hh * d.hd + dd, i1 = i0 + half;
-    float a = qs[i0], c = qs[i1];
-    if (qb) {
-      a += qb[i0];
-      c += qb[i1];
-    }
-    qs[i0] = a * cs[dd] - c * cs[half + dd];
-    qs[i1] = a * cs[half + dd] + c * cs[dd];
-  }
-  for (size_t i = threadIdx.x; i < d.nkv * half; i += blockDim.x) {
-    const size_t hh = i / half, dd = i % half, i0 = hh * d.hd + dd, i1 = i0 + half;
-    float a = ks[i0], c = ks[i1];
-    if (kb) {
-      a += kb[i0];
-      c += kb[i1];
-    }
-    const float r0 = a * cs[dd] - c * cs[half + dd], r1 = a * cs[half + dd] + c * cs[dd];
-    ks[i0] = r0;
-    ks[i1] = r1;
-    kc[i0] = r0;
-    kc[i1] = r1;
-    float v0 = vs[i0], v1 = vs[i1];
-    if (vb) {
-      v0 += vb[i0];
-      v1 += vb[i1];
-    }
-    vc[i0] = v0;
-    vc[i1] = v1;
-  }
-}
+// Split-KV decode attention with the q/k/v bias, the rotary embedding and the KV-cache write of
+// the new position folded in (model.cpp:312-372, embedding.cpp:36-75, attention.cpp:23-42).
+// One CTA per (query head, KV split, sequence).  Every CTA rotates its own query head; the split
+// that contains the new position takes that position's key/value from the fresh projections
+// (and, for the first query head of a KV group, stores them in the cache) instead of reading
+// the cache.  Scores of the slice (four timesteps in flight per warp), a local softmax, the
+// weighted values (eight loads in flight per thread); partial (max, sum, vector) go to scratch
+// and the last split to arrive for a head merges them in split order and normalises.
+constexpr int ATT_THREADS = 256;
 
-// Split-KV decode attention.  One CTA per (query head, KV split, sequence): scores of its slice
-// of cached keys (four timesteps in flight per warp), a local softmax, the weighted sum of its
-// values; partial (max, sum, vector) go to scratch and the last split to arrive for a head
-// merges them in split order and normalises (model.cpp:338-372, attention.cpp:23-42).
-constexpr int ATT_THREADS = 128;
-constexpr int ATT_MAX_SPLIT_LEN = 2048;
+struct AttnArgs {
+  const float *q, *k, *v;          // fresh projections [batch][heads*hd]
+  const float *qb, *kb, *vb;       // biases or null
+  const float *cs_table;           // [max_seq][hd/2 cos | hd/2 sin]
+  const size_t *positions;
+  float *kv;                       // cache
+  float *out;                      // [batch][nh*hd]
+  float *partial;
+  unsigned *counters;
+  int n_splits;
+  size_t layer;
+};
 
-__global__ void __launch_bounds__(ATT_THREADS) k_decode_attn(const float *q, const float *kv, const size_t *positions,
-                                                             float *out, float *partial, unsigned *counters, int n_splits,
-                                                             size_t layer, RopeDims d) {
+__global__ void __launch_bounds__(ATT_THREADS) k_decode_attn(const AttnArgs a, const RopeDims d) {
   asm volatile("griddepcontrol.launch_dependents;");  // a following GEMV may prefetch its weights
   extern __shared__ float sm[];
   float *sc = sm;                    // [split_len]
-  float *qs = sc + d.split_len;      // [hd]
-  float *red = qs + d.hd;            // [32]
+  float *qs = sc + d.split_len;      // [hd] rotated query
+  float *kn = qs + d.hd;             // [hd] rotated key of the new position
+  float *vn = kn + d.hd;             // [hd] value of the new position
+  float *red = vn + d.hd;            // [32]
   float *acc = red + 32;             // [ATT_THREADS]
   __shared__ int is_last;
-  const size_t head = blockIdx.x, split = blockIdx.y, b = blockIdx.z, seq = positions[b] + 1;
-  const size_t kvh = head / (d.nh / d.nkv), kv_dim = d.nkv * d.hd;
-  const float *kc = kv + b * d.seq_stride + (layer * 2) * d.max_seq * kv_dim + kvh * d.hd;
-  const float *vc = kc + d.max_seq * kv_dim;
+  const size_t head = blockIdx.x, split = blockIdx.y, b = blockIdx.z, pos = a.positions[b], seq = pos + 1;
+  const size_t group = d.nh / d.nkv, kvh = head / group, kv_dim = d.nkv * d.hd, half = d.hd / 2;
+  float *kc_w = a.kv + b * d.seq_stride + (a.layer * 2) * d.max_seq * kv_dim + kvh * d.hd;
+  float *vc_w = kc_w + d.max_seq * kv_dim;
+  const float *kc = kc_w, *vc = vc_w;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = ATT_THREADS / 32;
-  // slice of this split: equal slices rounded up to 16 timesteps
+  const int n_splits = a.n_splits;
   size_t len = (seq + n_splits - 1) / n_splits;
   len = (len + 15) / 16 * 16;
   const size_t t0 = min(split * len, seq), t1 = min(t0 + len, seq), n = t1 - t0;
-  for (size_t i = threadIdx.x; i < d.hd; i += ATT_THREADS) qs[i] = q[(b * d.nh + head) * d.hd + i];
+  const bool has_new = (pos >= t0 && pos < t1);
+  const float *cs = a.cs_table + pos * d.hd;
+  // rotate the query head (and the new key), pairs (i, i + hd/2)
+  for (size_t i = threadIdx.x; i < half; i += ATT_THREADS) {
+    const float c = cs[i], sn = cs[half + i];
+    const size_t i0 = (b * d.nh + head) * d.hd + i, i1 = i0 + half;
+    float x0 = a.q[i0], x1 = a.q[i1];
+    if (a.qb) {
+      x0 += a.qb[head * d.hd + i];
+      x1 += a.qb[head * d.hd + i + half];
+    }
+    qs[i] = x0 * c - x1 * sn;
+    qs[i + half] = x0 * sn + x1 * c;
+    if (has_new) {
+      const size_t k0 = (b * d.nkv + kvh) * d.hd + i, k1 = k0 + half;
+      float y0 = a.k[k0], y1 = a.k[k1], v0 = a.v[k0], v1 = a.v[k1];
+      if (a.kb) {
+        y0 += a.kb[kvh * d.hd + i];
+        y1 += a.kb[kvh * d.hd + i + half];
+      }
+      if (a.vb) {
+        v0 += a.vb[kvh * d.hd + i];
+        v1 += a.vb[kvh * d.hd + i + half];
+      }
+      const float r0 = y0 * c - y1 * sn, r1 = y0 * sn + y1 * c;
+      kn[i] = r0;
+      kn[i + half] = r1;
+      vn[i] = v0;
+      vn[i + half] = v1;
+      if (head % group == 0) {  // one writer per KV head
+        kc_w[pos * kv_dim + i] = r0;
+        kc_w[pos * kv_dim + i + half] = r1;
+        vc_w[pos * kv_dim + i] = v0;
+        vc_w[pos * kv_dim + i + half] = v1;
+      }
+    }
+  }
   __syncthreads();
   const float scale = 1.0f / sqrtf(float(d.hd));
   const size_t per = d.hd / 32;  // 2 or 4 (head_dim 64 or 128); other head dims take the generic loop
+  const size_t tnew = has_new ? pos - t0 : ~size_t(0);  // slice-local index of the new position
   for (size_t tb = warp * 4; tb < n; tb += nw * 4) {
     float s[4] = {0.f, 0.f, 0.f, 0.f};
     if (per == 4) {
       float4 kk[4];
       const float4 qv = reinterpret_cast<const float4 *>(qs)[lane];
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
-        kk[i] = (tb + i < n) ? reinterpret_cast<const float4 *>(kc + (t0 + tb + i) * kv_dim)[lane] : make_float4(0, 0, 0, 0);
+      for (int i = 0; i < 4; ++i) {
+        const size_t t = tb + i;
+        kk[i] = (t >= n) ? make_float4(0, 0, 0, 0)
+                : (t == tnew) ? reinterpret_cast<const float4 *>(kn)[lane]
+                              : reinterpret_cast<const float4 *>(kc + (t0 + t) * kv_dim)[lane];
+      }
 #pragma unroll
       for (int i = 0; i < 4; ++i) s[i] = qv.x * kk[i].x + qv.y * kk[i].y + qv.z * kk[i].z + qv.w * kk[i].w;
     } else if (per == 2) {
       float2 kk[4];
       const float2 qv = reinterpret_cast<const float2 *>(qs)[lane];
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
-        kk[i] = (tb + i < n) ? reinterpret_cast<const float2 *>(kc + (t0 + tb + i) * kv_dim)[lane] : make_float2(0, 0);
+      for (int i = 0; i < 4; ++i) {
+        const size_t t = tb + i;
+        kk[i] = (t >= n) ? make_float2(0, 0)
+                : (t == tnew) ? reinterpret_cast<const float2 *>(kn)[lane]
+                              : reinterpret_cast<const float2 *>(kc + (t0 + t) * kv_dim)[lane];
+      }
 #pragma unroll
       for (int i = 0; i < 4; ++i) s[i] = qv.x * kk[i].x + qv.y * kk[i].y;
     } else {
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
-        if (tb + i < n)
-          for (size_t c = lane; c < d.hd; c += 32) s[i] += qs[c] * kc[(t0 + tb + i) * kv_dim + c];
+      for (int i = 0; i < 4; ++i) {
+        const size_t t = tb + i;
+        if (t < n)
+          for (size_t c = lane; c < d.hd; c += 32) s[i] += qs[c] * (t == tnew ? kn[c] : kc[(t0 + t) * kv_dim + c]);
+      }
     }
 #pragma unroll
     for (int m = 16; m > 0; m >>= 1) {
@@ -229,23 +249,28 @@ __global__ void __launch_bounds__(ATT_THREADS) k_decode_attn(const float *q, con
   }
   sum = block_sum(sum, red);
   __syncthreads();
-  // weighted values: thread = (group, dim); groups stride over timesteps, 4 loads in flight
+  // weighted values: thread = (group, dim); groups stride over the slice, 8 loads in flight.
+  // The new position (if in this slice) is left out here and added from shared memory below.
   const size_t groups = ATT_THREADS / d.hd, g = threadIdx.x / d.hd, dd = threadIdx.x % d.hd;
-  float a = 0.0f;
-  if (g < groups) {
+  const size_t n_old = has_new ? n - 1 : n;  // the new position is always the last of its slice
+  float av = 0.0f;
+  {
     size_t t = g;
-    for (; t + 3 * groups < n; t += 4 * groups) {
-      const float v0 = vc[(t0 + t) * kv_dim + dd], v1 = vc[(t0 + t + groups) * kv_dim + dd];
-      const float v2 = vc[(t0 + t + 2 * groups) * kv_dim + dd], v3 = vc[(t0 + t + 3 * groups) * kv_dim + dd];
-      a += sc[t] * v0 + sc[t + groups] * v1 + sc[t + 2 * groups] * v2 + sc[t + 3 * groups] * v3;
+    for (; t + 7 * groups < n_old; t += 8 * groups) {
+      float vv[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) vv[i] = vc[(t0 + t + i * groups) * kv_dim + dd];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) av += sc[t + i * groups] * vv[i];
     }
-    for (; t < n; t += groups) a += sc[t] * vc[(t0 + t) * kv_dim + dd];
+    for (; t < n_old; t += groups) av += sc[t] * vc[(t0 + t) * kv_dim + dd];
+    if (has_new && g == 0) av += sc[n - 1] * vn[dd];
   }
-  acc[threadIdx.x] = a;
+  acc[threadIdx.x] = av;
   __syncthreads();
   // partial record of this split: [hd values | max | sum]
   const size_t rec = d.hd + 2;
-  float *prt = partial + ((b * d.nh + head) * n_splits + split) * rec;
+  float *prt = a.partial + ((b * d.nh + head) * n_splits + split) * rec;
   if (threadIdx.x < d.hd) {
     float v = 0.0f;
     for (size_t k2 = 0; k2 < groups; ++k2) v += acc[k2 * d.hd + threadIdx.x];
@@ -256,7 +281,7 @@ __global__ void __launch_bounds__(ATT_THREADS) k_decode_attn(const float *q, con
     prt[d.hd + 1] = sum;
   }
   __syncthreads();
-  unsigned *ctr = counters + b * d.nh + head;
+  unsigned *ctr = a.counters + b * d.nh + head;
   if (threadIdx.x == 0) {
     __threadfence();
     is_last = (atomicAdd(ctr, 1u) == unsigned(n_splits - 1));
@@ -264,7 +289,7 @@ __global__ void __launch_bounds__(ATT_THREADS) k_decode_attn(const float *q, con
   }
   __syncthreads();
   if (!is_last) return;
-  const float *all = partial + ((b * d.nh + head) * n_splits) * rec;
+  const float *all = a.partial + ((b * d.nh + head) * n_splits) * rec;
   float gmx = -INFINITY;
   for (int k2 = 0; k2 < n_splits; ++k2) gmx = fmaxf(gmx, __ldcg(all + k2 * rec + d.hd));
   if (threadIdx.x < d.hd) {
@@ -275,7 +300,7 @@ __global__ void __launch_bounds__(ATT_THREADS) k_decode_attn(const float *q, con
       tot += w * __ldcg(all + k2 * rec + threadIdx.x);
       den += w * l2;
     }
-    out[(b * d.nh + head) * d.hd + threadIdx.x] = tot * (1.0f / den);
+    a.out[(b * d.nh + head) * d.hd + threadIdx.x] = tot * (1.0f / den);
   }
   if (threadIdx.x == 0) *ctr = 0u;
 }
@@ -309,14 +334,6 @@ int launch_add_rmsnorm(lmb_ctx *ctx, float *d_hidden, const float *d_add, const 
   return LMB_OK;
 }
 
-int launch_rope_kv(lmb_ctx *ctx, float *q, float *k, const float *v, const float *qb, const float *kb, const float *vb,
-                   const float *cs_table, const size_t *positions, float *kv, size_t layer, const RopeDims &d, size_t batch) {
-  k_rope_kv<<<unsigned(batch), 256, 0, ctx->stream>>>(q, k, v, qb, kb, vb, cs_table, positions, kv, layer, d);
-  ctx->launches++;
-  LMB_CUDA(cudaGetLastError());
-  return LMB_OK;
-}
-
 int decode_attn_splits(const lmb_ctx *ctx, size_t nh, size_t batch, size_t max_seq) {
   size_t n = (size_t(2) * ctx->sm_count + nh * batch - 1) / (nh * batch);
   const size_t most = (max_seq + 63) / 64;  // no slice shorter than 64 timesteps at full context
@@ -324,18 +341,22 @@ int decode_attn_splits(const lmb_ctx *ctx, size_t nh, size_t batch, size_t max_s
   return int(n > most ? most : n);
 }
 
-int launch_decode_attn(lmb_ctx *ctx, const float *q, const float *kv, const size_t *positions, float *out, float *partial,
-                       unsigned *counters, int n_splits, size_t layer, const RopeDims &d0, size_t batch) {
+// q/k/v are the fresh projections of this step; the kernel applies bias and RoPE, writes the new
+// position into the cache and attends over positions 0..pos.
+int launch_decode_attn(lmb_ctx *ctx, const float *q, const float *k, const float *v, const float *qb, const float *kb,
+                       const float *vb, const float *cs_table, const size_t *positions, float *kv, float *out,
+                       float *partial, unsigned *counters, int n_splits, size_t layer, const RopeDims &d0, size_t batch) {
   RopeDims d = d0;
-  if (d.hd > ATT_THREADS || d.hd == 0 || ATT_THREADS % d.hd != 0) {
-    set_last_error("decode attention: head_dim must divide 128");
+  if (d.hd > ATT_THREADS || d.hd == 0 || ATT_THREADS % d.hd != 0 || d.hd % 2 != 0) {
+    set_last_error("decode attention: head_dim must be even and divide 256");
     return LMB_ERR_ARG;
   }
   size_t len = (d.max_seq + n_splits - 1) / n_splits;
   d.split_len = (len + 15) / 16 * 16;
-  const size_t smem = (d.split_len + d.hd + 32 + ATT_THREADS) * sizeof(float);
+  const size_t smem = (d.split_len + 3 * d.hd + 32 + ATT_THREADS) * sizeof(float);
+  AttnArgs a{q, k, v, qb, kb, vb, cs_table, positions, kv, out, partial, counters, n_splits, layer};
   dim3 grid(unsigned(d.nh), unsigned(n_splits), unsigned(batch));
-  k_decode_attn<<<grid, ATT_THREADS, smem, ctx->stream>>>(q, kv, positions, out, partial, counters, n_splits, layer, d);
+  k_decode_attn<<<grid, ATT_THREADS, smem, ctx->stream>>>(a, d);
   ctx->launches++;
   LMB_CUDA(cudaGetLastError());
   return LMB_OK;

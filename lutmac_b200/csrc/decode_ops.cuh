@@ -17,11 +17,10 @@ int launch_embed_rows(lmb_ctx *ctx, const int *d_tokens, const lmb_weight *embed
                       float *d_hidden);
 int launch_add_rmsnorm(lmb_ctx *ctx, float *d_hidden, const float *d_add, const float *d_w, float *d_out, size_t h,
                        size_t batch, float eps);
-int launch_rope_kv(lmb_ctx *ctx, float *q, float *k, const float *v, const float *qb, const float *kb, const float *vb,
-                   const float *cs_table, const size_t *positions, float *kv, size_t layer, const RopeDims &d, size_t batch);
 int decode_attn_splits(const lmb_ctx *ctx, size_t nh, size_t batch, size_t max_seq);
-int launch_decode_attn(lmb_ctx *ctx, const float *q, const float *kv, const size_t *positions, float *out, float *partial,
-                       unsigned *counters, int n_splits, size_t layer, const RopeDims &d, size_t batch);
+int launch_decode_attn(lmb_ctx *ctx, const float *q, const float *k, const float *v, const float *qb, const float *kb,
+                       const float *vb, const float *cs_table, const size_t *positions, float *kv, float *out,
+                       float *partial, unsigned *counters, int n_splits, size_t layer, const RopeDims &d, size_t batch);
 int launch_silu_mul(lmb_ctx *ctx, const float *gate, const float *up, float *out, size_t n);
 
 }  // namespace lmb

@@ -590,8 +590,8 @@ int ctas_per_sm(int kind) { return kind_info(kind).lut ? 3 : 2; }
 // CTAs (which costs a trip through global scratch) by minimising a makespan estimate in units
 // of "one warp evaluates one 256-column block":
 //     waves of CTAs x (blocks per warp + prologue share + fixed CTA cost [+ split-K hand-off]).
-// `other_ctas` are CTAs that other jobs of the same launch bring along.
-Plan make_plan(int kind, size_t row_tiles, size_t bpr, size_t batch, int sm_count, size_t other_ctas = 0) {
+// `other_row_tiles` are the row-tiles of the other jobs of the same launch.
+Plan make_plan(int kind, size_t row_tiles, size_t bpr, size_t batch, int sm_count, size_t other_row_tiles = 0) {
   const bool lut = kind_info(kind).lut;
   const size_t s_cap = lut ? 12 : 48;  // 48 KiB of tables / activations per CTA
   const size_t slots = size_t(sm_count) * ctas_per_sm(kind);
@@ -606,6 +606,8 @@ Plan make_plan(int kind, size_t row_tiles, size_t bpr, size_t batch, int sm_coun
       if (S > s_cap) continue;
       if ((bpr + S - 1) / S != n_ks) continue;  // not a distinct split
       const size_t own = n_rg * n_ks * batch;
+      // other jobs of the launch are assumed to be cut the same way
+      const size_t other_ctas = (other_row_tiles + R - 1) / R * n_ks * batch;
       const double per_warp = double((S + wpr - 1) / wpr);
       const double cta_time = per_warp + prologue_per_block * double((S + 7) / 8) + fixed + (n_ks > 1 ? split_cost : 0.0);
       // with plenty of CTAs from other jobs the GPU is busy anyway: minimise this job's total
@@ -633,11 +635,11 @@ int prepare_jobs(lmb_ctx *ctx, int kind, const LinearArgs *args, int njobs, Job 
   const size_t batch = args[0].batch;
   std::vector<Plan> plans(static_cast<size_t>(njobs));
   size_t scratch_need = 0, counter_need = 0;
-  size_t total_rg = 0;
-  for (int j = 0; j < njobs; ++j) total_rg += (args[j].w->row_tiles + 7) / 8 * batch;
+  size_t total_rt = 0;
+  for (int j = 0; j < njobs; ++j) total_rt += args[j].w->row_tiles;
   for (int j = 0; j < njobs; ++j) {
     const lmb_weight *w = args[j].w;
-    const size_t others = total_rg - (w->row_tiles + 7) / 8 * batch;
+    const size_t others = total_rt - w->row_tiles;
     plans[size_t(j)] = make_plan(kind, w->row_tiles, w->bpr, batch, ctx->sm_count, others);
     if (plans[size_t(j)].n_ks > 1) {
       scratch_need += batch * plans[size_t(j)].n_ks * w->row_tiles * TILE_ROWS;

@@ -173,7 +173,7 @@ int lmb_model_create(lmb_ctx *ctx, const lmb_model_config *c, lmb_model **out) {
   LMB_REQUIRE(g == 1 || (ctx->comm && ctx->tp_size == g && ctx->tp_rank == c->tp_rank),
               "lmb_model_create: tensor-parallel model needs lmb_tp_init on its context first");
   LMB_REQUIRE(c->num_attention_heads % c->num_key_value_heads == 0, "lmb_model_create: heads not divisible by kv heads");
-  LMB_REQUIRE(c->head_dim > 0 && c->head_dim % 2 == 0 && 128 % c->head_dim == 0, "lmb_model_create: head_dim must divide 128");
+  LMB_REQUIRE(c->head_dim > 0 && c->head_dim % 2 == 0 && 256 % c->head_dim == 0, "lmb_model_create: head_dim must divide 256");
   LMB_REQUIRE(c->num_attention_heads % g == 0 && c->num_key_value_heads % g == 0 && c->intermediate_size % g == 0 &&
                   c->vocab_size % g == 0,
               "lmb_model_create: heads, kv heads, intermediate and vocab sizes must divide by tp_size");
@@ -460,9 +460,8 @@ int lmb_model_forward(lmb_model *m, const int *token_ids, const size_t *position
       float *qkv[3] = {m->q, m->k, m->v};
       st = gemv_group(m, 3, &L.w[0], &L.rot[0], m->hidden, h, qkv, batch, norm1);
       if (st != LMB_OK) break;
-      st = launch_rope_kv(ctx, m->q, m->k, m->v, L.qb, L.kb, L.vb, m->cs_table, m->d_pos, m->kv, l, rd, batch);
-      if (st != LMB_OK) break;
-      st = launch_decode_attn(ctx, m->q, m->kv, m->d_pos, m->att, m->att_partial, m->att_counters, n_splits, l, rd, batch);
+      st = launch_decode_attn(ctx, m->q, m->k, m->v, L.qb, L.kb, L.vb, m->cs_table, m->d_pos, m->kv, m->att, m->att_partial,
+                              m->att_counters, n_splits, l, rd, batch);
       if (st != LMB_OK) break;
       st = gemv1(m, L.w[3], L.rot[3], m->att, m->nh * hd, m->hidden, batch, res);
       if (st != LMB_OK) break;
@@ -485,9 +484,8 @@ int lmb_model_forward(lmb_model *m, const int *token_ids, const size_t *position
     float *qkv[3] = {m->q, m->k, m->v};
     st = gemv_group(m, 3, &L.w[0], &L.rot[0], m->normed, h, qkv, batch);
     if (st != LMB_OK) break;
-    st = launch_rope_kv(ctx, m->q, m->k, m->v, L.qb, L.kb, L.vb, m->cs_table, m->d_pos, m->kv, l, rd, batch);
-    if (st != LMB_OK) break;
-    st = launch_decode_attn(ctx, m->q, m->kv, m->d_pos, m->att, m->att_partial, m->att_counters, n_splits, l, rd, batch);
+    st = launch_decode_attn(ctx, m->q, m->k, m->v, L.qb, L.kb, L.vb, m->cs_table, m->d_pos, m->kv, m->att, m->att_partial,
+                            m->att_counters, n_splits, l, rd, batch);
     if (st != LMB_OK) break;
     st = gemv1(m, L.w[3], L.rot[3], m->att, m->nh * hd, m->proj, batch);
     if (st != LMB_OK) break;
