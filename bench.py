@@ -250,6 +250,7 @@ def run_ours(args):
     h2d = N_LAYERS * sum(4 * K for _, _, K in synth.LLAMA32_1B_SHAPES)
     d2h = N_LAYERS * sum(4 * M for _, M, _ in synth.LLAMA32_1B_SHAPES)
     e2e_val = None
+    hgroup = None
     if not args.no_e2e:
         from lutmac_b200.api import HostGroup
         host_in = [np.ascontiguousarray(acts[li][n]) for li in range(N_LAYERS) for n, _, _ in synth.LLAMA32_1B_SHAPES]
@@ -270,6 +271,7 @@ def run_ours(args):
         e2e_val = world * step_bytes * e2e_steps / e2e_s / 1e9
 
     if rank != 0:
+        dist.destroy_process_group()
         return
     peak, peak_src = load_peaks()
     per_launch_bytes = step_bytes  # one launch per step
@@ -286,12 +288,20 @@ def run_ours(args):
             "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "call": "lmb_group_run_host: the step's 112 lut_linear calls with host inputs and outputs"},
             "gpu_launches": int(gpu_launches), "clocks": clocks}
+    if world == 1 and not args.no_decode:
+        # side measurement: config[2], one decode step of the random-init Llama-3.2-1B shape (4-bit
+        # projections, int8 tied head, 512 cached positions, batch 1); not the headline metric
+        from lutmac_b200.decode_bench import run_decode
+        del group, hgroup, dev, flat  # free the suite's device memory first
+        line["decode"] = run_decode(ctx, "llama-3.2-1b", INT4, 512, 1, steps=30)
     if world == 1 and not args.no_cpu:
         backend, kind = cpu_backend()
         b, t = cpu_suite_pass(backend, layers, acts, N_LAYERS, 1)
         line["cpu_baseline"] = {"value": b / t / 1e9, "unit": UNIT, "cores": 1, "kind": kind,
                                 "sample": f"one full suite pass ({N_LAYERS} layers), reference kernel as shipped (1 thread)"}
     print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
 
 
 def main():
@@ -303,6 +313,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-chain", action="store_true", help="skip the chain-of-single-launches side measurement")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    ap.add_argument("--no-decode", action="store_true", help="skip the decode-step side measurement")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
