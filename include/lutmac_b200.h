@@ -229,6 +229,23 @@ int lmb_model_kv_import(lmb_model *m, size_t seq, const float *h_in);
 /* Algorithmic bytes one decode step reads at the given context length (weights + KV + embedding row). */
 int lmb_model_step_bytes(lmb_model *m, size_t position, uint64_t *bytes_out);
 
+/* ---- .lutmac files: replaces load_lutmac (src/format.cpp:292-505) and load_model
+ * (include/lutmac/model.hpp:147, src/model.cpp:576-699) -------------------------------------------
+ * lmb_file_* expose the parsed header (kind = block kind or -1 for raw fp32 tensors) and read one
+ * tensor's bytes; lmb_model_load builds the device-resident model: tensor names are mapped to
+ * slots like the reference does, the head is tied to the embedding when the file has none.
+ * max_seq = 0 keeps the reference's 2048 cache positions. */
+typedef struct lmb_file lmb_file;
+int lmb_file_open(const char *path, lmb_file **out);
+int lmb_file_close(lmb_file *f);
+int lmb_file_config(const lmb_file *f, lmb_model_config *cfg_out);
+int lmb_file_tensor_count(const lmb_file *f, size_t *n);
+int lmb_file_tensor_info(const lmb_file *f, size_t i, const char **name, int *kind, int *quant_bits, size_t *dim0,
+                         size_t *dim1, size_t *num_blocks);
+int lmb_file_read_tensor(lmb_file *f, size_t i, void *dst, size_t dst_bytes);
+int lmb_model_load(lmb_ctx *ctx, const char *path, size_t max_batch, size_t max_seq, int tp_rank, int tp_size,
+                   lmb_model **out);
+
 /* ---- tensor parallelism (no counterpart in the reference, which is single-process) ---------------
  * One process per GPU.  Rank 0 obtains a 128-byte NCCL unique id, the host distributes it by
  * whatever means it has, every rank calls lmb_tp_init with it.  Collectives run on the

@@ -89,6 +89,14 @@ SIGNATURES = {
     "lmb_model_kv_export": (C.c_int, [vp, sz, vp]),
     "lmb_model_kv_import": (C.c_int, [vp, sz, vp]),
     "lmb_model_step_bytes": (C.c_int, [vp, sz, C.POINTER(C.c_uint64)]),
+    "lmb_file_open": (C.c_int, [C.c_char_p, C.POINTER(vp)]),
+    "lmb_file_close": (C.c_int, [vp]),
+    "lmb_file_config": (C.c_int, [vp, C.POINTER(ModelConfig)]),
+    "lmb_file_tensor_count": (C.c_int, [vp, C.POINTER(sz)]),
+    "lmb_file_tensor_info": (C.c_int, [vp, sz, C.POINTER(C.c_char_p), C.POINTER(C.c_int), C.POINTER(C.c_int),
+                                       C.POINTER(sz), C.POINTER(sz), C.POINTER(sz)]),
+    "lmb_file_read_tensor": (C.c_int, [vp, sz, vp, sz]),
+    "lmb_model_load": (C.c_int, [vp, C.c_char_p, sz, sz, C.c_int, C.c_int, C.POINTER(vp)]),
     "lmb_tp_unique_id": (C.c_int, [vp]),
     "lmb_tp_init": (C.c_int, [vp, vp, C.c_int, C.c_int]),
     "lmb_tp_destroy": (C.c_int, [vp]),

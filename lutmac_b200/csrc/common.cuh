@@ -162,6 +162,7 @@ int launch_gemv(lmb_ctx *ctx, const LinearArgs *args, int njobs, bool rotate, in
 int launch_fwht256(lmb_ctx *ctx, float *d_x, size_t n);
 int launch_debug_luts(lmb_ctx *ctx, const float *d_x, size_t x_len, bool rotate, float *d_out);
 
+int model_tie_head(lmb_model *m);
 int ensure_scratch(lmb_ctx *ctx, size_t floats, size_t counters);
 int ensure_stage(lmb_ctx *ctx, size_t bytes);
 

@@ -69,7 +69,7 @@ struct lmb_model {
   lmb_model_config cfg;
   size_t nh = 0, nkv = 0, inter = 0, vocab_local = 0;  // this rank's share
   lmb_weight *embed = nullptr, *lm_head = nullptr;
-  bool head_tied = false, head_rot = false;
+  bool head_tied = false, head_rot = false, embed_rot = false;
   const void *embed_host = nullptr;
   float *final_norm = nullptr;
   std::vector<LayerW> layers;
@@ -284,7 +284,7 @@ int lmb_model_set_weight(lmb_model *m, int layer, int slot, int kind, int quant_
   lmb_weight **dst = nullptr;
   size_t r0 = 0, r1 = M, b0 = 0, b1 = bpr, wantM = 0, wantK = 0;
   if (slot == LMB_SLOT_EMBED) {
-    dst = &m->embed; wantM = c.vocab_size; wantK = h; m->embed_host = blocks;
+    dst = &m->embed; wantM = c.vocab_size; wantK = h; m->embed_host = blocks; m->embed_rot = rot;
   } else if (slot == LMB_SLOT_LM_HEAD) {
     dst = &m->lm_head; wantM = c.vocab_size; wantK = h; r0 = M * r / g; r1 = M * (r + 1) / g; m->head_rot = rot;
     if (g == 1 && m->embed && blocks == m->embed_host && kind == m->embed->ref_kind) {  // tied: share the device copy
@@ -341,6 +341,18 @@ int lmb_model_set_vector(lmb_model *m, int layer, int which, const float *data, 
 }
 
 }  // extern "C"
+
+namespace lmb {
+// lm_head = embed_tokens without a second device copy (load_model's tied head, model.cpp:667-689).
+int model_tie_head(lmb_model *m) {
+  if (m->cfg.tp_size != 1 || !m->embed) return LMB_ERR_STATE;
+  if (m->lm_head && !m->head_tied) lmb_weight_free(m->lm_head);
+  m->lm_head = m->embed;
+  m->head_tied = true;
+  m->head_rot = m->embed_rot;
+  return LMB_OK;
+}
+}  // namespace lmb
 
 namespace {
 

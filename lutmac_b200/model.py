@@ -45,6 +45,27 @@ class Model:
                     self._set_vector(i, name, L[name])
         self._logits = np.empty((max_batch, self.vocab), np.float32)
 
+    @classmethod
+    def load(cls, path: str, ctx: Optional[Context] = None, max_batch: int = 1, max_seq: int = 0, tp_rank: int = 0,
+             tp_size: int = 1) -> "Model":
+        """load_model(path) of the reference (include/lutmac/model.hpp:147): parse a .lutmac file
+        and build the device-resident model from it (max_seq = 0 keeps the reference's 2048)."""
+        self = cls.__new__(cls)
+        self.ctx = ctx or default_context()
+        f = C.c_void_p()
+        check(lib().lmb_file_open(path.encode(), C.byref(f)))
+        cfg = _lib.ModelConfig()
+        check(lib().lmb_file_config(f, C.byref(cfg)))
+        lib().lmb_file_close(f)
+        h = C.c_void_p()
+        check(lib().lmb_model_load(self.ctx.h, path.encode(), max_batch, max_seq, tp_rank, tp_size, C.byref(h)))
+        self.h = h
+        self.spec = None
+        self.vocab = cfg.vocab_size
+        self.max_batch = max_batch
+        self._logits = np.empty((max_batch, self.vocab), np.float32)
+        return self
+
     def _set_weight(self, layer, name, t):
         check(lib().lmb_model_set_weight(self.h, layer, SLOTS[name], t.kind, t.quant_bits, _vp(t.blocks), t.M, t.K))
 

@@ -304,6 +304,32 @@ class Reference:
         L.ref_load_model.argtypes = [C.c_char_p]
         L.ref_load_model.restype = C.c_void_p
 
+    def save_lutmac(self, path, spec):
+        """Write a model spec through the reference's own save_lutmac (src/format.cpp:146-290)."""
+        c = spec.cfg
+        ents = spec_file_tensors(spec)
+        arr = (RefFileTensor * len(ents))()
+        keep = []
+        for i, (name, kind, qb, data, M, K) in enumerate(ents):
+            nb = name.encode()
+            keep.append((nb, data))
+            arr[i] = RefFileTensor(nb, kind, qb, data.ctypes.data, M, K)
+        self.lib.ref_save_lutmac.argtypes = [C.c_char_p] + [C.c_size_t] * 7 + [C.c_float] * 3 + [C.POINTER(RefFileTensor), C.c_size_t]
+        rc = self.lib.ref_save_lutmac(path.encode(), c["vocab"], c["hidden"], c["inter"], c["n_layers"], c["n_heads"],
+                                      c["n_kv_heads"], c["head_dim"], c["rope_theta"], c["rope_factor"], c["eps"], arr, len(ents))
+        assert rc == 0, "save_lutmac failed"
+
+    def load_model_logits(self, path, tokens, vocab):
+        """load_model + forward per token through the reference; returns [len(tokens), vocab]."""
+        h = self.lib.ref_load_model(path.encode())
+        assert h, "reference load_model returned null"
+        out = []
+        for p, t in enumerate(tokens):
+            self.lib.ref_model_forward(h, int(t), p)
+            out.append(np.ctypeslib.as_array(self.lib.ref_model_logits(h), shape=(vocab,)).copy())
+        self.lib.ref_model_free(h)
+        return np.stack(out)
+
     def gemv(self, kind, blocks, act, M, K):
         act = np.ascontiguousarray(act, np.float32)
         assert act.size >= (K + 255) // 256 * 256
@@ -418,6 +444,33 @@ class Reference:
         x = np.array(x, np.float32, copy=True)
         self.lib.ref_softmax(_ptr(x, _f32p), x.size)
         return x
+
+
+class RefFileTensor(C.Structure):
+    _fields_ = [("name", C.c_char_p), ("kind", C.c_int), ("quant_bits", C.c_int), ("data", C.c_void_p),
+                ("M", C.c_size_t), ("K", C.c_size_t)]
+
+
+def spec_file_tensors(spec):
+    """(name, kind or -1, quant_bits, array, M, K) for every tensor of a model spec, with the names
+    load_model maps to slots (src/model.cpp:589-664); no lm_head entry: the head is tied."""
+    out = [(spec.embed.name or "model.embed_tokens.weight", spec.embed.kind, spec.embed.quant_bits, spec.embed.blocks,
+            spec.embed.M, spec.embed.K),
+           ("model.norm.weight", -1, 32, np.ascontiguousarray(spec.final_norm, np.float32), spec.final_norm.size, 0)]
+    for i, L in enumerate(spec.layers):
+        pre = f"model.layers.{i}."
+        for key, nm in (("input_norm", "input_layernorm.weight"), ("post_norm", "post_attention_layernorm.weight"),
+                        ("q_bias", "self_attn.q_proj.bias"), ("k_bias", "self_attn.k_proj.bias"),
+                        ("v_bias", "self_attn.v_proj.bias")):
+            if L.get(key) is not None:
+                v = np.ascontiguousarray(L[key], np.float32)
+                out.append((pre + nm, -1, 32, v, v.size, 0))
+        for key, nm in (("q", "self_attn.q_proj.weight"), ("k", "self_attn.k_proj.weight"), ("v", "self_attn.v_proj.weight"),
+                        ("o", "self_attn.o_proj.weight"), ("gate", "mlp.gate_proj.weight"), ("up", "mlp.up_proj.weight"),
+                        ("down", "mlp.down_proj.weight")):
+            t = L[key]
+            out.append((pre + nm, t.kind, t.quant_bits, t.blocks, t.M, t.K))
+    return out
 
 
 class ReferenceModel:

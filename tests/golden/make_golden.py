@@ -114,10 +114,29 @@ def model_cases(ref: Reference):
     return out
 
 
+FILE_CASES = (("tiny_int4", INT4, {}), ("tiny_ternary_bias", TERNARY, {"qkv_bias": True}))
+FILE_SHAPE = dict(vocab=256, hidden=256, inter=256, n_layers=1, n_heads=4, n_kv_heads=1, head_dim=64)
+FILE_TOKENS = [5, 200, 17]
+
+
+def file_cases(ref: Reference):
+    """.lutmac files written by the reference's save_lutmac, and the logits its load_model +
+    Model::forward produce from them."""
+    out = {"tokens": np.array(FILE_TOKENS)}
+    for name, kind, over in FILE_CASES:
+        spec = synth.model_spec(synth.tiny_model_shape(**dict(FILE_SHAPE, **over)), kind, seed=21, max_seq=2048)
+        path = os.path.join(HERE, name + ".lutmac")
+        ref.save_lutmac(path, spec)
+        out[name + "_logits"] = ref.load_model_logits(path, FILE_TOKENS, spec.cfg["vocab"])
+        print(name + ".lutmac", os.path.getsize(path) // 1024, "KiB")
+    return out
+
+
 def main():
     ref = Reference()
     for name, fn in (("gemv", gemv_cases), ("linear", linear_cases), ("transform", transform_cases),
-                     ("quantize", quantizer_cases), ("glue", glue_cases), ("model", model_cases)):
+                     ("quantize", quantizer_cases), ("glue", glue_cases), ("model", model_cases),
+                     ("files", file_cases)):
         data = fn(ref)
         path = os.path.join(HERE, name + ".npz")
         np.savez_compressed(path, **data)
