@@ -421,11 +421,17 @@ template <> struct Unit<LMB_INT8> {
 // ---------------------------------------------------------------------------------------------
 // The kernel
 // ---------------------------------------------------------------------------------------------
+// Row-blocks a warp keeps in flight (in registers) besides the one it evaluates: small units
+// need more of them to cover the HBM latency with the two or three CTAs an SM holds.
+__host__ __device__ constexpr int prefetch_depth(int kind) {
+  return kind == DK_TERNARY_MMA ? 3 : kind == LMB_TERNARY ? 2 : kind == LMB_INT2 ? 2 : kind == LMB_BINARY ? 3
+       : kind == LMB_INT8 ? 0 : 1;
+}
+
 template <int KIND>
 __global__ void __launch_bounds__(THREADS) k_gemv(const __grid_constant__ GemvParams p) {
   using U = Unit<KIND>;
   constexpr int FPB = U::FPB;
-  constexpr bool PREFETCH = kind_info(KIND).chunks <= 8;  // double-buffer a unit in registers
   constexpr size_t TB = tile_bytes(KIND);
   extern __shared__ __align__(1024) float smem[];
   __shared__ float part[THREADS];
@@ -459,9 +465,14 @@ __global__ void __launch_bounds__(THREADS) k_gemv(const __grid_constant__ GemvPa
   const bool active = rtl < nrt && sub < ns;
   const uint8_t *row_tiles = job.tiles + (size_t(rt0 + rtl) * job.bpr + b0) * TB;
 
-  // weights do not depend on the preceding kernel: fetch the first unit before waiting for it
-  U cur;
-  if (active) cur.load(row_tiles + size_t(sub) * TB, lane);
+  // weights do not depend on the preceding kernel: fetch the first units before waiting for it
+  constexpr int NSLOT = prefetch_depth(KIND) + 1;  // a ring of row-blocks held in registers
+  U slot[NSLOT];
+  if (active) {
+#pragma unroll
+    for (int sl = 0; sl < NSLOT; ++sl)
+      if (sub + sl * wpr < ns) slot[sl].load(row_tiles + size_t(sub + sl * wpr) * TB, lane);
+  }
 
   pdl_wait();
 
@@ -506,16 +517,16 @@ __global__ void __launch_bounds__(THREADS) k_gemv(const __grid_constant__ GemvPa
   typename U::Acc accs;
   U::acc_init(accs);
   if (active) {
-    for (int bl = sub; bl < ns; bl += wpr) {
-      const bool more = bl + wpr < ns;
-      if constexpr (PREFETCH) {
-        U nxt;
-        if (more) nxt.load(row_tiles + size_t(bl + wpr) * TB, lane);
-        cur.eval(smem + size_t(bl) * FPB, xsum[bl], xaux + 4 * bl, accs);
-        if (more) cur = nxt;
-      } else {
-        cur.eval(smem + size_t(bl) * FPB, xsum[bl], xaux + 4 * bl, accs);
-        if (more) cur.load(row_tiles + size_t(bl + wpr) * TB, lane);
+    // each slot is evaluated and at once refilled with the row-block NSLOT steps ahead, so that
+    // NSLOT-1 loads are in flight during every evaluation
+    for (int base = sub; base < ns; base += NSLOT * wpr) {
+#pragma unroll
+      for (int sl = 0; sl < NSLOT; ++sl) {
+        const int bl = base + sl * wpr;
+        if (bl < ns) {
+          slot[sl].eval(smem + size_t(bl) * FPB, xsum[bl], xaux + 4 * bl, accs);
+          if (bl + NSLOT * wpr < ns) slot[sl].load(row_tiles + size_t(bl + NSLOT * wpr) * TB, lane);
+        }
       }
     }
   }
