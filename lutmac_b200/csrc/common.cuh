@@ -38,17 +38,17 @@ constexpr int SM_COUNT_HINT = 148;
 //            bits of the interleaved (b1,b2) pairs split into two MSB-first bit planes.
 //   INT3     6 chunks; chunk 3j+p = Q_{2-p}[16j..16j+15] (j < 2): bit planes of the 3-bit
 //            code, most significant plane first.
-//   INT4     8 chunks in the operand order of the 8-bit integer MMA instead of one row per lane:
-//            chunk h*4+q of lane (g = lane/4, tid = lane%4) = four words {row 16h+g: k-steps 2q,
-//            2q+1; row 16h+g+8: k-steps 2q, 2q+1}; byte j of the word of k-step s holds column
-//            32s+4tid+j in its low nibble and column 32s+16+4tid+j in its high nibble.
+//   INT4     8 chunks in the operand order of the 8-bit integer MMA (m16n8k32) instead of one
+//            row per lane: chunk h*4+q of lane (g = lane/4, tid = lane%4) = four words
+//            {WA(2q), WB(2q), WA(2q+1), WB(2q+1)}; byte j of WA(s) is column 32s+4tid+j, of WB(s)
+//            column 32s+16+4tid+j; the low nibble is row 16h+g, the high nibble row 16h+g+8.
+//            Scales: float 4g+m = scale of row g+8m.
 //   INT5     10 chunks; 0..7 = low nibbles packed like INT4, 8..9 = bit-4 plane.
 //   INT6     12 chunks; 0..7 = low nibbles, 8..9 = bit-4 plane, 10..11 = bit-5 plane.
 //   INT8     16 chunks; chunk c = data[16c..16c+15] unchanged.
-//   DK_TERNARY_MMA  4 chunks of 2-bit codes t+1 in MMA operand order: chunk h*2+qq of lane
-//            (g, tid) = four words {row 16h+g: k-steps 4qq..4qq+1, 4qq+2..4qq+3; row 16h+g+8:
-//            the same}; byte j of a word holds four 2-bit fields p = 0..3: field p is column
-//            32(s0 + p/2) + 16(p%2) + 4tid + j with s0 the word's first k-step.
+//   DK_TERNARY_MMA  4 chunks of 2-bit codes t+1 in MMA operand order: chunk q of lane (g, tid) =
+//            {WA(2q), WB(2q), WA(2q+1), WB(2q+1)} with the same columns per byte as INT4; the
+//            2-bit field m (bits 2m, 2m+1) of every byte is row g+8m.  Scales as for INT4.
 // ---------------------------------------------------------------------------------------------
 // Device-only layout kind: ternary weights as 2-bit codes (t+1) in the operand order of the
 // 8-bit integer MMA.  lmb_weight::kind holds the device layout, lmb_weight::ref_kind the

@@ -20,17 +20,17 @@ __device__ float tile_elem(int kind, const uint8_t *tiles, size_t bpr, size_t ro
   switch (kind) {
   case LMB_INT8: return float(int8_t(pay(j / 16, j % 16))) * s0;
   case LMB_INT4: {  // MMA operand order, see common.cuh
-    const size_t h = l / 16, g = l % 8, hi8 = (l % 16) / 8, s = j / 32, kk = j % 32, tid = (kk % 16) / 4;
-    const size_t lane = g * 4 + tid, chunk = h * 4 + s / 2, word = hi8 * 2 + s % 2;
+    const size_t h = l / 16, g = l % 8, s = j / 32, kk = j % 32, tid = (kk % 16) / 4;
+    const size_t lane = g * 4 + tid, chunk = h * 4 + s / 2, word = (s % 2) * 2 + kk / 16;
     const uint8_t byte = tile[(chunk * TILE_ROWS + lane) * 16 + word * 4 + kk % 4];
-    const int nib = (kk >= 16) ? (byte >> 4) : (byte & 15);
-    return float(nib - 8) * s0;
+    const int nib = ((l % 16) >= 8) ? (byte >> 4) : (byte & 15);
+    return float(nib - 8) * sc[4 * g + l / 8];
   }
   case DK_TERNARY_MMA: {  // 2-bit codes t+1 in MMA operand order, see common.cuh
-    const size_t h = l / 16, g = l % 8, hi8 = (l % 16) / 8, s = j / 32, kk = j % 32, tid = (kk % 16) / 4;
-    const size_t lane = g * 4 + tid, chunk = h * 2 + s / 4, word = hi8 * 2 + (s % 4) / 2, pf = 2 * (s % 2) + kk / 16;
-    const unsigned code = (tile[(chunk * TILE_ROWS + lane) * 16 + word * 4 + kk % 4] >> (2 * pf)) & 3u;
-    return (float(int(code)) - 1.0f) * s0;
+    const size_t m = l / 8, g = l % 8, s = j / 32, kk = j % 32, tid = (kk % 16) / 4;
+    const size_t lane = g * 4 + tid, chunk = s / 2, word = (s % 2) * 2 + kk / 16;
+    const unsigned code = (tile[(chunk * TILE_ROWS + lane) * 16 + word * 4 + kk % 4] >> (2 * m)) & 3u;
+    return (float(int(code)) - 1.0f) * sc[4 * g + m];
   }
   case LMB_TERNARY: {
     const size_t jb = j / 8;

@@ -73,11 +73,11 @@ __device__ __forceinline__ void fwht256_warp(float v[8], int lane) {
   }
 #pragma unroll
   for (int m = 1; m < 32; m <<= 1) {
-    const bool upper = (lane & m) != 0;
+    const float sgn = (lane & m) ? -1.0f : 1.0f;  // upper half of a butterfly: other - own (exact as an FMA by +-1)
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const float o = __shfl_xor_sync(0xffffffffu, v[j], m);
-      v[j] = upper ? (o - v[j]) : (v[j] + o);
+      v[j] = fmaf(v[j], sgn, o);
     }
   }
 #pragma unroll

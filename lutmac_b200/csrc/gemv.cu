@@ -243,149 +243,153 @@ __device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, 
 
 __device__ __forceinline__ void mma_prologue(const float (&v)[8], int lane, float *blk, float *bscale, int *dsum);
 
+// Shared by the two integer-MMA units.  The activations of a block are 32-bit fixed point with
+// one exponent per block, cut into four signed base-256 digits that occupy columns 0..3 of the
+// B operand (columns 4..7 repeat them and their results are ignored).  Several rows share one
+// weight word: row g + 8m sits in bit-field m of every byte, so `word & mask_m` IS the A
+// operand of that row, scaled by 2^(field offset); the power of two is folded into the row's
+// scale.  Accumulators are exact integers; the zero point is removed with the digit sums.
+struct MmaAcc { float r[4]; };  // rows g, g+8, g+16, g+24: digits 0,1 on lanes tid 0, digits 2,3 on tid 1
+__device__ __forceinline__ void mma_acc_init(MmaAcc &a) { a.r[0] = a.r[1] = a.r[2] = a.r[3] = 0.0f; }
+__device__ __forceinline__ float mma_acc_row(const MmaAcc &a, int lane) {
+  const int src = 4 * (lane & 7);
+  float r[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k)
+    r[k] = __shfl_sync(0xffffffffu, a.r[k], src) + 65536.0f * __shfl_sync(0xffffffffu, a.r[k], src + 1);
+  const int k = lane >> 3;
+  return k == 0 ? r[0] : (k == 1 ? r[1] : (k == 2 ? r[2] : r[3]));
+}
+// c0,c1: digit pair of a row; dz = zero point * digit-pair sum, already shifted to the row's field
+__device__ __forceinline__ float mma_row_value(int c0, int c1, uint32_t dz) {
+  return float(int(uint32_t(c0) + 256u * uint32_t(c1) - dz));
+}
+
 template <> struct Unit<LMB_INT4> {
   static constexpr int FPB = 256;  // 1 KiB per block: 256 activations x 4 digit bytes, in B-operand order
   uint4 v[8];
-  float sc;
-  struct Acc { float r[4]; };  // rows g, g+8, g+16, g+24 of the tile; meaningful on lanes with lane%4 == 0
-  static __device__ __forceinline__ void acc_init(Acc &a) { a.r[0] = a.r[1] = a.r[2] = a.r[3] = 0.0f; }
-  static __device__ __forceinline__ float acc_row(const Acc &a, int lane) {
-    const int src = 4 * (lane & 7);
-    const float r0 = __shfl_sync(0xffffffffu, a.r[0], src), r1 = __shfl_sync(0xffffffffu, a.r[1], src);
-    const float r2 = __shfl_sync(0xffffffffu, a.r[2], src), r3 = __shfl_sync(0xffffffffu, a.r[3], src);
-    const int k = lane >> 3;
-    return k == 0 ? r0 : (k == 1 ? r1 : (k == 2 ? r2 : r3));
-  }
+  float4 sc;  // scales of rows g, g+8, g+16, g+24
+  using Acc = MmaAcc;
+  static __device__ __forceinline__ void acc_init(Acc &a) { mma_acc_init(a); }
+  static __device__ __forceinline__ float acc_row(const Acc &a, int lane) { return mma_acc_row(a, lane); }
   __device__ __forceinline__ void load(const uint8_t *tile, int lane) {
 #pragma unroll
     for (int c = 0; c < 8; ++c) v[c] = ld_stream_v4(tile + (size_t(c) * TILE_ROWS + lane) * 16);
-    sc = ld_stream_f32(tile + size_t(8) * TILE_ROWS * 16 + size_t(lane) * 4);
+    const uint4 s4 = ld_stream_v4(tile + size_t(8) * TILE_ROWS * 16 + size_t(lane >> 2) * 16);
+    sc = make_float4(__uint_as_float(s4.x), __uint_as_float(s4.y), __uint_as_float(s4.z), __uint_as_float(s4.w));
   }
-  __device__ __forceinline__ void eval(const float *blk, float blockscale, const int *dsum, Acc &acc) const {
+  __device__ __forceinline__ void eval(const float *blk, float blockscale, const int *aux, Acc &acc) const {
     const int lane = threadIdx.x & 31, g = lane >> 2, tid = lane & 3;
-    const uint4 *dig = reinterpret_cast<const uint4 *>(blk);
-    uint4 bq[4];
+    const uint4 *dig = reinterpret_cast<const uint4 *>(blk) + ((g & 3) * 4 + tid);
+    constexpr uint32_t LO = 0x0F0F0F0Fu, HI = 0xF0F0F0F0u;
+    int c[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
 #pragma unroll
-    for (int q = 0; q < 4; ++q) bq[q] = (g < 4) ? dig[(q * 4 + g) * 4 + tid] : make_uint4(0u, 0u, 0u, 0u);
-    const int d_lo = (tid < 2) ? dsum[2 * tid] : 0, d_hi = (tid < 2) ? dsum[2 * tid + 1] : 0;
-    constexpr uint32_t M4 = 0x0F0F0F0Fu;
+    for (int q = 0; q < 4; ++q) {
+      const uint4 b = dig[q * 16];  // {k-step 2q: b0, b1; k-step 2q+1: b0, b1}
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      int c[4] = {0, 0, 0, 0};
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const uint4 w = v[h * 4 + q];  // {row g: k-steps 2q, 2q+1; row g+8: k-steps 2q, 2q+1}
-        mma_u8s8(c, w.x & M4, w.z & M4, (w.x >> 4) & M4, (w.z >> 4) & M4, bq[q].x, bq[q].y);
-        mma_u8s8(c, w.y & M4, w.w & M4, (w.y >> 4) & M4, (w.w >> 4) & M4, bq[q].z, bq[q].w);
+      for (int h = 0; h < 2; ++h) {
+        const uint4 w = v[h * 4 + q];  // rows 16h+g (low nibbles) and 16h+g+8 (high nibbles)
+        mma_u8s8(c[h], w.x & LO, w.x & HI, w.y & LO, w.y & HI, b.x, b.y);
+        mma_u8s8(c[h], w.z & LO, w.z & HI, w.w & LO, w.w & HI, b.z, b.w);
       }
-      // columns = digits: this lane holds digits 2tid, 2tid+1 of rows g (c0,c1) and g+8 (c2,c3)
-      const float f0 = float((c[0] - 8 * d_lo) + 256 * (c[1] - 8 * d_hi));
-      const float f1 = float((c[2] - 8 * d_lo) + 256 * (c[3] - 8 * d_hi));
-      const float t0 = f0 + 65536.0f * __shfl_down_sync(0xffffffffu, f0, 1);
-      const float t1 = f1 + 65536.0f * __shfl_down_sync(0xffffffffu, f1, 1);
-      const float s0 = __shfl_sync(0xffffffffu, sc, 16 * h + g), s1 = __shfl_sync(0xffffffffu, sc, 16 * h + g + 8);
-      acc.r[2 * h] += t0 * (blockscale * s0);
-      acc.r[2 * h + 1] += t1 * (blockscale * s1);
     }
+    const uint32_t d8 = 8u * uint32_t(aux[tid]);  // zero point 8
+    const float b16 = blockscale * 0.0625f;
+    acc.r[0] += mma_row_value(c[0][0], c[0][1], d8) * (blockscale * sc.x);
+    acc.r[1] += mma_row_value(c[0][2], c[0][3], d8 << 4) * (b16 * sc.y);
+    acc.r[2] += mma_row_value(c[1][0], c[1][1], d8) * (blockscale * sc.z);
+    acc.r[3] += mma_row_value(c[1][2], c[1][3], d8 << 4) * (b16 * sc.w);
   }
   // One warp per 256-block: load (zero padded), optionally rotate, convert to fixed point with
   // the block's exponent, split into signed base-256 digits and store them in B-operand order;
-  // *bscale = 2^(E-30), dsum[d] = sum of digit d over the block.
-  static __device__ __forceinline__ void prologue(const float (&v)[8], int lane, float *blk, float *bscale, int *dsum) {
-    mma_prologue(v, lane, blk, bscale, dsum);
+  // *bscale = 2^(E-30), aux[p] = sum over the block of digit 2p + 256 * digit 2p+1.
+  static __device__ __forceinline__ void prologue(const float (&v)[8], int lane, float *blk, float *bscale, int *aux) {
+    mma_prologue(v, lane, blk, bscale, aux);
   }
 };
 
 // (definition of the shared MMA prologue)
-__device__ __forceinline__ void mma_prologue(const float (&v)[8], int lane, float *blk, float *bscale, int *dsum) {
-  {
-    float amax = 0.0f;
+__device__ __forceinline__ void mma_prologue(const float (&v)[8], int lane, float *blk, float *bscale, int *aux) {
+  float amax = 0.0f;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+  for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+  // non-negative floats order like their bit patterns
+  const uint32_t am = __reduce_max_sync(0xffffffffu, __float_as_uint(amax));
+  int e = int((am >> 23) & 0xFFu) - 126;  // amax < 2^e
+  e = max(e, -90);                        // keeps 2^(30-e) finite for vanishing blocks
+  const float inv = __uint_as_float(uint32_t(127 + 30 - e) << 23);
+  // q = round(v * 2^(30-e)), |q| <= 2^30.  Adding 0x808080 and flipping the same bits turns the
+  // four bytes of q into its signed base-256 digits (the top byte is the signed top digit).
+  uint32_t w[8];
 #pragma unroll
-    for (int m = 16; m > 0; m >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
-    int e = 0;
-    frexpf(amax, &e);          // amax < 2^e
-    e = max(e, -90);           // keeps 2^(30-e) finite for vanishing blocks
-    const float inv = ldexpf(1.0f, 30 - e);
-    uint32_t words[4][2] = {{0u, 0u}, {0u, 0u}, {0u, 0u}, {0u, 0u}};
-    int ds[4] = {0, 0, 0, 0};
+  for (int j = 0; j < 8; ++j) w[j] = (uint32_t(__float2int_rn(v[j] * inv)) + 0x00808080u) ^ 0x00808080u;
+  // 4x4 byte transposes: words[d][h] = digit d of elements 4h..4h+3
+  uint32_t words[4][2];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      int q = __float2int_rn(v[j] * inv);  // |q| <= 2^30
+  for (int h = 0; h < 2; ++h) {
+    const uint32_t t0 = __byte_perm(w[4 * h], w[4 * h + 1], 0x5140), t1 = __byte_perm(w[4 * h + 2], w[4 * h + 3], 0x5140);
+    const uint32_t t2 = __byte_perm(w[4 * h], w[4 * h + 1], 0x7362), t3 = __byte_perm(w[4 * h + 2], w[4 * h + 3], 0x7362);
+    words[0][h] = __byte_perm(t0, t1, 0x5410);
+    words[1][h] = __byte_perm(t0, t1, 0x7632);
+    words[2][h] = __byte_perm(t2, t3, 0x5410);
+    words[3][h] = __byte_perm(t2, t3, 0x7632);
+  }
+  // element j of lane l is column 8l+j: k-step s = l/4, position kk = 8(l%4)+j inside it
+  const int s = lane >> 2, reg = (lane & 3) >> 1, tidb = 2 * (lane & 1);
+  uint32_t *dst = reinterpret_cast<uint32_t *>(blk) + ((s >> 1) * 16 + tidb) * 4 + (s & 1) * 2 + reg;
 #pragma unroll
-      for (int d = 0; d < 4; ++d) {
-        const int dig = (d < 3) ? int(int8_t(q & 0xFF)) : q;
-        q = (q - dig) >> 8;
-        ds[d] += dig;
-        words[d][j >> 2] |= uint32_t(dig & 0xFF) << (8 * (j & 3));
-      }
-    }
-    // element j of lane l is column 8l+j: k-step s = l/4, position kk = 8(l%4)+j inside it
-    const int s = lane >> 2, reg = (lane & 3) >> 1, tidb = 2 * (lane & 1);
-    uint32_t *dst = reinterpret_cast<uint32_t *>(blk);
+  for (int d = 0; d < 4; ++d) {
+    dst[d * 16] = words[d][0];
+    dst[d * 16 + 4] = words[d][1];
+  }
+  int ds[4];
 #pragma unroll
-    for (int d = 0; d < 4; ++d) {
-      const int base = (((s >> 1) * 4 + d) * 4 + tidb) * 4 + (s & 1) * 2 + reg;
-      dst[base] = words[d][0];
-      dst[base + 4] = words[d][1];
-    }
-#pragma unroll
-    for (int d = 0; d < 4; ++d) {
-#pragma unroll
-      for (int m = 16; m > 0; m >>= 1) ds[d] += __shfl_xor_sync(0xffffffffu, ds[d], m);
-    }
-    if (lane == 0) {
-      *bscale = (amax > 0.0f) ? ldexpf(1.0f, e - 30) : 0.0f;
-      dsum[0] = ds[0]; dsum[1] = ds[1]; dsum[2] = ds[2]; dsum[3] = ds[3];
-    }
+  for (int d = 0; d < 4; ++d) ds[d] = __dp4a(int(words[d][0]), 0x01010101, __dp4a(int(words[d][1]), 0x01010101, 0));
+  const int d01 = __reduce_add_sync(0xffffffffu, ds[0] + 256 * ds[1]);
+  const int d23 = __reduce_add_sync(0xffffffffu, ds[2] + 256 * ds[3]);
+  if (lane == 0) {
+    *bscale = (am != 0u) ? __uint_as_float(uint32_t(127 + e - 30) << 23) : 0.0f;
+    *reinterpret_cast<int4 *>(aux) = make_int4(d01, d23, 0, 0);
   }
 }
 
-// Ternary weights as 2-bit codes t+1 on the same integer MMA path (zero point 1): one word
-// yields the four A-operand registers of a row for two k-steps by shift-and-mask.
+// Ternary weights as 2-bit codes t+1 on the same integer MMA path (zero point 1): the four
+// 2-bit fields of a byte belong to rows g, g+8, g+16, g+24 of the tile.
 template <> struct Unit<DK_TERNARY_MMA> {
   static constexpr int FPB = 256;
   uint4 v[4];
-  float sc;
-  using Acc = Unit<LMB_INT4>::Acc;
-  static __device__ __forceinline__ void acc_init(Acc &a) { Unit<LMB_INT4>::acc_init(a); }
-  static __device__ __forceinline__ float acc_row(const Acc &a, int lane) { return Unit<LMB_INT4>::acc_row(a, lane); }
+  float4 sc;
+  using Acc = MmaAcc;
+  static __device__ __forceinline__ void acc_init(Acc &a) { mma_acc_init(a); }
+  static __device__ __forceinline__ float acc_row(const Acc &a, int lane) { return mma_acc_row(a, lane); }
   __device__ __forceinline__ void load(const uint8_t *tile, int lane) {
 #pragma unroll
     for (int c = 0; c < 4; ++c) v[c] = ld_stream_v4(tile + (size_t(c) * TILE_ROWS + lane) * 16);
-    sc = ld_stream_f32(tile + size_t(4) * TILE_ROWS * 16 + size_t(lane) * 4);
+    const uint4 s4 = ld_stream_v4(tile + size_t(4) * TILE_ROWS * 16 + size_t(lane >> 2) * 16);
+    sc = make_float4(__uint_as_float(s4.x), __uint_as_float(s4.y), __uint_as_float(s4.z), __uint_as_float(s4.w));
   }
-  __device__ __forceinline__ void eval(const float *blk, float blockscale, const int *dsum, Acc &acc) const {
+  __device__ __forceinline__ void eval(const float *blk, float blockscale, const int *aux, Acc &acc) const {
     const int lane = threadIdx.x & 31, g = lane >> 2, tid = lane & 3;
-    const uint4 *dig = reinterpret_cast<const uint4 *>(blk);
-    uint4 bq[4];
+    const uint4 *dig = reinterpret_cast<const uint4 *>(blk) + ((g & 3) * 4 + tid);
+    constexpr uint32_t F0 = 0x03030303u, F1 = 0x0C0C0C0Cu, F2 = 0x30303030u, F3 = 0xC0C0C0C0u;
+    int c[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
 #pragma unroll
-    for (int q = 0; q < 4; ++q) bq[q] = (g < 4) ? dig[(q * 4 + g) * 4 + tid] : make_uint4(0u, 0u, 0u, 0u);
-    const int d_lo = (tid < 2) ? dsum[2 * tid] : 0, d_hi = (tid < 2) ? dsum[2 * tid + 1] : 0;
-    constexpr uint32_t M2 = 0x03030303u;
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      int c[4] = {0, 0, 0, 0};
-#pragma unroll
-      for (int qq = 0; qq < 2; ++qq) {
-        const uint4 w = v[h * 2 + qq];  // {row g: k-steps 4qq..+1, 4qq+2..+3; row g+8: the same}
-        mma_u8s8(c, w.x & M2, w.z & M2, (w.x >> 2) & M2, (w.z >> 2) & M2, bq[2 * qq].x, bq[2 * qq].y);
-        mma_u8s8(c, (w.x >> 4) & M2, (w.z >> 4) & M2, (w.x >> 6) & M2, (w.z >> 6) & M2, bq[2 * qq].z, bq[2 * qq].w);
-        mma_u8s8(c, w.y & M2, w.w & M2, (w.y >> 2) & M2, (w.w >> 2) & M2, bq[2 * qq + 1].x, bq[2 * qq + 1].y);
-        mma_u8s8(c, (w.y >> 4) & M2, (w.w >> 4) & M2, (w.y >> 6) & M2, (w.w >> 6) & M2, bq[2 * qq + 1].z, bq[2 * qq + 1].w);
-      }
-      const float f0 = float((c[0] - d_lo) + 256 * (c[1] - d_hi));
-      const float f1 = float((c[2] - d_lo) + 256 * (c[3] - d_hi));
-      const float t0 = f0 + 65536.0f * __shfl_down_sync(0xffffffffu, f0, 1);
-      const float t1 = f1 + 65536.0f * __shfl_down_sync(0xffffffffu, f1, 1);
-      const float s0 = __shfl_sync(0xffffffffu, sc, 16 * h + g), s1 = __shfl_sync(0xffffffffu, sc, 16 * h + g + 8);
-      acc.r[2 * h] += t0 * (blockscale * s0);
-      acc.r[2 * h + 1] += t1 * (blockscale * s1);
+    for (int q = 0; q < 4; ++q) {
+      const uint4 b = dig[q * 16];
+      const uint4 w = v[q];  // {k-step 2q: columns +0..15, +16..31; k-step 2q+1: the same}
+      mma_u8s8(c[0], w.x & F0, w.x & F1, w.y & F0, w.y & F1, b.x, b.y);
+      mma_u8s8(c[1], w.x & F2, w.x & F3, w.y & F2, w.y & F3, b.x, b.y);
+      mma_u8s8(c[0], w.z & F0, w.z & F1, w.w & F0, w.w & F1, b.z, b.w);
+      mma_u8s8(c[1], w.z & F2, w.z & F3, w.w & F2, w.w & F3, b.z, b.w);
     }
+    const uint32_t d1 = uint32_t(aux[tid]);  // zero point 1
+    acc.r[0] += mma_row_value(c[0][0], c[0][1], d1) * (blockscale * sc.x);
+    acc.r[1] += mma_row_value(c[0][2], c[0][3], d1 << 2) * ((blockscale * 0.25f) * sc.y);
+    acc.r[2] += mma_row_value(c[1][0], c[1][1], d1 << 4) * ((blockscale * 0.0625f) * sc.z);
+    acc.r[3] += mma_row_value(c[1][2], c[1][3], d1 << 6) * ((blockscale * 0.015625f) * sc.w);
   }
-  static __device__ __forceinline__ void prologue(const float (&v)[8], int lane, float *blk, float *bscale, int *dsum) {
-    mma_prologue(v, lane, blk, bscale, dsum);
+  static __device__ __forceinline__ void prologue(const float (&v)[8], int lane, float *blk, float *bscale, int *aux) {
+    mma_prologue(v, lane, blk, bscale, aux);
   }
 };
 
@@ -429,14 +433,14 @@ __host__ __device__ constexpr int prefetch_depth(int kind) {
 }
 
 template <int KIND>
-__global__ void __launch_bounds__(THREADS) k_gemv(const __grid_constant__ GemvParams p) {
+__global__ void __launch_bounds__(THREADS, KIND == LMB_INT8 ? 1 : 2) k_gemv(const __grid_constant__ GemvParams p) {
   using U = Unit<KIND>;
   constexpr int FPB = U::FPB;
   constexpr size_t TB = tile_bytes(KIND);
   extern __shared__ __align__(1024) float smem[];
   __shared__ float part[THREADS];
   __shared__ float xsum[64];
-  __shared__ int xaux[64 * 4];
+  __shared__ __align__(16) int xaux[64 * 4];
   __shared__ int is_last;
 
   pdl_launch_dependents();
@@ -495,22 +499,26 @@ __global__ void __launch_bounds__(THREADS) k_gemv(const __grid_constant__ GemvPa
     inv_rms = 1.0f / sqrtf(ss / float(job.x_len) + p.eps);
     __syncthreads();  // part[] is reused below
   }
-  for (int bl = warp; bl < ns; bl += WARPS) {
-    float v[8];
-    load_x8(x, job.x_len, size_t(b0 + bl), lane, v);
-    if (p.xmode == XMODE_RMSNORM) {
-      float w8[8];
-      load_x8(job.x2, job.x_len, size_t(b0 + bl), lane, w8);
+  {
+    // one warp per block, the next block's activations are fetched while this one is converted
+    float v[8], w8[8], nv[8];
+    const float *x2 = (p.xmode == XMODE_SILU_MUL) ? job.x2 + size_t(batch) * job.x_stride : job.x2;
+    if (warp < ns) load_x8(x, job.x_len, size_t(b0 + warp), lane, nv);
+    for (int bl = warp; bl < ns; bl += WARPS) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = v[j] * inv_rms * w8[j];
-    } else if (p.xmode == XMODE_SILU_MUL) {
-      float u8[8];  // silu(gate) * up, model.cpp:36,414-416
-      load_x8(job.x2 + size_t(batch) * job.x_stride, job.x_len, size_t(b0 + bl), lane, u8);
+      for (int j = 0; j < 8; ++j) v[j] = nv[j];
+      if (p.xmode != XMODE_PLAIN) load_x8(x2, job.x_len, size_t(b0 + bl), lane, w8);
+      if (bl + WARPS < ns) load_x8(x, job.x_len, size_t(b0 + bl + WARPS), lane, nv);
+      if (p.xmode == XMODE_RMSNORM) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = (v[j] / (1.0f + expf(-v[j]))) * u8[j];
+        for (int j = 0; j < 8; ++j) v[j] = v[j] * inv_rms * w8[j];
+      } else if (p.xmode == XMODE_SILU_MUL) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = (v[j] / (1.0f + expf(-v[j]))) * w8[j];  // silu(gate) * up, model.cpp:36,414-416
+      }
+      if (p.rotate) fwht256_warp(v, lane);
+      U::prologue(v, lane, smem + size_t(bl) * FPB, xsum + bl, xaux + 4 * bl);
     }
-    if (p.rotate) fwht256_warp(v, lane);
-    U::prologue(v, lane, smem + size_t(bl) * FPB, xsum + bl, xaux + 4 * bl);
   }
   __syncthreads();
 

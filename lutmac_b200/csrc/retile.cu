@@ -194,12 +194,15 @@ void lane_to_block(int kind, const uint8_t *pay, const float *sc, uint8_t *blk) 
   }
 }
 
-// INT4 tiles are stored in the operand order of the 8-bit integer MMA (m16n8k32): chunk h*4+q of
-// lane (g, tid) holds four words {row 16h+g: k-steps 2q, 2q+1; row 16h+g+8: k-steps 2q, 2q+1};
-// byte j of the word of k-step s carries column 32s+4tid+j in its low nibble and column
-// 32s+16+4tid+j in its high nibble, so that `w & 0x0F0F0F0F` and `(w >> 4) & 0x0F0F0F0F` are the
-// two A-operand registers of a row without any further shuffling.  A pure permutation of the
-// nibbles of the 32 row-blocks of a tile.
+// INT4 and DK_TERNARY_MMA tiles are stored in the operand order of the 8-bit integer MMA
+// (m16n8k32).  Lane (g, tid) of a warp owns, for k-step s (columns 32s..32s+31), a word WA whose
+// byte j belongs to column 32s+4tid+j and a word WB whose byte j belongs to column 32s+16+4tid+j;
+// inside every byte several ROWS share the bits:
+//   INT4     low nibble = row 16h+g, high nibble = row 16h+g+8; chunk h*4+q = {WA(2q), WB(2q), WA(2q+1), WB(2q+1)}
+//   ternary  2-bit field m = row g+8m;                         chunk q     = {WA(2q), WB(2q), WA(2q+1), WB(2q+1)}
+// so `word & field_mask` is an A-operand register of that row (scaled by the field's power of
+// two) without a shift.  A pure permutation of the codes of the 32 row-blocks of a tile.  The
+// scales of these kinds are stored in the matching order: float 4g+m = scale of row g+8m.
 inline unsigned int4_code(const uint8_t *rowmajor, size_t row, size_t col) {
   const size_t jb = col / 2;
   const uint8_t byte = rowmajor[(jb / 16) * 512 + row * 16 + jb % 16];
@@ -210,51 +213,46 @@ inline void int4_set(uint8_t *rowmajor, size_t row, size_t col, unsigned code) {
   uint8_t &byte = rowmajor[(jb / 16) * 512 + row * 16 + jb % 16];
   byte = (col % 2 == 0) ? uint8_t((byte & 0x0F) | (code << 4)) : uint8_t((byte & 0xF0) | code);
 }
+// fn(index of the byte in the tile, row of the low nibble (the high nibble is row + 8), column)
 template <class Fn> inline void int4_fragment_walk(Fn &&fn) {
   for (size_t h = 0; h < 2; ++h)
     for (size_t q = 0; q < 4; ++q)
       for (size_t g = 0; g < 8; ++g)
         for (size_t tid = 0; tid < 4; ++tid)
-          for (size_t hi8 = 0; hi8 < 2; ++hi8)
-            for (size_t so = 0; so < 2; ++so)
-              for (size_t j = 0; j < 4; ++j) {
-                const size_t row = 16 * h + g + 8 * hi8, s = 2 * q + so;
-                const size_t idx = ((h * 4 + q) * 32 + g * 4 + tid) * 16 + (hi8 * 2 + so) * 4 + j;
-                fn(idx, row, 32 * s + 4 * tid + j, 32 * s + 16 + 4 * tid + j);
-              }
+          for (size_t wi = 0; wi < 4; ++wi)
+            for (size_t j = 0; j < 4; ++j) {
+              const size_t s = 2 * q + wi / 2, col = 32 * s + 16 * (wi % 2) + 4 * tid + j;
+              fn(((h * 4 + q) * 32 + g * 4 + tid) * 16 + wi * 4 + j, 16 * h + g, col);
+            }
 }
 void int4_to_fragments(uint8_t *payload) {  // 4096 bytes, in place
   uint8_t src[4096];
   std::memcpy(src, payload, 4096);
-  int4_fragment_walk([&](size_t idx, size_t row, size_t col_lo, size_t col_hi) {
-    payload[idx] = uint8_t((int4_code(src, row, col_hi) << 4) | int4_code(src, row, col_lo));
+  int4_fragment_walk([&](size_t idx, size_t row, size_t col) {
+    payload[idx] = uint8_t((int4_code(src, row + 8, col) << 4) | int4_code(src, row, col));
   });
 }
 void int4_from_fragments(uint8_t *payload) {
   uint8_t src[4096];
   std::memcpy(src, payload, 4096);
   std::memset(payload, 0, 4096);
-  int4_fragment_walk([&](size_t idx, size_t row, size_t col_lo, size_t col_hi) {
-    int4_set(payload, row, col_lo, src[idx] & 15u);
-    int4_set(payload, row, col_hi, src[idx] >> 4);
+  int4_fragment_walk([&](size_t idx, size_t row, size_t col) {
+    int4_set(payload, row, col, src[idx] & 15u);
+    int4_set(payload, row + 8, col, src[idx] >> 4);
   });
 }
 
-// DK_TERNARY_MMA: the same idea for 2-bit codes (2048 payload bytes per tile).
+// fn(index of the byte in the tile, bit offset of the field, row, column)
 template <class Fn> inline void tern_fragment_walk(Fn &&fn) {
-  for (size_t h = 0; h < 2; ++h)
-    for (size_t qq = 0; qq < 2; ++qq)
-      for (size_t g = 0; g < 8; ++g)
-        for (size_t tid = 0; tid < 4; ++tid)
-          for (size_t hi8 = 0; hi8 < 2; ++hi8)
-            for (size_t pair = 0; pair < 2; ++pair)
-              for (size_t j = 0; j < 4; ++j)
-                for (size_t pf = 0; pf < 4; ++pf) {
-                  const size_t row = 16 * h + g + 8 * hi8, s = 4 * qq + 2 * pair + pf / 2;
-                  const size_t col = 32 * s + 16 * (pf % 2) + 4 * tid + j;
-                  const size_t idx = ((h * 2 + qq) * 32 + g * 4 + tid) * 16 + (hi8 * 2 + pair) * 4 + j;
-                  fn(idx, 2 * pf, row, col);
-                }
+  for (size_t q = 0; q < 4; ++q)
+    for (size_t g = 0; g < 8; ++g)
+      for (size_t tid = 0; tid < 4; ++tid)
+        for (size_t wi = 0; wi < 4; ++wi)
+          for (size_t j = 0; j < 4; ++j)
+            for (size_t m = 0; m < 4; ++m) {
+              const size_t s = 2 * q + wi / 2, col = 32 * s + 16 * (wi % 2) + 4 * tid + j;
+              fn((q * 32 + g * 4 + tid) * 16 + wi * 4 + j, 2 * m, g + 8 * m, col);
+            }
 }
 inline unsigned tern_code(const uint8_t *rowmajor, size_t row, size_t col) {
   const size_t jb = col / 4;
@@ -277,6 +275,11 @@ void tern_from_fragments(uint8_t *payload) {
     const size_t jb = col / 4;
     payload[(jb / 16) * 512 + row * 16 + jb % 16] |= uint8_t(code << (2 * (col % 4)));
   });
+}
+
+// scale of row l of a tile: index into the tile's scale array
+inline size_t scale_slot(int kind, size_t l) {
+  return (kind == LMB_INT4 || kind == DK_TERNARY_MMA) ? 4 * (l % 8) + l / 8 : l;
 }
 
 template <class F> void parallel_tiles(size_t n, F &&f) {
@@ -317,7 +320,7 @@ void retile(int kind, const uint8_t *blocks, size_t src_bpr, size_t row0, size_t
         block_to_lane(kind, blk, pay.data(), sc);
         for (int c = 0; c < ki.chunks; ++c) std::memcpy(tile + (size_t(c) * TILE_ROWS + l) * 16, pay.data() + 16 * c, 16);
         float *ts = reinterpret_cast<float *>(tile + size_t(ki.chunks) * TILE_ROWS * 16);
-        for (int s = 0; s < ki.nscales; ++s) ts[size_t(s) * TILE_ROWS + l] = sc[s];
+        for (int s = 0; s < ki.nscales; ++s) ts[size_t(s) * TILE_ROWS + scale_slot(kind, l)] = sc[s];
       }
       if (kind == LMB_INT4) int4_to_fragments(tile);
       if (kind == DK_TERNARY_MMA) tern_to_fragments(tile);
@@ -347,7 +350,7 @@ void untile(int kind, const uint8_t *tiled, size_t M, size_t bpr, uint8_t *block
         if (r >= M) break;
         for (int c = 0; c < ki.chunks; ++c) std::memcpy(pay.data() + 16 * c, paysrc + (size_t(c) * TILE_ROWS + l) * 16, 16);
         const float *ts = reinterpret_cast<const float *>(tile + size_t(ki.chunks) * TILE_ROWS * 16);
-        for (int s = 0; s < ki.nscales; ++s) sc[s] = ts[size_t(s) * TILE_ROWS + l];
+        for (int s = 0; s < ki.nscales; ++s) sc[s] = ts[size_t(s) * TILE_ROWS + scale_slot(kind, l)];
         lane_to_block(kind, pay.data(), sc, blocks + (r * bpr + b) * size_t(ki.ref_bytes));
       }
     }
