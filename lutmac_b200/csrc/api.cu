@@ -355,7 +355,12 @@ int lmb_weight_upload_shard(lmb_ctx *ctx, int kind, const void *blocks, size_t M
   lmb_weight *w = new (std::nothrow) lmb_weight();
   if (!w) return LMB_ERR_ALLOC;
   w->ref_kind = kind;
-  w->kind = (kind == LMB_TERNARY && !ctx->ternary_lut) ? DK_TERNARY_MMA : kind;
+  w->kind = kind;
+  if (!ctx->ternary_lut) {  // the integer-MMA layouts are the default for these kinds
+    if (kind == LMB_TERNARY) w->kind = DK_TERNARY_MMA;
+    if (kind == LMB_INT2) w->kind = DK_INT2_MMA;
+    if (kind == LMB_BINARY) w->kind = DK_BINARY_MMA;
+  }
   w->device = ctx->device;
   w->M = row1 - row0;
   w->bpr = blk1 - blk0;

@@ -49,11 +49,22 @@ constexpr int SM_COUNT_HINT = 148;
 //   DK_TERNARY_MMA  4 chunks of 2-bit codes t+1 in MMA operand order: chunk q of lane (g, tid) =
 //            {WA(2q), WB(2q), WA(2q+1), WB(2q+1)} with the same columns per byte as INT4; the
 //            2-bit field m (bits 2m, 2m+1) of every byte is row g+8m.  Scales as for INT4.
+//   DK_INT2_MMA  the DK_TERNARY_MMA arrangement with the field holding b1 (bit 2m) and b2
+//            (bit 2m+1) of the residual-binary pair; scales [plane][4g+m].
+//   DK_BINARY_MMA  2 chunks: words W(sp, ab), sp < 4, ab < 2, word index 2sp+ab; byte j, bit
+//            m+4kh of W(sp, ab) is row g+8m, column 32(2sp+kh) + 16ab + 4tid + j.
 // ---------------------------------------------------------------------------------------------
 // Device-only layout kind: ternary weights as 2-bit codes (t+1) in the operand order of the
 // 8-bit integer MMA.  lmb_weight::kind holds the device layout, lmb_weight::ref_kind the
 // reference block kind it was made from.
 constexpr int DK_TERNARY_MMA = 16;
+// The same for INT2 (residual binary) and BINARY blocks.
+constexpr int DK_INT2_MMA = 17;
+constexpr int DK_BINARY_MMA = 18;
+
+__host__ __device__ constexpr bool kind_is_mma(int kind) {
+  return kind == LMB_INT4 || kind == DK_TERNARY_MMA || kind == DK_INT2_MMA || kind == DK_BINARY_MMA;
+}
 
 struct KindInfo {
   int ref_bytes;   // sizeof the reference block struct
@@ -72,6 +83,8 @@ __host__ __device__ constexpr KindInfo kind_info(int kind) {
        : kind == LMB_INT6    ? KindInfo{196, 12, 1, false}
        : kind == LMB_INT8    ? KindInfo{260, 16, 1, false}
        : kind == DK_TERNARY_MMA ? KindInfo{68, 4, 1, false}
+       : kind == DK_INT2_MMA ? KindInfo{72, 4, 2, false}
+       : kind == DK_BINARY_MMA ? KindInfo{36, 2, 1, false}
                              : KindInfo{0, 0, 0, false};
 }
 

@@ -32,6 +32,19 @@ __device__ float tile_elem(int kind, const uint8_t *tiles, size_t bpr, size_t ro
     const unsigned code = (tile[(chunk * TILE_ROWS + lane) * 16 + word * 4 + kk % 4] >> (2 * m)) & 3u;
     return (float(int(code)) - 1.0f) * sc[4 * g + m];
   }
+  case DK_INT2_MMA: {
+    const size_t m = l / 8, g = l % 8, s = j / 32, kk = j % 32, tid = (kk % 16) / 4;
+    const size_t lane = g * 4 + tid, chunk = s / 2, word = (s % 2) * 2 + kk / 16;
+    const unsigned f = (tile[(chunk * TILE_ROWS + lane) * 16 + word * 4 + kk % 4] >> (2 * m)) & 3u;
+    const float s1 = sc[4 * g + m], s2 = sc[TILE_ROWS + 4 * g + m];
+    return ((f & 1u) ? s1 : -s1) + ((f & 2u) ? s2 : -s2);
+  }
+  case DK_BINARY_MMA: {
+    const size_t m = l / 8, g = l % 8, s = j / 32, kk = j % 32, tid = (kk % 16) / 4;
+    const size_t lane = g * 4 + tid, wi = (s / 2) * 2 + kk / 16;
+    const unsigned v = (tile[((wi / 4) * TILE_ROWS + lane) * 16 + (wi % 4) * 4 + kk % 4] >> (m + 4 * (s % 2))) & 1u;
+    return v ? sc[4 * g + m] : -sc[4 * g + m];
+  }
   case LMB_TERNARY: {
     const size_t jb = j / 8;
     const unsigned p = (pay(jb / 8, jb % 8) >> bit) & 1u, n = (pay(jb / 8, 8 + jb % 8) >> bit) & 1u;

@@ -264,6 +264,10 @@ __device__ __forceinline__ float mma_acc_row(const MmaAcc &a, int lane) {
 __device__ __forceinline__ float mma_row_value(int c0, int c1, uint32_t dz) {
   return float(int(uint32_t(c0) + 256u * uint32_t(c1) - dz));
 }
+// the same for a +-1 bit plane: sum((2b-1) x) = 2 sum(b x) - sum(x); modular arithmetic, the result fits
+__device__ __forceinline__ float mma_plane_value(uint32_t c0, uint32_t c1, uint32_t dz) {
+  return float(int(2u * c0 + 512u * c1 - dz));
+}
 
 template <> struct Unit<LMB_INT4> {
   static constexpr int FPB = 256;  // 1 KiB per block: 256 activations x 4 digit bytes, in B-operand order
@@ -393,6 +397,104 @@ template <> struct Unit<DK_TERNARY_MMA> {
   }
 };
 
+// INT2 (residual binary, w = +-s1 +- s2) as two +-1 bit planes on the integer MMA path: the
+// ternary arrangement with bit 2m = b1 and bit 2m+1 = b2 of row g+8m; one accumulator per plane.
+template <> struct Unit<DK_INT2_MMA> {
+  static constexpr int FPB = 256;
+  uint4 v[4];
+  float4 sc[2];
+  using Acc = MmaAcc;
+  static __device__ __forceinline__ void acc_init(Acc &a) { mma_acc_init(a); }
+  static __device__ __forceinline__ float acc_row(const Acc &a, int lane) { return mma_acc_row(a, lane); }
+  __device__ __forceinline__ void load(const uint8_t *tile, int lane) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) v[c] = ld_stream_v4(tile + (size_t(c) * TILE_ROWS + lane) * 16);
+#pragma unroll
+    for (int p = 0; p < 2; ++p) {
+      const uint4 s4 = ld_stream_v4(tile + size_t(4) * TILE_ROWS * 16 + size_t(p) * TILE_ROWS * 4 + size_t(lane >> 2) * 16);
+      sc[p] = make_float4(__uint_as_float(s4.x), __uint_as_float(s4.y), __uint_as_float(s4.z), __uint_as_float(s4.w));
+    }
+  }
+  __device__ __forceinline__ void eval(const float *blk, float blockscale, const int *aux, Acc &acc) const {
+    const int lane = threadIdx.x & 31, g = lane >> 2, tid = lane & 3;
+    const uint4 *dig = reinterpret_cast<const uint4 *>(blk) + ((g & 3) * 4 + tid);
+    constexpr uint32_t M1 = 0x01010101u;
+    int c[2][2][4] = {{{0, 0, 0, 0}, {0, 0, 0, 0}}, {{0, 0, 0, 0}, {0, 0, 0, 0}}};  // [row half][plane]
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const uint4 b = dig[q * 16];
+      const uint4 w = v[q];
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int p = 0; p < 2; ++p) {
+          const int sh = 4 * h + p;  // rows g+16h (bit 4h+p) and g+16h+8 (bit 4h+2+p)
+          mma_u8s8(c[h][p], w.x & (M1 << sh), w.x & (M1 << (sh + 2)), w.y & (M1 << sh), w.y & (M1 << (sh + 2)), b.x, b.y);
+          mma_u8s8(c[h][p], w.z & (M1 << sh), w.z & (M1 << (sh + 2)), w.w & (M1 << sh), w.w & (M1 << (sh + 2)), b.z, b.w);
+        }
+    }
+    const uint32_t d = uint32_t(aux[tid]);
+    const float s1[4] = {sc[0].x, sc[0].y, sc[0].z, sc[0].w}, s2[4] = {sc[1].x, sc[1].y, sc[1].z, sc[1].w};
+#pragma unroll
+    for (int m = 0; m < 4; ++m) {
+      const int h = m >> 1, j = m & 1;
+      const float f1 = blockscale * (1.0f / float(1 << (2 * m))), f2 = blockscale * (1.0f / float(2 << (2 * m)));
+      float t = mma_plane_value(uint32_t(c[h][0][2 * j]), uint32_t(c[h][0][2 * j + 1]), d << (2 * m)) * (f1 * s1[m]);
+      t = fmaf(mma_plane_value(uint32_t(c[h][1][2 * j]), uint32_t(c[h][1][2 * j + 1]), d << (2 * m + 1)), f2 * s2[m], t);
+      acc.r[m] += t;
+    }
+  }
+  static __device__ __forceinline__ void prologue(const float (&v)[8], int lane, float *blk, float *bscale, int *aux) {
+    mma_prologue(v, lane, blk, bscale, aux);
+  }
+};
+
+// BINARY (w = +-s) as one +-1 bit plane: bit m + 4kh of a byte is row g+8m of the first (kh = 0)
+// or second (kh = 1) k-step of the word's pair; one accumulator per kh, merged by an exact shift.
+template <> struct Unit<DK_BINARY_MMA> {
+  static constexpr int FPB = 256;
+  uint4 v[2];
+  float4 sc;
+  using Acc = MmaAcc;
+  static __device__ __forceinline__ void acc_init(Acc &a) { mma_acc_init(a); }
+  static __device__ __forceinline__ float acc_row(const Acc &a, int lane) { return mma_acc_row(a, lane); }
+  __device__ __forceinline__ void load(const uint8_t *tile, int lane) {
+#pragma unroll
+    for (int c = 0; c < 2; ++c) v[c] = ld_stream_v4(tile + (size_t(c) * TILE_ROWS + lane) * 16);
+    const uint4 s4 = ld_stream_v4(tile + size_t(2) * TILE_ROWS * 16 + size_t(lane >> 2) * 16);
+    sc = make_float4(__uint_as_float(s4.x), __uint_as_float(s4.y), __uint_as_float(s4.z), __uint_as_float(s4.w));
+  }
+  __device__ __forceinline__ void eval(const float *blk, float blockscale, const int *aux, Acc &acc) const {
+    const int lane = threadIdx.x & 31, g = lane >> 2, tid = lane & 3;
+    const uint4 *dig = reinterpret_cast<const uint4 *>(blk) + ((g & 3) * 4 + tid);
+    constexpr uint32_t M1 = 0x01010101u;
+    int c[2][2][4] = {{{0, 0, 0, 0}, {0, 0, 0, 0}}, {{0, 0, 0, 0}, {0, 0, 0, 0}}};  // [row half][kh]
+    const uint32_t wa[4] = {v[0].x, v[0].z, v[1].x, v[1].z}, wb[4] = {v[0].y, v[0].w, v[1].y, v[1].w};
+#pragma unroll
+    for (int sp = 0; sp < 4; ++sp) {
+      const uint4 b = dig[sp * 16];  // {k-step 2sp: b0, b1; k-step 2sp+1: b0, b1}
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int s0 = 2 * h, s1 = 2 * h + 4;
+        mma_u8s8(c[h][0], wa[sp] & (M1 << s0), wa[sp] & (M1 << (s0 + 1)), wb[sp] & (M1 << s0), wb[sp] & (M1 << (s0 + 1)), b.x, b.y);
+        mma_u8s8(c[h][1], wa[sp] & (M1 << s1), wa[sp] & (M1 << (s1 + 1)), wb[sp] & (M1 << s1), wb[sp] & (M1 << (s1 + 1)), b.z, b.w);
+      }
+    }
+    const uint32_t d = uint32_t(aux[tid]);
+    const float s[4] = {sc.x, sc.y, sc.z, sc.w};
+#pragma unroll
+    for (int m = 0; m < 4; ++m) {
+      const int h = m >> 1, j = m & 1;
+      // the kh = 1 sums carry 16 times the field's power of two: an exact shift brings them back
+      const uint32_t c0 = uint32_t(c[h][0][2 * j] + (c[h][1][2 * j] >> 4)), c1 = uint32_t(c[h][0][2 * j + 1] + (c[h][1][2 * j + 1] >> 4));
+      acc.r[m] += mma_plane_value(c0, c1, d << m) * ((blockscale * (1.0f / float(1 << m))) * s[m]);
+    }
+  }
+  static __device__ __forceinline__ void prologue(const float (&v)[8], int lane, float *blk, float *bscale, int *aux) {
+    mma_prologue(v, lane, blk, bscale, aux);
+  }
+};
+
 template <> struct Unit<LMB_INT8> {
   static constexpr int FPB = 256;
   uint4 v[16];
@@ -428,7 +530,7 @@ template <> struct Unit<LMB_INT8> {
 // Row-blocks a warp keeps in flight (in registers) besides the one it evaluates: small units
 // need more of them to cover the HBM latency with the two or three CTAs an SM holds.
 __host__ __device__ constexpr int prefetch_depth(int kind) {
-  return kind == DK_TERNARY_MMA ? 3 : kind == LMB_TERNARY ? 2 : kind == LMB_INT2 ? 2 : kind == LMB_BINARY ? 3
+  return kind == DK_TERNARY_MMA ? 3 : kind == DK_INT2_MMA ? 2 : kind == DK_BINARY_MMA ? 5 : kind == LMB_TERNARY ? 2 : kind == LMB_INT2 ? 2 : kind == LMB_BINARY ? 3
        : kind == LMB_INT8 ? 0 : 1;
 }
 
@@ -741,6 +843,8 @@ int launch_params_kind(lmb_ctx *ctx, int kind, const GemvParams &p, int ctas, in
   case LMB_INT4: return launch_params<LMB_INT4>(ctx, p, ctas, s_max, batch);
   case LMB_INT8: return launch_params<LMB_INT8>(ctx, p, ctas, s_max, batch);
   case DK_TERNARY_MMA: return launch_params<DK_TERNARY_MMA>(ctx, p, ctas, s_max, batch);
+  case DK_INT2_MMA: return launch_params<DK_INT2_MMA>(ctx, p, ctas, s_max, batch);
+  case DK_BINARY_MMA: return launch_params<DK_BINARY_MMA>(ctx, p, ctas, s_max, batch);
   default: set_last_error("launch_gemv: kind has no device kernel"); return LMB_ERR_ARG;
   }
 }
@@ -756,6 +860,8 @@ int configure_gemv(lmb_ctx *ctx) {
   LMB_CUDA(cudaFuncSetAttribute(k_gemv<LMB_INT4>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
   LMB_CUDA(cudaFuncSetAttribute(k_gemv<LMB_INT8>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
   LMB_CUDA(cudaFuncSetAttribute(k_gemv<DK_TERNARY_MMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  LMB_CUDA(cudaFuncSetAttribute(k_gemv<DK_INT2_MMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  LMB_CUDA(cudaFuncSetAttribute(k_gemv<DK_BINARY_MMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
   return LMB_OK;
 }
 
@@ -813,7 +919,8 @@ int lmb_group_create(lmb_ctx *ctx, size_t n, const lmb_weight *const *ws, const 
     args[i] = LinearArgs{ws[i], nullptr, d_xs[i], ws[i]->K, ws[i]->K, d_ys[i], ws[i]->M, 1, false, nullptr, nullptr};
   }
   const int kind = ws[0]->kind;
-  const bool auto_rot = (kind == LMB_TERNARY || kind == DK_TERNARY_MMA || kind == LMB_BINARY || kind == LMB_INT2);
+  const bool auto_rot = (kind == LMB_TERNARY || kind == DK_TERNARY_MMA || kind == LMB_BINARY || kind == LMB_INT2 ||
+                         kind == DK_INT2_MMA || kind == DK_BINARY_MMA);
   std::vector<Job> jobs(n);
   std::vector<int2> map;
   lmb_group *g = new (std::nothrow) lmb_group();
@@ -983,7 +1090,8 @@ int lmb_linear_static_scratch(const lmb_weight *w, const float *d_bias, const fl
   p.njobs = 1;
   p.xmode = XMODE_PLAIN;
   p.eps = 0.0f;
-  const bool auto_rot = (kind == LMB_TERNARY || kind == DK_TERNARY_MMA || kind == LMB_BINARY || kind == LMB_INT2);
+  const bool auto_rot = (kind == LMB_TERNARY || kind == DK_TERNARY_MMA || kind == LMB_BINARY || kind == LMB_INT2 ||
+                         kind == DK_INT2_MMA || kind == DK_BINARY_MMA);
   p.rotate = ((flags & LMB_ROTATE) || ((flags & LMB_AUTO_ROTATE) && auto_rot)) ? 1 : 0;
   p.jobs_dev = nullptr;
   p.cta_map = nullptr;

@@ -63,9 +63,19 @@ void block_to_lane(int kind, const uint8_t *blk, uint8_t *pay, float *sc) {
     break;
   }
   case LMB_BINARY:
+  case DK_BINARY_MMA:  // row-major sign bits; permuted per tile later
     std::memcpy(pay, blk, 32);
     std::memcpy(sc, blk + 32, 4);
     break;
+  case DK_INT2_MMA: {  // row-major 2-bit fields b1 | b2 << 1 (column c in byte c/4, bits 2(c%4)); permuted per tile later
+    std::memset(pay, 0, 64);
+    for (size_t i = 0; i < 256; ++i) {
+      const unsigned code = (blk[i / 4] >> (6 - 2 * (i % 4))) & 3u;  // (b1 << 1) | b2, types.hpp Int2Block
+      pay[i / 4] |= uint8_t(((code >> 1) | ((code & 1u) << 1)) << (2 * (i % 4)));
+    }
+    std::memcpy(sc, blk + 64, 8);
+    break;
+  }
   case LMB_INT2: {
     uint8_t b1[32] = {0}, b2[32] = {0};
     for (size_t i = 0; i < 256; ++i) {
@@ -140,9 +150,19 @@ void lane_to_block(int kind, const uint8_t *pay, const float *sc, uint8_t *blk) 
     break;
   }
   case LMB_BINARY:
+  case DK_BINARY_MMA:
     std::memcpy(blk, pay, 32);
     std::memcpy(blk + 32, sc, 4);
     break;
+  case DK_INT2_MMA: {
+    std::memset(blk, 0, 64);
+    for (size_t i = 0; i < 256; ++i) {
+      const unsigned f = (pay[i / 4] >> (2 * (i % 4))) & 3u;  // b1 | b2 << 1
+      blk[i / 4] |= uint8_t((((f & 1u) << 1) | (f >> 1)) << (6 - 2 * (i % 4)));
+    }
+    std::memcpy(blk + 64, sc, 8);
+    break;
+  }
   case LMB_INT2: {
     uint8_t b1[32], b2[32];
     for (int c = 0; c < 4; ++c) {
@@ -277,10 +297,41 @@ void tern_from_fragments(uint8_t *payload) {
   });
 }
 
-// scale of row l of a tile: index into the tile's scale array
-inline size_t scale_slot(int kind, size_t l) {
-  return (kind == LMB_INT4 || kind == DK_TERNARY_MMA) ? 4 * (l % 8) + l / 8 : l;
+// fn(index of the byte in the tile, bit, row, column)
+template <class Fn> inline void bin_fragment_walk(Fn &&fn) {
+  for (size_t wi = 0; wi < 8; ++wi)
+    for (size_t g = 0; g < 8; ++g)
+      for (size_t tid = 0; tid < 4; ++tid)
+        for (size_t j = 0; j < 4; ++j)
+          for (size_t m = 0; m < 4; ++m)
+            for (size_t kh = 0; kh < 2; ++kh) {
+              const size_t sp = wi / 2, ab = wi % 2, col = 32 * (2 * sp + kh) + 16 * ab + 4 * tid + j;
+              fn(((wi / 4) * 32 + g * 4 + tid) * 16 + (wi % 4) * 4 + j, m + 4 * kh, g + 8 * m, col);
+            }
 }
+void bin_to_fragments(uint8_t *payload) {  // 1024 bytes, in place
+  uint8_t src[1024];
+  std::memcpy(src, payload, 1024);
+  std::memset(payload, 0, 1024);
+  bin_fragment_walk([&](size_t idx, size_t bit, size_t row, size_t col) {
+    const size_t jb = col / 8;
+    const unsigned v = (src[(jb / 16) * 512 + row * 16 + jb % 16] >> (7 - col % 8)) & 1u;
+    payload[idx] |= uint8_t(v << bit);
+  });
+}
+void bin_from_fragments(uint8_t *payload) {
+  uint8_t src[1024];
+  std::memcpy(src, payload, 1024);
+  std::memset(payload, 0, 1024);
+  bin_fragment_walk([&](size_t idx, size_t bit, size_t row, size_t col) {
+    const size_t jb = col / 8;
+    const unsigned v = (src[idx] >> bit) & 1u;
+    payload[(jb / 16) * 512 + row * 16 + jb % 16] |= uint8_t(v << (7 - col % 8));
+  });
+}
+
+// scale of row l of a tile: index into the tile's scale array
+inline size_t scale_slot(int kind, size_t l) { return kind_is_mma(kind) ? 4 * (l % 8) + l / 8 : l; }
 
 template <class F> void parallel_tiles(size_t n, F &&f) {
   unsigned hw = std::max(1u, std::thread::hardware_concurrency());
@@ -323,7 +374,8 @@ void retile(int kind, const uint8_t *blocks, size_t src_bpr, size_t row0, size_t
         for (int s = 0; s < ki.nscales; ++s) ts[size_t(s) * TILE_ROWS + scale_slot(kind, l)] = sc[s];
       }
       if (kind == LMB_INT4) int4_to_fragments(tile);
-      if (kind == DK_TERNARY_MMA) tern_to_fragments(tile);
+      if (kind == DK_TERNARY_MMA || kind == DK_INT2_MMA) tern_to_fragments(tile);
+      if (kind == DK_BINARY_MMA) bin_to_fragments(tile);
     }
   });
 }
@@ -340,11 +392,14 @@ void untile(int kind, const uint8_t *tiled, size_t M, size_t bpr, uint8_t *block
       if (kind == LMB_INT4) {
         std::memcpy(rowmajor, tile, 4096);
         int4_from_fragments(rowmajor);
-      } else if (kind == DK_TERNARY_MMA) {
+      } else if (kind == DK_TERNARY_MMA || kind == DK_INT2_MMA) {
         std::memcpy(rowmajor, tile, 2048);
         tern_from_fragments(rowmajor);
+      } else if (kind == DK_BINARY_MMA) {
+        std::memcpy(rowmajor, tile, 1024);
+        bin_from_fragments(rowmajor);
       }
-      const uint8_t *paysrc = (kind == LMB_INT4 || kind == DK_TERNARY_MMA) ? rowmajor : tile;
+      const uint8_t *paysrc = kind_is_mma(kind) ? rowmajor : tile;
       for (size_t l = 0; l < TILE_ROWS; ++l) {
         size_t r = rt * TILE_ROWS + l;
         if (r >= M) break;

@@ -224,25 +224,27 @@ def test_host_group_matches_oracle(ctx, oracle):
             assert rel_l2(y, oracle.lut_linear(INT4, 4, t.blocks, t.M, t.K, None, x)[0]) < TOL
 
 
+@pytest.mark.parametrize("kind,qbits", [(TERNARY, 2), (INT2, 2), (BINARY, 1)])
 @pytest.mark.parametrize("which", ["mma", "lut"])
-def test_ternary_both_device_layouts(ctx, ctx_lut, oracle, which):
-    """Ternary weights run on the integer tensor-core kernel by default and on the table-lookup
-    kernel on request; both must match the oracle, with and without rotation, and round-trip."""
+def test_both_device_layouts(ctx, ctx_lut, oracle, which, kind, qbits):
+    """Ternary, INT2 and binary weights run on the integer tensor-core kernel by default and on
+    the table-lookup kernel on request; both must match the oracle, with and without rotation,
+    and download bit-exactly."""
     c = ctx if which == "mma" else ctx_lut
     rng = np.random.default_rng(21)
     for (M, K) in EDGE_SHAPES + [(2048, 2048), (1024, 8192)]:
-        t = synth.ternary_tensor(rng, M, K)
+        t = synth.tensor(rng, kind, M, K)
         x = synth.activations(rng, K)
         for flags in (0, _lib.AUTO_ROTATE):
             y = run_linear(c, t, x, flags=flags)[0]
-            want = (oracle.lut_linear(TERNARY, 2, t.blocks, M, K, None, x)[0] if flags
-                    else oracle.gemv(TERNARY, t.blocks, np.pad(x, (0, blocks_per_row(K) * 256 - K)), M, K))
+            want = (oracle.lut_linear(kind, qbits, t.blocks, M, K, None, x)[0] if flags
+                    else oracle.gemv(kind, t.blocks, np.pad(x, (0, blocks_per_row(K) * 256 - K)), M, K))
             err = rel_l2(y, want)
             assert err < TOL or np.max(np.abs(y - want)) < 1e-6, (which, M, K, flags, err)
-    t = synth.ternary_tensor(rng, 70, 768)
+    t = synth.tensor(rng, kind, 70, 768)
     w = c.upload(t)
     back = w.download()
-    for f in BLOCK_DTYPES[TERNARY].names:
+    for f in BLOCK_DTYPES[kind].names:
         assert np.array_equal(back[f], t.blocks[f]), f
     w.free()
 
@@ -251,7 +253,7 @@ def test_extreme_activation_ranges(ctx, oracle):
     """The integer tensor-core kernels quantise x per 256-block with a shared exponent: blocks
     of very different magnitude, tiny values, and an all-zero block must still match."""
     rng = np.random.default_rng(31)
-    for kind in (INT4, TERNARY):
+    for kind in (INT4, TERNARY, INT2, BINARY):
         t = synth.tensor(rng, kind, 96, 1024)
         x = synth.activations(rng, 1024)
         x[:256] *= 1e-20
