@@ -12,14 +12,20 @@ from .model import Model
 
 def run_decode(ctx, shape_name: str, kind: int, ctx_len: int, batch: int = 1, steps: int = 20, warmup: int = 3,
                seed: int = 0, shared_layers: int = 0, max_seq: int = 2048, tp_rank: int = 0, tp_size: int = 1,
-               spec=None):
+               spec=None, random_kv: bool = False):
     spec = spec or synth.model_spec(synth.MODEL_SHAPES[shape_name], kind, seed=seed, max_seq=max_seq,
                                     shared_layers=shared_layers)
     m = Model(spec, ctx, max_batch=batch, tp_rank=tp_rank, tp_size=tp_size)
     rng = np.random.default_rng(seed + 1)
     vocab = spec.cfg["vocab"]
-    for p in range(ctx_len):  # prefill by decode, like the reference (src/inference.cpp:275-278)
-        m.forward(rng.integers(0, vocab, size=batch), [p] * batch, fetch=False)
+    if random_kv and batch == 1 and tp_size == 1:
+        # a cache of random keys and values instead of ctx_len prefill steps (profiling runs)
+        c = spec.cfg
+        n = c["n_layers"] * 2 * c["max_seq"] * c["n_kv_heads"] * c["head_dim"]
+        m.kv_import((rng.standard_normal(n) * 0.1).astype(np.float32))
+    else:
+        for p in range(ctx_len):  # prefill by decode, like the reference (src/inference.cpp:275-278)
+            m.forward(rng.integers(0, vocab, size=batch), [p] * batch, fetch=False)
     toks = rng.integers(0, vocab, size=batch)
     pos = [ctx_len] * batch
     for _ in range(warmup):
