@@ -59,6 +59,7 @@ struct GemvParams {
   int njobs;
   int rotate;
   int xmode;   // how the activations are formed in the prologue (XMODE_*)
+  int batch;   // sequences of the launch
   float eps;   // XMODE_RMSNORM
   // a prepared group of any number of jobs: job table and per-CTA (job, first CTA of the job)
   // pairs in device memory; null for ordinary launches
@@ -241,18 +242,29 @@ __device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, 
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ void mma_prologue(const float (&v)[8], int lane, float *blk, float *bscale, int *dsum);
+__device__ __forceinline__ void mma_prologue(const float (&v)[8], int lane, float *blk, float *bscale, int *aux2);
 
-// Shared by the two integer-MMA units.  The activations of a block are 32-bit fixed point with
-// one exponent per block, cut into four signed base-256 digits that occupy columns 0..3 of the
-// B operand (columns 4..7 repeat them and their results are ignored).  Several rows share one
-// weight word: row g + 8m sits in bit-field m of every byte, so `word & mask_m` IS the A
-// operand of that row, scaled by 2^(field offset); the power of two is folded into the row's
-// scale.  Accumulators are exact integers; the zero point is removed with the digit sums.
-struct MmaAcc { float r[4]; };  // rows g, g+8, g+16, g+24: digits 0,1 on lanes tid 0, digits 2,3 on tid 1
+// Where a warp finds the prepared activations of its sequences (see the kernel's prologue).
+struct MmaX {
+  const float *dig;  // digits of block 0 of the first sequence, [seq][block][FPB]
+  const float *bs;   // block scales, [seq][64]
+  const int *aux;    // digit-pair sums, [pair][64][4] = {seq 2p: d01, d23; seq 2p+1: d01, d23}
+  int seq_stride;    // floats between the digits of consecutive sequences; 0: one sequence only
+  int bs_stride;     // 64, or 0 with one sequence
+};
+
+// Shared by the integer-MMA units.  The activations of a block are 32-bit fixed point with one
+// exponent per block, cut into four signed base-256 digits.  The B operand of one MMA carries
+// the digits of two sequences: columns 0..3 the first, columns 4..7 the second (with a single
+// sequence they repeat the first and their results are ignored).  Several rows share one weight
+// word: row g + 8m sits in a bit-field of every byte, so `word & mask` IS the A operand of that
+// row, scaled by 2^(field offset); the power of two is folded into the row's scale.
+// Accumulators are exact integers; the zero point is removed with the digit sums.
+struct MmaAcc { float r[4]; };  // rows g, g+8, g+16, g+24; lanes tid 0,1: first sequence (digits 0,1 / 2,3), tid 2,3: second
 __device__ __forceinline__ void mma_acc_init(MmaAcc &a) { a.r[0] = a.r[1] = a.r[2] = a.r[3] = 0.0f; }
-__device__ __forceinline__ float mma_acc_row(const MmaAcc &a, int lane) {
-  const int src = 4 * (lane & 7);
+// value of row `lane` of the tile for the first (half = 0) or second sequence of the pair
+__device__ __forceinline__ float mma_acc_row(const MmaAcc &a, int lane, int half = 0) {
+  const int src = 4 * (lane & 7) + 2 * half;
   float r[4];
 #pragma unroll
   for (int k = 0; k < 4; ++k)
@@ -268,52 +280,88 @@ __device__ __forceinline__ float mma_row_value(int c0, int c1, uint32_t dz) {
 __device__ __forceinline__ float mma_plane_value(uint32_t c0, uint32_t c1, uint32_t dz) {
   return float(int(2u * c0 + 512u * c1 - dz));
 }
+__device__ __forceinline__ float4 as_float4(uint4 u) {
+  return make_float4(__uint_as_float(u.x), __uint_as_float(u.y), __uint_as_float(u.z), __uint_as_float(u.w));
+}
 
-template <> struct Unit<LMB_INT4> {
-  static constexpr int FPB = 256;  // 1 KiB per block: 256 activations x 4 digit bytes, in B-operand order
-  uint4 v[8];
-  float4 sc;  // scales of rows g, g+8, g+16, g+24
+// Common frame of the MMA units: Derived supplies the payload, `mma_block` (all MMAs of one
+// row-tile-block for PG sequence pairs) and `finish` (integer sums -> scaled floats).
+template <class Derived, int PG_> struct MmaUnitBase {
+  static constexpr int FPB = 256;  // 1 KiB per block and sequence: 256 activations x 4 digit bytes, in B-operand order
+  static constexpr int PG = PG_;   // sequence pairs evaluated per pass over the A operands
   using Acc = MmaAcc;
   static __device__ __forceinline__ void acc_init(Acc &a) { mma_acc_init(a); }
-  static __device__ __forceinline__ float acc_row(const Acc &a, int lane) { return mma_acc_row(a, lane); }
+  static __device__ __forceinline__ float acc_row(const Acc &a, int lane, int half = 0) { return mma_acc_row(a, lane, half); }
+  // One warp per 256-block and sequence: convert to fixed point with the block's exponent, split
+  // into signed base-256 digits and store them in B-operand order; *bscale = 2^(E-30),
+  // aux2[0..1] = sums over the block of digit 0 + 256 digit 1 and digit 2 + 256 digit 3.
+  static __device__ __forceinline__ void prologue(const float (&v)[8], int lane, float *blk, float *bscale, int *aux2) {
+    mma_prologue(v, lane, blk, bscale, aux2);
+  }
+  template <int NP> __device__ __forceinline__ void eval(const MmaX &xo, int bl, Acc (&acc)[NP]) const {
+    const int lane = threadIdx.x & 31, g = lane >> 2, tid = lane & 3;
+    const uint4 *dig = reinterpret_cast<const uint4 *>(xo.dig + size_t(bl) * FPB + size_t(g >> 2) * xo.seq_stride) + ((g & 3) * 4 + tid);
+    const int ps = xo.seq_stride >> 1;  // uint4 between consecutive pairs
+    constexpr int STEP = NP < PG ? NP : PG;
+#pragma unroll
+    for (int p0 = 0; p0 < NP; p0 += STEP) {
+      typename Derived::template Sums<STEP> c;
+      static_cast<const Derived *>(this)->template mma_block<STEP>(dig + size_t(p0) * ps, ps, c);
+#pragma unroll
+      for (int p = 0; p < STEP; ++p) {
+        const uint32_t d = uint32_t(xo.aux[((p0 + p) * 64 + bl) * 4 + tid]);
+        const float bs = xo.bs[(2 * (p0 + p) + (tid >> 1)) * xo.bs_stride + bl];
+        static_cast<const Derived *>(this)->finish(c, p, d, bs, acc[p0 + p]);
+      }
+    }
+  }
+};
+
+template <> struct Unit<LMB_INT4> : MmaUnitBase<Unit<LMB_INT4>, 4> {
+  uint4 v[8];
+  float4 sc;  // scales of rows g, g+8, g+16, g+24
+  template <int N> struct Sums { int c[N][2][4]; };
   __device__ __forceinline__ void load(const uint8_t *tile, int lane) {
 #pragma unroll
     for (int c = 0; c < 8; ++c) v[c] = ld_stream_v4(tile + (size_t(c) * TILE_ROWS + lane) * 16);
-    const uint4 s4 = ld_stream_v4(tile + size_t(8) * TILE_ROWS * 16 + size_t(lane >> 2) * 16);
-    sc = make_float4(__uint_as_float(s4.x), __uint_as_float(s4.y), __uint_as_float(s4.z), __uint_as_float(s4.w));
+    sc = as_float4(ld_stream_v4(tile + size_t(8) * TILE_ROWS * 16 + size_t(lane >> 2) * 16));
   }
-  __device__ __forceinline__ void eval(const float *blk, float blockscale, const int *aux, Acc &acc) const {
-    const int lane = threadIdx.x & 31, g = lane >> 2, tid = lane & 3;
-    const uint4 *dig = reinterpret_cast<const uint4 *>(blk) + ((g & 3) * 4 + tid);
+  template <int N> __device__ __forceinline__ void mma_block(const uint4 *dig, int ps, Sums<N> &s) const {
     constexpr uint32_t LO = 0x0F0F0F0Fu, HI = 0xF0F0F0F0u;
-    int c[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
+#pragma unroll
+    for (int p = 0; p < N; ++p)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) s.c[p][h][0] = s.c[p][h][1] = s.c[p][h][2] = s.c[p][h][3] = 0;
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
-      const uint4 b = dig[q * 16];  // {k-step 2q: b0, b1; k-step 2q+1: b0, b1}
+      uint4 b[N];  // {k-step 2q: b0, b1; k-step 2q+1: b0, b1}
+#pragma unroll
+      for (int p = 0; p < N; ++p) b[p] = dig[q * 16 + p * ps];
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         const uint4 w = v[h * 4 + q];  // rows 16h+g (low nibbles) and 16h+g+8 (high nibbles)
-        mma_u8s8(c[h], w.x & LO, w.x & HI, w.y & LO, w.y & HI, b.x, b.y);
-        mma_u8s8(c[h], w.z & LO, w.z & HI, w.w & LO, w.w & HI, b.z, b.w);
+        const uint32_t a0 = w.x & LO, a1 = w.x & HI, a2 = w.y & LO, a3 = w.y & HI;
+        const uint32_t e0 = w.z & LO, e1 = w.z & HI, e2 = w.w & LO, e3 = w.w & HI;
+#pragma unroll
+        for (int p = 0; p < N; ++p) {
+          mma_u8s8(s.c[p][h], a0, a1, a2, a3, b[p].x, b[p].y);
+          mma_u8s8(s.c[p][h], e0, e1, e2, e3, b[p].z, b[p].w);
+        }
       }
     }
-    const uint32_t d8 = 8u * uint32_t(aux[tid]);  // zero point 8
-    const float b16 = blockscale * 0.0625f;
-    acc.r[0] += mma_row_value(c[0][0], c[0][1], d8) * (blockscale * sc.x);
-    acc.r[1] += mma_row_value(c[0][2], c[0][3], d8 << 4) * (b16 * sc.y);
-    acc.r[2] += mma_row_value(c[1][0], c[1][1], d8) * (blockscale * sc.z);
-    acc.r[3] += mma_row_value(c[1][2], c[1][3], d8 << 4) * (b16 * sc.w);
   }
-  // One warp per 256-block: load (zero padded), optionally rotate, convert to fixed point with
-  // the block's exponent, split into signed base-256 digits and store them in B-operand order;
-  // *bscale = 2^(E-30), aux[p] = sum over the block of digit 2p + 256 * digit 2p+1.
-  static __device__ __forceinline__ void prologue(const float (&v)[8], int lane, float *blk, float *bscale, int *aux) {
-    mma_prologue(v, lane, blk, bscale, aux);
+  template <int N> __device__ __forceinline__ void finish(const Sums<N> &s, int p, uint32_t d, float bs, Acc &acc) const {
+    const uint32_t d8 = 8u * d;  // zero point 8
+    const float b16 = bs * 0.0625f;
+    acc.r[0] += mma_row_value(s.c[p][0][0], s.c[p][0][1], d8) * (bs * sc.x);
+    acc.r[1] += mma_row_value(s.c[p][0][2], s.c[p][0][3], d8 << 4) * (b16 * sc.y);
+    acc.r[2] += mma_row_value(s.c[p][1][0], s.c[p][1][1], d8) * (bs * sc.z);
+    acc.r[3] += mma_row_value(s.c[p][1][2], s.c[p][1][3], d8 << 4) * (b16 * sc.w);
   }
 };
 
 // (definition of the shared MMA prologue)
-__device__ __forceinline__ void mma_prologue(const float (&v)[8], int lane, float *blk, float *bscale, int *aux) {
+__device__ __forceinline__ void mma_prologue(const float (&v)[8], int lane, float *blk, float *bscale, int *aux2) {
   float amax = 0.0f;
 #pragma unroll
   for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
@@ -353,145 +401,152 @@ __device__ __forceinline__ void mma_prologue(const float (&v)[8], int lane, floa
   const int d23 = __reduce_add_sync(0xffffffffu, ds[2] + 256 * ds[3]);
   if (lane == 0) {
     *bscale = (am != 0u) ? __uint_as_float(uint32_t(127 + e - 30) << 23) : 0.0f;
-    *reinterpret_cast<int4 *>(aux) = make_int4(d01, d23, 0, 0);
+    aux2[0] = d01;
+    aux2[1] = d23;
   }
 }
 
 // Ternary weights as 2-bit codes t+1 on the same integer MMA path (zero point 1): the four
 // 2-bit fields of a byte belong to rows g, g+8, g+16, g+24 of the tile.
-template <> struct Unit<DK_TERNARY_MMA> {
-  static constexpr int FPB = 256;
+template <> struct Unit<DK_TERNARY_MMA> : MmaUnitBase<Unit<DK_TERNARY_MMA>, 4> {
   uint4 v[4];
   float4 sc;
-  using Acc = MmaAcc;
-  static __device__ __forceinline__ void acc_init(Acc &a) { mma_acc_init(a); }
-  static __device__ __forceinline__ float acc_row(const Acc &a, int lane) { return mma_acc_row(a, lane); }
+  template <int N> struct Sums { int c[N][2][4]; };
   __device__ __forceinline__ void load(const uint8_t *tile, int lane) {
 #pragma unroll
     for (int c = 0; c < 4; ++c) v[c] = ld_stream_v4(tile + (size_t(c) * TILE_ROWS + lane) * 16);
-    const uint4 s4 = ld_stream_v4(tile + size_t(4) * TILE_ROWS * 16 + size_t(lane >> 2) * 16);
-    sc = make_float4(__uint_as_float(s4.x), __uint_as_float(s4.y), __uint_as_float(s4.z), __uint_as_float(s4.w));
+    sc = as_float4(ld_stream_v4(tile + size_t(4) * TILE_ROWS * 16 + size_t(lane >> 2) * 16));
   }
-  __device__ __forceinline__ void eval(const float *blk, float blockscale, const int *aux, Acc &acc) const {
-    const int lane = threadIdx.x & 31, g = lane >> 2, tid = lane & 3;
-    const uint4 *dig = reinterpret_cast<const uint4 *>(blk) + ((g & 3) * 4 + tid);
+  template <int N> __device__ __forceinline__ void mma_block(const uint4 *dig, int ps, Sums<N> &s) const {
     constexpr uint32_t F0 = 0x03030303u, F1 = 0x0C0C0C0Cu, F2 = 0x30303030u, F3 = 0xC0C0C0C0u;
-    int c[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
+#pragma unroll
+    for (int p = 0; p < N; ++p)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) s.c[p][h][0] = s.c[p][h][1] = s.c[p][h][2] = s.c[p][h][3] = 0;
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
-      const uint4 b = dig[q * 16];
       const uint4 w = v[q];  // {k-step 2q: columns +0..15, +16..31; k-step 2q+1: the same}
-      mma_u8s8(c[0], w.x & F0, w.x & F1, w.y & F0, w.y & F1, b.x, b.y);
-      mma_u8s8(c[1], w.x & F2, w.x & F3, w.y & F2, w.y & F3, b.x, b.y);
-      mma_u8s8(c[0], w.z & F0, w.z & F1, w.w & F0, w.w & F1, b.z, b.w);
-      mma_u8s8(c[1], w.z & F2, w.z & F3, w.w & F2, w.w & F3, b.z, b.w);
+#pragma unroll
+      for (int p = 0; p < N; ++p) {
+        const uint4 b = dig[q * 16 + p * ps];
+        mma_u8s8(s.c[p][0], w.x & F0, w.x & F1, w.y & F0, w.y & F1, b.x, b.y);
+        mma_u8s8(s.c[p][1], w.x & F2, w.x & F3, w.y & F2, w.y & F3, b.x, b.y);
+        mma_u8s8(s.c[p][0], w.z & F0, w.z & F1, w.w & F0, w.w & F1, b.z, b.w);
+        mma_u8s8(s.c[p][1], w.z & F2, w.z & F3, w.w & F2, w.w & F3, b.z, b.w);
+      }
     }
-    const uint32_t d1 = uint32_t(aux[tid]);  // zero point 1
-    acc.r[0] += mma_row_value(c[0][0], c[0][1], d1) * (blockscale * sc.x);
-    acc.r[1] += mma_row_value(c[0][2], c[0][3], d1 << 2) * ((blockscale * 0.25f) * sc.y);
-    acc.r[2] += mma_row_value(c[1][0], c[1][1], d1 << 4) * ((blockscale * 0.0625f) * sc.z);
-    acc.r[3] += mma_row_value(c[1][2], c[1][3], d1 << 6) * ((blockscale * 0.015625f) * sc.w);
   }
-  static __device__ __forceinline__ void prologue(const float (&v)[8], int lane, float *blk, float *bscale, int *aux) {
-    mma_prologue(v, lane, blk, bscale, aux);
+  template <int N> __device__ __forceinline__ void finish(const Sums<N> &s, int p, uint32_t d1, float bs, Acc &acc) const {
+    acc.r[0] += mma_row_value(s.c[p][0][0], s.c[p][0][1], d1) * (bs * sc.x);  // zero point 1
+    acc.r[1] += mma_row_value(s.c[p][0][2], s.c[p][0][3], d1 << 2) * ((bs * 0.25f) * sc.y);
+    acc.r[2] += mma_row_value(s.c[p][1][0], s.c[p][1][1], d1 << 4) * ((bs * 0.0625f) * sc.z);
+    acc.r[3] += mma_row_value(s.c[p][1][2], s.c[p][1][3], d1 << 6) * ((bs * 0.015625f) * sc.w);
   }
 };
 
 // INT2 (residual binary, w = +-s1 +- s2) as two +-1 bit planes on the integer MMA path: the
 // ternary arrangement with bit 2m = b1 and bit 2m+1 = b2 of row g+8m; one accumulator per plane.
-template <> struct Unit<DK_INT2_MMA> {
-  static constexpr int FPB = 256;
+template <> struct Unit<DK_INT2_MMA> : MmaUnitBase<Unit<DK_INT2_MMA>, 2> {
   uint4 v[4];
   float4 sc[2];
-  using Acc = MmaAcc;
-  static __device__ __forceinline__ void acc_init(Acc &a) { mma_acc_init(a); }
-  static __device__ __forceinline__ float acc_row(const Acc &a, int lane) { return mma_acc_row(a, lane); }
+  template <int N> struct Sums { int c[N][2][2][4]; };  // [pair][row half][plane]
   __device__ __forceinline__ void load(const uint8_t *tile, int lane) {
 #pragma unroll
     for (int c = 0; c < 4; ++c) v[c] = ld_stream_v4(tile + (size_t(c) * TILE_ROWS + lane) * 16);
 #pragma unroll
-    for (int p = 0; p < 2; ++p) {
-      const uint4 s4 = ld_stream_v4(tile + size_t(4) * TILE_ROWS * 16 + size_t(p) * TILE_ROWS * 4 + size_t(lane >> 2) * 16);
-      sc[p] = make_float4(__uint_as_float(s4.x), __uint_as_float(s4.y), __uint_as_float(s4.z), __uint_as_float(s4.w));
-    }
+    for (int p = 0; p < 2; ++p)
+      sc[p] = as_float4(ld_stream_v4(tile + size_t(4) * TILE_ROWS * 16 + size_t(p) * TILE_ROWS * 4 + size_t(lane >> 2) * 16));
   }
-  __device__ __forceinline__ void eval(const float *blk, float blockscale, const int *aux, Acc &acc) const {
-    const int lane = threadIdx.x & 31, g = lane >> 2, tid = lane & 3;
-    const uint4 *dig = reinterpret_cast<const uint4 *>(blk) + ((g & 3) * 4 + tid);
+  template <int N> __device__ __forceinline__ void mma_block(const uint4 *dig, int ps, Sums<N> &s) const {
     constexpr uint32_t M1 = 0x01010101u;
-    int c[2][2][4] = {{{0, 0, 0, 0}, {0, 0, 0, 0}}, {{0, 0, 0, 0}, {0, 0, 0, 0}}};  // [row half][plane]
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      const uint4 b = dig[q * 16];
-      const uint4 w = v[q];
+    for (int p = 0; p < N; ++p)
 #pragma unroll
       for (int h = 0; h < 2; ++h)
 #pragma unroll
-        for (int p = 0; p < 2; ++p) {
-          const int sh = 4 * h + p;  // rows g+16h (bit 4h+p) and g+16h+8 (bit 4h+2+p)
-          mma_u8s8(c[h][p], w.x & (M1 << sh), w.x & (M1 << (sh + 2)), w.y & (M1 << sh), w.y & (M1 << (sh + 2)), b.x, b.y);
-          mma_u8s8(c[h][p], w.z & (M1 << sh), w.z & (M1 << (sh + 2)), w.w & (M1 << sh), w.w & (M1 << (sh + 2)), b.z, b.w);
+        for (int pl = 0; pl < 2; ++pl) s.c[p][h][pl][0] = s.c[p][h][pl][1] = s.c[p][h][pl][2] = s.c[p][h][pl][3] = 0;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const uint4 w = v[q];
+      uint4 b[N];
+#pragma unroll
+      for (int p = 0; p < N; ++p) b[p] = dig[q * 16 + p * ps];
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int pl = 0; pl < 2; ++pl) {
+          const int sh = 4 * h + pl;  // rows g+16h (bit 4h+pl) and g+16h+8 (bit 4h+2+pl)
+          const uint32_t a0 = w.x & (M1 << sh), a1 = w.x & (M1 << (sh + 2)), a2 = w.y & (M1 << sh), a3 = w.y & (M1 << (sh + 2));
+          const uint32_t e0 = w.z & (M1 << sh), e1 = w.z & (M1 << (sh + 2)), e2 = w.w & (M1 << sh), e3 = w.w & (M1 << (sh + 2));
+#pragma unroll
+          for (int p = 0; p < N; ++p) {
+            mma_u8s8(s.c[p][h][pl], a0, a1, a2, a3, b[p].x, b[p].y);
+            mma_u8s8(s.c[p][h][pl], e0, e1, e2, e3, b[p].z, b[p].w);
+          }
         }
     }
-    const uint32_t d = uint32_t(aux[tid]);
+  }
+  template <int N> __device__ __forceinline__ void finish(const Sums<N> &s, int p, uint32_t d, float bs, Acc &acc) const {
     const float s1[4] = {sc[0].x, sc[0].y, sc[0].z, sc[0].w}, s2[4] = {sc[1].x, sc[1].y, sc[1].z, sc[1].w};
 #pragma unroll
     for (int m = 0; m < 4; ++m) {
       const int h = m >> 1, j = m & 1;
-      const float f1 = blockscale * (1.0f / float(1 << (2 * m))), f2 = blockscale * (1.0f / float(2 << (2 * m)));
-      float t = mma_plane_value(uint32_t(c[h][0][2 * j]), uint32_t(c[h][0][2 * j + 1]), d << (2 * m)) * (f1 * s1[m]);
-      t = fmaf(mma_plane_value(uint32_t(c[h][1][2 * j]), uint32_t(c[h][1][2 * j + 1]), d << (2 * m + 1)), f2 * s2[m], t);
+      const float f1 = bs * (1.0f / float(1 << (2 * m))), f2 = bs * (1.0f / float(2 << (2 * m)));
+      float t = mma_plane_value(uint32_t(s.c[p][h][0][2 * j]), uint32_t(s.c[p][h][0][2 * j + 1]), d << (2 * m)) * (f1 * s1[m]);
+      t = fmaf(mma_plane_value(uint32_t(s.c[p][h][1][2 * j]), uint32_t(s.c[p][h][1][2 * j + 1]), d << (2 * m + 1)), f2 * s2[m], t);
       acc.r[m] += t;
     }
-  }
-  static __device__ __forceinline__ void prologue(const float (&v)[8], int lane, float *blk, float *bscale, int *aux) {
-    mma_prologue(v, lane, blk, bscale, aux);
   }
 };
 
 // BINARY (w = +-s) as one +-1 bit plane: bit m + 4kh of a byte is row g+8m of the first (kh = 0)
 // or second (kh = 1) k-step of the word's pair; one accumulator per kh, merged by an exact shift.
-template <> struct Unit<DK_BINARY_MMA> {
-  static constexpr int FPB = 256;
+template <> struct Unit<DK_BINARY_MMA> : MmaUnitBase<Unit<DK_BINARY_MMA>, 2> {
   uint4 v[2];
   float4 sc;
-  using Acc = MmaAcc;
-  static __device__ __forceinline__ void acc_init(Acc &a) { mma_acc_init(a); }
-  static __device__ __forceinline__ float acc_row(const Acc &a, int lane) { return mma_acc_row(a, lane); }
+  template <int N> struct Sums { int c[N][2][2][4]; };  // [pair][row half][kh]
   __device__ __forceinline__ void load(const uint8_t *tile, int lane) {
 #pragma unroll
     for (int c = 0; c < 2; ++c) v[c] = ld_stream_v4(tile + (size_t(c) * TILE_ROWS + lane) * 16);
-    const uint4 s4 = ld_stream_v4(tile + size_t(2) * TILE_ROWS * 16 + size_t(lane >> 2) * 16);
-    sc = make_float4(__uint_as_float(s4.x), __uint_as_float(s4.y), __uint_as_float(s4.z), __uint_as_float(s4.w));
+    sc = as_float4(ld_stream_v4(tile + size_t(2) * TILE_ROWS * 16 + size_t(lane >> 2) * 16));
   }
-  __device__ __forceinline__ void eval(const float *blk, float blockscale, const int *aux, Acc &acc) const {
-    const int lane = threadIdx.x & 31, g = lane >> 2, tid = lane & 3;
-    const uint4 *dig = reinterpret_cast<const uint4 *>(blk) + ((g & 3) * 4 + tid);
+  template <int N> __device__ __forceinline__ void mma_block(const uint4 *dig, int ps, Sums<N> &s) const {
     constexpr uint32_t M1 = 0x01010101u;
-    int c[2][2][4] = {{{0, 0, 0, 0}, {0, 0, 0, 0}}, {{0, 0, 0, 0}, {0, 0, 0, 0}}};  // [row half][kh]
+#pragma unroll
+    for (int p = 0; p < N; ++p)
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int kh = 0; kh < 2; ++kh) s.c[p][h][kh][0] = s.c[p][h][kh][1] = s.c[p][h][kh][2] = s.c[p][h][kh][3] = 0;
     const uint32_t wa[4] = {v[0].x, v[0].z, v[1].x, v[1].z}, wb[4] = {v[0].y, v[0].w, v[1].y, v[1].w};
 #pragma unroll
     for (int sp = 0; sp < 4; ++sp) {
-      const uint4 b = dig[sp * 16];  // {k-step 2sp: b0, b1; k-step 2sp+1: b0, b1}
+      uint4 b[N];  // {k-step 2sp: b0, b1; k-step 2sp+1: b0, b1}
+#pragma unroll
+      for (int p = 0; p < N; ++p) b[p] = dig[sp * 16 + p * ps];
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         const int s0 = 2 * h, s1 = 2 * h + 4;
-        mma_u8s8(c[h][0], wa[sp] & (M1 << s0), wa[sp] & (M1 << (s0 + 1)), wb[sp] & (M1 << s0), wb[sp] & (M1 << (s0 + 1)), b.x, b.y);
-        mma_u8s8(c[h][1], wa[sp] & (M1 << s1), wa[sp] & (M1 << (s1 + 1)), wb[sp] & (M1 << s1), wb[sp] & (M1 << (s1 + 1)), b.z, b.w);
+        const uint32_t a0 = wa[sp] & (M1 << s0), a1 = wa[sp] & (M1 << (s0 + 1)), a2 = wb[sp] & (M1 << s0), a3 = wb[sp] & (M1 << (s0 + 1));
+        const uint32_t e0 = wa[sp] & (M1 << s1), e1 = wa[sp] & (M1 << (s1 + 1)), e2 = wb[sp] & (M1 << s1), e3 = wb[sp] & (M1 << (s1 + 1));
+#pragma unroll
+        for (int p = 0; p < N; ++p) {
+          mma_u8s8(s.c[p][h][0], a0, a1, a2, a3, b[p].x, b[p].y);
+          mma_u8s8(s.c[p][h][1], e0, e1, e2, e3, b[p].z, b[p].w);
+        }
       }
     }
-    const uint32_t d = uint32_t(aux[tid]);
-    const float s[4] = {sc.x, sc.y, sc.z, sc.w};
+  }
+  template <int N> __device__ __forceinline__ void finish(const Sums<N> &s, int p, uint32_t d, float bs, Acc &acc) const {
+    const float sv[4] = {sc.x, sc.y, sc.z, sc.w};
 #pragma unroll
     for (int m = 0; m < 4; ++m) {
       const int h = m >> 1, j = m & 1;
       // the kh = 1 sums carry 16 times the field's power of two: an exact shift brings them back
-      const uint32_t c0 = uint32_t(c[h][0][2 * j] + (c[h][1][2 * j] >> 4)), c1 = uint32_t(c[h][0][2 * j + 1] + (c[h][1][2 * j + 1] >> 4));
-      acc.r[m] += mma_plane_value(c0, c1, d << m) * ((blockscale * (1.0f / float(1 << m))) * s[m]);
+      const uint32_t c0 = uint32_t(s.c[p][h][0][2 * j] + (s.c[p][h][1][2 * j] >> 4));
+      const uint32_t c1 = uint32_t(s.c[p][h][0][2 * j + 1] + (s.c[p][h][1][2 * j + 1] >> 4));
+      acc.r[m] += mma_plane_value(c0, c1, d << m) * ((bs * (1.0f / float(1 << m))) * sv[m]);
     }
-  }
-  static __device__ __forceinline__ void prologue(const float (&v)[8], int lane, float *blk, float *bscale, int *aux) {
-    mma_prologue(v, lane, blk, bscale, aux);
   }
 };
 
@@ -534,15 +589,19 @@ __host__ __device__ constexpr int prefetch_depth(int kind) {
        : kind == LMB_INT8 ? 0 : 1;
 }
 
-template <int KIND>
-__global__ void __launch_bounds__(THREADS, KIND == LMB_INT8 ? 1 : 2) k_gemv(const __grid_constant__ GemvParams p) {
+template <int KIND, int NSEQ>
+__global__ void __launch_bounds__(THREADS, (KIND == LMB_INT8 || NSEQ == 8) ? 1 : 2) k_gemv(const __grid_constant__ GemvParams p) {
+  // NSEQ sequences share one pass over the weights (integer-MMA kinds only: two sequences per
+  // MMA); the other kinds run one sequence per CTA, blockIdx.y selecting it.
+  static_assert(NSEQ == 1 || kind_is_mma(KIND), "several sequences per pass need an integer-MMA kind");
   using U = Unit<KIND>;
   constexpr int FPB = U::FPB;
   constexpr size_t TB = tile_bytes(KIND);
+  constexpr int NP = (NSEQ + 1) / 2;
   extern __shared__ __align__(1024) float smem[];
-  __shared__ float part[THREADS];
-  __shared__ float xsum[64];
-  __shared__ __align__(16) int xaux[64 * 4];
+  __shared__ float part[NSEQ][THREADS];
+  __shared__ float xsum[NSEQ * 64];
+  __shared__ __align__(16) int xaux[NP * 64 * 4];
   __shared__ int is_last;
 
   pdl_launch_dependents();
@@ -560,7 +619,8 @@ __global__ void __launch_bounds__(THREADS, KIND == LMB_INT8 ? 1 : 2) k_gemv(cons
   const Job &job = p.jobs_dev ? p.jobs_dev[j] : p.job[j];
   const int local = int(blockIdx.x) - first;
   const int rg = local / job.n_ks, ks = local - rg * job.n_ks;
-  const int batch = blockIdx.y;
+  const int batch0 = blockIdx.y * NSEQ;               // first sequence of this CTA
+  const int nb = min(NSEQ, p.batch - batch0);         // sequences of this CTA
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int rt0 = rg * job.R;
   const int nrt = min(job.R, job.row_tiles - rt0);
@@ -572,7 +632,7 @@ __global__ void __launch_bounds__(THREADS, KIND == LMB_INT8 ? 1 : 2) k_gemv(cons
   const uint8_t *row_tiles = job.tiles + (size_t(rt0 + rtl) * job.bpr + b0) * TB;
 
   // weights do not depend on the preceding kernel: fetch the first units before waiting for it
-  constexpr int NSLOT = prefetch_depth(KIND) + 1;  // a ring of row-blocks held in registers
+  constexpr int NSLOT = (NSEQ > 2 ? 1 : prefetch_depth(KIND)) + 1;  // a ring of row-blocks held in registers
   U slot[NSLOT];
   if (active) {
 #pragma unroll
@@ -582,90 +642,149 @@ __global__ void __launch_bounds__(THREADS, KIND == LMB_INT8 ? 1 : 2) k_gemv(cons
 
   pdl_wait();
 
-  const float *x = job.x + size_t(batch) * job.x_stride;
-  float inv_rms = 1.0f;
+  const float *x = job.x + size_t(batch0) * job.x_stride;
+  float *inv_rms = part[0];  // [sequence] after the block below (XMODE_RMSNORM)
   if (p.xmode == XMODE_RMSNORM) {
-    // RMSNorm of the whole input vector (src/layers/norm.cpp:18-34), recomputed by every CTA
-    float ss = 0.0f;
+    // RMSNorm of the whole input vectors (src/layers/norm.cpp:18-34), recomputed by every CTA
+    float ss[NSEQ];
+#pragma unroll
+    for (int q = 0; q < NSEQ; ++q) ss[q] = 0.0f;
     for (unsigned i = threadIdx.x; i < job.x_len; i += THREADS) {
-      const float v = x[i];
-      ss += v * v;
+#pragma unroll
+      for (int q = 0; q < NSEQ; ++q) {
+        const float v = (q < nb) ? x[size_t(q) * job.x_stride + i] : 0.0f;
+        ss[q] += v * v;
+      }
     }
 #pragma unroll
-    for (int m = 16; m > 0; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
-    if (lane == 0) part[warp] = ss;
-    __syncthreads();
-    ss = 0.0f;
+    for (int q = 0; q < NSEQ; ++q) {
 #pragma unroll
-    for (int k = 0; k < WARPS; ++k) ss += part[k];
-    inv_rms = 1.0f / sqrtf(ss / float(job.x_len) + p.eps);
-    __syncthreads();  // part[] is reused below
+      for (int m = 16; m > 0; m >>= 1) ss[q] += __shfl_xor_sync(0xffffffffu, ss[q], m);
+      if (lane == 0) xsum[q * WARPS + warp] = ss[q];  // xsum is free until the prologue below
+    }
+    __syncthreads();
+    if (threadIdx.x < NSEQ) {
+      float t = 0.0f;
+#pragma unroll
+      for (int k = 0; k < WARPS; ++k) t += xsum[threadIdx.x * WARPS + k];
+      inv_rms[threadIdx.x] = 1.0f / sqrtf(t / float(job.x_len) + p.eps);
+    }
+    __syncthreads();
   }
   {
-    // one warp per block, the next block's activations are fetched while this one is converted
+    // one warp per (sequence, block); the next item's activations are fetched while this one is converted
     float v[8], w8[8], nv[8];
-    const float *x2 = (p.xmode == XMODE_SILU_MUL) ? job.x2 + size_t(batch) * job.x_stride : job.x2;
-    if (warp < ns) load_x8(x, job.x_len, size_t(b0 + warp), lane, nv);
-    for (int bl = warp; bl < ns; bl += WARPS) {
+    const int items = ns * nb;
+    if (warp < items) load_x8(x + size_t(warp / ns) * job.x_stride, job.x_len, size_t(b0 + warp % ns), lane, nv);
+    for (int it = warp; it < items; it += WARPS) {
+      const int q = it / ns, bl = it - q * ns;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = nv[j];
-      if (p.xmode != XMODE_PLAIN) load_x8(x2, job.x_len, size_t(b0 + bl), lane, w8);
-      if (bl + WARPS < ns) load_x8(x, job.x_len, size_t(b0 + bl + WARPS), lane, nv);
+      for (int e = 0; e < 8; ++e) v[e] = nv[e];
+      if (p.xmode == XMODE_RMSNORM) load_x8(job.x2, job.x_len, size_t(b0 + bl), lane, w8);
+      if (p.xmode == XMODE_SILU_MUL) load_x8(job.x2 + size_t(batch0 + q) * job.x_stride, job.x_len, size_t(b0 + bl), lane, w8);
+      if (it + WARPS < items) {
+        const int nq = (it + WARPS) / ns;
+        load_x8(x + size_t(nq) * job.x_stride, job.x_len, size_t(b0 + (it + WARPS) - nq * ns), lane, nv);
+      }
       if (p.xmode == XMODE_RMSNORM) {
+        const float ir = inv_rms[q];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = v[j] * inv_rms * w8[j];
+        for (int e = 0; e < 8; ++e) v[e] = v[e] * ir * w8[e];
       } else if (p.xmode == XMODE_SILU_MUL) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = (v[j] / (1.0f + expf(-v[j]))) * w8[j];  // silu(gate) * up, model.cpp:36,414-416
+        for (int e = 0; e < 8; ++e) v[e] = (v[e] / (1.0f + expf(-v[e]))) * w8[e];  // silu(gate) * up, model.cpp:36,414-416
       }
       if (p.rotate) fwht256_warp(v, lane);
-      U::prologue(v, lane, smem + size_t(bl) * FPB, xsum + bl, xaux + 4 * bl);
+      if constexpr (kind_is_mma(KIND)) {
+        int *aux = xaux + ((q >> 1) * 64 + bl) * 4;
+        U::prologue(v, lane, smem + (size_t(q) * job.S + bl) * FPB, xsum + q * 64 + bl, aux + 2 * (q & 1));
+        if ((q | 1) >= nb && lane == 0) aux[2] = aux[3] = 0;  // no second sequence in this pair
+      } else {
+        U::prologue(v, lane, smem + size_t(bl) * FPB, xsum + bl, xaux + 4 * bl);
+      }
     }
   }
   __syncthreads();
 
-  typename U::Acc accs;
-  U::acc_init(accs);
-  if (active) {
-    // each slot is evaluated and at once refilled with the row-block NSLOT steps ahead, so that
-    // NSLOT-1 loads are in flight during every evaluation
-    for (int base = sub; base < ns; base += NSLOT * wpr) {
+  // each slot is evaluated and at once refilled with the row-block NSLOT steps ahead, so that
+  // NSLOT-1 loads are in flight during every evaluation
+  float acc[NSEQ];
+  if constexpr (kind_is_mma(KIND)) {
+    typename U::Acc accs[NP];
 #pragma unroll
-      for (int sl = 0; sl < NSLOT; ++sl) {
-        const int bl = base + sl * wpr;
-        if (bl < ns) {
-          slot[sl].eval(smem + size_t(bl) * FPB, xsum[bl], xaux + 4 * bl, accs);
-          if (bl + NSLOT * wpr < ns) slot[sl].load(row_tiles + size_t(bl + NSLOT * wpr) * TB, lane);
+    for (int q = 0; q < NP; ++q) U::acc_init(accs[q]);
+    const MmaX xo{smem, xsum, xaux, NSEQ > 1 ? job.S * FPB : 0, NSEQ > 1 ? 64 : 0};
+    if (active) {
+      for (int base = sub; base < ns; base += NSLOT * wpr) {
+#pragma unroll
+        for (int sl = 0; sl < NSLOT; ++sl) {
+          const int bl = base + sl * wpr;
+          if (bl < ns) {
+            slot[sl].template eval<NP>(xo, bl, accs);
+            if (bl + NSLOT * wpr < ns) slot[sl].load(row_tiles + size_t(bl + NSLOT * wpr) * TB, lane);
+          }
         }
       }
     }
+#pragma unroll
+    for (int q = 0; q < NSEQ; ++q) acc[q] = U::acc_row(accs[q >> 1], lane, q & 1);  // warp-uniform: every lane takes part
+  } else {
+    typename U::Acc accs;
+    U::acc_init(accs);
+    if (active) {
+      for (int base = sub; base < ns; base += NSLOT * wpr) {
+#pragma unroll
+        for (int sl = 0; sl < NSLOT; ++sl) {
+          const int bl = base + sl * wpr;
+          if (bl < ns) {
+            slot[sl].eval(smem + size_t(bl) * FPB, xsum[bl], xaux + 4 * bl, accs);
+            if (bl + NSLOT * wpr < ns) slot[sl].load(row_tiles + size_t(bl + NSLOT * wpr) * TB, lane);
+          }
+        }
+      }
+    }
+    acc[0] = U::acc_row(accs, lane);
   }
-  const float acc = U::acc_row(accs, lane);  // warp-uniform control flow: every lane takes part
 
   // combine the warps that share a row-tile, in warp order: thread t ends up with row rt0*32 + t
-  part[threadIdx.x] = acc;
+  if (p.xmode == XMODE_RMSNORM) __syncthreads();  // inv_rms (in part[0]) has been read by everyone
+#pragma unroll
+  for (int q = 0; q < NSEQ; ++q) part[q][threadIdx.x] = acc[q];
   __syncthreads();
   const int t = threadIdx.x;
   const bool owns_row = t < nrt * TILE_ROWS;
-  float s = 0.0f;
-  if (owns_row) {
-    const int r = t >> 5;
-    for (int k = 0; k < wpr; ++k) s += part[(r * wpr + k) * 32 + (t & 31)];
+  float s[NSEQ];
+#pragma unroll
+  for (int q = 0; q < NSEQ; ++q) {
+    s[q] = 0.0f;
+    if (owns_row) {
+      const int r = t >> 5;
+      for (int k = 0; k < wpr; ++k) s[q] += part[q][(r * wpr + k) * 32 + (t & 31)];
+    }
   }
   const int row = rt0 * TILE_ROWS + t;
   if (job.n_ks == 1) {
     if (owns_row && row < job.M) {
-      if (job.bias) s += job.bias[row];
-      if (job.residual) s += job.residual[size_t(batch) * job.y_stride + row];
-      job.y[size_t(batch) * job.y_stride + row] = s;
+      const float bias = job.bias ? job.bias[row] : 0.0f;
+#pragma unroll
+      for (int q = 0; q < NSEQ; ++q)
+        if (q < nb) {
+          float o = s[q];
+          if (job.bias) o += bias;
+          if (job.residual) o += job.residual[size_t(batch0 + q) * job.y_stride + row];
+          job.y[size_t(batch0 + q) * job.y_stride + row] = o;
+        }
     }
     return;
   }
   // split K: publish the partial sums, the last slice to arrive adds them in slice order
-  float *scr = job.scratch + size_t(batch) * job.n_ks * job.mp;
-  if (owns_row) scr[size_t(ks) * job.mp + row] = s;
+  if (owns_row) {
+#pragma unroll
+    for (int q = 0; q < NSEQ; ++q)
+      if (q < nb) job.scratch[(size_t(batch0 + q) * job.n_ks + ks) * job.mp + row] = s[q];
+  }
   __syncthreads();
-  unsigned *ctr = job.counters + size_t(batch) * job.n_rg + rg;
+  unsigned *ctr = job.counters + size_t(blockIdx.y) * job.n_rg + rg;
   if (t == 0) {
     __threadfence();  // cumulative: publishes the CTA's partial sums (ordered before it by the barrier)
     is_last = (atomicAdd(ctr, 1u) == unsigned(job.n_ks - 1));
@@ -674,11 +793,17 @@ __global__ void __launch_bounds__(THREADS, KIND == LMB_INT8 ? 1 : 2) k_gemv(cons
   __syncthreads();
   if (!is_last) return;
   if (owns_row && row < job.M) {
-    float tot = 0.0f;
-    for (int k = 0; k < job.n_ks; ++k) tot += __ldcg(scr + size_t(k) * job.mp + row);
-    if (job.bias) tot += job.bias[row];
-    if (job.residual) tot += job.residual[size_t(batch) * job.y_stride + row];
-    job.y[size_t(batch) * job.y_stride + row] = tot;
+    const float bias = job.bias ? job.bias[row] : 0.0f;
+#pragma unroll
+    for (int q = 0; q < NSEQ; ++q)
+      if (q < nb) {
+        const float *scr = job.scratch + size_t(batch0 + q) * job.n_ks * job.mp;
+        float tot = 0.0f;
+        for (int k = 0; k < job.n_ks; ++k) tot += __ldcg(scr + size_t(k) * job.mp + row);
+        if (job.bias) tot += bias;
+        if (job.residual) tot += job.residual[size_t(batch0 + q) * job.y_stride + row];
+        job.y[size_t(batch0 + q) * job.y_stride + row] = tot;
+      }
   }
   if (t == 0) *ctr = 0u;  // ready for the next launch
 }
@@ -712,11 +837,12 @@ int ctas_per_sm(int kind) { return kind_info(kind).lut ? 3 : 2; }
 // of "one warp evaluates one 256-column block":
 //     waves of CTAs x (blocks per warp + prologue share + fixed CTA cost [+ split-K hand-off]).
 // `other_row_tiles` are the row-tiles of the other jobs of the same launch.
-Plan make_plan(int kind, size_t row_tiles, size_t bpr, size_t batch, int sm_count, size_t other_row_tiles = 0) {
+Plan make_plan(int kind, size_t row_tiles, size_t bpr, size_t batch, int sm_count, size_t other_row_tiles = 0, int nseq = 1) {
   const bool lut = kind_info(kind).lut;
-  const size_t s_cap = lut ? 12 : 48;  // 48 KiB of tables / activations per CTA
-  const size_t slots = size_t(sm_count) * ctas_per_sm(kind);
-  const double prologue_per_block = lut ? 1.0 : 0.5, fixed = 1.5, split_cost = 2.5;
+  // 48 KiB of tables / activations per CTA (96 KiB when 4 or 8 sequences share a pass)
+  const size_t s_cap = lut ? 12 : nseq == 1 ? 48 : nseq == 8 ? 12 : 24;
+  const size_t slots = size_t(sm_count) * (nseq == 8 ? 1 : ctas_per_sm(kind));
+  const double prologue_per_block = (lut ? 1.0 : 0.5) * nseq, fixed = 1.5, split_cost = 2.5;
   Plan best{};
   double best_cost = 1e30;
   for (int R = 8; R >= 1; R >>= 1) {
@@ -749,11 +875,19 @@ Plan make_plan(int kind, size_t row_tiles, size_t bpr, size_t batch, int sm_coun
   return best;
 }
 
+// Sequences that share one pass over the weights (template parameter NSEQ of k_gemv).
+int seqs_per_pass(int kind, size_t batch) {
+  if (!kind_is_mma(kind) || batch <= 1) return 1;
+  return batch == 2 ? 2 : batch <= 4 ? 4 : 8;
+}
+
 // Plans every job of a launch and fills the job descriptors (scratch regions are carved out of
 // the context's scratch buffer, which is grown here when the stream is not capturing).
 int prepare_jobs(lmb_ctx *ctx, int kind, const LinearArgs *args, int njobs, Job *jobs, int *ctas_out, int *s_max_out,
                  std::vector<int2> *cta_map) {
   const size_t batch = args[0].batch;
+  const int nseq = seqs_per_pass(kind, batch);
+  const size_t ny = (batch + size_t(nseq) - 1) / size_t(nseq);  // grid.y
   std::vector<Plan> plans(static_cast<size_t>(njobs));
   size_t scratch_need = 0, counter_need = 0;
   size_t total_rt = 0;
@@ -761,10 +895,10 @@ int prepare_jobs(lmb_ctx *ctx, int kind, const LinearArgs *args, int njobs, Job 
   for (int j = 0; j < njobs; ++j) {
     const lmb_weight *w = args[j].w;
     const size_t others = total_rt - w->row_tiles;
-    plans[size_t(j)] = make_plan(kind, w->row_tiles, w->bpr, batch, ctx->sm_count, others);
+    plans[size_t(j)] = make_plan(kind, w->row_tiles, w->bpr, ny, ctx->sm_count, others, nseq);
     if (plans[size_t(j)].n_ks > 1) {
       scratch_need += batch * plans[size_t(j)].n_ks * w->row_tiles * TILE_ROWS;
-      counter_need += batch * plans[size_t(j)].n_rg;
+      counter_need += ny * plans[size_t(j)].n_rg;
     }
   }
   if (scratch_need > ctx->scratch_floats || counter_need > ctx->n_counters) {
@@ -805,7 +939,7 @@ int prepare_jobs(lmb_ctx *ctx, int kind, const LinearArgs *args, int njobs, Job 
     jb.counters = ctx->counters + counter_off;
     if (pl.n_ks > 1) {
       scratch_off += batch * pl.n_ks * jb.mp;
-      counter_off += batch * pl.n_rg;
+      counter_off += ny * pl.n_rg;
     }
     if (cta_map)
       for (int c = 0; c < pl.ctas; ++c) cta_map->push_back(make_int2(j, ctas));
@@ -818,51 +952,71 @@ int prepare_jobs(lmb_ctx *ctx, int kind, const LinearArgs *args, int njobs, Job 
   return LMB_OK;
 }
 
-template <int KIND> int launch_params(lmb_ctx *ctx, const GemvParams &p, int ctas, int s_max, size_t batch) {
+template <int KIND, int NSEQ> int launch_params(lmb_ctx *ctx, GemvParams &p, int ctas, int s_max, size_t batch) {
+  p.batch = int(batch);
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(unsigned(ctas), unsigned(batch));
+  cfg.gridDim = dim3(unsigned(ctas), unsigned((batch + NSEQ - 1) / NSEQ));
   cfg.blockDim = dim3(THREADS);
-  cfg.dynamicSmemBytes = size_t(s_max) * Unit<KIND>::FPB * sizeof(float);
+  cfg.dynamicSmemBytes = size_t(s_max) * Unit<KIND>::FPB * sizeof(float) * NSEQ;
   cfg.stream = ctx->stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = ctx->pdl ? 1 : 0;
-  LMB_CUDA(cudaLaunchKernelEx(&cfg, k_gemv<KIND>, p));
+  LMB_CUDA(cudaLaunchKernelEx(&cfg, k_gemv<KIND, NSEQ>, p));
   ctx->launches++;
   return LMB_OK;
 }
 
-int launch_params_kind(lmb_ctx *ctx, int kind, const GemvParams &p, int ctas, int s_max, size_t batch) {
+template <int KIND> int launch_params_mma(lmb_ctx *ctx, GemvParams &p, int ctas, int s_max, size_t batch) {
+  switch (seqs_per_pass(KIND, batch)) {
+  case 1: return launch_params<KIND, 1>(ctx, p, ctas, s_max, batch);
+  case 2: return launch_params<KIND, 2>(ctx, p, ctas, s_max, batch);
+  case 4: return launch_params<KIND, 4>(ctx, p, ctas, s_max, batch);
+  default: return launch_params<KIND, 8>(ctx, p, ctas, s_max, batch);
+  }
+}
+
+int launch_params_kind(lmb_ctx *ctx, int kind, GemvParams &p, int ctas, int s_max, size_t batch) {
   switch (kind) {
-  case LMB_TERNARY: return launch_params<LMB_TERNARY>(ctx, p, ctas, s_max, batch);
-  case LMB_BINARY: return launch_params<LMB_BINARY>(ctx, p, ctas, s_max, batch);
-  case LMB_INT2: return launch_params<LMB_INT2>(ctx, p, ctas, s_max, batch);
-  case LMB_INT3: return launch_params<LMB_INT3>(ctx, p, ctas, s_max, batch);
-  case LMB_INT4: return launch_params<LMB_INT4>(ctx, p, ctas, s_max, batch);
-  case LMB_INT8: return launch_params<LMB_INT8>(ctx, p, ctas, s_max, batch);
-  case DK_TERNARY_MMA: return launch_params<DK_TERNARY_MMA>(ctx, p, ctas, s_max, batch);
-  case DK_INT2_MMA: return launch_params<DK_INT2_MMA>(ctx, p, ctas, s_max, batch);
-  case DK_BINARY_MMA: return launch_params<DK_BINARY_MMA>(ctx, p, ctas, s_max, batch);
+  case LMB_TERNARY: return launch_params<LMB_TERNARY, 1>(ctx, p, ctas, s_max, batch);
+  case LMB_BINARY: return launch_params<LMB_BINARY, 1>(ctx, p, ctas, s_max, batch);
+  case LMB_INT2: return launch_params<LMB_INT2, 1>(ctx, p, ctas, s_max, batch);
+  case LMB_INT3: return launch_params<LMB_INT3, 1>(ctx, p, ctas, s_max, batch);
+  case LMB_INT8: return launch_params<LMB_INT8, 1>(ctx, p, ctas, s_max, batch);
+  case LMB_INT4: return launch_params_mma<LMB_INT4>(ctx, p, ctas, s_max, batch);
+  case DK_TERNARY_MMA: return launch_params_mma<DK_TERNARY_MMA>(ctx, p, ctas, s_max, batch);
+  case DK_INT2_MMA: return launch_params_mma<DK_INT2_MMA>(ctx, p, ctas, s_max, batch);
+  case DK_BINARY_MMA: return launch_params_mma<DK_BINARY_MMA>(ctx, p, ctas, s_max, batch);
   default: set_last_error("launch_gemv: kind has no device kernel"); return LMB_ERR_ARG;
   }
 }
 
 }  // namespace
 
-int configure_gemv(lmb_ctx *ctx) {
-  const int bytes = 64 * 1024;
-  LMB_CUDA(cudaFuncSetAttribute(k_gemv<LMB_TERNARY>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-  LMB_CUDA(cudaFuncSetAttribute(k_gemv<LMB_BINARY>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-  LMB_CUDA(cudaFuncSetAttribute(k_gemv<LMB_INT2>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-  LMB_CUDA(cudaFuncSetAttribute(k_gemv<LMB_INT3>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-  LMB_CUDA(cudaFuncSetAttribute(k_gemv<LMB_INT4>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-  LMB_CUDA(cudaFuncSetAttribute(k_gemv<LMB_INT8>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-  LMB_CUDA(cudaFuncSetAttribute(k_gemv<DK_TERNARY_MMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-  LMB_CUDA(cudaFuncSetAttribute(k_gemv<DK_INT2_MMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-  LMB_CUDA(cudaFuncSetAttribute(k_gemv<DK_BINARY_MMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+template <int KIND> int configure_mma() {
+  const int small = 64 * 1024, large = 100 * 1024;
+  LMB_CUDA(cudaFuncSetAttribute(k_gemv<KIND, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, small));
+  LMB_CUDA(cudaFuncSetAttribute(k_gemv<KIND, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, small));
+  LMB_CUDA(cudaFuncSetAttribute(k_gemv<KIND, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, large));
+  LMB_CUDA(cudaFuncSetAttribute(k_gemv<KIND, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, large));
   return LMB_OK;
+}
+
+int configure_gemv(lmb_ctx *ctx) {
+  (void)ctx;
+  const int bytes = 64 * 1024;
+  LMB_CUDA(cudaFuncSetAttribute(k_gemv<LMB_TERNARY, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  LMB_CUDA(cudaFuncSetAttribute(k_gemv<LMB_BINARY, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  LMB_CUDA(cudaFuncSetAttribute(k_gemv<LMB_INT2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  LMB_CUDA(cudaFuncSetAttribute(k_gemv<LMB_INT3, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  LMB_CUDA(cudaFuncSetAttribute(k_gemv<LMB_INT8, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  int st = configure_mma<LMB_INT4>();
+  if (st == LMB_OK) st = configure_mma<DK_TERNARY_MMA>();
+  if (st == LMB_OK) st = configure_mma<DK_INT2_MMA>();
+  if (st == LMB_OK) st = configure_mma<DK_BINARY_MMA>();
+  return st;
 }
 
 // Up to MAX_JOBS independent GEMVs of one kind and one batch size in a single launch.

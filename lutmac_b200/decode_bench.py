@@ -18,11 +18,13 @@ def run_decode(ctx, shape_name: str, kind: int, ctx_len: int, batch: int = 1, st
     m = Model(spec, ctx, max_batch=batch, tp_rank=tp_rank, tp_size=tp_size)
     rng = np.random.default_rng(seed + 1)
     vocab = spec.cfg["vocab"]
-    if random_kv and batch == 1 and tp_size == 1:
+    if random_kv and tp_size == 1:
         # a cache of random keys and values instead of ctx_len prefill steps (profiling runs)
         c = spec.cfg
         n = c["n_layers"] * 2 * c["max_seq"] * c["n_kv_heads"] * c["head_dim"]
-        m.kv_import((rng.standard_normal(n) * 0.1).astype(np.float32))
+        kv = (rng.standard_normal(n) * 0.1).astype(np.float32)
+        for b in range(batch):
+            m.kv_import(kv, seq=b)
     else:
         for p in range(ctx_len):  # prefill by decode, like the reference (src/inference.cpp:275-278)
             m.forward(rng.integers(0, vocab, size=batch), [p] * batch, fetch=False)

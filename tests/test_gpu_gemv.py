@@ -249,6 +249,23 @@ def test_both_device_layouts(ctx, ctx_lut, oracle, which, kind, qbits):
     w.free()
 
 
+@pytest.mark.parametrize("kind,qbits", [(INT4, 4), (TERNARY, 2), (INT2, 2), (BINARY, 1), (INT8, 8)])
+def test_batched_sequences_share_the_weight_pass(ctx, oracle, kind, qbits):
+    """Batches of 2, 4 and 8 sequences are evaluated in one pass over the weights on the
+    integer tensor-core kernels (two sequences per MMA); every batch size, odd ones included,
+    must give each sequence the result it gets alone.  Split K and bias included."""
+    rng = np.random.default_rng(5)
+    for (M, K) in [(96, 768), (40, 300), (256, 6144), (2048, 2048)]:
+        t = synth.tensor(rng, kind, M, K)
+        bias = rng.standard_normal(M).astype(np.float32)
+        for batch in (2, 3, 4, 5, 8, 9, 17):
+            x = np.concatenate([synth.activations(rng, K) * (10.0 ** (i % 3 - 1)) for i in range(batch)])
+            y = run_linear(ctx, t, x, bias=bias, batch=batch, flags=_lib.AUTO_ROTATE)
+            want = oracle.lut_linear(kind, qbits, t.blocks, M, K, bias, x, batch)
+            for b in range(batch):
+                assert rel_l2(y[b], want[b]) < TOL, (KIND_NAMES[kind], M, K, batch, b)
+
+
 def test_extreme_activation_ranges(ctx, oracle):
     """The integer tensor-core kernels quantise x per 256-block with a shared exponent: blocks
     of very different magnitude, tiny values, and an all-zero block must still match."""
