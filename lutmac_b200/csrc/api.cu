@@ -346,7 +346,6 @@ int lmb_weight_upload_shard(lmb_ctx *ctx, int kind, const void *blocks, size_t M
                             size_t row1, size_t blk0, size_t blk1, lmb_weight **out) {
   LMB_REQUIRE(ctx && blocks && out, "lmb_weight_upload: null argument");
   LMB_REQUIRE(kind_valid(kind), "lmb_weight_upload: unknown block kind");
-  LMB_REQUIRE(kind != LMB_INT5 && kind != LMB_INT6, "lmb_weight_upload: 5/6-bit kinds have no device kernel yet");
   const size_t src_bpr = (K + BLK - 1) / BLK;
   LMB_REQUIRE(M > 0 && K > 0, "lmb_weight_upload: empty shape");
   LMB_REQUIRE(row0 < row1 && row1 <= M && blk0 < blk1 && blk1 <= src_bpr, "lmb_weight_upload: bad shard range");
@@ -360,6 +359,7 @@ int lmb_weight_upload_shard(lmb_ctx *ctx, int kind, const void *blocks, size_t M
     if (kind == LMB_TERNARY) w->kind = DK_TERNARY_MMA;
     if (kind == LMB_INT2) w->kind = DK_INT2_MMA;
     if (kind == LMB_BINARY) w->kind = DK_BINARY_MMA;
+    if (kind == LMB_INT8) w->kind = DK_INT8_MMA;
   }
   w->device = ctx->device;
   w->M = row1 - row0;

@@ -43,14 +43,18 @@ constexpr int SM_COUNT_HINT = 148;
 //            {WA(2q), WB(2q), WA(2q+1), WB(2q+1)}; byte j of WA(s) is column 32s+4tid+j, of WB(s)
 //            column 32s+16+4tid+j; the low nibble is row 16h+g, the high nibble row 16h+g+8.
 //            Scales: float 4g+m = scale of row g+8m.
-//   INT5     10 chunks; 0..7 = low nibbles packed like INT4, 8..9 = bit-4 plane.
-//   INT6     12 chunks; 0..7 = low nibbles, 8..9 = bit-4 plane, 10..11 = bit-5 plane.
+//   INT5     10 chunks; 0..7 = low nibbles of the 5-bit codes in the INT4 arrangement, 8..9 = the
+//            bit-4 plane in the DK_BINARY_MMA arrangement.
+//   INT6     12 chunks; as INT5 plus 10..11 = the bit-5 plane.
 //   INT8     16 chunks; chunk c = data[16c..16c+15] unchanged.
 //   DK_TERNARY_MMA  4 chunks of 2-bit codes t+1 in MMA operand order: chunk q of lane (g, tid) =
 //            {WA(2q), WB(2q), WA(2q+1), WB(2q+1)} with the same columns per byte as INT4; the
 //            2-bit field m (bits 2m, 2m+1) of every byte is row g+8m.  Scales as for INT4.
 //   DK_INT2_MMA  the DK_TERNARY_MMA arrangement with the field holding b1 (bit 2m) and b2
 //            (bit 2m+1) of the residual-binary pair; scales [plane][4g+m].
+//   DK_INT8_MMA  16 chunks: chunk 8h+s of lane (g, tid) = the four A-operand registers of k-step s
+//            for rows 16h+g / 16h+g+8: {row g: columns 32s+4tid..+3, row g+8: the same, row g:
+//            columns 32s+16+4tid..+3, row g+8: the same}.
 //   DK_BINARY_MMA  2 chunks: words W(sp, ab), sp < 4, ab < 2, word index 2sp+ab; byte j, bit
 //            m+4kh of W(sp, ab) is row g+8m, column 32(2sp+kh) + 16ab + 4tid + j.
 // ---------------------------------------------------------------------------------------------
@@ -61,9 +65,12 @@ constexpr int DK_TERNARY_MMA = 16;
 // The same for INT2 (residual binary) and BINARY blocks.
 constexpr int DK_INT2_MMA = 17;
 constexpr int DK_BINARY_MMA = 18;
+// INT8 blocks in the operand order of the signed 8-bit MMA (the tile's words are the operands).
+constexpr int DK_INT8_MMA = 19;
 
 __host__ __device__ constexpr bool kind_is_mma(int kind) {
-  return kind == LMB_INT4 || kind == DK_TERNARY_MMA || kind == DK_INT2_MMA || kind == DK_BINARY_MMA;
+  return kind == LMB_INT4 || kind == LMB_INT5 || kind == LMB_INT6 || kind == DK_TERNARY_MMA || kind == DK_INT2_MMA ||
+         kind == DK_BINARY_MMA || kind == DK_INT8_MMA;
 }
 
 struct KindInfo {
@@ -85,6 +92,7 @@ __host__ __device__ constexpr KindInfo kind_info(int kind) {
        : kind == DK_TERNARY_MMA ? KindInfo{68, 4, 1, false}
        : kind == DK_INT2_MMA ? KindInfo{72, 4, 2, false}
        : kind == DK_BINARY_MMA ? KindInfo{36, 2, 1, false}
+       : kind == DK_INT8_MMA ? KindInfo{260, 16, 1, false}
                              : KindInfo{0, 0, 0, false};
 }
 

@@ -19,12 +19,24 @@ __device__ float tile_elem(int kind, const uint8_t *tiles, size_t bpr, size_t ro
   const unsigned bit = 7u - unsigned(j % 8);
   switch (kind) {
   case LMB_INT8: return float(int8_t(pay(j / 16, j % 16))) * s0;
-  case LMB_INT4: {  // MMA operand order, see common.cuh
-    const size_t h = l / 16, g = l % 8, s = j / 32, kk = j % 32, tid = (kk % 16) / 4;
+  case LMB_INT4:
+  case LMB_INT5:
+  case LMB_INT6: {  // MMA operand order, see common.cuh
+    const size_t h = l / 16, g = l % 8, m = l / 8, s = j / 32, kk = j % 32, tid = (kk % 16) / 4;
     const size_t lane = g * 4 + tid, chunk = h * 4 + s / 2, word = (s % 2) * 2 + kk / 16;
     const uint8_t byte = tile[(chunk * TILE_ROWS + lane) * 16 + word * 4 + kk % 4];
-    const int nib = ((l % 16) >= 8) ? (byte >> 4) : (byte & 15);
-    return float(nib - 8) * sc[4 * g + l / 8];
+    int code = ((l % 16) >= 8) ? (byte >> 4) : (byte & 15);
+    for (int pl = 0; pl < kind - 4; ++pl) {  // bit planes 4 (and 5) in the binary arrangement
+      const size_t wi = (s / 2) * 2 + kk / 16;
+      const uint8_t pb = tile[4096 + 1024 * pl + ((wi / 4) * TILE_ROWS + lane) * 16 + (wi % 4) * 4 + kk % 4];
+      code |= int((pb >> (m + 4 * (s % 2))) & 1u) << (4 + pl);
+    }
+    return float(code - (8 << (kind - 4))) * sc[4 * g + m];
+  }
+  case DK_INT8_MMA: {
+    const size_t h = l / 16, g = l % 8, s = j / 32, kk = j % 32, tid = (kk % 16) / 4;
+    const size_t a = 2 * (kk / 16) + (l % 16) / 8;
+    return float(int8_t(tile[((h * 8 + s) * TILE_ROWS + g * 4 + tid) * 16 + a * 4 + kk % 4])) * sc[4 * g + l / 8];
   }
   case DK_TERNARY_MMA: {  // 2-bit codes t+1 in MMA operand order, see common.cuh
     const size_t m = l / 8, g = l % 8, s = j / 32, kk = j % 32, tid = (kk % 16) / 4;

@@ -242,6 +242,14 @@ __device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, 
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+__device__ __forceinline__ void mma_s8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
 __device__ __forceinline__ void mma_prologue(const float (&v)[8], int lane, float *blk, float *bscale, int *aux2);
 
 // Where a warp finds the prepared activations of its sequences (see the kernel's prologue).
@@ -550,6 +558,119 @@ template <> struct Unit<DK_BINARY_MMA> : MmaUnitBase<Unit<DK_BINARY_MMA>, 2> {
   }
 };
 
+// 5- and 6-bit codes: the low nibbles on the INT4 arrangement plus one +-0/1 bit plane per extra
+// bit on the DK_BINARY_MMA arrangement; the partial sums are put back on a common scale by exact
+// shifts and the zero point (16 / 32) is removed with the digit sums.
+template <int BITS> struct WideUnit : MmaUnitBase<Unit<BITS>, 1> {
+  static constexpr int NPL = BITS - 4;
+  using Acc = MmaAcc;
+  uint4 v[8 + 2 * NPL];
+  float4 sc;
+  template <int N> struct Sums {
+    int n[N][2][4];            // nibbles, [row half]
+    int pl[N][NPL][2][2][4];   // planes, [plane][row half][kh]
+  };
+  __device__ __forceinline__ void load(const uint8_t *tile, int lane) {
+#pragma unroll
+    for (int c = 0; c < 8 + 2 * NPL; ++c) v[c] = ld_stream_v4(tile + (size_t(c) * TILE_ROWS + lane) * 16);
+    sc = as_float4(ld_stream_v4(tile + size_t(8 + 2 * NPL) * TILE_ROWS * 16 + size_t(lane >> 2) * 16));
+  }
+  template <int N> __device__ __forceinline__ void mma_block(const uint4 *dig, int ps, Sums<N> &s) const {
+    constexpr uint32_t LO = 0x0F0F0F0Fu, HI = 0xF0F0F0F0u, M1 = 0x01010101u;
+#pragma unroll
+    for (int p = 0; p < N; ++p)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        s.n[p][h][0] = s.n[p][h][1] = s.n[p][h][2] = s.n[p][h][3] = 0;
+#pragma unroll
+        for (int pl = 0; pl < NPL; ++pl)
+#pragma unroll
+          for (int kh = 0; kh < 2; ++kh) s.pl[p][pl][h][kh][0] = s.pl[p][pl][h][kh][1] = s.pl[p][pl][h][kh][2] = s.pl[p][pl][h][kh][3] = 0;
+      }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      uint4 b[N];  // {k-step 2q: b0, b1; k-step 2q+1: b0, b1}
+#pragma unroll
+      for (int p = 0; p < N; ++p) b[p] = dig[q * 16 + p * ps];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const uint4 w = v[h * 4 + q];
+#pragma unroll
+        for (int p = 0; p < N; ++p) {
+          mma_u8s8(s.n[p][h], w.x & LO, w.x & HI, w.y & LO, w.y & HI, b[p].x, b[p].y);
+          mma_u8s8(s.n[p][h], w.z & LO, w.z & HI, w.w & LO, w.w & HI, b[p].z, b[p].w);
+        }
+#pragma unroll
+        for (int pl = 0; pl < NPL; ++pl) {
+          const uint4 pv = v[8 + 2 * pl + (q >> 1)];
+          const uint32_t wa = (q & 1) ? pv.z : pv.x, wb = (q & 1) ? pv.w : pv.y;
+          const int s0 = 2 * h, s1 = 2 * h + 4;
+#pragma unroll
+          for (int p = 0; p < N; ++p) {
+            mma_u8s8(s.pl[p][pl][h][0], wa & (M1 << s0), wa & (M1 << (s0 + 1)), wb & (M1 << s0), wb & (M1 << (s0 + 1)), b[p].x, b[p].y);
+            mma_u8s8(s.pl[p][pl][h][1], wa & (M1 << s1), wa & (M1 << (s1 + 1)), wb & (M1 << s1), wb & (M1 << (s1 + 1)), b[p].z, b[p].w);
+          }
+        }
+      }
+    }
+  }
+  template <int N> __device__ __forceinline__ void finish(const Sums<N> &s, int p, uint32_t d, float bs, Acc &acc) const {
+    const float sv[4] = {sc.x, sc.y, sc.z, sc.w};
+#pragma unroll
+    for (int m = 0; m < 4; ++m) {
+      const int h = m >> 1, j = m & 1;
+      int i0 = s.n[p][h][2 * j] >> (4 * j), i1 = s.n[p][h][2 * j + 1] >> (4 * j);  // exact: multiples of 16 in the high-nibble rows
+#pragma unroll
+      for (int pl = 0; pl < NPL; ++pl) {
+        i0 += ((s.pl[p][pl][h][0][2 * j] + (s.pl[p][pl][h][1][2 * j] >> 4)) >> m) << (4 + pl);
+        i1 += ((s.pl[p][pl][h][0][2 * j + 1] + (s.pl[p][pl][h][1][2 * j + 1] >> 4)) >> m) << (4 + pl);
+      }
+      acc.r[m] += mma_row_value(i0, i1, d << (BITS - 1)) * (bs * sv[m]);  // zero point 2^(BITS-1)
+    }
+  }
+};
+template <> struct Unit<LMB_INT5> : WideUnit<5> {};
+template <> struct Unit<LMB_INT6> : WideUnit<6> {};
+
+// 8-bit weights on the signed 8-bit MMA: the tile's words are the A operands as they are.
+template <> struct Unit<DK_INT8_MMA> : MmaUnitBase<Unit<DK_INT8_MMA>, 2> {
+  uint4 v[16];
+  float4 sc;
+  template <int N> struct Sums { int c[N][2][4]; };
+  __device__ __forceinline__ void load(const uint8_t *tile, int lane) {
+#pragma unroll
+    for (int c = 0; c < 16; ++c) v[c] = ld_stream_v4(tile + (size_t(c) * TILE_ROWS + lane) * 16);
+    sc = as_float4(ld_stream_v4(tile + size_t(16) * TILE_ROWS * 16 + size_t(lane >> 2) * 16));
+  }
+  template <int N> __device__ __forceinline__ void mma_block(const uint4 *dig, int ps, Sums<N> &s) const {
+#pragma unroll
+    for (int p = 0; p < N; ++p)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) s.c[p][h][0] = s.c[p][h][1] = s.c[p][h][2] = s.c[p][h][3] = 0;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      uint4 b[N];
+#pragma unroll
+      for (int p = 0; p < N; ++p) b[p] = dig[q * 16 + p * ps];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const uint4 w0 = v[h * 8 + 2 * q], w1 = v[h * 8 + 2 * q + 1];
+#pragma unroll
+        for (int p = 0; p < N; ++p) {
+          mma_s8s8(s.c[p][h], w0.x, w0.y, w0.z, w0.w, b[p].x, b[p].y);
+          mma_s8s8(s.c[p][h], w1.x, w1.y, w1.z, w1.w, b[p].z, b[p].w);
+        }
+      }
+    }
+  }
+  template <int N> __device__ __forceinline__ void finish(const Sums<N> &s, int p, uint32_t, float bs, Acc &acc) const {
+    acc.r[0] += mma_row_value(s.c[p][0][0], s.c[p][0][1], 0u) * (bs * sc.x);
+    acc.r[1] += mma_row_value(s.c[p][0][2], s.c[p][0][3], 0u) * (bs * sc.y);
+    acc.r[2] += mma_row_value(s.c[p][1][0], s.c[p][1][1], 0u) * (bs * sc.z);
+    acc.r[3] += mma_row_value(s.c[p][1][2], s.c[p][1][3], 0u) * (bs * sc.w);
+  }
+};
+
 template <> struct Unit<LMB_INT8> {
   static constexpr int FPB = 256;
   uint4 v[16];
@@ -585,12 +706,23 @@ template <> struct Unit<LMB_INT8> {
 // Row-blocks a warp keeps in flight (in registers) besides the one it evaluates: small units
 // need more of them to cover the HBM latency with the two or three CTAs an SM holds.
 __host__ __device__ constexpr int prefetch_depth(int kind) {
-  return kind == DK_TERNARY_MMA ? 3 : kind == DK_INT2_MMA ? 2 : kind == DK_BINARY_MMA ? 5 : kind == LMB_TERNARY ? 2 : kind == LMB_INT2 ? 2 : kind == LMB_BINARY ? 3
+  return kind == DK_TERNARY_MMA ? 3 : kind == DK_INT2_MMA ? 2 : kind == DK_BINARY_MMA ? 5 : kind == LMB_TERNARY ? 2
+       : (kind == LMB_INT5 || kind == LMB_INT6 || kind == DK_INT8_MMA) ? 0 : kind == LMB_INT2 ? 2 : kind == LMB_BINARY ? 3
        : kind == LMB_INT8 ? 0 : 1;
 }
 
+// Resident CTAs per SM the kernel is compiled for (128 or 255 registers per thread).
+__host__ __device__ constexpr bool kind_is_wide(int kind) { return kind == LMB_INT5 || kind == LMB_INT6 || kind == DK_INT8_MMA; }
+__host__ __device__ constexpr int min_ctas(int kind, int nseq) {
+  return (kind == LMB_INT8 || nseq == 8 || (nseq == 4 && kind_is_wide(kind))) ? 1 : 2;
+}
+// Most sequences one pass over the weights serves.
+__host__ __device__ constexpr int max_seqs_per_pass(int kind) {
+  return !kind_is_mma(kind) ? 1 : (kind == LMB_INT5 || kind == LMB_INT6) ? 2 : 8;
+}
+
 template <int KIND, int NSEQ>
-__global__ void __launch_bounds__(THREADS, (KIND == LMB_INT8 || NSEQ == 8) ? 1 : 2) k_gemv(const __grid_constant__ GemvParams p) {
+__global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __grid_constant__ GemvParams p) {
   // NSEQ sequences share one pass over the weights (integer-MMA kinds only: two sequences per
   // MMA); the other kinds run one sequence per CTA, blockIdx.y selecting it.
   static_assert(NSEQ == 1 || kind_is_mma(KIND), "several sequences per pass need an integer-MMA kind");
@@ -841,7 +973,7 @@ Plan make_plan(int kind, size_t row_tiles, size_t bpr, size_t batch, int sm_coun
   const bool lut = kind_info(kind).lut;
   // 48 KiB of tables / activations per CTA (96 KiB when 4 or 8 sequences share a pass)
   const size_t s_cap = lut ? 12 : nseq == 1 ? 48 : nseq == 8 ? 12 : 24;
-  const size_t slots = size_t(sm_count) * (nseq == 8 ? 1 : ctas_per_sm(kind));
+  const size_t slots = size_t(sm_count) * (min_ctas(kind, nseq) == 1 ? 1 : ctas_per_sm(kind));
   const double prologue_per_block = (lut ? 1.0 : 0.5) * nseq, fixed = 1.5, split_cost = 2.5;
   Plan best{};
   double best_cost = 1e30;
@@ -878,7 +1010,8 @@ Plan make_plan(int kind, size_t row_tiles, size_t bpr, size_t batch, int sm_coun
 // Sequences that share one pass over the weights (template parameter NSEQ of k_gemv).
 int seqs_per_pass(int kind, size_t batch) {
   if (!kind_is_mma(kind) || batch <= 1) return 1;
-  return batch == 2 ? 2 : batch <= 4 ? 4 : 8;
+  const int n = batch == 2 ? 2 : batch <= 4 ? 4 : 8;
+  return n < max_seqs_per_pass(kind) ? n : max_seqs_per_pass(kind);
 }
 
 // Plans every job of a launch and fills the job descriptors (scratch regions are carved out of
@@ -973,8 +1106,12 @@ template <int KIND> int launch_params_mma(lmb_ctx *ctx, GemvParams &p, int ctas,
   switch (seqs_per_pass(KIND, batch)) {
   case 1: return launch_params<KIND, 1>(ctx, p, ctas, s_max, batch);
   case 2: return launch_params<KIND, 2>(ctx, p, ctas, s_max, batch);
-  case 4: return launch_params<KIND, 4>(ctx, p, ctas, s_max, batch);
-  default: return launch_params<KIND, 8>(ctx, p, ctas, s_max, batch);
+  case 4:
+    if constexpr (max_seqs_per_pass(KIND) >= 4) return launch_params<KIND, 4>(ctx, p, ctas, s_max, batch);
+    return LMB_ERR_STATE;
+  default:
+    if constexpr (max_seqs_per_pass(KIND) >= 8) return launch_params<KIND, 8>(ctx, p, ctas, s_max, batch);
+    return LMB_ERR_STATE;
   }
 }
 
@@ -989,6 +1126,9 @@ int launch_params_kind(lmb_ctx *ctx, int kind, GemvParams &p, int ctas, int s_ma
   case DK_TERNARY_MMA: return launch_params_mma<DK_TERNARY_MMA>(ctx, p, ctas, s_max, batch);
   case DK_INT2_MMA: return launch_params_mma<DK_INT2_MMA>(ctx, p, ctas, s_max, batch);
   case DK_BINARY_MMA: return launch_params_mma<DK_BINARY_MMA>(ctx, p, ctas, s_max, batch);
+  case LMB_INT5: return launch_params_mma<LMB_INT5>(ctx, p, ctas, s_max, batch);
+  case LMB_INT6: return launch_params_mma<LMB_INT6>(ctx, p, ctas, s_max, batch);
+  case DK_INT8_MMA: return launch_params_mma<DK_INT8_MMA>(ctx, p, ctas, s_max, batch);
   default: set_last_error("launch_gemv: kind has no device kernel"); return LMB_ERR_ARG;
   }
 }
@@ -999,8 +1139,10 @@ template <int KIND> int configure_mma() {
   const int small = 64 * 1024, large = 100 * 1024;
   LMB_CUDA(cudaFuncSetAttribute(k_gemv<KIND, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, small));
   LMB_CUDA(cudaFuncSetAttribute(k_gemv<KIND, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, small));
-  LMB_CUDA(cudaFuncSetAttribute(k_gemv<KIND, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, large));
-  LMB_CUDA(cudaFuncSetAttribute(k_gemv<KIND, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, large));
+  if constexpr (max_seqs_per_pass(KIND) >= 4)
+    LMB_CUDA(cudaFuncSetAttribute(k_gemv<KIND, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, large));
+  if constexpr (max_seqs_per_pass(KIND) >= 8)
+    LMB_CUDA(cudaFuncSetAttribute(k_gemv<KIND, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, large));
   return LMB_OK;
 }
 
@@ -1016,6 +1158,9 @@ int configure_gemv(lmb_ctx *ctx) {
   if (st == LMB_OK) st = configure_mma<DK_TERNARY_MMA>();
   if (st == LMB_OK) st = configure_mma<DK_INT2_MMA>();
   if (st == LMB_OK) st = configure_mma<DK_BINARY_MMA>();
+  if (st == LMB_OK) st = configure_mma<LMB_INT5>();
+  if (st == LMB_OK) st = configure_mma<LMB_INT6>();
+  if (st == LMB_OK) st = configure_mma<DK_INT8_MMA>();
   return st;
 }
 

@@ -122,6 +122,7 @@ void block_to_lane(int kind, const uint8_t *blk, uint8_t *pay, float *sc) {
     break;
   }
   case LMB_INT8:
+  case DK_INT8_MMA:  // row-major bytes; permuted per tile later
     std::memcpy(sc, blk, 4);
     std::memcpy(pay, blk + 4, 256);
     break;
@@ -208,6 +209,7 @@ void lane_to_block(int kind, const uint8_t *pay, const float *sc, uint8_t *blk) 
     break;
   }
   case LMB_INT8:
+  case DK_INT8_MMA:
     std::memcpy(blk, sc, 4);
     std::memcpy(blk + 4, pay, 256);
     break;
@@ -330,6 +332,25 @@ void bin_from_fragments(uint8_t *payload) {
   });
 }
 
+// fn(index of the byte in the tile, row, column)
+template <class Fn> inline void int8_fragment_walk(Fn &&fn) {
+  for (size_t h = 0; h < 2; ++h)
+    for (size_t st = 0; st < 8; ++st)
+      for (size_t g = 0; g < 8; ++g)
+        for (size_t tid = 0; tid < 4; ++tid)
+          for (size_t a = 0; a < 4; ++a)
+            for (size_t j = 0; j < 4; ++j)
+              fn(((h * 8 + st) * 32 + g * 4 + tid) * 16 + a * 4 + j, 16 * h + g + 8 * (a % 2), 32 * st + 16 * (a / 2) + 4 * tid + j);
+}
+void int8_to_fragments(uint8_t *payload) {  // 8192 bytes, in place
+  std::vector<uint8_t> src(payload, payload + 8192);
+  int8_fragment_walk([&](size_t idx, size_t row, size_t col) { payload[idx] = src[(col / 16) * 512 + row * 16 + col % 16]; });
+}
+void int8_from_fragments(uint8_t *payload) {
+  std::vector<uint8_t> src(payload, payload + 8192);
+  int8_fragment_walk([&](size_t idx, size_t row, size_t col) { payload[(col / 16) * 512 + row * 16 + col % 16] = src[idx]; });
+}
+
 // scale of row l of a tile: index into the tile's scale array
 inline size_t scale_slot(int kind, size_t l) { return kind_is_mma(kind) ? 4 * (l % 8) + l / 8 : l; }
 
@@ -373,7 +394,10 @@ void retile(int kind, const uint8_t *blocks, size_t src_bpr, size_t row0, size_t
         float *ts = reinterpret_cast<float *>(tile + size_t(ki.chunks) * TILE_ROWS * 16);
         for (int s = 0; s < ki.nscales; ++s) ts[size_t(s) * TILE_ROWS + scale_slot(kind, l)] = sc[s];
       }
-      if (kind == LMB_INT4) int4_to_fragments(tile);
+      if (kind == LMB_INT4 || kind == LMB_INT5 || kind == LMB_INT6) int4_to_fragments(tile);
+      if (kind == LMB_INT5 || kind == LMB_INT6) bin_to_fragments(tile + 4096);
+      if (kind == LMB_INT6) bin_to_fragments(tile + 5120);
+      if (kind == DK_INT8_MMA) int8_to_fragments(tile);
       if (kind == DK_TERNARY_MMA || kind == DK_INT2_MMA) tern_to_fragments(tile);
       if (kind == DK_BINARY_MMA) bin_to_fragments(tile);
     }
@@ -388,10 +412,15 @@ void untile(int kind, const uint8_t *tiled, size_t M, size_t bpr, uint8_t *block
     float sc[2];
     for (size_t b = 0; b < bpr; ++b) {
       const uint8_t *tile = tiled + (rt * bpr + b) * tb;
-      uint8_t rowmajor[4096];
-      if (kind == LMB_INT4) {
-        std::memcpy(rowmajor, tile, 4096);
+      uint8_t rowmajor[8192];
+      if (kind == LMB_INT4 || kind == LMB_INT5 || kind == LMB_INT6) {
+        std::memcpy(rowmajor, tile, size_t(ki.chunks) * 512);
         int4_from_fragments(rowmajor);
+        if (kind != LMB_INT4) bin_from_fragments(rowmajor + 4096);
+        if (kind == LMB_INT6) bin_from_fragments(rowmajor + 5120);
+      } else if (kind == DK_INT8_MMA) {
+        std::memcpy(rowmajor, tile, 8192);
+        int8_from_fragments(rowmajor);
       } else if (kind == DK_TERNARY_MMA || kind == DK_INT2_MMA) {
         std::memcpy(rowmajor, tile, 2048);
         tern_from_fragments(rowmajor);

@@ -8,14 +8,14 @@ import numpy as np
 import pytest
 
 from lutmac_b200 import _lib, api, synth
-from lutmac_b200.blocks import (BINARY, BLOCK_DTYPES, INT2, INT3, INT4, INT8, KIND_NAMES, TERNARY, PackedTensor,
+from lutmac_b200.blocks import (BINARY, BLOCK_DTYPES, INT2, INT3, INT4, INT5, INT6, INT8, KIND_NAMES, TERNARY, PackedTensor,
                                 blocks_per_row)
 from tests.conftest import rel_l2
 
 pytestmark = pytest.mark.gpu
 
 TOL = 1e-5
-KINDS = (TERNARY, BINARY, INT2, INT3, INT4, INT8)
+KINDS = (TERNARY, BINARY, INT2, INT3, INT4, INT5, INT6, INT8)
 GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 GEMV_SHAPES = ((1, 4), (3, 256), (16, 256), (33, 300), (40, 768), (64, 2048))
 
@@ -249,7 +249,7 @@ def test_both_device_layouts(ctx, ctx_lut, oracle, which, kind, qbits):
     w.free()
 
 
-@pytest.mark.parametrize("kind,qbits", [(INT4, 4), (TERNARY, 2), (INT2, 2), (BINARY, 1), (INT8, 8)])
+@pytest.mark.parametrize("kind,qbits", [(INT4, 4), (TERNARY, 2), (INT2, 2), (BINARY, 1), (INT8, 8), (INT5, 5), (INT6, 6)])
 def test_batched_sequences_share_the_weight_pass(ctx, oracle, kind, qbits):
     """Batches of 2, 4 and 8 sequences are evaluated in one pass over the weights on the
     integer tensor-core kernels (two sequences per MMA); every batch size, odd ones included,
@@ -270,7 +270,7 @@ def test_extreme_activation_ranges(ctx, oracle):
     """The integer tensor-core kernels quantise x per 256-block with a shared exponent: blocks
     of very different magnitude, tiny values, and an all-zero block must still match."""
     rng = np.random.default_rng(31)
-    for kind in (INT4, TERNARY, INT2, BINARY):
+    for kind in (INT4, TERNARY, INT2, BINARY, INT5, INT6, INT8):
         t = synth.tensor(rng, kind, 96, 1024)
         x = synth.activations(rng, 1024)
         x[:256] *= 1e-20
