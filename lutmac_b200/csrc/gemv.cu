@@ -257,8 +257,7 @@ struct MmaX {
   const float *dig;  // digits of block 0 of the first sequence, [seq][block][FPB]
   const float *bs;   // block scales, [seq][64]
   const int *aux;    // digit-pair sums, [pair][64][4] = {seq 2p: d01, d23; seq 2p+1: d01, d23}
-  int seq_stride;    // floats between the digits of consecutive sequences; 0: one sequence only
-  int bs_stride;     // 64, or 0 with one sequence
+  int seq_stride;    // floats between the digits of consecutive sequences
 };
 
 // Shared by the integer-MMA units.  The activations of a block are 32-bit fixed point with one
@@ -306,10 +305,12 @@ template <class Derived, int PG_> struct MmaUnitBase {
   static __device__ __forceinline__ void prologue(const float (&v)[8], int lane, float *blk, float *bscale, int *aux2) {
     mma_prologue(v, lane, blk, bscale, aux2);
   }
-  template <int NP> __device__ __forceinline__ void eval(const MmaX &xo, int bl, Acc (&acc)[NP]) const {
+  // MULTI: more than one sequence (the second half of every B operand is a real sequence)
+  template <int NP, bool MULTI> __device__ __forceinline__ void eval(const MmaX &xo, int bl, Acc (&acc)[NP]) const {
     const int lane = threadIdx.x & 31, g = lane >> 2, tid = lane & 3;
-    const uint4 *dig = reinterpret_cast<const uint4 *>(xo.dig + size_t(bl) * FPB + size_t(g >> 2) * xo.seq_stride) + ((g & 3) * 4 + tid);
-    const int ps = xo.seq_stride >> 1;  // uint4 between consecutive pairs
+    const uint4 *dig = reinterpret_cast<const uint4 *>(xo.dig + size_t(bl) * FPB + (MULTI ? size_t(g >> 2) * xo.seq_stride : 0)) +
+                       ((g & 3) * 4 + tid);
+    const int ps = MULTI ? xo.seq_stride >> 1 : 0;  // uint4 between consecutive pairs
     constexpr int STEP = NP < PG ? NP : PG;
 #pragma unroll
     for (int p0 = 0; p0 < NP; p0 += STEP) {
@@ -318,7 +319,7 @@ template <class Derived, int PG_> struct MmaUnitBase {
 #pragma unroll
       for (int p = 0; p < STEP; ++p) {
         const uint32_t d = uint32_t(xo.aux[((p0 + p) * 64 + bl) * 4 + tid]);
-        const float bs = xo.bs[(2 * (p0 + p) + (tid >> 1)) * xo.bs_stride + bl];
+        const float bs = MULTI ? xo.bs[(2 * (p0 + p) + (tid >> 1)) * 64 + bl] : xo.bs[bl];
         static_cast<const Derived *>(this)->finish(c, p, d, bs, acc[p0 + p]);
       }
     }
@@ -807,15 +808,15 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
     // one warp per (sequence, block); the next item's activations are fetched while this one is converted
     float v[8], w8[8], nv[8];
     const int items = ns * nb;
-    if (warp < items) load_x8(x + size_t(warp / ns) * job.x_stride, job.x_len, size_t(b0 + warp % ns), lane, nv);
+    if (warp < items) load_x8(x + size_t(NSEQ == 1 ? 0 : warp / ns) * job.x_stride, job.x_len, size_t(b0 + (NSEQ == 1 ? warp : warp % ns)), lane, nv);
     for (int it = warp; it < items; it += WARPS) {
-      const int q = it / ns, bl = it - q * ns;
+      const int q = NSEQ == 1 ? 0 : it / ns, bl = it - q * ns;
 #pragma unroll
       for (int e = 0; e < 8; ++e) v[e] = nv[e];
       if (p.xmode == XMODE_RMSNORM) load_x8(job.x2, job.x_len, size_t(b0 + bl), lane, w8);
       if (p.xmode == XMODE_SILU_MUL) load_x8(job.x2 + size_t(batch0 + q) * job.x_stride, job.x_len, size_t(b0 + bl), lane, w8);
       if (it + WARPS < items) {
-        const int nq = (it + WARPS) / ns;
+        const int nq = NSEQ == 1 ? 0 : (it + WARPS) / ns;
         load_x8(x + size_t(nq) * job.x_stride, job.x_len, size_t(b0 + (it + WARPS) - nq * ns), lane, nv);
       }
       if (p.xmode == XMODE_RMSNORM) {
@@ -845,14 +846,14 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
     typename U::Acc accs[NP];
 #pragma unroll
     for (int q = 0; q < NP; ++q) U::acc_init(accs[q]);
-    const MmaX xo{smem, xsum, xaux, NSEQ > 1 ? job.S * FPB : 0, NSEQ > 1 ? 64 : 0};
+    const MmaX xo{smem, xsum, xaux, job.S * FPB};
     if (active) {
       for (int base = sub; base < ns; base += NSLOT * wpr) {
 #pragma unroll
         for (int sl = 0; sl < NSLOT; ++sl) {
           const int bl = base + sl * wpr;
           if (bl < ns) {
-            slot[sl].template eval<NP>(xo, bl, accs);
+            slot[sl].template eval<NP, (NSEQ > 1)>(xo, bl, accs);
             if (bl + NSLOT * wpr < ns) slot[sl].load(row_tiles + size_t(bl + NSLOT * wpr) * TB, lane);
           }
         }
@@ -975,6 +976,7 @@ Plan make_plan(int kind, size_t row_tiles, size_t bpr, size_t batch, int sm_coun
   const size_t s_cap = lut ? 12 : nseq == 1 ? 48 : nseq == 8 ? 12 : 24;
   const size_t slots = size_t(sm_count) * (min_ctas(kind, nseq) == 1 ? 1 : ctas_per_sm(kind));
   const double prologue_per_block = (lut ? 1.0 : 0.5) * nseq, fixed = 1.5, split_cost = 2.5;
+  const bool throughput = (other_row_tiles + 7) / 8 * batch >= 2 * slots;
   Plan best{};
   double best_cost = 1e30;
   for (int R = 8; R >= 1; R >>= 1) {
@@ -989,9 +991,9 @@ Plan make_plan(int kind, size_t row_tiles, size_t bpr, size_t batch, int sm_coun
       const size_t other_ctas = (other_row_tiles + R - 1) / R * n_ks * batch;
       const double per_warp = double((S + wpr - 1) / wpr);
       const double cta_time = per_warp + prologue_per_block * double((S + 7) / 8) + fixed + (n_ks > 1 ? split_cost : 0.0);
-      // with plenty of CTAs from other jobs the GPU is busy anyway: minimise this job's total
-      // CTA time; otherwise minimise the time until its last CTA finishes
-      const double cost = (other_ctas >= 2 * slots ? double(own) * cta_time / double(slots)
+      // with plenty of work from other jobs (even cut 8 row-tiles per CTA) the GPU is busy anyway:
+      // minimise this job's total CTA time; otherwise minimise the time until its last CTA finishes
+      const double cost = (throughput ? double(own) * cta_time / double(slots)
                                                    : double((own + other_ctas + slots - 1) / slots) * cta_time) +
                           1e-3 * double(n_ks) + 1e-4 * double(8 / R);
       if (cost < best_cost) {

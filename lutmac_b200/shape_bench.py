@@ -71,17 +71,38 @@ def main(argv=None):
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--random-kv", action="store_true", help="fill the KV cache with random values instead of prefilling")
+    ap.add_argument("--shared-layers", type=int, default=0, help="generate this many distinct layers and repeat them")
+    ap.add_argument("--tp", action="store_true", help="tensor parallel over the ranks of a torch.distributed.run launch")
     a = ap.parse_args(argv)
-    ctx = Context(0)
+    rank, world = 0, 1
+    if a.tp:
+        import os
+
+        import torch.distributed as dist
+
+        from . import tp
+        rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+        dist.init_process_group("gloo")  # rendezvous only; the data path is NCCL inside the library
+        ctx = Context(int(os.environ.get("LOCAL_RANK", rank)))
+        tp.init_tp(ctx, dist)
+    else:
+        ctx = Context(0)
     if a.lut:
         ctx.set_option(_lib.OPT_TERNARY_LUT, 1)
     if a.decode:
         from .decode_bench import run_decode
-        out = run_decode(ctx, a.decode, KIND_BY_NAME[a.kind], a.context, a.batch, steps=a.steps, random_kv=a.random_kv)
+        out = run_decode(ctx, a.decode, KIND_BY_NAME[a.kind], a.context, a.batch, steps=a.steps, random_kv=a.random_kv,
+                         shared_layers=a.shared_layers, tp_rank=rank, tp_size=world)
+        out["tp"] = world
     else:
         out = run_shape(ctx, KIND_BY_NAME[a.kind], a.M, a.K, a.copies, a.reps, not a.no_graph,
                         0 if a.no_rotate else _lib.AUTO_ROTATE)
-    print(json.dumps(out))
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    if a.tp:
+        dist.barrier()
+        _lib.lib().lmb_tp_destroy(ctx.h)
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":
