@@ -100,6 +100,9 @@ SIGNATURES = {
     "lmb_tp_unique_id": (C.c_int, [vp]),
     "lmb_tp_init": (C.c_int, [vp, vp, C.c_int, C.c_int]),
     "lmb_tp_destroy": (C.c_int, [vp]),
+    "lmb_tp_peer_create": (C.c_int, [vp, sz, vp]),
+    "lmb_tp_peer_open": (C.c_int, [vp, vp]),
+    "lmb_tp_peer_status": (C.c_int, [vp, C.POINTER(C.c_int)]),
     "lmb_allreduce_sum": (C.c_int, [vp, vp, sz]),
     "lmb_allgather": (C.c_int, [vp, vp, vp, sz]),
 }

@@ -125,8 +125,42 @@ int cuda_fail(cudaError_t e, const char *what);
 // ---------------------------------------------------------------------------------------------
 // Opaque handles of the C ABI
 // ---------------------------------------------------------------------------------------------
+namespace lmb {
+// One-shot all-reduce over peer memory (tensor parallelism, one process per GPU).  Every rank
+// owns one exchange block, mapped by all ranks: a header (arrival flags, epoch, CTA counter,
+// time-out flag) and the partial vectors [2 parities][ranks][cap floats].  The kernel that
+// produces a partial vector stores it into every rank's block; the kernel that consumes the sum
+// waits for the flags of all ranks and adds the partials in rank order.
+constexpr int MAX_TP = 8;
+constexpr size_t XCHG_HEADER_BYTES = 1024;
+struct XchgHeader {
+  unsigned flags[MAX_TP];  // flags[r] = number of partial vectors of rank r completed in this block
+  unsigned pad0[24];
+  unsigned epoch;          // all-reduces this rank has produced
+  unsigned pad1[15];
+  unsigned done;           // CTAs of the running producer kernel that have finished
+  unsigned pad2[15];
+  unsigned timed_out;      // set when a consumer gave up waiting
+};
+struct PeerXchg {
+  bool ready = false;
+  size_t cap = 0;            // floats per (parity, rank) slot
+  void *local = nullptr;     // this rank's block
+  void *peer[MAX_TP] = {};   // every rank's block as mapped here (own block included)
+};
+// What a GEMV launch needs to deliver its output to all ranks (n = 0: ordinary output).
+struct PeerOut {
+  float *data[MAX_TP];
+  unsigned *flags[MAX_TP];
+  unsigned *epoch, *done;
+  int n, rank;
+  unsigned cap;
+};
+}  // namespace lmb
+
 struct lmb_ctx {
   int device = 0;
+  lmb::PeerXchg xchg;
   cudaStream_t own_stream = nullptr;
   cudaStream_t stream = nullptr;  // the stream work is issued on (own_stream unless overridden)
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
@@ -175,6 +209,7 @@ struct LinearArgs {
   bool rotate;
   const float *x2 = nullptr;        // norm weight (XMODE_RMSNORM) or the vector multiplied in (XMODE_SILU_MUL)
   const float *residual = nullptr;  // added to the output (same layout as y; may alias y)
+  bool to_peers = false;            // deliver y into every rank's exchange block instead (single-job launches)
 };
 // How the GEMV prologue forms its activations from x.
 enum { XMODE_PLAIN = 0, XMODE_RMSNORM = 1, XMODE_SILU_MUL = 2 };

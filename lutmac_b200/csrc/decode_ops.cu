@@ -137,6 +137,44 @@ __global__ void __launch_bounds__(1024) k_add_rmsnorm(float *hidden, const float
   for (size_t i = threadIdx.x; i < h; i += blockDim.x) o[i] = x[i] * inv * w[i];
 }
 
+// Tensor-parallel form of k_add_rmsnorm: the vector to add is the sum over ranks of the partial
+// vectors in this rank's exchange block.  Waits (bounded) until every rank's partial of the
+// current epoch has arrived, adds them in rank order (so that every rank computes the same
+// bits), then normalises.  One CTA per sequence.
+__global__ void __launch_bounds__(1024) k_tp_sum_add_rmsnorm(float *hidden, XchgHeader *hdr, const float *data, int tp,
+                                                             unsigned cap, const float *w, float *out, size_t h, float eps) {
+  asm volatile("griddepcontrol.launch_dependents;");
+  __shared__ float red[32];
+  const unsigned epoch = *reinterpret_cast<volatile unsigned *>(&hdr->epoch);  // already counts the vector to consume
+  if (int(threadIdx.x) < tp) {
+    const volatile unsigned *flag = hdr->flags + threadIdx.x;
+    unsigned spins = 0;
+    while (int(*flag - epoch) < 0) {
+      if (*reinterpret_cast<volatile unsigned *>(&hdr->timed_out) || ++spins > (1u << 22)) {  // about a second: give up, report, carry on with what is there
+        hdr->timed_out = 1u;
+        break;
+      }
+      __nanosleep(100);
+    }
+    __threadfence_system();  // the partial vectors were written before the flag
+  }
+  __syncthreads();
+  const float *part = data + size_t((epoch - 1u) & 1u) * tp * cap + size_t(blockIdx.x) * h;
+  float *x = hidden + size_t(blockIdx.x) * h;
+  float *o = out + size_t(blockIdx.x) * h;
+  float ss = 0.0f;
+  for (size_t i = threadIdx.x; i < h; i += blockDim.x) {
+    float add = 0.0f;
+    for (int r = 0; r < tp; ++r) add += __ldcg(part + size_t(r) * cap + i);
+    const float v = x[i] + add;
+    x[i] = v;
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / float(h) + eps);
+  for (size_t i = threadIdx.x; i < h; i += blockDim.x) o[i] = x[i] * inv * w[i];
+}
+
 // Split-KV decode attention with the q/k/v bias, the rotary embedding and the KV-cache write of
 // the new position folded in (model.cpp:312-372, embedding.cpp:36-75, attention.cpp:23-42).
 // One CTA per (query head, KV split, sequence).  Every CTA rotates its own query head; the split
@@ -354,6 +392,21 @@ int launch_add_rmsnorm(lmb_ctx *ctx, float *d_hidden, const float *d_add, const 
                        size_t batch, float eps) {
   const int threads = h >= 4096 ? 1024 : (h >= 1024 ? 512 : 256);
   k_add_rmsnorm<<<unsigned(batch), threads, 0, ctx->stream>>>(d_hidden, d_add, d_w, d_out, h, eps);
+  ctx->launches++;
+  LMB_CUDA(cudaGetLastError());
+  return LMB_OK;
+}
+
+int launch_tp_sum_add_rmsnorm(lmb_ctx *ctx, float *d_hidden, const float *d_w, float *d_out, size_t h, size_t batch, float eps) {
+  if (!ctx->xchg.ready || batch * h > ctx->xchg.cap) {
+    set_last_error("tensor-parallel sum: exchange block missing or too small");
+    return LMB_ERR_STATE;
+  }
+  const int threads = h >= 4096 ? 1024 : (h >= 1024 ? 512 : 256);
+  XchgHeader *hdr = static_cast<XchgHeader *>(ctx->xchg.local);
+  const float *data = reinterpret_cast<const float *>(static_cast<const char *>(ctx->xchg.local) + XCHG_HEADER_BYTES);
+  k_tp_sum_add_rmsnorm<<<unsigned(batch), threads, 0, ctx->stream>>>(d_hidden, hdr, data, ctx->tp_size, unsigned(ctx->xchg.cap),
+                                                                     d_w, d_out, h, eps);
   ctx->launches++;
   LMB_CUDA(cudaGetLastError());
   return LMB_OK;

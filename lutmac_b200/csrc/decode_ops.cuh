@@ -17,6 +17,8 @@ int launch_embed_rows(lmb_ctx *ctx, const int *d_tokens, const lmb_weight *embed
                       float *d_hidden);
 int launch_add_rmsnorm(lmb_ctx *ctx, float *d_hidden, const float *d_add, const float *d_w, float *d_out, size_t h,
                        size_t batch, float eps);
+// hidden += sum over ranks of the partial vectors in the exchange block; out = RMSNorm(hidden) * w
+int launch_tp_sum_add_rmsnorm(lmb_ctx *ctx, float *d_hidden, const float *d_w, float *d_out, size_t h, size_t batch, float eps);
 int decode_attn_splits(const lmb_ctx *ctx, size_t nh, size_t batch, size_t max_seq);
 int launch_decode_attn(lmb_ctx *ctx, const float *q, const float *k, const float *v, const float *qb, const float *kb,
                        const float *vb, const float *cs_table, const size_t *positions, float *kv, float *out,

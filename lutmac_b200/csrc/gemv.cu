@@ -65,6 +65,7 @@ struct GemvParams {
   // pairs in device memory; null for ordinary launches
   const Job *jobs_dev;
   const int2 *cta_map;
+  PeerOut peer;  // peer.n > 0: job 0's output goes to every rank's exchange block
 };
 
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
@@ -775,6 +776,8 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
 
   pdl_wait();
 
+  // tensor-parallel output: the epoch selects the parity of the exchange slot
+  const unsigned epoch = p.peer.n ? *reinterpret_cast<volatile unsigned *>(p.peer.epoch) : 0u;
   const float *x = job.x + size_t(batch0) * job.x_stride;
   float *inv_rms = part[0];  // [sequence] after the block below (XMODE_RMSNORM)
   if (p.xmode == XMODE_RMSNORM) {
@@ -896,6 +899,30 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
     }
   }
   const int row = rt0 * TILE_ROWS + t;
+  // one output element; with tensor parallelism it goes to this rank's slot in every rank's block
+  auto emit = [&](int q, float o) {
+    const size_t at = size_t(batch0 + q) * job.y_stride + row;
+    if (p.peer.n == 0) {
+      job.y[at] = o;
+    } else {
+      const size_t slot = (size_t(epoch & 1u) * p.peer.n + p.peer.rank) * p.peer.cap + at;
+      for (int r = 0; r < p.peer.n; ++r) p.peer.data[r][slot] = o;
+    }
+  };
+  // every CTA reports in before it leaves; the last one of the launch publishes the vector
+  auto leave = [&]() {
+    if (p.peer.n == 0) return;
+    __syncthreads();
+    if (t == 0) {
+      __threadfence_system();
+      if (atomicAdd(p.peer.done, 1u) == gridDim.x * gridDim.y - 1u) {
+        *p.peer.done = 0u;
+        *reinterpret_cast<volatile unsigned *>(p.peer.epoch) = epoch + 1u;
+        __threadfence_system();
+        for (int r = 0; r < p.peer.n; ++r) *reinterpret_cast<volatile unsigned *>(p.peer.flags[r] + p.peer.rank) = epoch + 1u;
+      }
+    }
+  };
   if (job.n_ks == 1) {
     if (owns_row && row < job.M) {
       const float bias = job.bias ? job.bias[row] : 0.0f;
@@ -905,9 +932,10 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
           float o = s[q];
           if (job.bias) o += bias;
           if (job.residual) o += job.residual[size_t(batch0 + q) * job.y_stride + row];
-          job.y[size_t(batch0 + q) * job.y_stride + row] = o;
+          emit(q, o);
         }
     }
+    leave();
     return;
   }
   // split K: publish the partial sums, the last slice to arrive adds them in slice order
@@ -924,7 +952,10 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
     __threadfence();
   }
   __syncthreads();
-  if (!is_last) return;
+  if (!is_last) {  // uniform over the CTA
+    leave();
+    return;
+  }
   if (owns_row && row < job.M) {
     const float bias = job.bias ? job.bias[row] : 0.0f;
 #pragma unroll
@@ -935,10 +966,11 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
         for (int k = 0; k < job.n_ks; ++k) tot += __ldcg(scr + size_t(k) * job.mp + row);
         if (job.bias) tot += bias;
         if (job.residual) tot += job.residual[size_t(batch0 + q) * job.y_stride + row];
-        job.y[size_t(batch0 + q) * job.y_stride + row] = tot;
+        emit(q, tot);
       }
   }
   if (t == 0) *ctr = 0u;  // ready for the next launch
+  leave();
 }
 
 // Tables only (debug view used by the parity tests): the same prologue, one warp per block.
@@ -1185,6 +1217,23 @@ int launch_gemv(lmb_ctx *ctx, const LinearArgs *args, int njobs, bool rotate, in
   p.eps = eps;
   p.jobs_dev = nullptr;
   p.cta_map = nullptr;
+  p.peer.n = 0;
+  if (args[0].to_peers) {
+    if (njobs != 1 || !ctx->xchg.ready || args[0].batch * args[0].y_stride > ctx->xchg.cap) {
+      set_last_error("launch_gemv: peer output needs one job, an opened exchange block and batch x rows within its capacity");
+      return LMB_ERR_STATE;
+    }
+    p.peer.n = ctx->tp_size;
+    p.peer.rank = ctx->tp_rank;
+    p.peer.cap = unsigned(ctx->xchg.cap);
+    XchgHeader *mine = static_cast<XchgHeader *>(ctx->xchg.local);
+    p.peer.epoch = &mine->epoch;
+    p.peer.done = &mine->done;
+    for (int r = 0; r < ctx->tp_size; ++r) {
+      p.peer.flags[r] = static_cast<XchgHeader *>(ctx->xchg.peer[r])->flags;
+      p.peer.data[r] = reinterpret_cast<float *>(static_cast<char *>(ctx->xchg.peer[r]) + XCHG_HEADER_BYTES);
+    }
+  }
   int ctas = 0, s_max = 1;
   int st = prepare_jobs(ctx, kind, args, njobs, p.job, &ctas, &s_max, nullptr);
   if (st != LMB_OK) return st;
@@ -1255,6 +1304,7 @@ int lmb_group_launch(lmb_ctx *ctx, lmb_group *g) {
   p.eps = 0.0f;
   p.jobs_dev = g->d_jobs;
   p.cta_map = g->d_map;
+  p.peer.n = 0;
   return launch_params_kind(ctx, g->kind, p, g->ctas, g->s_max, 1);
 }
 
@@ -1396,6 +1446,7 @@ int lmb_linear_static_scratch(const lmb_weight *w, const float *d_bias, const fl
   p.rotate = ((flags & LMB_ROTATE) || ((flags & LMB_AUTO_ROTATE) && auto_rot)) ? 1 : 0;
   p.jobs_dev = nullptr;
   p.cta_map = nullptr;
+  p.peer.n = 0;
   Job &jb = p.job[0];
   jb.tiles = w->d_tiles;
   jb.x = d_x;

@@ -88,6 +88,7 @@ struct lmb_model {
   // read from device buffers, so the graph never changes)
   bool use_graph = true, capturing = false;
   bool fused = true;  // norm / activation / residual fused into the GEMV launches (unsharded models)
+  bool tp_peers = true;  // tensor parallelism: partial vectors through peer memory (else NCCL all-reduce)
   std::vector<cudaGraphExec_t> graphs;      // index = batch
   std::vector<uint64_t> graph_launches;
 };
@@ -129,8 +130,66 @@ int lmb_tp_init(lmb_ctx *ctx, const void *id128, int rank, int size) {
   return LMB_OK;
 }
 
+int lmb_tp_peer_create(lmb_ctx *ctx, size_t max_floats, void *handle64_out) {
+  LMB_REQUIRE(ctx && handle64_out && max_floats > 0, "lmb_tp_peer_create: bad argument");
+  LMB_REQUIRE(ctx->tp_size > 1 && ctx->tp_size <= MAX_TP, "lmb_tp_peer_create: call lmb_tp_init first (2 to 8 ranks)");
+  LMB_REQUIRE(!ctx->xchg.local, "lmb_tp_peer_create: the exchange block exists already");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  static_assert(sizeof(XchgHeader) <= XCHG_HEADER_BYTES, "exchange header size");
+  LMB_CUDA(cudaSetDevice(ctx->device));
+  const size_t cap = (max_floats + 63) / 64 * 64;
+  const size_t bytes = XCHG_HEADER_BYTES + size_t(2) * ctx->tp_size * cap * sizeof(float);
+  void *blk = nullptr;
+  LMB_CUDA(cudaMalloc(&blk, bytes));
+  cudaError_t e = cudaMemset(blk, 0, bytes);
+  cudaIpcMemHandle_t hnd;
+  if (e == cudaSuccess) e = cudaIpcGetMemHandle(&hnd, blk);
+  if (e != cudaSuccess) {
+    cudaFree(blk);
+    return cuda_fail(e, "lmb_tp_peer_create");
+  }
+  std::memcpy(handle64_out, &hnd, 64);
+  ctx->xchg.local = blk;
+  ctx->xchg.cap = cap;
+  return LMB_OK;
+}
+
+int lmb_tp_peer_open(lmb_ctx *ctx, const void *handles) {
+  LMB_REQUIRE(ctx && handles && ctx->xchg.local && !ctx->xchg.ready, "lmb_tp_peer_open: create the local block first (once)");
+  LMB_CUDA(cudaSetDevice(ctx->device));
+  for (int r = 0; r < ctx->tp_size; ++r) {
+    if (r == ctx->tp_rank) {
+      ctx->xchg.peer[r] = ctx->xchg.local;
+      continue;
+    }
+    cudaIpcMemHandle_t hnd;
+    std::memcpy(&hnd, static_cast<const char *>(handles) + size_t(r) * 64, 64);
+    LMB_CUDA(cudaIpcOpenMemHandle(&ctx->xchg.peer[r], hnd, cudaIpcMemLazyEnablePeerAccess));
+  }
+  ctx->xchg.ready = true;
+  return LMB_OK;
+}
+
+int lmb_tp_peer_status(lmb_ctx *ctx, int *timed_out) {
+  LMB_REQUIRE(ctx && timed_out, "lmb_tp_peer_status: null argument");
+  *timed_out = 0;
+  if (!ctx->xchg.local) return LMB_OK;
+  unsigned v = 0;
+  LMB_CUDA(cudaStreamSynchronize(ctx->stream));
+  LMB_CUDA(cudaMemcpy(&v, &static_cast<XchgHeader *>(ctx->xchg.local)->timed_out, sizeof v, cudaMemcpyDeviceToHost));
+  *timed_out = int(v);
+  return LMB_OK;
+}
+
 int lmb_tp_destroy(lmb_ctx *ctx) {
   LMB_REQUIRE(ctx, "lmb_tp_destroy: null context");
+  if (ctx->xchg.local) {
+    cudaStreamSynchronize(ctx->stream);
+    for (int r = 0; r < ctx->tp_size; ++r)
+      if (r != ctx->tp_rank && ctx->xchg.peer[r]) cudaIpcCloseMemHandle(ctx->xchg.peer[r]);
+    cudaFree(ctx->xchg.local);
+    ctx->xchg = PeerXchg();
+  }
   if (ctx->comm) {
     cudaStreamSynchronize(ctx->stream);
     nccl().CommDestroy(ctx->comm);
@@ -197,6 +256,8 @@ int lmb_model_create(lmb_ctx *ctx, const lmb_model_config *c, lmb_model **out) {
     m->use_graph = !(gv && gv[0] == '0');
     const char *fv = getenv("LMB_MODEL_FUSED");
     m->fused = !(fv && fv[0] == '0');
+    const char *pv = std::getenv("LMB_TP_PEERS");
+    m->tp_peers = !(pv && pv[0] == '0');
   }
   const size_t B = c->max_batch, h = c->hidden_size, hd = c->head_dim;
   m->seq_stride = c->num_hidden_layers * 2 * c->max_seq_len * m->nkv * hd;
@@ -489,9 +550,31 @@ int lmb_model_forward(lmb_model *m, const int *token_ids, const size_t *position
     if (st != LMB_OK) return st;
   } else {
   const float *pending = nullptr;  // residual branch not yet added to hidden
+  // Tensor parallelism over peer memory: o_proj and down_proj store their partial vectors straight
+  // into every rank's exchange block; the next normalisation waits for all ranks and adds them.
+  const bool peers = c.tp_size > 1 && ctx->xchg.ready && batch * h <= ctx->xchg.cap && m->tp_peers;
+  bool in_flight = false;  // a partial vector is on its way through the exchange block
+  auto norm = [&](const float *w) {
+    int r = in_flight ? launch_tp_sum_add_rmsnorm(ctx, m->hidden, w, m->normed, h, batch, c.rms_norm_eps)
+                      : launch_add_rmsnorm(ctx, m->hidden, pending, w, m->normed, h, batch, c.rms_norm_eps);
+    in_flight = false;
+    pending = nullptr;
+    return r;
+  };
+  auto row_reduce = [&](const lmb_weight *w, bool rot, const float *x, size_t x_len, const Fuse &f) {
+    if (peers) {
+      LinearArgs a{w, nullptr, x, x_len, x_len, m->proj, w->M, batch, rot, f.x2, nullptr, true};
+      in_flight = true;
+      return launch_gemv(ctx, &a, 1, rot, f.xmode, c.rms_norm_eps);
+    }
+    int r = gemv1(m, w, rot, x, x_len, m->proj, batch, f);
+    if (r == LMB_OK && c.tp_size > 1) r = lmb_allreduce_sum(ctx, m->proj, batch * h);
+    pending = m->proj;
+    return r;
+  };
   for (size_t l = 0; l < m->layers.size() && st == LMB_OK; ++l) {
     LayerW &L = m->layers[l];
-    st = launch_add_rmsnorm(ctx, m->hidden, pending, L.in_norm, m->normed, h, batch, c.rms_norm_eps);
+    st = norm(L.in_norm);
     if (st != LMB_OK) break;
     float *qkv[3] = {m->q, m->k, m->v};
     st = gemv_group(m, 3, &L.w[0], &L.rot[0], m->normed, h, qkv, batch);
@@ -499,23 +582,20 @@ int lmb_model_forward(lmb_model *m, const int *token_ids, const size_t *position
     st = launch_decode_attn(ctx, m->q, m->k, m->v, L.qb, L.kb, L.vb, m->cs_table, m->d_pos, m->kv, m->att, m->att_partial,
                             m->att_counters, n_splits, l, rd, batch);
     if (st != LMB_OK) break;
-    st = gemv1(m, L.w[3], L.rot[3], m->att, m->nh * hd, m->proj, batch);
+    st = row_reduce(L.w[3], L.rot[3], m->att, m->nh * hd, Fuse());
     if (st != LMB_OK) break;
-    if (c.tp_size > 1 && (st = lmb_allreduce_sum(ctx, m->proj, batch * h)) != LMB_OK) break;
-    st = launch_add_rmsnorm(ctx, m->hidden, m->proj, L.post_norm, m->normed, h, batch, c.rms_norm_eps);
+    st = norm(L.post_norm);
     if (st != LMB_OK) break;
     float *gu[2] = {m->gate, m->up};
     st = gemv_group(m, 2, &L.w[4], &L.rot[4], m->normed, h, gu, batch);
     if (st != LMB_OK) break;
-    st = launch_silu_mul(ctx, m->gate, m->up, m->act, batch * m->inter);
-    if (st != LMB_OK) break;
-    st = gemv1(m, L.w[6], L.rot[6], m->act, m->inter, m->proj, batch);
-    if (st != LMB_OK) break;
-    if (c.tp_size > 1 && (st = lmb_allreduce_sum(ctx, m->proj, batch * h)) != LMB_OK) break;
-    pending = m->proj;
+    Fuse act;  // SiLU(gate) * up in the prologue of down_proj (element-wise, so a column shard needs no exchange)
+    act.xmode = XMODE_SILU_MUL;
+    act.x2 = m->up;
+    st = row_reduce(L.w[6], L.rot[6], m->gate, m->inter, act);
   }
   if (st != LMB_OK) return st;
-  st = launch_add_rmsnorm(ctx, m->hidden, pending, m->final_norm, m->normed, h, batch, c.rms_norm_eps);
+  st = norm(m->final_norm);
   if (st != LMB_OK) return st;
   if (c.tp_size > 1) {
     st = gemv1(m, m->lm_head, m->head_rot, m->normed, h, m->logits_local, batch);

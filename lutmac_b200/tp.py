@@ -35,9 +35,10 @@ def shard(name: str, t: PackedTensor, rank: int, size: int) -> PackedTensor:
     return shard_rows(t, rank, size) if name in ROW_SHARDED else shard_blocks(t, rank, size)
 
 
-def init_tp(ctx, dist) -> None:
+def init_tp(ctx, dist, peer_floats: int = 32 * 8192) -> None:
     """Create the context's NCCL communicator: rank 0 makes the unique id, torch.distributed
-    (any backend) carries it to the others."""
+    (any backend) carries it to the others.  peer_floats > 0 also sets up the exchange blocks of
+    the peer-memory all-reduce (max batch x hidden size floats per vector)."""
     from ._lib import check, lib
     rank, size = dist.get_rank(), dist.get_world_size()
     ident = (C.c_char * 128)()
@@ -47,3 +48,20 @@ def init_tp(ctx, dist) -> None:
     dist.broadcast_object_list(obj, src=0)
     buf = (C.c_char * 128).from_buffer_copy(obj[0])
     check(lib().lmb_tp_init(ctx.h, buf, rank, size))
+    if size > 1 and peer_floats > 0:
+        # exchange blocks for the all-reduce over peer memory: gather the IPC handles of all ranks
+        handle = (C.c_char * 64)()
+        check(lib().lmb_tp_peer_create(ctx.h, peer_floats, handle))
+        handles = [None] * size
+        dist.all_gather_object(handles, bytes(handle))
+        allh = (C.c_char * (64 * size)).from_buffer_copy(b"".join(handles))
+        check(lib().lmb_tp_peer_open(ctx.h, allh))
+        dist.barrier()
+
+
+def peer_timed_out(ctx) -> bool:
+    """True when a tensor-parallel kernel gave up waiting for another rank's partial vector."""
+    from ._lib import check, lib
+    v = C.c_int(0)
+    check(lib().lmb_tp_peer_status(ctx.h, C.byref(v)))
+    return bool(v.value)

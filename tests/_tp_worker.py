@@ -22,7 +22,8 @@ def main():
     ctx = Context(local)
     tp.init_tp(ctx, dist)
     out = {}
-    for name, kind in (("int4", INT4), ("ternary", TERNARY)):
+    for name, kind, peers in (("int4", INT4, "1"), ("ternary", TERNARY, "1"), ("int4_nccl", INT4, "0")):
+        os.environ["LMB_TP_PEERS"] = peers  # read when the model is created
         shape = synth.tiny_model_shape(hidden=512, inter=1024, n_heads=8, n_kv_heads=2, head_dim=64, n_layers=3)
         spec = synth.model_spec(shape, kind, seed=7, max_seq=32)
         m = Model(spec, ctx, max_batch=2, tp_rank=rank, tp_size=world)
@@ -30,6 +31,7 @@ def main():
         for p, t in enumerate(((3, 9), (100, 4), (7, 7), (500, 1))):
             logits.append(m.forward(np.array(t), [p, p]).copy())
         m.close()
+        assert not tp.peer_timed_out(ctx), "a rank gave up waiting for a partial vector"
         if rank == 0:
             from oracle.oracle import Oracle, OracleModel
             orc = Oracle()
