@@ -28,6 +28,8 @@
 #include <new>
 #include <vector>
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "device_utils.cuh"
 
@@ -1007,7 +1009,7 @@ Plan make_plan(int kind, size_t row_tiles, size_t bpr, size_t batch, int sm_coun
   // 48 KiB of tables / activations per CTA (96 KiB when 4 or 8 sequences share a pass)
   const size_t s_cap = lut ? 12 : nseq == 1 ? 48 : nseq == 8 ? 12 : 24;
   const size_t slots = size_t(sm_count) * (min_ctas(kind, nseq) == 1 ? 1 : ctas_per_sm(kind));
-  const double prologue_per_block = (lut ? 1.0 : 0.5) * nseq, fixed = 1.5, split_cost = 2.5;
+  const double prologue_per_block = 1.5 * nseq, fixed = 1.5, split_cost = 2.5;
   const bool throughput = (other_row_tiles + 7) / 8 * batch >= 2 * slots;
   Plan best{};
   double best_cost = 1e30;
