@@ -66,9 +66,9 @@ int lmb_ctx_destroy(lmb_ctx *ctx);
  * pointer); NULL returns to the context's own stream. */
 int lmb_ctx_set_stream(lmb_ctx *ctx, void *cuda_stream);
 int lmb_ctx_sync(lmb_ctx *ctx);
-/* Options.  LMB_OPT_TERNARY_LUT = 1: ternary, INT2 and binary weights uploaded afterwards use
- * the table-lookup kernel (16-entry group tables, the reference's LUT formulation) instead of
- * the default integer tensor-core kernel.  LMB_OPT_PDL = 0: plain stream order instead of programmatic dependent
+/* Options.  LMB_OPT_TERNARY_LUT = 1: ternary, INT2, INT3 and binary weights uploaded afterwards
+ * use the table-lookup kernel (16-entry group tables, the reference's LUT formulation), INT8
+ * weights the dequantise+FMA kernel, instead of the default integer tensor-core kernels.  LMB_OPT_PDL = 0: plain stream order instead of programmatic dependent
  * launch between consecutive kernels. */
 enum { LMB_OPT_TERNARY_LUT = 1, LMB_OPT_PDL = 2 };
 int lmb_ctx_set_option(lmb_ctx *ctx, int option, int value);

@@ -360,6 +360,7 @@ int lmb_weight_upload_shard(lmb_ctx *ctx, int kind, const void *blocks, size_t M
     if (kind == LMB_INT2) w->kind = DK_INT2_MMA;
     if (kind == LMB_BINARY) w->kind = DK_BINARY_MMA;
     if (kind == LMB_INT8) w->kind = DK_INT8_MMA;
+    if (kind == LMB_INT3) w->kind = DK_INT3_MMA;
   }
   w->device = ctx->device;
   w->M = row1 - row0;

@@ -52,6 +52,8 @@ constexpr int SM_COUNT_HINT = 148;
 //            2-bit field m (bits 2m, 2m+1) of every byte is row g+8m.  Scales as for INT4.
 //   DK_INT2_MMA  the DK_TERNARY_MMA arrangement with the field holding b1 (bit 2m) and b2
 //            (bit 2m+1) of the residual-binary pair; scales [plane][4g+m].
+//   DK_INT3_MMA  6 chunks: chunks 2p, 2p+1 = bit plane p (p = 0 the least significant bit of the
+//            3-bit code) in the DK_BINARY_MMA arrangement.
 //   DK_INT8_MMA  16 chunks: chunk 8h+s of lane (g, tid) = the four A-operand registers of k-step s
 //            for rows 16h+g / 16h+g+8: {row g: columns 32s+4tid..+3, row g+8: the same, row g:
 //            columns 32s+16+4tid..+3, row g+8: the same}.
@@ -67,10 +69,12 @@ constexpr int DK_INT2_MMA = 17;
 constexpr int DK_BINARY_MMA = 18;
 // INT8 blocks in the operand order of the signed 8-bit MMA (the tile's words are the operands).
 constexpr int DK_INT8_MMA = 19;
+// INT3 blocks as three bit planes in the DK_BINARY_MMA arrangement.
+constexpr int DK_INT3_MMA = 20;
 
 __host__ __device__ constexpr bool kind_is_mma(int kind) {
   return kind == LMB_INT4 || kind == LMB_INT5 || kind == LMB_INT6 || kind == DK_TERNARY_MMA || kind == DK_INT2_MMA ||
-         kind == DK_BINARY_MMA || kind == DK_INT8_MMA;
+         kind == DK_BINARY_MMA || kind == DK_INT8_MMA || kind == DK_INT3_MMA;
 }
 
 struct KindInfo {
@@ -93,6 +97,7 @@ __host__ __device__ constexpr KindInfo kind_info(int kind) {
        : kind == DK_INT2_MMA ? KindInfo{72, 4, 2, false}
        : kind == DK_BINARY_MMA ? KindInfo{36, 2, 1, false}
        : kind == DK_INT8_MMA ? KindInfo{260, 16, 1, false}
+       : kind == DK_INT3_MMA ? KindInfo{100, 6, 1, false}
                              : KindInfo{0, 0, 0, false};
 }
 

@@ -33,6 +33,16 @@ __device__ float tile_elem(int kind, const uint8_t *tiles, size_t bpr, size_t ro
     }
     return float(code - (8 << (kind - 4))) * sc[4 * g + m];
   }
+  case DK_INT3_MMA: {
+    const size_t m = l / 8, g = l % 8, s = j / 32, kk = j % 32, tid = (kk % 16) / 4;
+    const size_t lane = g * 4 + tid, wi = (s / 2) * 2 + kk / 16;
+    int code = 0;
+    for (int pl = 0; pl < 3; ++pl) {
+      const uint8_t pb = tile[1024 * pl + ((wi / 4) * TILE_ROWS + lane) * 16 + (wi % 4) * 4 + kk % 4];
+      code |= int((pb >> (m + 4 * (s % 2))) & 1u) << pl;
+    }
+    return float(code - 4) * sc[4 * g + m];
+  }
   case DK_INT8_MMA: {
     const size_t h = l / 16, g = l % 8, s = j / 32, kk = j % 32, tid = (kk % 16) / 4;
     const size_t a = 2 * (kk / 16) + (l % 16) / 8;

@@ -562,13 +562,16 @@ template <> struct Unit<DK_BINARY_MMA> : MmaUnitBase<Unit<DK_BINARY_MMA>, 2> {
   }
 };
 
-// 5- and 6-bit codes: the low nibbles on the INT4 arrangement plus one +-0/1 bit plane per extra
-// bit on the DK_BINARY_MMA arrangement; the partial sums are put back on a common scale by exact
-// shifts and the zero point (16 / 32) is removed with the digit sums.
-template <int BITS> struct WideUnit : MmaUnitBase<Unit<BITS>, 1> {
-  static constexpr int NPL = BITS - 4;
+// Codes made of bit planes on the DK_BINARY_MMA arrangement, optionally on top of low nibbles on
+// the INT4 arrangement: 3-bit = planes 0..2; 5- and 6-bit = nibbles + planes 4 (and 5).  The
+// partial sums are put back on a common scale by exact shifts and the zero point 2^(BITS-1) is
+// removed with the digit sums.
+template <int KIND, int BITS, bool NIB> struct PlanesUnit : MmaUnitBase<Unit<KIND>, 1> {
+  static constexpr int NPL = NIB ? BITS - 4 : BITS;  // bit planes
+  static constexpr int P0 = NIB ? 4 : 0;             // weight of the first plane: 2^P0
+  static constexpr int NC = NIB ? 8 : 0;             // nibble chunks
   using Acc = MmaAcc;
-  uint4 v[8 + 2 * NPL];
+  uint4 v[NC + 2 * NPL];
   float4 sc;
   template <int N> struct Sums {
     int n[N][2][4];            // nibbles, [row half]
@@ -576,8 +579,8 @@ template <int BITS> struct WideUnit : MmaUnitBase<Unit<BITS>, 1> {
   };
   __device__ __forceinline__ void load(const uint8_t *tile, int lane) {
 #pragma unroll
-    for (int c = 0; c < 8 + 2 * NPL; ++c) v[c] = ld_stream_v4(tile + (size_t(c) * TILE_ROWS + lane) * 16);
-    sc = as_float4(ld_stream_v4(tile + size_t(8 + 2 * NPL) * TILE_ROWS * 16 + size_t(lane >> 2) * 16));
+    for (int c = 0; c < NC + 2 * NPL; ++c) v[c] = ld_stream_v4(tile + (size_t(c) * TILE_ROWS + lane) * 16);
+    sc = as_float4(ld_stream_v4(tile + size_t(NC + 2 * NPL) * TILE_ROWS * 16 + size_t(lane >> 2) * 16));
   }
   template <int N> __device__ __forceinline__ void mma_block(const uint4 *dig, int ps, Sums<N> &s) const {
     constexpr uint32_t LO = 0x0F0F0F0Fu, HI = 0xF0F0F0F0u, M1 = 0x01010101u;
@@ -598,15 +601,17 @@ template <int BITS> struct WideUnit : MmaUnitBase<Unit<BITS>, 1> {
       for (int p = 0; p < N; ++p) b[p] = dig[q * 16 + p * ps];
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
-        const uint4 w = v[h * 4 + q];
+        if constexpr (NIB) {
+          const uint4 w = v[h * 4 + q];
 #pragma unroll
-        for (int p = 0; p < N; ++p) {
-          mma_u8s8(s.n[p][h], w.x & LO, w.x & HI, w.y & LO, w.y & HI, b[p].x, b[p].y);
-          mma_u8s8(s.n[p][h], w.z & LO, w.z & HI, w.w & LO, w.w & HI, b[p].z, b[p].w);
+          for (int p = 0; p < N; ++p) {
+            mma_u8s8(s.n[p][h], w.x & LO, w.x & HI, w.y & LO, w.y & HI, b[p].x, b[p].y);
+            mma_u8s8(s.n[p][h], w.z & LO, w.z & HI, w.w & LO, w.w & HI, b[p].z, b[p].w);
+          }
         }
 #pragma unroll
         for (int pl = 0; pl < NPL; ++pl) {
-          const uint4 pv = v[8 + 2 * pl + (q >> 1)];
+          const uint4 pv = v[NC + 2 * pl + (q >> 1)];
           const uint32_t wa = (q & 1) ? pv.z : pv.x, wb = (q & 1) ? pv.w : pv.y;
           const int s0 = 2 * h, s1 = 2 * h + 4;
 #pragma unroll
@@ -623,18 +628,23 @@ template <int BITS> struct WideUnit : MmaUnitBase<Unit<BITS>, 1> {
 #pragma unroll
     for (int m = 0; m < 4; ++m) {
       const int h = m >> 1, j = m & 1;
-      int i0 = s.n[p][h][2 * j] >> (4 * j), i1 = s.n[p][h][2 * j + 1] >> (4 * j);  // exact: multiples of 16 in the high-nibble rows
+      int i0 = 0, i1 = 0;
+      if constexpr (NIB) {  // exact: multiples of 16 in the high-nibble rows
+        i0 = s.n[p][h][2 * j] >> (4 * j);
+        i1 = s.n[p][h][2 * j + 1] >> (4 * j);
+      }
 #pragma unroll
       for (int pl = 0; pl < NPL; ++pl) {
-        i0 += ((s.pl[p][pl][h][0][2 * j] + (s.pl[p][pl][h][1][2 * j] >> 4)) >> m) << (4 + pl);
-        i1 += ((s.pl[p][pl][h][0][2 * j + 1] + (s.pl[p][pl][h][1][2 * j + 1] >> 4)) >> m) << (4 + pl);
+        i0 += ((s.pl[p][pl][h][0][2 * j] + (s.pl[p][pl][h][1][2 * j] >> 4)) >> m) << (P0 + pl);
+        i1 += ((s.pl[p][pl][h][0][2 * j + 1] + (s.pl[p][pl][h][1][2 * j + 1] >> 4)) >> m) << (P0 + pl);
       }
       acc.r[m] += mma_row_value(i0, i1, d << (BITS - 1)) * (bs * sv[m]);  // zero point 2^(BITS-1)
     }
   }
 };
-template <> struct Unit<LMB_INT5> : WideUnit<5> {};
-template <> struct Unit<LMB_INT6> : WideUnit<6> {};
+template <> struct Unit<LMB_INT5> : PlanesUnit<LMB_INT5, 5, true> {};
+template <> struct Unit<LMB_INT6> : PlanesUnit<LMB_INT6, 6, true> {};
+template <> struct Unit<DK_INT3_MMA> : PlanesUnit<DK_INT3_MMA, 3, false> {};
 
 // 8-bit weights on the signed 8-bit MMA: the tile's words are the A operands as they are.
 template <> struct Unit<DK_INT8_MMA> : MmaUnitBase<Unit<DK_INT8_MMA>, 2> {
@@ -711,7 +721,7 @@ template <> struct Unit<LMB_INT8> {
 // need more of them to cover the HBM latency with the two or three CTAs an SM holds.
 __host__ __device__ constexpr int prefetch_depth(int kind) {
   return kind == DK_TERNARY_MMA ? 3 : kind == DK_INT2_MMA ? 2 : kind == DK_BINARY_MMA ? 5 : kind == LMB_TERNARY ? 2
-       : (kind == LMB_INT5 || kind == LMB_INT6 || kind == DK_INT8_MMA) ? 0 : kind == LMB_INT2 ? 2 : kind == LMB_BINARY ? 3
+       : (kind == LMB_INT5 || kind == LMB_INT6 || kind == DK_INT8_MMA) ? 0 : kind == DK_INT3_MMA ? 1 : kind == LMB_INT2 ? 2 : kind == LMB_BINARY ? 3
        : kind == LMB_INT8 ? 0 : 1;
 }
 
@@ -722,7 +732,7 @@ __host__ __device__ constexpr int min_ctas(int kind, int nseq) {
 }
 // Most sequences one pass over the weights serves.
 __host__ __device__ constexpr int max_seqs_per_pass(int kind) {
-  return !kind_is_mma(kind) ? 1 : (kind == LMB_INT5 || kind == LMB_INT6) ? 2 : 8;
+  return !kind_is_mma(kind) ? 1 : (kind == LMB_INT5 || kind == LMB_INT6 || kind == DK_INT3_MMA) ? 2 : 8;
 }
 
 template <int KIND, int NSEQ>
@@ -1165,6 +1175,7 @@ int launch_params_kind(lmb_ctx *ctx, int kind, GemvParams &p, int ctas, int s_ma
   case LMB_INT5: return launch_params_mma<LMB_INT5>(ctx, p, ctas, s_max, batch);
   case LMB_INT6: return launch_params_mma<LMB_INT6>(ctx, p, ctas, s_max, batch);
   case DK_INT8_MMA: return launch_params_mma<DK_INT8_MMA>(ctx, p, ctas, s_max, batch);
+  case DK_INT3_MMA: return launch_params_mma<DK_INT3_MMA>(ctx, p, ctas, s_max, batch);
   default: set_last_error("launch_gemv: kind has no device kernel"); return LMB_ERR_ARG;
   }
 }
@@ -1197,6 +1208,7 @@ int configure_gemv(lmb_ctx *ctx) {
   if (st == LMB_OK) st = configure_mma<LMB_INT5>();
   if (st == LMB_OK) st = configure_mma<LMB_INT6>();
   if (st == LMB_OK) st = configure_mma<DK_INT8_MMA>();
+  if (st == LMB_OK) st = configure_mma<DK_INT3_MMA>();
   return st;
 }
 

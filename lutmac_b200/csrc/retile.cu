@@ -102,6 +102,15 @@ void block_to_lane(int kind, const uint8_t *blk, uint8_t *pay, float *sc) {
     std::memcpy(sc, blk + 96, 4);
     break;
   }
+  case DK_INT3_MMA: {  // three row-major MSB-first bit planes, least significant first; permuted per tile later
+    std::memset(pay, 0, 96);
+    for (size_t i = 0; i < 256; ++i) {
+      unsigned code = stream_get(blk, 96, i, 3);
+      for (int p = 0; p < 3; ++p) plane_set(pay + 32 * p, i, (code >> p) & 1u);
+    }
+    std::memcpy(sc, blk + 96, 4);
+    break;
+  }
   case LMB_INT4:
     std::memcpy(pay, blk, 128);
     std::memcpy(sc, blk + 128, 4);
@@ -185,6 +194,15 @@ void lane_to_block(int kind, const uint8_t *pay, const float *sc, uint8_t *blk) 
     std::memset(blk, 0, 96);
     for (size_t i = 0; i < 256; ++i) {
       unsigned code = plane_get(q[0], i) | (plane_get(q[1], i) << 1) | (plane_get(q[2], i) << 2);
+      stream_set(blk, 96, i, 3, code);
+    }
+    std::memcpy(blk + 96, sc, 4);
+    break;
+  }
+  case DK_INT3_MMA: {
+    std::memset(blk, 0, 96);
+    for (size_t i = 0; i < 256; ++i) {
+      unsigned code = plane_get(pay, i) | (plane_get(pay + 32, i) << 1) | (plane_get(pay + 64, i) << 2);
       stream_set(blk, 96, i, 3, code);
     }
     std::memcpy(blk + 96, sc, 4);
@@ -398,6 +416,8 @@ void retile(int kind, const uint8_t *blocks, size_t src_bpr, size_t row0, size_t
       if (kind == LMB_INT5 || kind == LMB_INT6) bin_to_fragments(tile + 4096);
       if (kind == LMB_INT6) bin_to_fragments(tile + 5120);
       if (kind == DK_INT8_MMA) int8_to_fragments(tile);
+      if (kind == DK_INT3_MMA)
+        for (size_t pl = 0; pl < 3; ++pl) bin_to_fragments(tile + 1024 * pl);
       if (kind == DK_TERNARY_MMA || kind == DK_INT2_MMA) tern_to_fragments(tile);
       if (kind == DK_BINARY_MMA) bin_to_fragments(tile);
     }
@@ -418,6 +438,9 @@ void untile(int kind, const uint8_t *tiled, size_t M, size_t bpr, uint8_t *block
         int4_from_fragments(rowmajor);
         if (kind != LMB_INT4) bin_from_fragments(rowmajor + 4096);
         if (kind == LMB_INT6) bin_from_fragments(rowmajor + 5120);
+      } else if (kind == DK_INT3_MMA) {
+        std::memcpy(rowmajor, tile, 3072);
+        for (size_t pl = 0; pl < 3; ++pl) bin_from_fragments(rowmajor + 1024 * pl);
       } else if (kind == DK_INT8_MMA) {
         std::memcpy(rowmajor, tile, 8192);
         int8_from_fragments(rowmajor);

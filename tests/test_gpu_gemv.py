@@ -224,7 +224,7 @@ def test_host_group_matches_oracle(ctx, oracle):
             assert rel_l2(y, oracle.lut_linear(INT4, 4, t.blocks, t.M, t.K, None, x)[0]) < TOL
 
 
-@pytest.mark.parametrize("kind,qbits", [(TERNARY, 2), (INT2, 2), (BINARY, 1)])
+@pytest.mark.parametrize("kind,qbits", [(TERNARY, 2), (INT2, 2), (BINARY, 1), (INT3, 3)])
 @pytest.mark.parametrize("which", ["mma", "lut"])
 def test_both_device_layouts(ctx, ctx_lut, oracle, which, kind, qbits):
     """Ternary, INT2 and binary weights run on the integer tensor-core kernel by default and on
@@ -249,7 +249,7 @@ def test_both_device_layouts(ctx, ctx_lut, oracle, which, kind, qbits):
     w.free()
 
 
-@pytest.mark.parametrize("kind,qbits", [(INT4, 4), (TERNARY, 2), (INT2, 2), (BINARY, 1), (INT8, 8), (INT5, 5), (INT6, 6)])
+@pytest.mark.parametrize("kind,qbits", [(INT4, 4), (TERNARY, 2), (INT2, 2), (BINARY, 1), (INT8, 8), (INT5, 5), (INT6, 6), (INT3, 3)])
 def test_batched_sequences_share_the_weight_pass(ctx, oracle, kind, qbits):
     """Batches of 2, 4 and 8 sequences are evaluated in one pass over the weights on the
     integer tensor-core kernels (two sequences per MMA); every batch size, odd ones included,
@@ -270,7 +270,7 @@ def test_extreme_activation_ranges(ctx, oracle):
     """The integer tensor-core kernels quantise x per 256-block with a shared exponent: blocks
     of very different magnitude, tiny values, and an all-zero block must still match."""
     rng = np.random.default_rng(31)
-    for kind in (INT4, TERNARY, INT2, BINARY, INT5, INT6, INT8):
+    for kind in (INT4, TERNARY, INT2, BINARY, INT3, INT5, INT6, INT8):
         t = synth.tensor(rng, kind, 96, 1024)
         x = synth.activations(rng, 1024)
         x[:256] *= 1e-20
