@@ -269,35 +269,38 @@ __global__ void __launch_bounds__(ATT_THREADS) k_decode_attn(const AttnArgs a, c
   const float scale = 1.0f / sqrtf(float(d.hd));
   const size_t per = d.hd / 32;  // 2 or 4 (head_dim 64 or 128); other head dims take the generic loop
   const size_t tnew = has_new ? pos - t0 : ~size_t(0);  // slice-local index of the new position
-  for (size_t tb = warp * 4; tb < n; tb += nw * 4) {
-    float s[4] = {0.f, 0.f, 0.f, 0.f};
+  constexpr int TS = 8;  // timesteps per warp and iteration: eight key loads in flight per lane
+  for (size_t tb = warp * TS; tb < n; tb += nw * TS) {
+    float s[TS];
+#pragma unroll
+    for (int i = 0; i < TS; ++i) s[i] = 0.0f;
     if (per == 4) {
-      float4 kk[4];
+      float4 kk[TS];
       const float4 qv = reinterpret_cast<const float4 *>(qs)[lane];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
+      for (int i = 0; i < TS; ++i) {
         const size_t t = tb + i;
         kk[i] = (t >= n) ? make_float4(0, 0, 0, 0)
                 : (t == tnew) ? reinterpret_cast<const float4 *>(kn)[lane]
                               : reinterpret_cast<const float4 *>(kc + (t0 + t) * kv_dim)[lane];
       }
 #pragma unroll
-      for (int i = 0; i < 4; ++i) s[i] = qv.x * kk[i].x + qv.y * kk[i].y + qv.z * kk[i].z + qv.w * kk[i].w;
+      for (int i = 0; i < TS; ++i) s[i] = qv.x * kk[i].x + qv.y * kk[i].y + qv.z * kk[i].z + qv.w * kk[i].w;
     } else if (per == 2) {
-      float2 kk[4];
+      float2 kk[TS];
       const float2 qv = reinterpret_cast<const float2 *>(qs)[lane];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
+      for (int i = 0; i < TS; ++i) {
         const size_t t = tb + i;
         kk[i] = (t >= n) ? make_float2(0, 0)
                 : (t == tnew) ? reinterpret_cast<const float2 *>(kn)[lane]
                               : reinterpret_cast<const float2 *>(kc + (t0 + t) * kv_dim)[lane];
       }
 #pragma unroll
-      for (int i = 0; i < 4; ++i) s[i] = qv.x * kk[i].x + qv.y * kk[i].y;
+      for (int i = 0; i < TS; ++i) s[i] = qv.x * kk[i].x + qv.y * kk[i].y;
     } else {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
+      for (int i = 0; i < TS; ++i) {
         const size_t t = tb + i;
         if (t < n)
           for (size_t c = lane; c < d.hd; c += 32) s[i] += qs[c] * (t == tnew ? kn[c] : kc[(t0 + t) * kv_dim + c]);
@@ -306,9 +309,11 @@ __global__ void __launch_bounds__(ATT_THREADS) k_decode_attn(const AttnArgs a, c
 #pragma unroll
     for (int m = 16; m > 0; m >>= 1) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) s[i] += __shfl_xor_sync(0xffffffffu, s[i], m);
+      for (int i = 0; i < TS; ++i) s[i] += __shfl_xor_sync(0xffffffffu, s[i], m);
     }
-    if (lane < 4 && tb + lane < n) sc[tb + lane] = (lane == 0 ? s[0] : lane == 1 ? s[1] : lane == 2 ? s[2] : s[3]) * scale;
+#pragma unroll
+    for (int i = 0; i < TS; ++i)
+      if (lane == i && tb + i < n) sc[tb + i] = s[i] * scale;
   }
   __syncthreads();
   float mx = -INFINITY;
@@ -322,19 +327,26 @@ __global__ void __launch_bounds__(ATT_THREADS) k_decode_attn(const AttnArgs a, c
   }
   sum = block_sum(sum, red);
   __syncthreads();
-  // weighted values: thread = (group, dim); groups stride over the slice, 8 loads in flight.
+  // weighted values: thread = (group, dim); groups stride over the slice, 16 loads in flight.
   // The new position (if in this slice) is left out here and added from shared memory below.
   const size_t groups = ATT_THREADS / d.hd, g = threadIdx.x / d.hd, dd = threadIdx.x % d.hd;
   const size_t n_old = has_new ? n - 1 : n;  // the new position is always the last of its slice
   float av = 0.0f;
   {
     size_t t = g;
-    for (; t + 7 * groups < n_old; t += 8 * groups) {
-      float vv[8];
+    for (; t + 15 * groups < n_old; t += 16 * groups) {
+      float vv[16];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) vv[i] = vc[(t0 + t + i * groups) * kv_dim + dd];
+      for (int i = 0; i < 16; ++i) vv[i] = vc[(t0 + t + i * groups) * kv_dim + dd];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) av += sc[t + i * groups] * vv[i];
+      for (int i = 0; i < 16; ++i) av += sc[t + i * groups] * vv[i];
+    }
+    for (; t + 3 * groups < n_old; t += 4 * groups) {
+      float vv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) vv[i] = vc[(t0 + t + i * groups) * kv_dim + dd];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) av += sc[t + i * groups] * vv[i];
     }
     for (; t < n_old; t += groups) av += sc[t] * vc[(t0 + t) * kv_dim + dd];
     if (has_new && g == 0) av += sc[n - 1] * vn[dd];
@@ -362,17 +374,38 @@ __global__ void __launch_bounds__(ATT_THREADS) k_decode_attn(const AttnArgs a, c
   }
   __syncthreads();
   if (!is_last) return;
+  // merge of the splits by the last CTA of the head: the (max, sum) pairs first, one thread per
+  // split, then the vectors with the splits dealt over the thread groups and four loads in flight
   const float *all = a.partial + ((b * d.nh + head) * n_splits) * rec;
-  float gmx = -INFINITY;
-  for (int k2 = 0; k2 < n_splits; ++k2) gmx = fmaxf(gmx, __ldcg(all + k2 * rec + d.hd));
-  if (threadIdx.x < d.hd) {
-    float tot = 0.0f, den = 0.0f;
-    for (int k2 = 0; k2 < n_splits; ++k2) {
-      const float m2 = __ldcg(all + k2 * rec + d.hd), l2 = __ldcg(all + k2 * rec + d.hd + 1);
-      const float w = (l2 > 0.0f) ? expf(m2 - gmx) : 0.0f;
-      tot += w * __ldcg(all + k2 * rec + threadIdx.x);
-      den += w * l2;
+  float *wk = sc;  // [n_splits] weights, reusing the score buffer (n_splits <= 32 <= split_len)
+  if (threadIdx.x < unsigned(n_splits)) {
+    red[threadIdx.x] = __ldcg(all + threadIdx.x * rec + d.hd);
+    wk[threadIdx.x] = __ldcg(all + threadIdx.x * rec + d.hd + 1);
+  }
+  __syncthreads();
+  float gmx = -INFINITY, den = 0.0f;
+  for (int k2 = 0; k2 < n_splits; ++k2) gmx = fmaxf(gmx, red[k2]);
+  for (int k2 = 0; k2 < n_splits; ++k2) den += (wk[k2] > 0.0f) ? expf(red[k2] - gmx) * wk[k2] : 0.0f;
+  __syncthreads();
+  if (threadIdx.x < unsigned(n_splits)) wk[threadIdx.x] = (wk[threadIdx.x] > 0.0f) ? expf(red[threadIdx.x] - gmx) : 0.0f;
+  __syncthreads();
+  {
+    float tot = 0.0f;
+    int k2 = int(g);
+    for (; k2 + 3 * int(groups) < n_splits; k2 += 4 * int(groups)) {
+      float pv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) pv[i] = __ldcg(all + (k2 + i * int(groups)) * rec + dd);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) tot += wk[k2 + i * int(groups)] * pv[i];
     }
+    for (; k2 < n_splits; k2 += int(groups)) tot += wk[k2] * __ldcg(all + k2 * rec + dd);
+    acc[threadIdx.x] = tot;
+  }
+  __syncthreads();
+  if (threadIdx.x < d.hd) {
+    float tot = 0.0f;
+    for (size_t k2 = 0; k2 < groups; ++k2) tot += acc[k2 * d.hd + threadIdx.x];
     a.out[(b * d.nh + head) * d.hd + threadIdx.x] = tot * (1.0f / den);
   }
   if (threadIdx.x == 0) *ctr = 0u;
