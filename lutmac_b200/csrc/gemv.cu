@@ -30,6 +30,8 @@
 
 #include <cstdlib>
 
+#include <algorithm>
+
 #include "common.cuh"
 #include "device_utils.cuh"
 
@@ -1120,11 +1122,24 @@ int prepare_jobs(lmb_ctx *ctx, int kind, const LinearArgs *args, int njobs, Job 
       scratch_off += batch * pl.n_ks * jb.mp;
       counter_off += ny * pl.n_rg;
     }
-    if (cta_map)
-      for (int c = 0; c < pl.ctas; ++c) cta_map->push_back(make_int2(j, ctas));
     ctas += pl.ctas;
     jb.cta_end = ctas;
     s_max = pl.S > s_max ? pl.S : s_max;
+  }
+  if (cta_map) {
+    // prepared groups: the jobs with the longest CTAs get the lowest block indices, so that
+    // they start first and the short ones fill the tail of the launch
+    std::vector<int> order(static_cast<size_t>(njobs));
+    for (int j = 0; j < njobs; ++j) order[size_t(j)] = j;
+    std::stable_sort(order.begin(), order.end(), [&](int a, int b) {
+      const Plan &pa = plans[size_t(a)], &pb = plans[size_t(b)];
+      return pa.R * pa.S > pb.R * pb.S;
+    });
+    int first = 0;
+    for (int j : order) {
+      for (int c = 0; c < plans[size_t(j)].ctas; ++c) cta_map->push_back(make_int2(j, first));
+      first += plans[size_t(j)].ctas;
+    }
   }
   *ctas_out = ctas;
   *s_max_out = s_max;
