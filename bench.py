@@ -100,7 +100,7 @@ def load_peaks():
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one group launch of the suite, from the ncu
 # capture summarised in profiles/k_gemv_int4_suite_group.md
-NCU_DRAM_BYTES_PER_GROUP_LAUNCH = 509369344
+NCU_DRAM_BYTES_PER_GROUP_LAUNCH = 508589056
 
 
 def load_traffic():
