@@ -161,6 +161,9 @@ int lmb_group_launch(lmb_ctx *ctx, lmb_group *g);
  * (outputs[i] = M_i floats). */
 int lmb_group_create_host(lmb_ctx *ctx, size_t n, const lmb_weight *const *ws, unsigned flags, lmb_group **out);
 int lmb_group_run_host(lmb_ctx *ctx, lmb_group *g, const float *const *inputs, float *const *outputs);
+/* The pinned host buffers of job i of a host group: an input written there and an output read
+ * from there need no staging copy (pass the same pointers to lmb_group_run_host). */
+int lmb_group_host_io(lmb_group *g, size_t i, float **h_in, float **h_out);
 int lmb_group_destroy(lmb_group *g);
 
 /* ---- kernel API on host pointers: replaces the dispatchers lut_gemv, lut_gemv_binary,
@@ -187,6 +190,11 @@ int lmb_apply_hadamard_rotation_host(float *data, size_t n);         /* in place
 /* ---- debug views used by the parity tests ----------------------------------------------------------
  * LUT tables exactly as the kernel prologue builds them: ceil(x_len/256)*64 groups x 16 entries
  * (precompute_luts, lut_gemm.hpp:53-58), after optional rotation. */
+/* How a GEMV of this shape would be cut into CTAs on a GPU with sm_count SMs (no GPU needed):
+ * out5 = {row-tiles per CTA, blocks per K slice, row groups, K slices, sequences per pass}.
+ * kind is a device layout kind as reported by lmb_weight_info; other_rows = rows of the other
+ * jobs of the same launch. */
+int lmb_debug_plan(int kind, size_t M, size_t K, size_t batch, size_t other_rows, int sm_count, int out5[5]);
 int lmb_debug_luts(lmb_ctx *ctx, const float *d_x, size_t x_len, unsigned flags, float *d_luts_out);
 /* Ternary LUT indices as the kernel consumes them: for every row and group of 4 weights the
  * (pos, neg) nibbles of extract_indices (lut_gemm.hpp:79-99); out = M*ceil(K/256)*64*2 bytes. */

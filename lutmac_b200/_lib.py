@@ -71,12 +71,14 @@ SIGNATURES = {
     "lmb_group_launch": (C.c_int, [vp, vp]),
     "lmb_group_create_host": (C.c_int, [vp, sz, C.POINTER(vp), C.c_uint, C.POINTER(vp)]),
     "lmb_group_run_host": (C.c_int, [vp, vp, C.POINTER(vp), C.POINTER(vp)]),
+    "lmb_group_host_io": (C.c_int, [vp, sz, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)]),
     "lmb_group_destroy": (C.c_int, [vp]),
     "lmb_gemv_host": (C.c_int, [C.c_int, vp, sz, vp, vp, sz, sz]),
     "lmb_linear_host": (C.c_int, [vp, vp, vp, vp, vp, sz, C.c_uint]),
     "lmb_linear_host_multi": (C.c_int, [vp, sz, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), C.c_uint]),
     "lmb_fwht256": (C.c_int, [vp, vp, sz]),
     "lmb_apply_hadamard_rotation_host": (C.c_int, [vp, sz]),
+    "lmb_debug_plan": (C.c_int, [C.c_int, sz, sz, sz, sz, C.c_int, C.POINTER(C.c_int)]),
     "lmb_debug_luts": (C.c_int, [vp, vp, sz, C.c_uint, vp]),
     "lmb_debug_ternary_indices": (C.c_int, [vp, vp, vp]),
     "lmb_model_create": (C.c_int, [vp, C.POINTER(ModelConfig), C.POINTER(vp)]),

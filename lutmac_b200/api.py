@@ -159,11 +159,24 @@ class HostGroup:
         h = C.c_void_p()
         check(lib().lmb_group_create_host(ctx.h, n, W, flags, C.byref(h)))
         self.h = h
-        self.outs = [np.empty(w.M, np.float32) for w in weights]
+        # inputs and outputs as views of the group's pinned staging buffers: data written to
+        # `ins` and read from `outs` is transferred without an intermediate host copy
+        self.ins, self.outs = [], []
+        for i, w in enumerate(weights):
+            pi, po = C.c_void_p(), C.c_void_p()
+            check(lib().lmb_group_host_io(h, i, C.byref(pi), C.byref(po)))
+            self.ins.append(np.ctypeslib.as_array((C.c_float * w.K).from_address(pi.value)))
+            self.outs.append(np.ctypeslib.as_array((C.c_float * w.M).from_address(po.value)))
         self._Y = (C.c_void_p * n)(*[y.ctypes.data for y in self.outs])
+        self._Xown = (C.c_void_p * n)(*[x.ctypes.data for x in self.ins])
         self._key, self._xs, self._X = None, None, None
 
-    def run(self, inputs):
+    def run(self, inputs=None):
+        """One step: host to device, one launch, device to host.  inputs=None takes the step's
+        inputs from `self.ins` (pinned memory); the results are in `self.outs`."""
+        if inputs is None:
+            check(lib().lmb_group_run_host(self.ctx.h, self.h, self._Xown, self._Y))
+            return self.outs
         # the pointer table is rebuilt only when the caller passes other array objects than last
         # time (building it costs more than the launch it feeds)
         key = tuple(map(id, inputs))

@@ -1400,14 +1400,40 @@ int lmb_group_run_host(lmb_ctx *ctx, lmb_group *g, const float *const *inputs, f
   LMB_REQUIRE(ctx && g && inputs && outputs, "lmb_group_run_host: null argument");
   LMB_REQUIRE(g->d_io, "lmb_group_run_host: the group was not made by lmb_group_create_host");
   const size_t n = size_t(g->njobs);
-  for (size_t i = 0; i < n; ++i) std::memcpy(g->h_io + g->in_off[i], inputs[i], g->in_len[i] * sizeof(float));
+  // inputs that already live in the group's pinned buffer (lmb_group_host_io) need no staging copy
+  for (size_t i = 0; i < n; ++i)
+    if (inputs[i] != g->h_io + g->in_off[i]) std::memcpy(g->h_io + g->in_off[i], inputs[i], g->in_len[i] * sizeof(float));
   LMB_CUDA(cudaMemcpyAsync(g->d_io, g->h_io, g->in_floats * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
   int st = lmb_group_launch(ctx, g);
   if (st != LMB_OK) return st;
   LMB_CUDA(cudaMemcpyAsync(g->h_io + g->in_floats, g->d_io + g->in_floats, g->out_floats * sizeof(float),
                            cudaMemcpyDeviceToHost, ctx->stream));
   LMB_CUDA(cudaStreamSynchronize(ctx->stream));
-  for (size_t i = 0; i < n; ++i) std::memcpy(outputs[i], g->h_io + g->out_off[i], g->out_len[i] * sizeof(float));
+  for (size_t i = 0; i < n; ++i)
+    if (outputs[i] != g->h_io + g->out_off[i]) std::memcpy(outputs[i], g->h_io + g->out_off[i], g->out_len[i] * sizeof(float));
+  return LMB_OK;
+}
+
+int lmb_debug_plan(int kind, size_t M, size_t K, size_t batch, size_t other_rows, int sm_count, int out5[5]) {
+  using namespace lmb;
+  LMB_REQUIRE(kind_valid(kind) && M > 0 && K > 0 && batch > 0 && sm_count > 0 && out5, "lmb_debug_plan: bad argument");
+  const int nseq = seqs_per_pass(kind, batch);
+  const size_t ny = (batch + size_t(nseq) - 1) / size_t(nseq);
+  const Plan pl = make_plan(kind, (M + TILE_ROWS - 1) / TILE_ROWS, (K + BLK - 1) / BLK, ny, sm_count,
+                            (other_rows + TILE_ROWS - 1) / TILE_ROWS, nseq);
+  out5[0] = pl.R;
+  out5[1] = pl.S;
+  out5[2] = pl.n_rg;
+  out5[3] = pl.n_ks;
+  out5[4] = nseq;
+  return LMB_OK;
+}
+
+int lmb_group_host_io(lmb_group *g, size_t i, float **h_in, float **h_out) {
+  using namespace lmb;
+  LMB_REQUIRE(g && g->d_io && i < size_t(g->njobs), "lmb_group_host_io: not a host group, or index out of range");
+  if (h_in) *h_in = g->h_io + g->in_off[i];
+  if (h_out) *h_out = g->h_io + g->out_off[i];
   return LMB_OK;
 }
 

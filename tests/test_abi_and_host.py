@@ -1,6 +1,7 @@
 """CPU: the C-ABI library loads and exports every symbol include/lutmac_b200.h declares, the
 host-side re-tiling is a bit-exact bijection, and the host logic (block structs, synthetic
 generators, byte accounting, tensor-parallel sharding) behaves.  No compute call needs a GPU."""
+import ctypes as C
 import os
 import re
 
@@ -127,3 +128,34 @@ def test_tp_sharding_reassembles(oracle):
     assert np.array_equal(rows, full)
     parts = [oracle.gemv(TERNARY, tp.shard_blocks(t, r, 2).blocks, x[r * 512:(r + 1) * 512], 64, 512) for r in range(2)]
     assert np.allclose(parts[0] + parts[1], full, rtol=1e-5, atol=1e-6)
+
+
+def _plan(kind, M, K, batch=1, other_rows=0, sms=148):
+    out = (C.c_int * 5)()
+    assert _lib.lib().lmb_debug_plan(kind, M, K, batch, other_rows, sms, out) == 0
+    return dict(zip(("R", "S", "n_rg", "n_ks", "nseq"), out))
+
+
+def test_planner_cuts_launches_sensibly():
+    """Host logic of the CTA planner (no GPU): slices fit the shared-memory budget, a launch of a
+    few big jobs is planned for latency as a whole (not one row-tile per CTA), prepared groups
+    that oversubscribe the GPU get the coarsest cut, batches share the weight pass."""
+    TERNARY_MMA, INT2_MMA = 16, 17
+    for kind, cap in ((INT4, 48), (TERNARY_MMA, 48), (INT3, 12)):
+        for M, K in ((2048, 2048), (8192, 28672), (128, 70000), (33, 300)):
+            p = _plan(kind, M, K)
+            assert 1 <= p["S"] <= cap and p["R"] in (1, 2, 4, 8)
+            assert (p["S"] * p["n_ks"]) >= (K + 255) // 256 > p["S"] * (p["n_ks"] - 1)
+            assert p["n_rg"] == -(-((M + 31) // 32) // p["R"])
+    # gate/up pair of a 70B-shaped layer: two jobs of 896 row-tiles must not be cut into 1792 CTAs
+    pair = _plan(TERNARY_MMA, 28672, 8192, other_rows=28672)
+    assert pair["n_rg"] * pair["n_ks"] <= 2 * 148
+    # one job of the bench suite among 111 others: coarsest cut, no K split
+    q = _plan(INT4, 2048, 2048, other_rows=23552 * 16 - 2048)
+    assert (q["R"], q["n_ks"]) == (8, 1)
+    # alone, the same job is spread over the GPU
+    alone = _plan(INT4, 2048, 8192)
+    assert alone["n_rg"] * alone["n_ks"] >= 148
+    # batches: 2, 4, 8 sequences per pass on the tensor-core kinds, 1 on the table-lookup kinds
+    assert [_plan(INT2_MMA, 8960, 1536, b)["nseq"] for b in (1, 2, 3, 5, 32)] == [1, 2, 4, 8, 8]
+    assert _plan(3, 8960, 1536, 8)["nseq"] == 1
