@@ -289,7 +289,7 @@ def run_ours(args):
                          "peak_source": peak_src, "kernel": "k_gemv<int4>",
                          "algorithmic_bytes_per_launch": per_launch_bytes, "traffic": load_traffic()},
             "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "call": "lmb_group_run_host: the step's 112 lut_linear calls with host inputs and outputs"},
+                    "call": "lmb_group_run_host: the step's 112 lut_linear calls, inputs read from and outputs written to pinned host memory"},
             "gpu_launches": int(gpu_launches), "clocks": clocks}
     if world == 1 and not args.no_decode:
         # side measurement: config[2], one decode step of the random-init Llama-3.2-1B shape (4-bit

@@ -195,6 +195,7 @@ int lmb_ctx_destroy(lmb_ctx *ctx) {
   if (ctx->own_stream) cudaStreamSynchronize(ctx->own_stream);
   if (ctx->scratch) cudaFree(ctx->scratch);
   if (ctx->counters) cudaFree(ctx->counters);
+  if (ctx->xprep) cudaFree(ctx->xprep);
   if (ctx->h_stage) cudaFreeHost(ctx->h_stage);
   if (ctx->d_stage) cudaFree(ctx->d_stage);
   if (ctx->ev0) cudaEventDestroy(ctx->ev0);

@@ -182,6 +182,9 @@ struct lmb_ctx {
   size_t scratch_floats = 0;
   unsigned *counters = nullptr;
   size_t n_counters = 0;
+  // activations prepared once per launch for batched GEMVs (digits, block scales, digit sums)
+  uint32_t *xprep = nullptr;
+  size_t xprep_blocks = 0;  // capacity in (sequence, block) pairs
   // staging buffers of the host-pointer entry points
   void *h_stage = nullptr;
   size_t h_stage_bytes = 0;

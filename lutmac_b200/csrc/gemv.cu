@@ -58,6 +58,9 @@ struct Job {
   unsigned x_len, x_stride, y_stride;
 };
 
+// One prepared (sequence, block): 256 words of digits in B-operand order, block scale, two digit-pair sums, pad.
+constexpr int PREP_WORDS = 256 + 4;
+
 struct GemvParams {
   Job job[MAX_JOBS];
   int njobs;
@@ -70,6 +73,9 @@ struct GemvParams {
   const Job *jobs_dev;
   const int2 *cta_map;
   PeerOut peer;  // peer.n > 0: job 0's output goes to every rank's exchange block
+  // activations already converted by k_prepare_x (batched launches whose jobs share one input):
+  // [sequence][block] records of PREP_WORDS words; null: every CTA converts its own slice
+  const uint32_t *prep;
 };
 
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
@@ -794,7 +800,7 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
   const unsigned epoch = p.peer.n ? *reinterpret_cast<volatile unsigned *>(p.peer.epoch) : 0u;
   const float *x = job.x + size_t(batch0) * job.x_stride;
   float *inv_rms = part[0];  // [sequence] after the block below (XMODE_RMSNORM)
-  if (p.xmode == XMODE_RMSNORM) {
+  if (p.xmode == XMODE_RMSNORM && !p.prep) {
     // RMSNorm of the whole input vectors (src/layers/norm.cpp:18-34), recomputed by every CTA
     float ss[NSEQ];
 #pragma unroll
@@ -821,7 +827,29 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
     }
     __syncthreads();
   }
-  {
+  if constexpr (kind_is_mma(KIND)) {
+    if (p.prep) {
+      // the launch's activations were converted once by k_prepare_x: copy this CTA's slice
+      const int items = ns * nb;
+      for (int it = warp; it < items; it += WARPS) {
+        const int q = NSEQ == 1 ? 0 : it / ns, bl = it - q * ns;
+        const uint32_t *src = p.prep + (size_t(batch0 + q) * job.bpr + b0 + bl) * PREP_WORDS;
+        uint4 *dst = reinterpret_cast<uint4 *>(smem + (size_t(q) * job.S + bl) * FPB);
+        const uint4 *s4 = reinterpret_cast<const uint4 *>(src);
+        dst[lane] = __ldg(s4 + lane);
+        dst[lane + 32] = __ldg(s4 + lane + 32);
+        if (lane == 0) {
+          const uint4 tail = __ldg(s4 + 64);  // {block scale, d01, d23, -}
+          int *aux = xaux + ((q >> 1) * 64 + bl) * 4;
+          xsum[q * 64 + bl] = __uint_as_float(tail.x);
+          aux[2 * (q & 1)] = int(tail.y);
+          aux[2 * (q & 1) + 1] = int(tail.z);
+          if ((q | 1) >= nb) aux[2] = aux[3] = 0;
+        }
+      }
+    }
+  }
+  if (!(kind_is_mma(KIND) && p.prep)) {
     // one warp per (sequence, block); the next item's activations are fetched while this one is converted
     float v[8], w8[8], nv[8];
     const int items = ns * nb;
@@ -897,7 +925,7 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
   }
 
   // combine the warps that share a row-tile, in warp order: thread t ends up with row rt0*32 + t
-  if (p.xmode == XMODE_RMSNORM) __syncthreads();  // inv_rms (in part[0]) has been read by everyone
+  if (p.xmode == XMODE_RMSNORM && !p.prep) __syncthreads();  // inv_rms (in part[0]) has been read by everyone
 #pragma unroll
   for (int q = 0; q < NSEQ; ++q) part[q][threadIdx.x] = acc[q];
   __syncthreads();
@@ -985,6 +1013,57 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
   }
   if (t == 0) *ctr = 0u;  // ready for the next launch
   leave();
+}
+
+// Conversion pass for batched launches: the activations of every (sequence, block) of the shared
+// input are normalised / gated / rotated and turned into fixed-point digits ONCE, instead of by
+// every CTA of the GEMV.  One warp per (sequence, block); grid = (ceil(bpr / 8), sequences).
+__global__ void __launch_bounds__(THREADS) k_prepare_x(const float *x, const float *x2, unsigned x_len, unsigned x_stride, int bpr,
+                                                       int xmode, int rotate, float eps, uint32_t *out) {
+  pdl_launch_dependents();
+  __shared__ float red[WARPS];
+  __shared__ __align__(16) float stage[WARPS][256];
+  __shared__ float bsc[WARPS];
+  __shared__ int aux2[WARPS][2];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, q = blockIdx.y;
+  const float *xq = x + size_t(q) * x_stride;
+  float inv_rms = 1.0f;
+  if (xmode == XMODE_RMSNORM) {
+    float ss = 0.0f;
+    for (unsigned i = threadIdx.x; i < x_len; i += THREADS) {
+      const float v = xq[i];
+      ss += v * v;
+    }
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    ss = 0.0f;
+#pragma unroll
+    for (int k = 0; k < WARPS; ++k) ss += red[k];
+    inv_rms = 1.0f / sqrtf(ss / float(x_len) + eps);
+  }
+  const int bl = blockIdx.x * WARPS + warp;
+  if (bl >= bpr) return;
+  float v[8], w8[8];
+  load_x8(xq, x_len, size_t(bl), lane, v);
+  if (xmode == XMODE_RMSNORM) {
+    load_x8(x2, x_len, size_t(bl), lane, w8);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = v[e] * inv_rms * w8[e];
+  } else if (xmode == XMODE_SILU_MUL) {
+    load_x8(x2 + size_t(q) * x_stride, x_len, size_t(bl), lane, w8);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = (v[e] / (1.0f + expf(-v[e]))) * w8[e];
+  }
+  if (rotate) fwht256_warp(v, lane);
+  mma_prologue(v, lane, stage[warp], &bsc[warp], aux2[warp]);
+  __syncwarp();
+  uint4 *dst = reinterpret_cast<uint4 *>(out + (size_t(q) * bpr + bl) * PREP_WORDS);
+  const uint4 *src = reinterpret_cast<const uint4 *>(stage[warp]);
+  dst[lane] = src[lane];
+  dst[lane + 32] = src[lane + 32];
+  if (lane == 0) dst[64] = make_uint4(__float_as_uint(bsc[warp]), uint32_t(aux2[warp][0]), uint32_t(aux2[warp][1]), 0u);
 }
 
 // Tables only (debug view used by the parity tests): the same prologue, one warp per block.
@@ -1266,6 +1345,36 @@ int launch_gemv(lmb_ctx *ctx, const LinearArgs *args, int njobs, bool rotate, in
   int ctas = 0, s_max = 1;
   int st = prepare_jobs(ctx, kind, args, njobs, p.job, &ctas, &s_max, nullptr);
   if (st != LMB_OK) return st;
+  // Batches of three or more sequences whose jobs read one input: convert the activations once
+  // for the whole launch instead of once per CTA.
+  p.prep = nullptr;
+  bool shared_x = seqs_per_pass(kind, args[0].batch) >= 4;
+  for (int j = 1; j < njobs && shared_x; ++j)
+    shared_x = args[j].x == args[0].x && args[j].x2 == args[0].x2 && args[j].x_len == args[0].x_len &&
+               args[j].x_stride == args[0].x_stride && args[j].w->bpr == args[0].w->bpr;
+  if (shared_x) {
+    const size_t bpr = args[0].w->bpr, need = args[0].batch * bpr;
+    if (need > ctx->xprep_blocks) {
+      cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+      LMB_CUDA(cudaStreamIsCapturing(ctx->stream, &cs));
+      if (cs == cudaStreamCaptureStatusNone) {
+        LMB_CUDA(cudaStreamSynchronize(ctx->stream));
+        if (ctx->xprep) LMB_CUDA(cudaFree(ctx->xprep));
+        ctx->xprep = nullptr;
+        ctx->xprep_blocks = 0;
+        LMB_CUDA(cudaMalloc(&ctx->xprep, need * PREP_WORDS * sizeof(uint32_t)));
+        ctx->xprep_blocks = need;
+      }
+    }
+    if (need <= ctx->xprep_blocks) {
+      dim3 grid(unsigned((bpr + WARPS - 1) / WARPS), unsigned(args[0].batch));
+      k_prepare_x<<<grid, THREADS, 0, ctx->stream>>>(args[0].x, args[0].x2, unsigned(args[0].x_len), unsigned(args[0].x_stride),
+                                                     int(bpr), xmode, rotate ? 1 : 0, eps, ctx->xprep);
+      ctx->launches++;
+      LMB_CUDA(cudaGetLastError());
+      p.prep = ctx->xprep;
+    }
+  }
   return launch_params_kind(ctx, kind, p, ctas, s_max, args[0].batch);
 }
 
@@ -1334,6 +1443,7 @@ int lmb_group_launch(lmb_ctx *ctx, lmb_group *g) {
   p.jobs_dev = g->d_jobs;
   p.cta_map = g->d_map;
   p.peer.n = 0;
+  p.prep = nullptr;
   return launch_params_kind(ctx, g->kind, p, g->ctas, g->s_max, 1);
 }
 
@@ -1502,6 +1612,7 @@ int lmb_linear_static_scratch(const lmb_weight *w, const float *d_bias, const fl
   p.jobs_dev = nullptr;
   p.cta_map = nullptr;
   p.peer.n = 0;
+  p.prep = nullptr;
   Job &jb = p.job[0];
   jb.tiles = w->d_tiles;
   jb.x = d_x;

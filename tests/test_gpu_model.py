@@ -67,6 +67,36 @@ def test_batched_decode_equals_independent_sequences(ctx, oracle):
     m.close()
 
 
+@pytest.mark.parametrize("env", [{"LMB_MODEL_FUSED": "0"}, {"LMB_MODEL_GRAPH": "0"}, {"LMB_MODEL_FUSED": "0", "LMB_MODEL_GRAPH": "0"}])
+def test_unfused_and_ungraphed_steps_match_the_fixtures(ctx, env, monkeypatch):
+    """The step can run without norm/activation fusion (the sequence tensor-parallel runs use)
+    and without graph capture; the switches are read when the model is created."""
+    for k, v in env.items():
+        monkeypatch.setenv(k, v)
+    g = np.load(os.path.join(GOLD, "model.npz"))
+    for name, kind, over in CASES[:2]:
+        spec = synth.model_spec(synth.tiny_model_shape(**over), kind, seed=11, max_seq=2048)
+        m = Model(spec, ctx)
+        for p, t in enumerate(g["tokens"]):
+            assert rel_l2(m.forward(int(t), p), g[name + "_logits"][p]) < TOL, (env, name, p)
+        m.close()
+
+
+def test_batch_of_eight_shares_the_weight_pass(ctx, oracle):
+    from oracle.oracle import OracleModel
+    spec = synth.model_spec(synth.tiny_model_shape(), TERNARY, seed=9, max_seq=32)
+    B = 8
+    m = Model(spec, ctx, max_batch=B)
+    oracles = [OracleModel(oracle, spec) for _ in range(B)]
+    rng = np.random.default_rng(2)
+    for p in range(4):
+        toks = rng.integers(0, spec.cfg["vocab"], size=B)
+        got = m.forward(toks, [p] * B)
+        for b in range(B):
+            assert rel_l2(got[b], oracles[b].forward(int(toks[b]), p)) < TOL, (p, b)
+    m.close()
+
+
 def test_model_errors(ctx):
     from lutmac_b200._lib import LutmacError
     spec = synth.model_spec(synth.tiny_model_shape(), INT4, seed=1, max_seq=8)
