@@ -1132,16 +1132,6 @@ Plan make_plan(int kind, size_t row_tiles, size_t bpr, size_t batch, int sm_coun
       }
     }
   }
-  if (const char *ov = std::getenv("LMB_PLAN")) {  // tuning aid: "R,n_ks"
-    int R = 0, nks = 0;
-    if (std::sscanf(ov, "%d,%d", &R, &nks) == 2 && (R == 8 || R == 4 || R == 2 || R == 1) && nks >= 1 && size_t(nks) <= bpr &&
-        (bpr + size_t(nks) - 1) / size_t(nks) <= s_cap) {
-      best.R = R;
-      best.n_rg = int((row_tiles + size_t(R) - 1) / size_t(R));
-      best.S = int((bpr + size_t(nks) - 1) / size_t(nks));
-      best.n_ks = int((bpr + size_t(best.S) - 1) / size_t(best.S));
-    }
-  }
   best.ctas = best.n_rg * best.n_ks;
   return best;
 }
