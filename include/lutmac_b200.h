@@ -267,9 +267,9 @@ int lmb_tp_destroy(lmb_ctx *ctx);
  * reference).  After lmb_tp_init every rank creates its exchange block (room for max_floats =
  * max batch x hidden size per partial vector) and gets a 64-byte inter-process handle; the host
  * gathers the handles of all ranks in rank order and every rank opens them.  From then on the
- * o_proj / down_proj kernels of lmb_model_forward store their partial outputs straight into
- * every rank's block and the following normalisation kernel waits (at most about a second) for
- * all ranks before it adds them; lmb_tp_peer_status reports whether a wait ever ran out.
+ * o_proj / down_proj kernels of lmb_model_forward store their partial outputs (tagged with an
+ * epoch) straight into every rank's block and the following normalisation kernel waits (at most
+ * about a second) for the words of all ranks before it adds them; lmb_tp_peer_status reports whether a wait ever ran out.
  * Without the block (or with LMB_TP_PEERS=0) the step uses lmb_allreduce_sum (NCCL). */
 int lmb_tp_peer_create(lmb_ctx *ctx, size_t max_floats, void *handle64_out);
 int lmb_tp_peer_open(lmb_ctx *ctx, const void *handles_rank_order);

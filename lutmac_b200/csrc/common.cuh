@@ -132,18 +132,19 @@ int cuda_fail(cudaError_t e, const char *what);
 // ---------------------------------------------------------------------------------------------
 namespace lmb {
 // One-shot all-reduce over peer memory (tensor parallelism, one process per GPU).  Every rank
-// owns one exchange block, mapped by all ranks: a header (arrival flags, epoch, CTA counter,
-// time-out flag) and the partial vectors [2 parities][ranks][cap floats].  The kernel that
-// produces a partial vector stores it into every rank's block; the kernel that consumes the sum
-// waits for the flags of all ranks and adds the partials in rank order.
+// owns one exchange block, mapped by all ranks: a header (epoch, CTA counter, time-out flag) and
+// the partial vectors [2 parities][ranks][cap] as 8-byte words {value, epoch tag}.  The kernel
+// that produces a partial vector stores every element, tagged, into every rank's block with one
+// 8-byte store (no fence, no separate flag); the kernel that consumes the sum reads each word
+// until its tag is the expected one and adds the partials in rank order.
 constexpr int MAX_TP = 8;
 constexpr size_t XCHG_HEADER_BYTES = 1024;
 struct XchgHeader {
-  unsigned flags[MAX_TP];  // flags[r] = number of partial vectors of rank r completed in this block
+  unsigned reserved[MAX_TP];
   unsigned pad0[24];
-  unsigned epoch;          // all-reduces this rank has produced
+  unsigned epoch;          // all-reduces this rank has consumed; the next vector carries the tag epoch + 1
   unsigned pad1[15];
-  unsigned done;           // CTAs of the running producer kernel that have finished
+  unsigned done;           // CTAs of the running consumer kernel that have finished
   unsigned pad2[15];
   unsigned timed_out;      // set when a consumer gave up waiting
 };
@@ -155,9 +156,8 @@ struct PeerXchg {
 };
 // What a GEMV launch needs to deliver its output to all ranks (n = 0: ordinary output).
 struct PeerOut {
-  float *data[MAX_TP];
-  unsigned *flags[MAX_TP];
-  unsigned *epoch, *done;
+  unsigned long long *data[MAX_TP];  // tagged words: value in the low half, epoch tag in the high half
+  unsigned *epoch;
   int n, rank;
   unsigned cap;
 };

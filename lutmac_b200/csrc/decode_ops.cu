@@ -148,34 +148,44 @@ __global__ void __launch_bounds__(1024) k_add_rmsnorm(float *hidden, const float
 }
 
 // Tensor-parallel form of k_add_rmsnorm: the vector to add is the sum over ranks of the partial
-// vectors in this rank's exchange block.  Waits (bounded) until every rank's partial of the
-// current epoch has arrived, adds them in rank order (so that every rank computes the same
-// bits), then normalises.  One CTA per sequence.
-__global__ void __launch_bounds__(1024) k_tp_sum_add_rmsnorm(float *hidden, XchgHeader *hdr, const float *data, int tp,
+// vectors in this rank's exchange block.  Every element is an 8-byte word {value, epoch tag}
+// written by its producer with one store; the reader polls the word (bounded) until the tag is
+// the expected one, adds the partials in rank order (so that every rank computes the same bits),
+// then normalises.  One CTA per sequence; the last CTA to finish advances the epoch.
+__device__ __forceinline__ unsigned long long ld_volatile_u64(const unsigned long long *p) {
+  unsigned long long v;
+  asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__global__ void __launch_bounds__(1024) k_tp_sum_add_rmsnorm(float *hidden, XchgHeader *hdr, const unsigned long long *data, int tp,
                                                              unsigned cap, const float *w, float *out, size_t h, float eps) {
   asm volatile("griddepcontrol.launch_dependents;");
   __shared__ float red[32];
-  const unsigned epoch = *reinterpret_cast<volatile unsigned *>(&hdr->epoch);  // already counts the vector to consume
-  if (int(threadIdx.x) < tp) {
-    const volatile unsigned *flag = hdr->flags + threadIdx.x;
-    unsigned spins = 0;
-    while (int(*flag - epoch) < 0) {
-      if (*reinterpret_cast<volatile unsigned *>(&hdr->timed_out) || ++spins > (1u << 22)) {  // about a second: give up, report, carry on with what is there
-        hdr->timed_out = 1u;
-        break;
-      }
-      __nanosleep(100);
-    }
-    __threadfence_system();  // the partial vectors were written before the flag
-  }
-  __syncthreads();
-  const float *part = data + size_t((epoch - 1u) & 1u) * tp * cap + size_t(blockIdx.x) * h;
+  const unsigned epoch = *reinterpret_cast<volatile unsigned *>(&hdr->epoch);
+  const unsigned tag = epoch + 1u;
+  const unsigned long long *part = data + size_t(epoch & 1u) * tp * cap + size_t(blockIdx.x) * h;
   float *x = hidden + size_t(blockIdx.x) * h;
   float *o = out + size_t(blockIdx.x) * h;
   float ss = 0.0f;
+  bool gave_up = *reinterpret_cast<volatile unsigned *>(&hdr->timed_out) != 0u;
   for (size_t i = threadIdx.x; i < h; i += blockDim.x) {
     float add = 0.0f;
-    for (int r = 0; r < tp; ++r) add += __ldcg(part + size_t(r) * cap + i);
+    for (int r = 0; r < tp; ++r) {
+      const unsigned long long *src = part + size_t(r) * cap + i;
+      unsigned long long word = ld_volatile_u64(src);
+      unsigned spins = 0;
+      while (unsigned(word >> 32) != tag && !gave_up) {
+        if (++spins > (1u << 22)) {  // about a second: give up, report, carry on with what is there
+          hdr->timed_out = 1u;
+          gave_up = true;
+          break;
+        }
+        __nanosleep(40);
+        word = ld_volatile_u64(src);
+      }
+      add += __uint_as_float(unsigned(word));
+    }
     const float v = x[i] + add;
     x[i] = v;
     ss += v * v;
@@ -183,6 +193,11 @@ __global__ void __launch_bounds__(1024) k_tp_sum_add_rmsnorm(float *hidden, Xchg
   ss = block_sum(ss, red);
   const float inv = 1.0f / sqrtf(ss / float(h) + eps);
   for (size_t i = threadIdx.x; i < h; i += blockDim.x) o[i] = x[i] * inv * w[i];
+  __syncthreads();
+  if (threadIdx.x == 0 && atomicAdd(&hdr->done, 1u) == gridDim.x - 1u) {
+    hdr->done = 0u;
+    *reinterpret_cast<volatile unsigned *>(&hdr->epoch) = tag;  // read by the next producer, a later kernel
+  }
 }
 
 // Split-KV decode attention with the q/k/v bias, the rotary embedding and the KV-cache write of
@@ -447,7 +462,8 @@ int launch_tp_sum_add_rmsnorm(lmb_ctx *ctx, float *d_hidden, const float *d_w, f
   }
   const int threads = h >= 4096 ? 1024 : (h >= 1024 ? 512 : 256);
   XchgHeader *hdr = static_cast<XchgHeader *>(ctx->xchg.local);
-  const float *data = reinterpret_cast<const float *>(static_cast<const char *>(ctx->xchg.local) + XCHG_HEADER_BYTES);
+  const unsigned long long *data =
+      reinterpret_cast<const unsigned long long *>(static_cast<const char *>(ctx->xchg.local) + XCHG_HEADER_BYTES);
   k_tp_sum_add_rmsnorm<<<unsigned(batch), threads, 0, ctx->stream>>>(d_hidden, hdr, data, ctx->tp_size, unsigned(ctx->xchg.cap),
                                                                      d_w, d_out, h, eps);
   ctx->launches++;

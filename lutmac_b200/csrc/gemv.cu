@@ -949,22 +949,10 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
     if (p.peer.n == 0) {
       job.y[at] = o;
     } else {
+      // value and tag travel in one 8-byte store: the reader needs no fence and no separate flag
       const size_t slot = (size_t(epoch & 1u) * p.peer.n + p.peer.rank) * p.peer.cap + at;
-      for (int r = 0; r < p.peer.n; ++r) p.peer.data[r][slot] = o;
-    }
-  };
-  // every CTA reports in before it leaves; the last one of the launch publishes the vector
-  auto leave = [&]() {
-    if (p.peer.n == 0) return;
-    __syncthreads();
-    if (t == 0) {
-      __threadfence_system();
-      if (atomicAdd(p.peer.done, 1u) == gridDim.x * gridDim.y - 1u) {
-        *p.peer.done = 0u;
-        *reinterpret_cast<volatile unsigned *>(p.peer.epoch) = epoch + 1u;
-        __threadfence_system();
-        for (int r = 0; r < p.peer.n; ++r) *reinterpret_cast<volatile unsigned *>(p.peer.flags[r] + p.peer.rank) = epoch + 1u;
-      }
+      const unsigned long long word = (static_cast<unsigned long long>(epoch + 1u) << 32) | __float_as_uint(o);
+      for (int r = 0; r < p.peer.n; ++r) *reinterpret_cast<volatile unsigned long long *>(p.peer.data[r] + slot) = word;
     }
   };
   if (job.n_ks == 1) {
@@ -979,7 +967,6 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
           emit(q, o);
         }
     }
-    leave();
     return;
   }
   // split K: publish the partial sums, the last slice to arrive adds them in slice order
@@ -996,10 +983,7 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
     __threadfence();
   }
   __syncthreads();
-  if (!is_last) {  // uniform over the CTA
-    leave();
-    return;
-  }
+  if (!is_last) return;  // uniform over the CTA
   if (owns_row && row < job.M) {
     const float bias = job.bias ? job.bias[row] : 0.0f;
 #pragma unroll
@@ -1014,7 +998,6 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
       }
   }
   if (t == 0) *ctr = 0u;  // ready for the next launch
-  leave();
 }
 
 // Conversion pass for batched launches: the activations of every (sequence, block) of the shared
@@ -1338,11 +1321,8 @@ int launch_gemv(lmb_ctx *ctx, const LinearArgs *args, int njobs, bool rotate, in
     p.peer.cap = unsigned(ctx->xchg.cap);
     XchgHeader *mine = static_cast<XchgHeader *>(ctx->xchg.local);
     p.peer.epoch = &mine->epoch;
-    p.peer.done = &mine->done;
-    for (int r = 0; r < ctx->tp_size; ++r) {
-      p.peer.flags[r] = static_cast<XchgHeader *>(ctx->xchg.peer[r])->flags;
-      p.peer.data[r] = reinterpret_cast<float *>(static_cast<char *>(ctx->xchg.peer[r]) + XCHG_HEADER_BYTES);
-    }
+    for (int r = 0; r < ctx->tp_size; ++r)
+      p.peer.data[r] = reinterpret_cast<unsigned long long *>(static_cast<char *>(ctx->xchg.peer[r]) + XCHG_HEADER_BYTES);
   }
   int ctas = 0, s_max = 1;
   int st = prepare_jobs(ctx, kind, args, njobs, p.job, &ctas, &s_max, nullptr);

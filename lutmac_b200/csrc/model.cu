@@ -138,7 +138,7 @@ int lmb_tp_peer_create(lmb_ctx *ctx, size_t max_floats, void *handle64_out) {
   static_assert(sizeof(XchgHeader) <= XCHG_HEADER_BYTES, "exchange header size");
   LMB_CUDA(cudaSetDevice(ctx->device));
   const size_t cap = (max_floats + 63) / 64 * 64;
-  const size_t bytes = XCHG_HEADER_BYTES + size_t(2) * ctx->tp_size * cap * sizeof(float);
+  const size_t bytes = XCHG_HEADER_BYTES + size_t(2) * ctx->tp_size * cap * sizeof(unsigned long long);
   void *blk = nullptr;
   LMB_CUDA(cudaMalloc(&blk, bytes));
   cudaError_t e = cudaMemset(blk, 0, bytes);
