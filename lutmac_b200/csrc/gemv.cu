@@ -1,37 +1,38 @@
 // GEMV kernels for every block kind, with the lut_linear prologue (zero padding, block-wise
-// FWHT rotation, group-of-4 table construction) and epilogue (block scales, RRQ residual
-// plane, bias) fused in.
+// FWHT rotation, optional RMSNorm or SiLU*up of the input) and epilogue (block scales, RRQ
+// residual plane, bias, residual add) fused in.
 //
-// Replaces, for the bit-plane kinds (ternary, binary, RRQ 2-bit, 3-bit): lut_gemv /
-// lut_gemv_binary / int2_gemv / int3_gemv (include/lutmac/lut_gemm.hpp:172-334, scalar loops
-// src/kernels/lut_gemm_scalar.cpp:7-61,228-259,298-350) in the lookup formulation of the
-// reference's table kernels -- ternary L[pos]-L[neg] (lut_gemm_simd.cpp:203-221), n-bit planes
-// sum_p 2^p L[idx_p] - zero_point*L[15] (lut_gemm_simd.cpp:352-366), RRQ primary*scale +
-// residual*scale2 (lut_gemm_simd.cpp:326-328) -- and for the nibble/byte kinds (4-bit, 8-bit):
-// int4_gemv / int8_gemv (lut_gemm.hpp:238-250,396-408; lut_gemm_scalar.cpp:186-222,265-292).
-// Prologue/epilogue: lut_linear (lut_gemm_scalar.cpp:85-113,174-178), precompute_luts
-// (lut_gemm.hpp:53-58), apply_hadamard_rotation (transform_simd.cpp:101-110).
+// Replaces lut_gemv / lut_gemv_binary / int2_gemv ... int8_gemv (include/lutmac/lut_gemm.hpp:
+// 172-408, scalar loops src/kernels/lut_gemm_scalar.cpp:7-61,186-428) and lut_linear
+// (lut_gemm_scalar.cpp:85-113,174-178) with precompute_luts (lut_gemm.hpp:53-58) and
+// apply_hadamard_rotation (transform_simd.cpp:101-110).  Two formulations:
+//   * integer tensor-core units (default for every kind): the weight tile is stored in the
+//     operand order of the 8-bit integer MMA with several rows sharing the bits of a byte, so an
+//     `and` with a mask yields an operand register; the activations of a 256-block become 32-bit
+//     fixed point with one exponent, cut into four signed base-256 digits (the B operand);
+//     sums are exact integers, the code's zero point is removed with the digit sums;
+//   * table-lookup units (the reference's own formulation, selectable): ternary L[pos]-L[neg]
+//     (lut_gemm_simd.cpp:203-221), n-bit planes sum_p 2^p L[idx_p] - zero_point*L[15]
+//     (lut_gemm_simd.cpp:352-366), RRQ primary*scale + residual*scale2 (lut_gemm_simd.cpp:
+//     326-328), with 16-entry group tables in shared memory; 8-bit as dequantise + FMA.
 //
 // Work decomposition.  One launch serves up to MAX_JOBS independent GEMVs of one kind (q/k/v
-// or gate/up of a layer share a launch).  A CTA of 8 warps owns a work item = (job, group of R
-// row-tiles of 32 rows, slice of S consecutive 256-column blocks).  A warp streams the weight
-// tiles of one row-tile, one row per lane, with 128-bit coalesced loads.  Bit-plane kinds look
-// each 4-bit plane nibble up in the 16-entry table of its group: all lanes of a warp address
-// the same 64-byte table, 16 entries in 16 distinct banks, so lookups never conflict.  When K
-// is split over several CTAs, partial sums go to a scratch buffer and the last CTA to arrive
-// for a row group adds them in slice order (deterministic).
+// or gate/up of a layer share a launch), any number through a prepared group.  A CTA of 8
+// warps owns a work item = (job, group of R row-tiles of 32 rows, slice of S consecutive
+// 256-column blocks).  A warp streams weight tiles with 128-bit coalesced loads through a ring
+// of register slots.  When K is split over several CTAs, partial sums go to a scratch buffer
+// and the last CTA to arrive for a row group adds them in slice order (deterministic).
+// Batches: 2, 4 or 8 sequences share one pass over the weights on the tensor-core units.
 //
 // Programmatic dependent launch: a kernel lets its successor start at once, the successor
 // prefetches its first weight tiles (weights never depend on a predecessor) and only then
 // waits for the predecessor's results before touching activations or writing anything.
+#include <algorithm>
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <vector>
-
-#include <cstdlib>
-
-#include <algorithm>
-#include <cstdio>
 #include <cstdlib>
 
 #include "common.cuh"
@@ -238,7 +239,7 @@ __device__ __forceinline__ void dq_prologue(const float (&v)[8], int lane, float
 }
 
 // ---------------------------------------------------------------------------------------------
-// 4-bit kind on the integer tensor-core path.  The dequantise+FMA form above costs about four
+// Integer tensor-core path.  A dequantise+FMA form of the 4-bit kernel cost about four
 // issue slots per weight and is bound by instruction issue at 0.3 of HBM bandwidth (ncu), so
 // the 4-bit codes are fed to the 8-bit integer MMA as they are (two masks per 8 codes) and the
 // activations are turned, once per 256-block, into 32-bit fixed point with a shared exponent,
