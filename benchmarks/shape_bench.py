@@ -1,4 +1,4 @@
-"""Per-shape GEMV timing: `python -m lutmac_b200.shape_bench --kind ternary --M 28672 --K 8192`.
+"""Per-shape GEMV timing: `python -m benchmarks.shape_bench --kind ternary --M 28672 --K 8192`.
 
 Uploads enough copies of one synthetic matrix that a pass over all of them exceeds L2, issues one
 `lmb_linear` per copy (captured once as a CUDA graph unless --no-graph) and reports the time per
@@ -12,9 +12,9 @@ import json
 
 import numpy as np
 
-from . import _lib, synth
-from .api import Context
-from .blocks import KIND_NAMES, algorithmic_bytes
+from lutmac_b200 import _lib, synth
+from lutmac_b200.api import Context
+from lutmac_b200.blocks import KIND_NAMES, algorithmic_bytes
 
 KIND_BY_NAME = {v: k for k, v in KIND_NAMES.items()}
 L2_BYTES = 126e6
@@ -80,7 +80,7 @@ def main(argv=None):
 
         import torch.distributed as dist
 
-        from . import tp
+        from lutmac_b200 import tp
         rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
         dist.init_process_group("gloo")  # rendezvous only; the data path is NCCL inside the library
         ctx = Context(int(os.environ.get("LOCAL_RANK", rank)))
@@ -93,7 +93,6 @@ def main(argv=None):
         from .decode_bench import run_decode
         out = run_decode(ctx, a.decode, KIND_BY_NAME[a.kind], a.context, a.batch, steps=a.steps, random_kv=a.random_kv,
                          shared_layers=a.shared_layers, tp_rank=rank, tp_size=world)
-        out["tp"] = world
     else:
         out = run_shape(ctx, KIND_BY_NAME[a.kind], a.M, a.K, a.copies, a.reps, not a.no_graph,
                         0 if a.no_rotate else _lib.AUTO_ROTATE)

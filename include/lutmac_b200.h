@@ -69,8 +69,10 @@ int lmb_ctx_sync(lmb_ctx *ctx);
 /* Options.  LMB_OPT_TERNARY_LUT = 1: ternary, INT2, INT3 and binary weights uploaded afterwards
  * use the table-lookup kernel (16-entry group tables, the reference's LUT formulation), INT8
  * weights the dequantise+FMA kernel, instead of the default integer tensor-core kernels.  LMB_OPT_PDL = 0: plain stream order instead of programmatic dependent
- * launch between consecutive kernels. */
-enum { LMB_OPT_TERNARY_LUT = 1, LMB_OPT_PDL = 2 };
+ * launch between consecutive kernels.
+ * LMB_OPT_SCRATCH_FLOATS = n: reallocate the split-K scratch at n floats (it starts at 4 Mi floats
+ * and grows on demand; graphs and groups made earlier notice the reallocation and are rebuilt). */
+enum { LMB_OPT_TERNARY_LUT = 1, LMB_OPT_PDL = 2, LMB_OPT_SCRATCH_FLOATS = 3 };
 int lmb_ctx_set_option(lmb_ctx *ctx, int option, int value);
 int lmb_device_count(int *out);
 /* Number of kernels this library has launched on the context since creation. */
@@ -195,6 +197,8 @@ int lmb_apply_hadamard_rotation_host(float *data, size_t n);         /* in place
  * kind is a device layout kind as reported by lmb_weight_info; other_rows = rows of the other
  * jobs of the same launch. */
 int lmb_debug_plan(int kind, size_t M, size_t K, size_t batch, size_t other_rows, int sm_count, int out5[5]);
+/* The same for a batch-1 launch of a resident weight alone (uses the weight's device layout kind). */
+int lmb_debug_plan_weight(const lmb_weight *w, int sm_count, int out5[5]);
 int lmb_debug_luts(lmb_ctx *ctx, const float *d_x, size_t x_len, unsigned flags, float *d_luts_out);
 /* Ternary LUT indices as the kernel consumes them: for every row and group of 4 weights the
  * (pos, neg) nibbles of extract_indices (lut_gemm.hpp:79-99); out = M*ceil(K/256)*64*2 bytes. */
@@ -224,6 +228,10 @@ int lmb_model_destroy(lmb_model *m);
 /* Full (unsharded) reference block arrays; the model keeps only its tensor-parallel shard. */
 int lmb_model_set_weight(lmb_model *m, int layer, int slot, int kind, int quant_bits, const void *blocks,
                          size_t M, size_t K);
+/* lm_head = embed_tokens without a second device copy: what load_model does when the file has
+ * no lm_head tensor (src/model.cpp:667-689).  Unsharded models only; a sharded model keeps its
+ * vocabulary rows of the head through lmb_model_set_weight(LMB_SLOT_LM_HEAD). */
+int lmb_model_tie_head(lmb_model *m);
 int lmb_model_set_vector(lmb_model *m, int layer, int which, const float *data, size_t n);
 /* One decode step for `batch` sequences: token_ids[b] at positions[b].  h_logits is NULL or
  * batch*vocab floats on the host. */
@@ -231,7 +239,8 @@ int lmb_model_forward(lmb_model *m, const int *token_ids, const size_t *position
 int lmb_model_logits_dev(lmb_model *m, const float **d_logits);
 int lmb_model_reset(lmb_model *m);
 /* KV cache exchange in the reference layout [layer][2][max_seq][kv_heads][head_dim]
- * (types.hpp:599-627) for sequence `seq`. */
+ * (types.hpp:599-627) for sequence `seq`.  The host buffer always has the layout of the whole
+ * model; a tensor-parallel rank reads / fills only the columns of its own KV heads. */
 int lmb_model_kv_export(lmb_model *m, size_t seq, float *h_out);
 int lmb_model_kv_import(lmb_model *m, size_t seq, const float *h_in);
 /* Algorithmic bytes one decode step reads at the given context length (weights + KV + embedding row). */
@@ -270,10 +279,18 @@ int lmb_tp_destroy(lmb_ctx *ctx);
  * o_proj / down_proj kernels of lmb_model_forward store their partial outputs (tagged with an
  * epoch) straight into every rank's block and the following normalisation kernel waits (at most
  * about a second) for the words of all ranks before it adds them; lmb_tp_peer_status reports whether a wait ever ran out.
+ * lmb_model_forward returns LMB_ERR_TIMEOUT for a step whose logits it fetched after a wait ran out.
  * Without the block (or with LMB_TP_PEERS=0) the step uses lmb_allreduce_sum (NCCL). */
 int lmb_tp_peer_create(lmb_ctx *ctx, size_t max_floats, void *handle64_out);
 int lmb_tp_peer_open(lmb_ctx *ctx, const void *handles_rank_order);
 int lmb_tp_peer_status(lmb_ctx *ctx, int *timed_out);
+/* Self-test of that bounded wait on ONE GPU, without NCCL and without a second process: builds a
+ * local exchange block for `ranks` ranks, posts the tagged partial vectors of the first `posted`
+ * ranks only (rank r contributes the value r + 1 in every element), runs the consumer kernel once
+ * with `spin_limit` polls per word and reports out4 = {timed_out flag, epoch afterwards, CTA
+ * counter afterwards, 1 if the hidden vector equals the sum of the posted partials}.  With
+ * posted < ranks the wait runs out and the kernel returns by itself: nothing faults or hangs. */
+int lmb_debug_tp_wait(lmb_ctx *ctx, int ranks, int posted, size_t h, unsigned spin_limit, int out4[4]);
 int lmb_allreduce_sum(lmb_ctx *ctx, float *d_buf, size_t n_floats);
 int lmb_allgather(lmb_ctx *ctx, const float *d_send, float *d_recv, size_t n_floats_per_rank);
 

@@ -19,6 +19,7 @@ ROTATE = 1
 AUTO_ROTATE = 2
 OPT_TERNARY_LUT = 1
 OPT_PDL = 2
+OPT_SCRATCH_FLOATS = 3
 
 f32p = C.POINTER(C.c_float)
 vp = C.c_void_p
@@ -79,11 +80,13 @@ SIGNATURES = {
     "lmb_fwht256": (C.c_int, [vp, vp, sz]),
     "lmb_apply_hadamard_rotation_host": (C.c_int, [vp, sz]),
     "lmb_debug_plan": (C.c_int, [C.c_int, sz, sz, sz, sz, C.c_int, C.POINTER(C.c_int)]),
+    "lmb_debug_plan_weight": (C.c_int, [vp, C.c_int, C.POINTER(C.c_int)]),
     "lmb_debug_luts": (C.c_int, [vp, vp, sz, C.c_uint, vp]),
     "lmb_debug_ternary_indices": (C.c_int, [vp, vp, vp]),
     "lmb_model_create": (C.c_int, [vp, C.POINTER(ModelConfig), C.POINTER(vp)]),
     "lmb_model_destroy": (C.c_int, [vp]),
     "lmb_model_set_weight": (C.c_int, [vp, C.c_int, C.c_int, C.c_int, C.c_int, vp, sz, sz]),
+    "lmb_model_tie_head": (C.c_int, [vp]),
     "lmb_model_set_vector": (C.c_int, [vp, C.c_int, C.c_int, vp, sz]),
     "lmb_model_forward": (C.c_int, [vp, C.POINTER(C.c_int), C.POINTER(sz), sz, vp]),
     "lmb_model_logits_dev": (C.c_int, [vp, C.POINTER(vp)]),
@@ -105,6 +108,7 @@ SIGNATURES = {
     "lmb_tp_peer_create": (C.c_int, [vp, sz, vp]),
     "lmb_tp_peer_open": (C.c_int, [vp, vp]),
     "lmb_tp_peer_status": (C.c_int, [vp, C.POINTER(C.c_int)]),
+    "lmb_debug_tp_wait": (C.c_int, [vp, C.c_int, C.c_int, sz, C.c_uint, C.POINTER(C.c_int)]),
     "lmb_allreduce_sum": (C.c_int, [vp, vp, sz]),
     "lmb_allgather": (C.c_int, [vp, vp, vp, sz]),
 }

@@ -31,6 +31,7 @@ int ensure_scratch(lmb_ctx *ctx, size_t floats, size_t counters) {
     ctx->scratch_floats = 0;
     LMB_CUDA(cudaMalloc(&ctx->scratch, floats * sizeof(float)));
     ctx->scratch_floats = floats;
+    ctx->scratch_gen++;
   }
   if (counters > ctx->n_counters) {
     if (ctx->counters) LMB_CUDA(cudaFree(ctx->counters));
@@ -39,6 +40,7 @@ int ensure_scratch(lmb_ctx *ctx, size_t floats, size_t counters) {
     LMB_CUDA(cudaMalloc(&ctx->counters, counters * sizeof(unsigned)));
     LMB_CUDA(cudaMemsetAsync(ctx->counters, 0, counters * sizeof(unsigned), ctx->stream));
     ctx->n_counters = counters;
+    ctx->scratch_gen++;
   }
   return LMB_OK;
 }
@@ -216,6 +218,15 @@ int lmb_ctx_set_option(lmb_ctx *ctx, int option, int value) {
   switch (option) {
   case LMB_OPT_TERNARY_LUT: ctx->ternary_lut = value != 0; return LMB_OK;
   case LMB_OPT_PDL: ctx->pdl = value != 0; return LMB_OK;
+  case LMB_OPT_SCRATCH_FLOATS: {
+    LMB_REQUIRE(value > 0, "lmb_ctx_set_option: the scratch size must be positive");
+    LMB_CUDA(cudaStreamSynchronize(ctx->stream));
+    if (ctx->scratch) LMB_CUDA(cudaFree(ctx->scratch));
+    ctx->scratch = nullptr;
+    ctx->scratch_floats = 0;
+    ctx->scratch_gen++;
+    return ensure_scratch(ctx, size_t(value), 0);
+  }
   default: set_last_error("lmb_ctx_set_option: unknown option"); return LMB_ERR_ARG;
   }
 }
@@ -297,6 +308,7 @@ int lmb_timer_stop(lmb_ctx *ctx, float *ms_out) {
 struct lmb_graph {
   cudaGraphExec_t exec = nullptr;
   uint64_t launches = 0;  // kernels captured in the graph
+  uint64_t scratch_gen = 0;  // lmb_ctx::scratch_gen at capture: the graph holds the scratch pointers of that generation
 };
 
 int lmb_graph_begin(lmb_ctx *ctx) {
@@ -323,6 +335,7 @@ int lmb_graph_end(lmb_ctx *ctx, lmb_graph **out) {
     return cuda_fail(e, "cudaGraphInstantiate");
   }
   h->launches = ctx->launches - ctx->capture_base;
+  h->scratch_gen = ctx->scratch_gen;
   ctx->launches = ctx->capture_base;  // captured launches have not run yet
   *out = h;
   return LMB_OK;
@@ -330,6 +343,11 @@ int lmb_graph_end(lmb_ctx *ctx, lmb_graph **out) {
 
 int lmb_graph_launch(lmb_ctx *ctx, lmb_graph *g) {
   LMB_REQUIRE(ctx && g && g->exec, "lmb_graph_launch: null argument");
+  if (g->scratch_gen != ctx->scratch_gen) {
+    set_last_error("lmb_graph_launch: the context's split-K scratch was reallocated after this graph was captured "
+                   "(a later call needed more); capture the graph again");
+    return LMB_ERR_STATE;
+  }
   LMB_CUDA(cudaGraphLaunch(g->exec, ctx->stream));
   ctx->launches += g->launches;
   return LMB_OK;

@@ -150,6 +150,7 @@ struct XchgHeader {
 };
 struct PeerXchg {
   bool ready = false;
+  unsigned spin_limit = 1u << 22;  // polls (about 40 ns apart) before a consumer gives up: about a second
   size_t cap = 0;            // floats per (parity, rank) slot
   void *local = nullptr;     // this rank's block
   void *peer[MAX_TP] = {};   // every rank's block as mapped here (own block included)
@@ -178,6 +179,9 @@ struct lmb_ctx {
   bool pdl = true;
   bool ternary_lut = false;  // upload ternary weights for the table-lookup kernel instead of the MMA kernel  // programmatic dependent launch between consecutive kernels
   // scratch for split-K partial sums and its arrival counters (grown on demand)
+  // scratch_gen counts reallocations of scratch / counters / xprep: a captured graph holds the raw
+  // pointers and must be captured again when the generation it was captured under is gone
+  uint64_t scratch_gen = 0;
   float *scratch = nullptr;
   size_t scratch_floats = 0;
   unsigned *counters = nullptr;
@@ -226,7 +230,7 @@ int launch_gemv(lmb_ctx *ctx, const LinearArgs *args, int njobs, bool rotate, in
 int launch_fwht256(lmb_ctx *ctx, float *d_x, size_t n);
 int launch_debug_luts(lmb_ctx *ctx, const float *d_x, size_t x_len, bool rotate, float *d_out);
 
-int model_tie_head(lmb_model *m);
+int model_tie_head(lmb_model *m);  // definition of lmb_model_tie_head
 int ensure_scratch(lmb_ctx *ctx, size_t floats, size_t counters);
 int ensure_stage(lmb_ctx *ctx, size_t bytes);
 

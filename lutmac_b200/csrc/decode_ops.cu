@@ -159,7 +159,8 @@ __device__ __forceinline__ unsigned long long ld_volatile_u64(const unsigned lon
 }
 
 __global__ void __launch_bounds__(1024) k_tp_sum_add_rmsnorm(float *hidden, XchgHeader *hdr, const unsigned long long *data, int tp,
-                                                             unsigned cap, const float *w, float *out, size_t h, float eps) {
+                                                             unsigned cap, const float *w, float *out, size_t h, float eps,
+                                                             unsigned spin_limit) {
   asm volatile("griddepcontrol.launch_dependents;");
   __shared__ float red[32];
   const unsigned epoch = *reinterpret_cast<volatile unsigned *>(&hdr->epoch);
@@ -176,7 +177,7 @@ __global__ void __launch_bounds__(1024) k_tp_sum_add_rmsnorm(float *hidden, Xchg
       unsigned long long word = ld_volatile_u64(src);
       unsigned spins = 0;
       while (unsigned(word >> 32) != tag && !gave_up) {
-        if (++spins > (1u << 22)) {  // about a second: give up, report, carry on with what is there
+        if (++spins > spin_limit) {  // give up, report, carry on with what is there
           hdr->timed_out = 1u;
           gave_up = true;
           break;
@@ -465,7 +466,7 @@ int launch_tp_sum_add_rmsnorm(lmb_ctx *ctx, float *d_hidden, const float *d_w, f
   const unsigned long long *data =
       reinterpret_cast<const unsigned long long *>(static_cast<const char *>(ctx->xchg.local) + XCHG_HEADER_BYTES);
   k_tp_sum_add_rmsnorm<<<unsigned(batch), threads, 0, ctx->stream>>>(d_hidden, hdr, data, ctx->tp_size, unsigned(ctx->xchg.cap),
-                                                                     d_w, d_out, h, eps);
+                                                                     d_w, d_out, h, eps, ctx->xchg.spin_limit);
   ctx->launches++;
   LMB_CUDA(cudaGetLastError());
   return LMB_OK;

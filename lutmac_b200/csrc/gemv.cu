@@ -31,9 +31,9 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 #include <new>
 #include <vector>
-#include <cstdlib>
 
 #include "common.cuh"
 #include "device_utils.cuh"
@@ -1347,6 +1347,7 @@ int launch_gemv(lmb_ctx *ctx, const LinearArgs *args, int njobs, bool rotate, in
         ctx->xprep_blocks = 0;
         LMB_CUDA(cudaMalloc(&ctx->xprep, need * PREP_WORDS * sizeof(uint32_t)));
         ctx->xprep_blocks = need;
+        ctx->scratch_gen++;
       }
     }
     if (need <= ctx->xprep_blocks) {
@@ -1367,6 +1368,11 @@ int launch_gemv(lmb_ctx *ctx, const LinearArgs *args, int njobs, bool rotate, in
 struct lmb_group {
   int kind = 0, ctas = 0, s_max = 1, njobs = 0;
   bool rotate = false;
+  // the job table holds pointers into the context's split-K scratch: it is rebuilt when the
+  // scratch has been reallocated since (lmb_ctx::scratch_gen)
+  uint64_t scratch_gen = 0;
+  std::vector<lmb::LinearArgs> args;
+  size_t map_entries = 0;
   lmb::Job *d_jobs = nullptr;
   int2 *d_map = nullptr;
   // host-buffer form (lmb_group_create_host): the group owns contiguous device and pinned
@@ -1400,6 +1406,9 @@ int lmb_group_create(lmb_ctx *ctx, size_t n, const lmb_weight *const *ws, const 
   g->njobs = int(n);
   g->rotate = (flags & LMB_ROTATE) || ((flags & LMB_AUTO_ROTATE) && auto_rot);
   int st = prepare_jobs(ctx, kind, args.data(), int(n), jobs.data(), &g->ctas, &g->s_max, &map);
+  g->scratch_gen = ctx->scratch_gen;
+  g->args = args;
+  g->map_entries = map.size();
   if (st == LMB_OK) {
     cudaError_t e = cudaMalloc(&g->d_jobs, n * sizeof(Job));
     if (e == cudaSuccess) e = cudaMalloc(&g->d_map, map.size() * sizeof(int2));
@@ -1418,6 +1427,23 @@ int lmb_group_create(lmb_ctx *ctx, size_t n, const lmb_weight *const *ws, const 
 int lmb_group_launch(lmb_ctx *ctx, lmb_group *g) {
   using namespace lmb;
   LMB_REQUIRE(ctx && g, "lmb_group_launch: null argument");
+  if (g->scratch_gen != ctx->scratch_gen) {
+    // same shapes, same plan: only the scratch addresses inside the job table change
+    std::vector<Job> jobs(g->args.size());
+    std::vector<int2> map;
+    int ctas = 0, s_max = 1;
+    int st = prepare_jobs(ctx, g->kind, g->args.data(), g->njobs, jobs.data(), &ctas, &s_max, &map);
+    if (st != LMB_OK) return st;
+    if (ctas != g->ctas || map.size() != g->map_entries) {
+      set_last_error("lmb_group_launch: the group's plan changed; create the group again");
+      return LMB_ERR_STATE;
+    }
+    LMB_CUDA(cudaStreamSynchronize(ctx->stream));
+    LMB_CUDA(cudaMemcpy(g->d_jobs, jobs.data(), jobs.size() * sizeof(Job), cudaMemcpyHostToDevice));
+    LMB_CUDA(cudaMemcpy(g->d_map, map.data(), map.size() * sizeof(int2), cudaMemcpyHostToDevice));
+    g->s_max = s_max;
+    g->scratch_gen = ctx->scratch_gen;
+  }
   GemvParams p;
   p.njobs = g->njobs;
   p.rotate = g->rotate ? 1 : 0;
@@ -1522,6 +1548,12 @@ int lmb_debug_plan(int kind, size_t M, size_t K, size_t batch, size_t other_rows
   return LMB_OK;
 }
 
+int lmb_debug_plan_weight(const lmb_weight *w, int sm_count, int out5[5]) {
+  using namespace lmb;
+  LMB_REQUIRE(w && out5 && sm_count > 0, "lmb_debug_plan_weight: bad argument");
+  return lmb_debug_plan(w->kind, w->M, w->K, 1, 0, sm_count, out5);
+}
+
 int lmb_group_host_io(lmb_group *g, size_t i, float **h_in, float **h_out) {
   using namespace lmb;
   LMB_REQUIRE(g && g->d_io && i < size_t(g->njobs), "lmb_group_host_io: not a host group, or index out of range");
@@ -1546,6 +1578,7 @@ struct StaticSetup {
   int sm_count = 0;
 };
 StaticSetup g_static_setup[64];  // per device ordinal
+std::mutex g_static_setup_mu;    // two host threads may make their first call at once
 }  // namespace
 
 int lmb_linear_static_scratch(const lmb_weight *w, const float *d_bias, const float *d_x, size_t x_len, float *d_y,
@@ -1558,6 +1591,8 @@ int lmb_linear_static_scratch(const lmb_weight *w, const float *d_bias, const fl
   LMB_REQUIRE(dev == w->device, "lmb_linear_static_scratch: the weight's device is not the current device");
   LMB_REQUIRE(dev >= 0 && dev < 64, "lmb_linear_static_scratch: device ordinal beyond 63");
   StaticSetup &su = g_static_setup[dev];
+  {
+  std::lock_guard<std::mutex> setup_lock(g_static_setup_mu);  // first calls from several host threads set up once
   if (!su.ready) {
     // Once per device, with that device current.  In host code the array names are only handles:
     // the device addresses the kernel needs come from cudaGetSymbolAddress.
@@ -1572,6 +1607,7 @@ int lmb_linear_static_scratch(const lmb_weight *w, const float *d_bias, const fl
     su.scratch = static_cast<float *>(ps);
     su.counters = static_cast<unsigned *>(pc);
     su.ready = true;
+  }
   }
   const int kind = w->kind;
   const Plan pl = make_plan(kind, w->row_tiles, w->bpr, 1, su.sm_count);

@@ -150,6 +150,7 @@ int lmb_file_open(const char *path, lmb_file **out) {
     size_t ss = tj.find("\"shape\": [");
     if (ss != std::string::npos) {
       size_t se = tj.find("]", ss);
+      if (se == std::string::npos) return fail("unterminated shape list");
       std::string body = tj.substr(ss + 10, se - ss - 10);
       size_t p2 = 0;
       while (p2 < body.size()) {
@@ -162,7 +163,31 @@ int lmb_file_open(const char *path, lmb_file **out) {
         p2 = comma + 1;
       }
     }
-    t.offset = f->data_start + size_t(js_int(tj, "offset"));
+    const long rel = js_int(tj, "offset");
+    if (rel < 0) return fail("negative tensor offset");
+    t.offset = f->data_start + size_t(rel);
+    // The header is not trusted: the payload must lie inside the file and a 2-D block tensor must
+    // hold exactly shape[0] * ceil(shape[1] / 256) blocks (what the upload will read).
+    {
+      const size_t lim = size_t(1) << 40;  // keeps the products below free of overflow
+      size_t bytes = 0;
+      if (t.kind >= 0) {
+        if (t.num_blocks > lim) return fail("implausible block count");
+        bytes = t.num_blocks * size_t(lmb::kind_info(t.kind).ref_bytes);
+        if (t.shape.size() == 2) {
+          if (t.shape[0] == 0 || t.shape[1] == 0 || t.shape[0] > lim || t.shape[1] > lim) return fail("bad tensor shape");
+          const size_t bpr = (t.shape[1] + 255) / 256;
+          if (t.shape[0] > lim / bpr || t.num_blocks != t.shape[0] * bpr) return fail("num_blocks does not match the tensor shape");
+        }
+      } else {
+        bytes = sizeof(float);
+        for (size_t sdim : t.shape) {
+          if (sdim > lim || (sdim != 0 && bytes > lim / sdim)) return fail("bad tensor shape");
+          bytes *= sdim;
+        }
+      }
+      if (t.offset > f->file_size || bytes > f->file_size - t.offset) return fail("tensor data runs past the end of the file");
+    }
     f->tensors.push_back(t);
     pos = cb + 1;
   }

@@ -70,7 +70,6 @@ struct lmb_model {
   size_t nh = 0, nkv = 0, inter = 0, vocab_local = 0;  // this rank's share
   lmb_weight *embed = nullptr, *lm_head = nullptr;
   bool head_tied = false, head_rot = false, embed_rot = false;
-  const void *embed_host = nullptr;
   float *final_norm = nullptr;
   std::vector<LayerW> layers;
   // activations [max_batch][...]
@@ -91,6 +90,7 @@ struct lmb_model {
   bool tp_peers = true;  // tensor parallelism: partial vectors through peer memory (else NCCL all-reduce)
   std::vector<cudaGraphExec_t> graphs;      // index = batch
   std::vector<uint64_t> graph_launches;
+  std::vector<uint64_t> graph_gen;  // lmb_ctx::scratch_gen each graph was captured under
 };
 
 static int dev_alloc(float **p, size_t n) {
@@ -181,6 +181,67 @@ int lmb_tp_peer_status(lmb_ctx *ctx, int *timed_out) {
   return LMB_OK;
 }
 
+int lmb_debug_tp_wait(lmb_ctx *ctx, int ranks, int posted, size_t h, unsigned spin_limit, int out4[4]) {
+  LMB_REQUIRE(ctx && out4 && ranks >= 2 && ranks <= MAX_TP && posted >= 0 && posted <= ranks && h > 0 && spin_limit > 0,
+              "lmb_debug_tp_wait: bad argument");
+  LMB_REQUIRE(!ctx->xchg.local, "lmb_debug_tp_wait: the context already has an exchange block");
+  LMB_CUDA(cudaSetDevice(ctx->device));
+  const size_t cap = (h + 63) / 64 * 64;
+  const size_t bytes = XCHG_HEADER_BYTES + size_t(2) * ranks * cap * sizeof(unsigned long long);
+  void *blk = nullptr;
+  float *hidden = nullptr, *w = nullptr, *out = nullptr;
+  std::vector<unsigned long long> words(size_t(2) * ranks * cap, 0ull);
+  for (int r = 0; r < posted; ++r)  // epoch 0: parity 0, tag 1; value r + 1
+    for (size_t i = 0; i < h; ++i) {
+      const float v = float(r + 1);
+      unsigned bits;
+      std::memcpy(&bits, &v, 4);
+      words[size_t(r) * cap + i] = (1ull << 32) | bits;
+    }
+  std::vector<float> ones(h, 1.0f), res(h, 0.0f);
+  XchgHeader hdr;
+  cudaError_t e = cudaMalloc(&blk, bytes);
+  if (e == cudaSuccess) e = cudaMemset(blk, 0, XCHG_HEADER_BYTES);
+  if (e == cudaSuccess) e = cudaMemcpy(static_cast<char *>(blk) + XCHG_HEADER_BYTES, words.data(), words.size() * 8, cudaMemcpyHostToDevice);
+  if (e == cudaSuccess) e = cudaMalloc(&hidden, h * 4);
+  if (e == cudaSuccess) e = cudaMalloc(&w, h * 4);
+  if (e == cudaSuccess) e = cudaMalloc(&out, h * 4);
+  if (e == cudaSuccess) e = cudaMemset(hidden, 0, h * 4);
+  if (e == cudaSuccess) e = cudaMemcpy(w, ones.data(), h * 4, cudaMemcpyHostToDevice);
+  int st = e == cudaSuccess ? LMB_OK : cuda_fail(e, "lmb_debug_tp_wait setup");
+  if (st == LMB_OK) {
+    // the context stands in for one rank of `ranks`; every "peer" block is the local one
+    const PeerXchg saved = ctx->xchg;
+    const int saved_size = ctx->tp_size;
+    ctx->xchg.local = blk;
+    ctx->xchg.cap = cap;
+    ctx->xchg.ready = true;
+    ctx->xchg.spin_limit = spin_limit;
+    ctx->tp_size = ranks;
+    st = launch_tp_sum_add_rmsnorm(ctx, hidden, w, out, h, 1, 1e-5f);
+    ctx->xchg = saved;
+    ctx->tp_size = saved_size;
+    if (st == LMB_OK) e = cudaStreamSynchronize(ctx->stream);
+    if (st == LMB_OK && e == cudaSuccess) e = cudaMemcpy(&hdr, blk, sizeof hdr, cudaMemcpyDeviceToHost);
+    if (st == LMB_OK && e == cudaSuccess) e = cudaMemcpy(res.data(), hidden, h * 4, cudaMemcpyDeviceToHost);
+    if (st == LMB_OK && e != cudaSuccess) st = cuda_fail(e, "lmb_debug_tp_wait");
+  }
+  if (st == LMB_OK) {
+    const float want = float(posted * (posted + 1) / 2);  // sum of the posted partial vectors
+    bool ok = true;
+    for (size_t i = 0; i < h; ++i) ok = ok && res[i] == want;
+    out4[0] = int(hdr.timed_out);
+    out4[1] = int(hdr.epoch);
+    out4[2] = int(hdr.done);
+    out4[3] = ok ? 1 : 0;
+  }
+  if (blk) cudaFree(blk);
+  if (hidden) cudaFree(hidden);
+  if (w) cudaFree(w);
+  if (out) cudaFree(out);
+  return st;
+}
+
 int lmb_tp_destroy(lmb_ctx *ctx) {
   LMB_REQUIRE(ctx, "lmb_tp_destroy: null context");
   if (ctx->xchg.local) {
@@ -231,6 +292,9 @@ int lmb_model_create(lmb_ctx *ctx, const lmb_model_config *c, lmb_model **out) {
   LMB_REQUIRE(c->tp_rank >= 0 && c->tp_rank < g, "lmb_model_create: tp_rank out of range");
   LMB_REQUIRE(g == 1 || (ctx->comm && ctx->tp_size == g && ctx->tp_rank == c->tp_rank),
               "lmb_model_create: tensor-parallel model needs lmb_tp_init on its context first");
+  LMB_REQUIRE(c->vocab_size > 0 && c->hidden_size > 0 && c->intermediate_size > 0 && c->num_attention_heads > 0 &&
+                  c->num_key_value_heads > 0,
+              "lmb_model_create: vocab, hidden, intermediate sizes and head counts must be positive");
   LMB_REQUIRE(c->num_attention_heads % c->num_key_value_heads == 0, "lmb_model_create: heads not divisible by kv heads");
   LMB_REQUIRE(c->head_dim > 0 && c->head_dim % 2 == 0 && 256 % c->head_dim == 0, "lmb_model_create: head_dim must divide 256");
   LMB_REQUIRE(c->num_attention_heads % g == 0 && c->num_key_value_heads % g == 0 && c->intermediate_size % g == 0 &&
@@ -345,15 +409,13 @@ int lmb_model_set_weight(lmb_model *m, int layer, int slot, int kind, int quant_
   lmb_weight **dst = nullptr;
   size_t r0 = 0, r1 = M, b0 = 0, b1 = bpr, wantM = 0, wantK = 0;
   if (slot == LMB_SLOT_EMBED) {
-    dst = &m->embed; wantM = c.vocab_size; wantK = h; m->embed_host = blocks; m->embed_rot = rot;
+    dst = &m->embed; wantM = c.vocab_size; wantK = h; m->embed_rot = rot;
+    if (m->head_tied) {  // the tied head shares the device copy that is about to be replaced
+      m->lm_head = nullptr;
+      m->head_tied = false;
+    }
   } else if (slot == LMB_SLOT_LM_HEAD) {
     dst = &m->lm_head; wantM = c.vocab_size; wantK = h; r0 = M * r / g; r1 = M * (r + 1) / g; m->head_rot = rot;
-    if (g == 1 && m->embed && blocks == m->embed_host && kind == m->embed->ref_kind) {  // tied: share the device copy
-      if (m->lm_head && !m->head_tied) lmb_weight_free(m->lm_head);
-      m->lm_head = m->embed;
-      m->head_tied = true;
-      return LMB_OK;
-    }
   } else {
     LMB_REQUIRE(layer >= 0 && size_t(layer) < m->layers.size(), "lmb_model_set_weight: layer out of range");
     LayerW &L = m->layers[size_t(layer)];
@@ -374,6 +436,11 @@ int lmb_model_set_weight(lmb_model *m, int layer, int slot, int kind, int quant_
   if (slot == LMB_SLOT_LM_HEAD) m->head_tied = false;
   *dst = nullptr;
   return lmb_weight_upload_shard(m->ctx, kind, blocks, M, K, r0, r1, b0, b1, dst);
+}
+
+int lmb_model_tie_head(lmb_model *m) {
+  LMB_REQUIRE(m, "lmb_model_tie_head: null model");
+  return model_tie_head(m);
 }
 
 int lmb_model_set_vector(lmb_model *m, int layer, int which, const float *data, size_t n) {
@@ -406,7 +473,14 @@ int lmb_model_set_vector(lmb_model *m, int layer, int which, const float *data, 
 namespace lmb {
 // lm_head = embed_tokens without a second device copy (load_model's tied head, model.cpp:667-689).
 int model_tie_head(lmb_model *m) {
-  if (m->cfg.tp_size != 1 || !m->embed) return LMB_ERR_STATE;
+  if (m->cfg.tp_size != 1 || !m->embed) {
+    set_last_error("lmb_model_tie_head: needs an unsharded model whose embedding is set");
+    return LMB_ERR_STATE;
+  }
+  for (auto &g : m->graphs) {  // captured steps hold the old head
+    if (g) cudaGraphExecDestroy(g);
+    g = nullptr;
+  }
   if (m->lm_head && !m->head_tied) lmb_weight_free(m->lm_head);
   m->lm_head = m->embed;
   m->head_tied = true;
@@ -480,6 +554,13 @@ int lmb_model_forward(lmb_model *m, const int *token_ids, const size_t *position
     if (m->graphs.size() <= batch) {
       m->graphs.resize(batch + 1, nullptr);
       m->graph_launches.resize(batch + 1, 0);
+      m->graph_gen.resize(batch + 1, 0);
+    }
+    if (m->graphs[batch] && m->graph_gen[batch] != ctx->scratch_gen) {
+      // the context's scratch buffers were reallocated since (a larger batch, another model or an
+      // lmb_linear call on this context): the graph's pointers are stale, capture it again
+      cudaGraphExecDestroy(m->graphs[batch]);
+      m->graphs[batch] = nullptr;
     }
     if (m->graphs[batch]) {
       LMB_CUDA(cudaGraphLaunch(m->graphs[batch], ctx->stream));
@@ -512,6 +593,7 @@ int lmb_model_forward(lmb_model *m, const int *token_ids, const size_t *position
       cudaGraphDestroy(g);
       if (e != cudaSuccess) return cuda_fail(e, "cudaGraphInstantiate(decode step)");
       m->graph_launches[batch] = ctx->launches - base;
+      m->graph_gen[batch] = ctx->scratch_gen;
       ctx->launches = base;
       (void)before;
       goto fetch;
@@ -611,6 +693,16 @@ fetch:
   if (h_logits) {
     LMB_CUDA(cudaMemcpyAsync(h_logits, m->logits, batch * c.vocab_size * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
     LMB_CUDA(cudaStreamSynchronize(ctx->stream));
+    if (c.tp_size > 1 && ctx->xchg.ready) {
+      // a consumer that gave up waiting for another rank's partial vector has produced garbage:
+      // the step reports it instead of returning the logits as if nothing had happened
+      unsigned flag = 0;
+      LMB_CUDA(cudaMemcpy(&flag, &static_cast<XchgHeader *>(ctx->xchg.local)->timed_out, sizeof flag, cudaMemcpyDeviceToHost));
+      if (flag) {
+        set_last_error("lmb_model_forward: a bounded wait for another rank's partial vector expired");
+        return LMB_ERR_TIMEOUT;
+      }
+    }
   }
   return LMB_OK;
 }
@@ -627,24 +719,26 @@ int lmb_model_reset(lmb_model *m) {
   return LMB_OK;
 }
 
+// The host side always sees the reference layout of the WHOLE model, [layer][2][max_seq][kv_heads][head_dim];
+// a tensor-parallel rank holds kv_heads / tp_size consecutive heads of every row: a strided copy.
 int lmb_model_kv_export(lmb_model *m, size_t seq, float *h_out) {
   LMB_REQUIRE(m && h_out && seq < m->cfg.max_batch, "lmb_model_kv_export: bad argument");
-  if (m->cfg.tp_size != 1) {
-    set_last_error("lmb_model_kv_export: only for unsharded models");
-    return LMB_ERR_STATE;
-  }
-  LMB_CUDA(cudaMemcpyAsync(h_out, m->kv + seq * m->seq_stride, m->seq_stride * sizeof(float), cudaMemcpyDeviceToHost, m->ctx->stream));
+  const lmb_model_config &c = m->cfg;
+  const size_t rows = c.num_hidden_layers * 2 * c.max_seq_len, full = c.num_key_value_heads * c.head_dim * sizeof(float),
+               mine = m->nkv * c.head_dim * sizeof(float);
+  LMB_CUDA(cudaMemcpy2DAsync(reinterpret_cast<char *>(h_out) + size_t(c.tp_rank) * mine, full, m->kv + seq * m->seq_stride, mine,
+                             mine, rows, cudaMemcpyDeviceToHost, m->ctx->stream));
   LMB_CUDA(cudaStreamSynchronize(m->ctx->stream));
   return LMB_OK;
 }
 
 int lmb_model_kv_import(lmb_model *m, size_t seq, const float *h_in) {
   LMB_REQUIRE(m && h_in && seq < m->cfg.max_batch, "lmb_model_kv_import: bad argument");
-  if (m->cfg.tp_size != 1) {
-    set_last_error("lmb_model_kv_import: only for unsharded models");
-    return LMB_ERR_STATE;
-  }
-  LMB_CUDA(cudaMemcpyAsync(m->kv + seq * m->seq_stride, h_in, m->seq_stride * sizeof(float), cudaMemcpyHostToDevice, m->ctx->stream));
+  const lmb_model_config &c = m->cfg;
+  const size_t rows = c.num_hidden_layers * 2 * c.max_seq_len, full = c.num_key_value_heads * c.head_dim * sizeof(float),
+               mine = m->nkv * c.head_dim * sizeof(float);
+  LMB_CUDA(cudaMemcpy2DAsync(m->kv + seq * m->seq_stride, mine, reinterpret_cast<const char *>(h_in) + size_t(c.tp_rank) * mine, full,
+                             mine, rows, cudaMemcpyHostToDevice, m->ctx->stream));
   LMB_CUDA(cudaStreamSynchronize(m->ctx->stream));
   return LMB_OK;
 }

@@ -34,7 +34,13 @@ class Model:
         check(lib().lmb_model_create(self.ctx.h, C.byref(cfg), C.byref(h)))
         self.h = h
         self._set_weight(0, "embed", spec.embed)
-        self._set_weight(0, "lm_head", spec.lm_head)
+        # a head that is the embedding's own block array is tied (one device copy), as load_model
+        # does for files without an lm_head tensor; anything else is uploaded as its own tensor
+        tied = (tp_size == 1 and spec.lm_head.kind == spec.embed.kind and spec.lm_head.blocks is spec.embed.blocks)
+        if tied:
+            check(lib().lmb_model_tie_head(self.h))
+        else:
+            self._set_weight(0, "lm_head", spec.lm_head)
         self._set_vector(0, "final_norm", spec.final_norm)
         uploaded = {}
         for i, L in enumerate(spec.layers):

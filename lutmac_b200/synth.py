@@ -166,13 +166,16 @@ MODEL_SHAPES = {
 }
 
 
-def model_spec(shape: Dict, kind: int, seed: int = 0, max_seq: int = 2048, shared_layers: int = 0) -> ModelSpec:
+def model_spec(shape: Dict, kind: int, seed: int = 0, max_seq: int = 2048, shared_layers: int = 0,
+               untied_head: bool = False) -> ModelSpec:
     """Random-init decoder of the given shape.  Projections use block kind `kind`; the embedding
     and the tied lm_head are int8, which is what the reference's quantizer produces for every
     bit width below 7.5 (tools/lutmac-quantize.cpp:385-389, src/model.cpp:667-689).
 
     shared_layers > 0 generates that many distinct layers and repeats them (keeps host memory
-    and generation time bounded for the 80-layer stack; device copies are still distinct)."""
+    and generation time bounded for the 80-layer stack; device copies are still distinct).
+    untied_head gives lm_head its own int8 tensor (drawn after everything else, so the other
+    tensors of a seed do not change) instead of sharing the embedding's block array."""
     rng = np.random.default_rng(seed)
     c = dict(shape)
     c["max_seq"] = max_seq
@@ -201,6 +204,8 @@ def model_spec(shape: Dict, kind: int, seed: int = 0, max_seq: int = 2048, share
             L["v_bias"] = (0.02 * rng.standard_normal(nkv * hd)).astype(np.float32)
         gen.append(L)
     spec.layers = [gen[i % n_gen] for i in range(c["n_layers"])]
+    if untied_head:
+        spec.lm_head = int8_tensor(rng, c["vocab"], h, 0.5, 1.5, name="lm_head.weight")
     return spec
 
 

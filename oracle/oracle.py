@@ -453,7 +453,8 @@ class RefFileTensor(C.Structure):
 
 def spec_file_tensors(spec):
     """(name, kind or -1, quant_bits, array, M, K) for every tensor of a model spec, with the names
-    load_model maps to slots (src/model.cpp:589-664); no lm_head entry: the head is tied."""
+    load_model maps to slots (src/model.cpp:589-664); an lm_head entry only when the head has a
+    block array of its own (otherwise load_model ties it to the embedding)."""
     out = [(spec.embed.name or "model.embed_tokens.weight", spec.embed.kind, spec.embed.quant_bits, spec.embed.blocks,
             spec.embed.M, spec.embed.K),
            ("model.norm.weight", -1, 32, np.ascontiguousarray(spec.final_norm, np.float32), spec.final_norm.size, 0)]
@@ -470,6 +471,9 @@ def spec_file_tensors(spec):
                         ("down", "mlp.down_proj.weight")):
             t = L[key]
             out.append((pre + nm, t.kind, t.quant_bits, t.blocks, t.M, t.K))
+    if spec.lm_head.blocks is not spec.embed.blocks:
+        t = spec.lm_head
+        out.append(("lm_head.weight", t.kind, t.quant_bits, t.blocks, t.M, t.K))
     return out
 
 

@@ -114,7 +114,8 @@ def model_cases(ref: Reference):
     return out
 
 
-FILE_CASES = (("tiny_int4", INT4, {}), ("tiny_ternary_bias", TERNARY, {"qkv_bias": True}))
+FILE_CASES = (("tiny_int4", INT4, {}), ("tiny_ternary_bias", TERNARY, {"qkv_bias": True}),
+              ("tiny_untied_head", INT4, {"untied_head": True}))
 FILE_SHAPE = dict(vocab=256, hidden=256, inter=256, n_layers=1, n_heads=4, n_kv_heads=1, head_dim=64)
 FILE_TOKENS = [5, 200, 17]
 
@@ -124,7 +125,10 @@ def file_cases(ref: Reference):
     Model::forward produce from them."""
     out = {"tokens": np.array(FILE_TOKENS)}
     for name, kind, over in FILE_CASES:
-        spec = synth.model_spec(synth.tiny_model_shape(**dict(FILE_SHAPE, **over)), kind, seed=21, max_seq=2048)
+        over = dict(over)
+        untied = over.pop("untied_head", False)
+        spec = synth.model_spec(synth.tiny_model_shape(**dict(FILE_SHAPE, **over)), kind, seed=21, max_seq=2048,
+                                untied_head=untied)
         path = os.path.join(HERE, name + ".lutmac")
         ref.save_lutmac(path, spec)
         out[name + "_logits"] = ref.load_model_logits(path, FILE_TOKENS, spec.cfg["vocab"])

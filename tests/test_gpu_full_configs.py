@@ -1,0 +1,101 @@
+"""GPU parity of ONE decode step at the sizes of the benchmark configurations, against the
+unmodified reference (Model::forward, src/model.cpp:47-453).
+
+Filling a 512- or 1024-token cache through the reference would take hours (1.5 to 20 s per token
+on one core), so the GPU fills the cache by decoding the context (prefill by decode, as
+src/inference.cpp:275-278 does), the cache is handed to the reference's Model::kv_cache
+(include/lutmac/model.hpp:74) and both sides compute the same next step.  Logits must agree
+within 1e-5 relative L2.  Reference steps of different sequences run in host threads, each on a
+Model of its own."""
+from concurrent.futures import ThreadPoolExecutor
+
+import numpy as np
+import pytest
+
+from lutmac_b200 import synth
+from lutmac_b200.blocks import INT2, INT4, TERNARY
+from lutmac_b200.model import Model
+from tests.conftest import rel_l2
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-5
+
+
+def reference_steps(reference, spec, caches, tokens, position):
+    """One reference Model per cache: import the cache, decode `tokens[i]` at `position`."""
+    from oracle.oracle import ReferenceModel
+
+    def one(i):
+        m = ReferenceModel(reference, spec)
+        m.kv()[:] = caches[i]
+        out = m.forward(int(tokens[i]), position)
+        m.close()
+        return out
+
+    with ThreadPoolExecutor(len(caches)) as ex:
+        return list(ex.map(one, range(len(caches))))
+
+
+def prefill(model, vocab, ctx_len, batch, seed):
+    rng = np.random.default_rng(seed)
+    for p in range(ctx_len):  # uniform-random token ids, as the configurations state
+        model.forward(rng.integers(0, vocab, size=batch), [p] * batch, fetch=False)
+    return rng.integers(0, vocab, size=batch)
+
+
+def test_config3_llama_1b_int4_context_512(ctx, reference):
+    """16 layers, hidden 2048, 32/8 heads of 64, FFN 8192, vocab 128256 with the tied int8 head,
+    4-bit projections, RoPE theta 5e5 with linear factor 32, 512 cached positions, batch 1."""
+    spec = synth.model_spec(synth.MODEL_SHAPES["llama-3.2-1b"], INT4, seed=0, max_seq=2048)
+    m = Model(spec, ctx)
+    tok = prefill(m, spec.cfg["vocab"], 512, 1, seed=1)
+    got = m.forward(tok, [512])[0].copy()
+    want = reference_steps(reference, spec, [m.kv_export(0)], tok, 512)[0]
+    err = rel_l2(got, want)
+    print(f"config 3 (16 layers, int4): logits rel L2 vs reference {err:.3e}")
+    assert np.isfinite(want).all() and err < TOL, err
+    m.close()
+
+
+def test_config4_qwen_1p5b_rrq_context_1024_batch_1_and_8(ctx, reference):
+    """28 layers, hidden 1536, 12/2 heads of 128, FFN 8960, vocab 151936, q/k/v bias, 2-bit RRQ
+    projections (scale2 != 0), 1024 cached positions; batch 1, then batch 8 (two of the eight
+    sequences are checked, each against a reference run of its own)."""
+    spec = synth.model_spec(synth.MODEL_SHAPES["qwen-2.5-1.5b"], INT2, seed=0, max_seq=2048)
+    m = Model(spec, ctx, max_batch=8)
+    vocab = spec.cfg["vocab"]
+    tok8 = prefill(m, vocab, 1024, 8, seed=2)
+    got8 = m.forward(tok8, [1024] * 8).copy()
+    caches = [m.kv_export(0), m.kv_export(7)]
+    # batch 1 on the same model: sequence 0 again, alone (the batch-1 kernels and graph)
+    got1 = m.forward(tok8[:1], [1024])[0].copy()
+    want = reference_steps(reference, spec, caches, [tok8[0], tok8[7]], 1024)
+    errs = {"batch 8, sequence 0": rel_l2(got8[0], want[0]), "batch 8, sequence 7": rel_l2(got8[7], want[1]),
+            "batch 1": rel_l2(got1, want[0])}
+    print("config 4 (28 layers, RRQ 2-bit): logits rel L2 vs reference " + ", ".join(f"{k} {v:.3e}" for k, v in errs.items()))
+    for k, v in errs.items():
+        assert v < TOL, (k, v)
+    m.close()
+
+
+def test_config5_llama_70b_shapes_ternary_8_layers_batch_1_and_16(ctx, reference):
+    """The 70B-shaped ternary stack at its true layer shapes (hidden 8192, 64/8 heads of 128, FFN
+    28672, vocab 128256) cut to 8 of its 80 layers -- what one reference step per checked sequence
+    costs about a minute for -- with two distinct random layers repeated four times.  Batch 16
+    (sequences 0 and 15 checked) and batch 1."""
+    shape = dict(synth.MODEL_SHAPES["llama-3-70b"], n_layers=8)
+    spec = synth.model_spec(shape, TERNARY, seed=0, max_seq=2048, shared_layers=2)
+    m = Model(spec, ctx, max_batch=16)
+    vocab = spec.cfg["vocab"]
+    ctx_len = 48
+    tok = prefill(m, vocab, ctx_len, 16, seed=3)
+    got16 = m.forward(tok, [ctx_len] * 16).copy()
+    caches = [m.kv_export(0), m.kv_export(15)]
+    got1 = m.forward(tok[:1], [ctx_len])[0].copy()
+    want = reference_steps(reference, spec, caches, [tok[0], tok[15]], ctx_len)
+    errs = {"batch 16, sequence 0": rel_l2(got16[0], want[0]), "batch 16, sequence 15": rel_l2(got16[15], want[1]),
+            "batch 1": rel_l2(got1, want[0])}
+    print("config 5 shapes (8 layers, ternary): logits rel L2 vs reference " + ", ".join(f"{k} {v:.3e}" for k, v in errs.items()))
+    for k, v in errs.items():
+        assert v < TOL, (k, v)
+    m.close()

@@ -97,6 +97,33 @@ def test_batch_of_eight_shares_the_weight_pass(ctx, oracle):
     m.close()
 
 
+def test_batch_size_changes_on_a_graphed_model(oracle):
+    """Batch 1 -> 8 -> 1 on one live model whose steps are captured graphs, on a context of its own
+    whose split-K scratch starts small: the larger batch needs more scratch, the buffers are
+    reallocated, and the graph captured for batch 1 must not be replayed with its stale pointers."""
+    from lutmac_b200.api import Context
+    from oracle.oracle import OracleModel
+    from lutmac_b200 import _lib
+    own = Context(0)
+    own.set_option(_lib.OPT_SCRATCH_FLOATS, 1024)  # every growth below frees and reallocates the buffer
+    # hidden 2048 / inter 6144: the down projection is split along K at batch 1 (few row-tiles)
+    spec = synth.model_spec(synth.tiny_model_shape(hidden=2048, inter=6144, n_heads=8, n_kv_heads=2, head_dim=64,
+                                                   n_layers=2, vocab=384), TERNARY, seed=13, max_seq=16)
+    B = 8
+    m = Model(spec, own, max_batch=B)
+    oracles = [OracleModel(oracle, spec) for _ in range(B)]
+    rng = np.random.default_rng(4)
+    pos = [0] * B
+    for step, nb in enumerate((1, 1, B, B, 1, 3, 1, B)):
+        toks = rng.integers(0, spec.cfg["vocab"], size=nb)
+        got = m.forward(toks, pos[:nb])
+        for b in range(nb):
+            assert rel_l2(got[b], oracles[b].forward(int(toks[b]), pos[b])) < TOL, (step, nb, b)
+            pos[b] += 1
+    m.close()
+    own.close()
+
+
 def test_model_errors(ctx):
     from lutmac_b200._lib import LutmacError
     spec = synth.model_spec(synth.tiny_model_shape(), INT4, seed=1, max_seq=8)

@@ -21,11 +21,24 @@ def device_synchronize():
     assert ctypes.CDLL("libcuda.so.1").cuCtxSynchronize() == 0
 
 
-@pytest.mark.parametrize("kind,M,K", [(INT4, 64, 8192), (TERNARY, 100, 4096), (INT4, 512, 2048)])
-def test_static_scratch_matches_lmb_linear_twice(ctx, oracle, kind, M, K):
+def planned_k_slices(w, M, K):
+    """K slices the planner cuts a batch-1 GEMV of this weight into (1 = the scratch is unused)."""
+    out = (ctypes.c_int * 5)()
+    _lib.check(_lib.lib().lmb_debug_plan_weight(w.h, 148, out))
+    return out[3]
+
+
+# (kind, M, K, must the planner split K?): the first and the last use the built-in array -- the last
+# is the down projection of the 70B-shaped decoder, the largest split of the decoder shapes --
+# the middle ones run in one slice and only exercise the entry point's plain path
+@pytest.mark.parametrize("kind,M,K,split", [(INT4, 64, 8192, True), (TERNARY, 100, 4096, False), (INT4, 512, 2048, False),
+                                            (TERNARY, 8192, 28672, True)])
+def test_static_scratch_matches_lmb_linear_twice(ctx, oracle, kind, M, K, split):
     rng = np.random.default_rng(kind * 7 + M)
     t = synth.tensor(rng, kind, M, K)
     w = ctx.upload(t)
+    if split:
+        assert planned_k_slices(w, M, K) > 1, "this case is meant to go through the built-in scratch array"
     results = []
     for call in range(2):  # two calls in a row: the second one finds the first one's leftovers
         x = synth.activations(rng, K)
