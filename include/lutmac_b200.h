@@ -234,9 +234,18 @@ int lmb_model_set_weight(lmb_model *m, int layer, int slot, int kind, int quant_
 int lmb_model_tie_head(lmb_model *m);
 int lmb_model_set_vector(lmb_model *m, int layer, int which, const float *data, size_t n);
 /* One decode step for `batch` sequences: token_ids[b] at positions[b].  h_logits is NULL or
- * batch*vocab floats on the host. */
+ * batch*vocab floats on the host.  Batch 1 of a model whose seven projections per layer share
+ * one block kind runs embedding and all layers as ONE persistent kernel (LMB_MODEL_PERSISTENT=0 in
+ * the environment at lmb_model_create selects the launch-per-projection step instead). */
 int lmb_model_forward(lmb_model *m, const int *token_ids, const size_t *positions, size_t batch, float *h_logits);
 int lmb_model_logits_dev(lmb_model *m, const float **d_logits);
+/* Failure-path test of the bounded waits between the phases of the persistent decode step (batch 1
+ * runs embedding and all layers as one kernel whose CTAs wait for each other through arrival
+ * counters): every wait expects `extra_arrivals` arrivals more than there are CTAs and polls at
+ * most `spin_limit` times (0 = the default, about a second).  With extra_arrivals > 0 the first
+ * wait runs out, the kernel records the phase and returns by itself, and the lmb_model_forward
+ * call that fetches logits returns LMB_ERR_TIMEOUT; (0, 0) restores normal operation. */
+int lmb_debug_model_waits(lmb_model *m, int extra_arrivals, unsigned spin_limit);
 int lmb_model_reset(lmb_model *m);
 /* KV cache exchange in the reference layout [layer][2][max_seq][kv_heads][head_dim]
  * (types.hpp:599-627) for sequence `seq`.  The host buffer always has the layout of the whole

@@ -89,6 +89,7 @@ SIGNATURES = {
     "lmb_model_tie_head": (C.c_int, [vp]),
     "lmb_model_set_vector": (C.c_int, [vp, C.c_int, C.c_int, vp, sz]),
     "lmb_model_forward": (C.c_int, [vp, C.POINTER(C.c_int), C.POINTER(sz), sz, vp]),
+    "lmb_debug_model_waits": (C.c_int, [vp, C.c_int, C.c_uint]),
     "lmb_model_logits_dev": (C.c_int, [vp, C.POINTER(vp)]),
     "lmb_model_reset": (C.c_int, [vp]),
     "lmb_model_kv_export": (C.c_int, [vp, sz, vp]),

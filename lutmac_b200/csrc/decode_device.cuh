@@ -1,0 +1,352 @@
+// Device code shared by the decode-step kernels (decode_ops.cu launches each piece on its own,
+// persist.cu runs them as phases of one persistent kernel): a dequantised weight element out of
+// the tile layout (embedding rows), block-wide reductions and one (head, KV split) item of the
+// split-KV decode attention.
+#pragma once
+
+#include "common.cuh"
+#include "decode_ops.cuh"
+
+namespace lmb {
+
+namespace {
+
+// Dequantised weight (row, col) out of the device tile layout: Block::get of types.hpp.
+__device__ float tile_elem(int kind, const uint8_t *tiles, size_t bpr, size_t row, size_t col) {
+  const size_t rt = row / TILE_ROWS, l = row % TILE_ROWS, b = col / BLK, j = col % BLK;
+  const KindInfo ki = kind_info(kind);
+  const uint8_t *tile = tiles + (rt * bpr + b) * (size_t(TILE_ROWS) * ki.ref_bytes);
+  const float *sc = reinterpret_cast<const float *>(tile + size_t(ki.chunks) * TILE_ROWS * 16);
+  const float s0 = sc[l];
+  auto pay = [&](size_t chunk, size_t byte) { return tile[(chunk * TILE_ROWS + l) * 16 + byte]; };
+  const unsigned bit = 7u - unsigned(j % 8);
+  switch (kind) {
+  case LMB_INT8: return float(int8_t(pay(j / 16, j % 16))) * s0;
+  case LMB_INT4:
+  case LMB_INT5:
+  case LMB_INT6: {  // MMA operand order, see common.cuh
+    const size_t h = l / 16, g = l % 8, m = l / 8, s = j / 32, kk = j % 32, tid = (kk % 16) / 4;
+    const size_t lane = g * 4 + tid, chunk = h * 4 + s / 2, word = (s % 2) * 2 + kk / 16;
+    const uint8_t byte = tile[(chunk * TILE_ROWS + lane) * 16 + word * 4 + kk % 4];
+    int code = ((l % 16) >= 8) ? (byte >> 4) : (byte & 15);
+    for (int pl = 0; pl < kind - 4; ++pl) {  // bit planes 4 (and 5) in the binary arrangement
+      const size_t wi = (s / 2) * 2 + kk / 16;
+      const uint8_t pb = tile[4096 + 1024 * pl + ((wi / 4) * TILE_ROWS + lane) * 16 + (wi % 4) * 4 + kk % 4];
+      code |= int((pb >> (m + 4 * (s % 2))) & 1u) << (4 + pl);
+    }
+    return float(code - (8 << (kind - 4))) * sc[4 * g + m];
+  }
+  case DK_INT3_MMA: {
+    const size_t m = l / 8, g = l % 8, s = j / 32, kk = j % 32, tid = (kk % 16) / 4;
+    const size_t lane = g * 4 + tid, wi = (s / 2) * 2 + kk / 16;
+    int code = 0;
+    for (int pl = 0; pl < 3; ++pl) {
+      const uint8_t pb = tile[1024 * pl + ((wi / 4) * TILE_ROWS + lane) * 16 + (wi % 4) * 4 + kk % 4];
+      code |= int((pb >> (m + 4 * (s % 2))) & 1u) << pl;
+    }
+    return float(code - 4) * sc[4 * g + m];
+  }
+  case DK_INT8_MMA: {
+    const size_t h = l / 16, g = l % 8, s = j / 32, kk = j % 32, tid = (kk % 16) / 4;
+    const size_t a = 2 * (kk / 16) + (l % 16) / 8;
+    return float(int8_t(tile[((h * 8 + s) * TILE_ROWS + g * 4 + tid) * 16 + a * 4 + kk % 4])) * sc[4 * g + l / 8];
+  }
+  case DK_TERNARY_MMA: {  // 2-bit codes t+1 in MMA operand order, see common.cuh
+    const size_t m = l / 8, g = l % 8, s = j / 32, kk = j % 32, tid = (kk % 16) / 4;
+    const size_t lane = g * 4 + tid, chunk = s / 2, word = (s % 2) * 2 + kk / 16;
+    const unsigned code = (tile[(chunk * TILE_ROWS + lane) * 16 + word * 4 + kk % 4] >> (2 * m)) & 3u;
+    return (float(int(code)) - 1.0f) * sc[4 * g + m];
+  }
+  case DK_INT2_MMA: {
+    const size_t m = l / 8, g = l % 8, s = j / 32, kk = j % 32, tid = (kk % 16) / 4;
+    const size_t lane = g * 4 + tid, chunk = s / 2, word = (s % 2) * 2 + kk / 16;
+    const unsigned f = (tile[(chunk * TILE_ROWS + lane) * 16 + word * 4 + kk % 4] >> (2 * m)) & 3u;
+    const float s1 = sc[4 * g + m], s2 = sc[TILE_ROWS + 4 * g + m];
+    return ((f & 1u) ? s1 : -s1) + ((f & 2u) ? s2 : -s2);
+  }
+  case DK_BINARY_MMA: {
+    const size_t m = l / 8, g = l % 8, s = j / 32, kk = j % 32, tid = (kk % 16) / 4;
+    const size_t lane = g * 4 + tid, wi = (s / 2) * 2 + kk / 16;
+    const unsigned v = (tile[((wi / 4) * TILE_ROWS + lane) * 16 + (wi % 4) * 4 + kk % 4] >> (m + 4 * (s % 2))) & 1u;
+    return v ? sc[4 * g + m] : -sc[4 * g + m];
+  }
+  case LMB_TERNARY: {
+    const size_t jb = j / 8;
+    const unsigned p = (pay(jb / 8, jb % 8) >> bit) & 1u, n = (pay(jb / 8, 8 + jb % 8) >> bit) & 1u;
+    return p ? s0 : (n ? -s0 : 0.0f);
+  }
+  case LMB_INT2: {
+    const size_t jb = j / 8;
+    const unsigned b1 = (pay(jb / 8, jb % 8) >> bit) & 1u, b2 = (pay(jb / 8, 8 + jb % 8) >> bit) & 1u;
+    const float s1 = sc[TILE_ROWS + l];
+    return (b1 ? s0 : -s0) + (b2 ? s1 : -s1);
+  }
+  case LMB_INT3: {
+    const size_t jb = j / 8, jj = jb / 16;
+    unsigned code = 0;
+    for (unsigned q = 0; q < 3; ++q) code |= ((pay(3 * jj + (2 - q), jb % 16) >> bit) & 1u) << q;
+    return float(int(code) - 4) * s0;
+  }
+  case LMB_BINARY: return (((pay((j / 8) / 16, (j / 8) % 16)) >> bit) & 1u) ? s0 : -s0;
+  default: return 0.0f;
+  }
+}
+
+__device__ __forceinline__ float block_sum(float v, float *red) {
+#pragma unroll
+  for (int m = 16; m > 0; m >>= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (lane < nw) ? red[lane] : 0.0f;
+#pragma unroll
+  for (int m = 16; m > 0; m >>= 1) t += __shfl_xor_sync(0xffffffffu, t, m);
+  return t;
+}
+
+__device__ __forceinline__ float block_max(float v, float *red) {
+#pragma unroll
+  for (int m = 16; m > 0; m >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, m));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (lane < nw) ? red[lane] : -INFINITY;
+#pragma unroll
+  for (int m = 16; m > 0; m >>= 1) t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, m));
+  return t;
+}
+
+// Split-KV decode attention with the q/k/v bias, the rotary embedding and the KV-cache write of
+// the new position folded in (model.cpp:312-372, embedding.cpp:36-75, attention.cpp:23-42).
+// One CTA per (query head, KV split, sequence).  Every CTA rotates its own query head; the split
+// that contains the new position takes that position's key/value from the fresh projections
+// (and, for the first query head of a KV group, stores them in the cache) instead of reading
+// the cache.  Scores of the slice (four timesteps in flight per warp), a local softmax, the
+// weighted values (eight loads in flight per thread); partial (max, sum, vector) go to scratch
+// and the last split to arrive for a head merges them in split order and normalises.
+constexpr int ATT_THREADS = 256;
+
+struct AttnArgs {
+  const float *q, *k, *v;          // fresh projections [batch][heads*hd]
+  const float *qb, *kb, *vb;       // biases or null
+  const float *cs_table;           // [max_seq][hd/2 cos | hd/2 sin]
+  const size_t *positions;
+  float *kv;                       // cache
+  float *out;                      // [batch][nh*hd]
+  float *partial;
+  unsigned *counters;
+  int n_splits;
+  size_t layer;
+};
+
+// FRESH_CG: the fresh projections were written earlier in the SAME kernel launch (persistent
+// decode step) and must be read around the L1 cache, which is not coherent within a launch.
+template <bool FRESH_CG> __device__ __forceinline__ float ld_fresh(const float *p) { return FRESH_CG ? __ldcg(p) : *p; }
+
+template <bool FRESH_CG>
+__device__ __forceinline__ void attn_item(const AttnArgs &a, const RopeDims &d, size_t head, size_t split, size_t b, float *sm,
+                                          int *is_last_p) {
+  float *sc = sm;                    // [split_len]
+  float *qs = sc + d.split_len;      // [hd] rotated query
+  float *kn = qs + d.hd;             // [hd] rotated key of the new position
+  float *vn = kn + d.hd;             // [hd] value of the new position
+  float *red = vn + d.hd;            // [32]
+  float *acc = red + 32;             // [ATT_THREADS]
+  const size_t pos = a.positions[b], seq = pos + 1;
+  const size_t group = d.nh / d.nkv, kvh = head / group, kv_dim = d.nkv * d.hd, half = d.hd / 2;
+  float *kc_w = a.kv + b * d.seq_stride + (a.layer * 2) * d.max_seq * kv_dim + kvh * d.hd;
+  float *vc_w = kc_w + d.max_seq * kv_dim;
+  const float *kc = kc_w, *vc = vc_w;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = ATT_THREADS / 32;
+  const int n_splits = a.n_splits;
+  size_t len = (seq + n_splits - 1) / n_splits;
+  len = (len + 15) / 16 * 16;
+  const size_t t0 = min(split * len, seq), t1 = min(t0 + len, seq), n = t1 - t0;
+  const bool has_new = (pos >= t0 && pos < t1);
+  const float *cs = a.cs_table + pos * d.hd;
+  // rotate the query head (and the new key), pairs (i, i + hd/2)
+  for (size_t i = threadIdx.x; i < half; i += ATT_THREADS) {
+    const float c = cs[i], sn = cs[half + i];
+    const size_t i0 = (b * d.nh + head) * d.hd + i, i1 = i0 + half;
+    float x0 = ld_fresh<FRESH_CG>(a.q + i0), x1 = ld_fresh<FRESH_CG>(a.q + i1);
+    if (a.qb) {
+      x0 += a.qb[head * d.hd + i];
+      x1 += a.qb[head * d.hd + i + half];
+    }
+    qs[i] = x0 * c - x1 * sn;
+    qs[i + half] = x0 * sn + x1 * c;
+    if (has_new) {
+      const size_t k0 = (b * d.nkv + kvh) * d.hd + i, k1 = k0 + half;
+      float y0 = ld_fresh<FRESH_CG>(a.k + k0), y1 = ld_fresh<FRESH_CG>(a.k + k1), v0 = ld_fresh<FRESH_CG>(a.v + k0), v1 = ld_fresh<FRESH_CG>(a.v + k1);
+      if (a.kb) {
+        y0 += a.kb[kvh * d.hd + i];
+        y1 += a.kb[kvh * d.hd + i + half];
+      }
+      if (a.vb) {
+        v0 += a.vb[kvh * d.hd + i];
+        v1 += a.vb[kvh * d.hd + i + half];
+      }
+      const float r0 = y0 * c - y1 * sn, r1 = y0 * sn + y1 * c;
+      kn[i] = r0;
+      kn[i + half] = r1;
+      vn[i] = v0;
+      vn[i + half] = v1;
+      if (head % group == 0) {  // one writer per KV head
+        kc_w[pos * kv_dim + i] = r0;
+        kc_w[pos * kv_dim + i + half] = r1;
+        vc_w[pos * kv_dim + i] = v0;
+        vc_w[pos * kv_dim + i + half] = v1;
+      }
+    }
+  }
+  __syncthreads();
+  const float scale = 1.0f / sqrtf(float(d.hd));
+  const size_t per = d.hd / 32;  // 2 or 4 (head_dim 64 or 128); other head dims take the generic loop
+  const size_t tnew = has_new ? pos - t0 : ~size_t(0);  // slice-local index of the new position
+  constexpr int TS = 8;  // timesteps per warp and iteration: eight key loads in flight per lane
+  for (size_t tb = warp * TS; tb < n; tb += nw * TS) {
+    float s[TS];
+#pragma unroll
+    for (int i = 0; i < TS; ++i) s[i] = 0.0f;
+    if (per == 4) {
+      float4 kk[TS];
+      const float4 qv = reinterpret_cast<const float4 *>(qs)[lane];
+#pragma unroll
+      for (int i = 0; i < TS; ++i) {
+        const size_t t = tb + i;
+        kk[i] = (t >= n) ? make_float4(0, 0, 0, 0)
+                : (t == tnew) ? reinterpret_cast<const float4 *>(kn)[lane]
+                              : reinterpret_cast<const float4 *>(kc + (t0 + t) * kv_dim)[lane];
+      }
+#pragma unroll
+      for (int i = 0; i < TS; ++i) s[i] = qv.x * kk[i].x + qv.y * kk[i].y + qv.z * kk[i].z + qv.w * kk[i].w;
+    } else if (per == 2) {
+      float2 kk[TS];
+      const float2 qv = reinterpret_cast<const float2 *>(qs)[lane];
+#pragma unroll
+      for (int i = 0; i < TS; ++i) {
+        const size_t t = tb + i;
+        kk[i] = (t >= n) ? make_float2(0, 0)
+                : (t == tnew) ? reinterpret_cast<const float2 *>(kn)[lane]
+                              : reinterpret_cast<const float2 *>(kc + (t0 + t) * kv_dim)[lane];
+      }
+#pragma unroll
+      for (int i = 0; i < TS; ++i) s[i] = qv.x * kk[i].x + qv.y * kk[i].y;
+    } else {
+#pragma unroll
+      for (int i = 0; i < TS; ++i) {
+        const size_t t = tb + i;
+        if (t < n)
+          for (size_t c = lane; c < d.hd; c += 32) s[i] += qs[c] * (t == tnew ? kn[c] : kc[(t0 + t) * kv_dim + c]);
+      }
+    }
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) {
+#pragma unroll
+      for (int i = 0; i < TS; ++i) s[i] += __shfl_xor_sync(0xffffffffu, s[i], m);
+    }
+#pragma unroll
+    for (int i = 0; i < TS; ++i)
+      if (lane == i && tb + i < n) sc[tb + i] = s[i] * scale;
+  }
+  __syncthreads();
+  float mx = -INFINITY;
+  for (size_t t = threadIdx.x; t < n; t += ATT_THREADS) mx = fmaxf(mx, sc[t]);
+  mx = block_max(mx, red);
+  float sum = 0.0f;
+  for (size_t t = threadIdx.x; t < n; t += ATT_THREADS) {
+    const float e = expf(sc[t] - mx);
+    sc[t] = e;
+    sum += e;
+  }
+  sum = block_sum(sum, red);
+  __syncthreads();
+  // weighted values: thread = (group, dim); groups stride over the slice, 16 loads in flight.
+  // The new position (if in this slice) is left out here and added from shared memory below.
+  const size_t groups = ATT_THREADS / d.hd, g = threadIdx.x / d.hd, dd = threadIdx.x % d.hd;
+  const size_t n_old = has_new ? n - 1 : n;  // the new position is always the last of its slice
+  float av = 0.0f;
+  {
+    size_t t = g;
+    for (; t + 15 * groups < n_old; t += 16 * groups) {
+      float vv[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) vv[i] = vc[(t0 + t + i * groups) * kv_dim + dd];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) av += sc[t + i * groups] * vv[i];
+    }
+    for (; t + 3 * groups < n_old; t += 4 * groups) {
+      float vv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) vv[i] = vc[(t0 + t + i * groups) * kv_dim + dd];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) av += sc[t + i * groups] * vv[i];
+    }
+    for (; t < n_old; t += groups) av += sc[t] * vc[(t0 + t) * kv_dim + dd];
+    if (has_new && g == 0) av += sc[n - 1] * vn[dd];
+  }
+  acc[threadIdx.x] = av;
+  __syncthreads();
+  // partial record of this split: [hd values | max | sum]
+  const size_t rec = d.hd + 2;
+  float *prt = a.partial + ((b * d.nh + head) * n_splits + split) * rec;
+  if (threadIdx.x < d.hd) {
+    float v = 0.0f;
+    for (size_t k2 = 0; k2 < groups; ++k2) v += acc[k2 * d.hd + threadIdx.x];
+    prt[threadIdx.x] = v;
+  }
+  if (threadIdx.x == 0) {
+    prt[d.hd] = mx;
+    prt[d.hd + 1] = sum;
+  }
+  __syncthreads();
+  unsigned *ctr = a.counters + b * d.nh + head;
+  if (threadIdx.x == 0) {
+    __threadfence();
+    *is_last_p = (atomicAdd(ctr, 1u) == unsigned(n_splits - 1));
+    __threadfence();
+  }
+  __syncthreads();
+  if (!*is_last_p) return;
+  // merge of the splits by the last CTA of the head: the (max, sum) pairs first, one thread per
+  // split, then the vectors with the splits dealt over the thread groups and four loads in flight
+  const float *all = a.partial + ((b * d.nh + head) * n_splits) * rec;
+  float *wk = sc;  // [n_splits] weights, reusing the score buffer (n_splits <= 32 <= split_len)
+  if (threadIdx.x < unsigned(n_splits)) {
+    red[threadIdx.x] = __ldcg(all + threadIdx.x * rec + d.hd);
+    wk[threadIdx.x] = __ldcg(all + threadIdx.x * rec + d.hd + 1);
+  }
+  __syncthreads();
+  float gmx = -INFINITY, den = 0.0f;
+  for (int k2 = 0; k2 < n_splits; ++k2) gmx = fmaxf(gmx, red[k2]);
+  for (int k2 = 0; k2 < n_splits; ++k2) den += (wk[k2] > 0.0f) ? expf(red[k2] - gmx) * wk[k2] : 0.0f;
+  __syncthreads();
+  if (threadIdx.x < unsigned(n_splits)) wk[threadIdx.x] = (wk[threadIdx.x] > 0.0f) ? expf(red[threadIdx.x] - gmx) : 0.0f;
+  __syncthreads();
+  {
+    float tot = 0.0f;
+    int k2 = int(g);
+    for (; k2 + 3 * int(groups) < n_splits; k2 += 4 * int(groups)) {
+      float pv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) pv[i] = __ldcg(all + (k2 + i * int(groups)) * rec + dd);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) tot += wk[k2 + i * int(groups)] * pv[i];
+    }
+    for (; k2 < n_splits; k2 += int(groups)) tot += wk[k2] * __ldcg(all + k2 * rec + dd);
+    acc[threadIdx.x] = tot;
+  }
+  __syncthreads();
+  if (threadIdx.x < d.hd) {
+    float tot = 0.0f;
+    for (size_t k2 = 0; k2 < groups; ++k2) tot += acc[k2 * d.hd + threadIdx.x];
+    a.out[(b * d.nh + head) * d.hd + threadIdx.x] = tot * (1.0f / den);
+  }
+  if (threadIdx.x == 0) *ctr = 0u;
+}
+
+}  // namespace
+
+}  // namespace lmb

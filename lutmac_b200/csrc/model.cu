@@ -12,7 +12,7 @@
 #include <new>
 #include <vector>
 
-#include "decode_ops.cuh"
+#include "model.cuh"
 
 namespace lmb {
 
@@ -57,41 +57,6 @@ constexpr int NCCL_FLOAT = 7, NCCL_SUM = 0;
 }  // namespace lmb
 
 using namespace lmb;
-
-struct LayerW {
-  lmb_weight *w[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};  // q k v o gate up down
-  bool rot[7] = {false, false, false, false, false, false, false};
-  float *in_norm = nullptr, *post_norm = nullptr, *qb = nullptr, *kb = nullptr, *vb = nullptr;
-};
-
-struct lmb_model {
-  lmb_ctx *ctx = nullptr;
-  lmb_model_config cfg;
-  size_t nh = 0, nkv = 0, inter = 0, vocab_local = 0;  // this rank's share
-  lmb_weight *embed = nullptr, *lm_head = nullptr;
-  bool head_tied = false, head_rot = false, embed_rot = false;
-  float *final_norm = nullptr;
-  std::vector<LayerW> layers;
-  // activations [max_batch][...]
-  float *hidden = nullptr, *normed = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *att = nullptr, *proj = nullptr,
-        *gate = nullptr, *up = nullptr, *act = nullptr, *logits = nullptr, *logits_local = nullptr;
-  float *att_partial = nullptr;      // [max_batch][nh][32 splits][hd + 2]
-  unsigned *att_counters = nullptr;  // [max_batch][nh]
-  float *kv = nullptr;        // [max_batch][L][2][max_seq][nkv][hd]
-  float *cs_table = nullptr;  // [max_seq][hd/2 cos | hd/2 sin]
-  int *d_tokens = nullptr;
-  size_t *d_pos = nullptr;
-  void *h_io = nullptr;  // pinned staging for tokens + positions
-  size_t seq_stride = 0;
-  // one instantiated CUDA graph of the whole step per batch size (token ids and positions are
-  // read from device buffers, so the graph never changes)
-  bool use_graph = true, capturing = false;
-  bool fused = true;  // norm / activation / residual fused into the GEMV launches (unsharded models)
-  bool tp_peers = true;  // tensor parallelism: partial vectors through peer memory (else NCCL all-reduce)
-  std::vector<cudaGraphExec_t> graphs;      // index = batch
-  std::vector<uint64_t> graph_launches;
-  std::vector<uint64_t> graph_gen;  // lmb_ctx::scratch_gen each graph was captured under
-};
 
 static int dev_alloc(float **p, size_t n) {
   LMB_CUDA(cudaMalloc(p, (n ? n : 1) * sizeof(float)));
@@ -322,6 +287,8 @@ int lmb_model_create(lmb_ctx *ctx, const lmb_model_config *c, lmb_model **out) {
     m->fused = !(fv && fv[0] == '0');
     const char *pv = std::getenv("LMB_TP_PEERS");
     m->tp_peers = !(pv && pv[0] == '0');
+    const char *sv = std::getenv("LMB_MODEL_PERSISTENT");
+    m->persistent = !(sv && sv[0] == '0');
   }
   const size_t B = c->max_batch, h = c->hidden_size, hd = c->head_dim;
   m->seq_stride = c->num_hidden_layers * 2 * c->max_seq_len * m->nkv * hd;
@@ -387,6 +354,7 @@ int lmb_model_destroy(lmb_model *m) {
   if (m->lm_head && !m->head_tied) lmb_weight_free(m->lm_head);
   lmb_weight_free(m->embed);
   for (auto g : m->graphs) if (g) cudaGraphExecDestroy(g);
+  persist_invalidate(m);
   if (m->d_tokens) cudaFree(m->d_tokens);
   if (m->d_pos) cudaFree(m->d_pos);
   if (m->h_io) cudaFreeHost(m->h_io);
@@ -401,6 +369,7 @@ int lmb_model_set_weight(lmb_model *m, int layer, int slot, int kind, int quant_
     if (g) cudaGraphExecDestroy(g);
     g = nullptr;
   }
+  persist_invalidate(m);
   const lmb_model_config &c = m->cfg;
   const size_t g = size_t(c.tp_size), r = size_t(c.tp_rank), bpr = (K + BLK - 1) / BLK;
   const size_t h = c.hidden_size, hd = c.head_dim;
@@ -463,7 +432,14 @@ int lmb_model_set_vector(lmb_model *m, int layer, int which, const float *data, 
     }
   }
   LMB_REQUIRE(n == want, "lmb_model_set_vector: length does not match the model config");
-  if (!*dst) LMB_CUDA(cudaMalloc(dst, keep * sizeof(float)));
+  if (!*dst) {
+    for (auto &gr : m->graphs) {  // a bias that did not exist when a step was captured or planned
+      if (gr) cudaGraphExecDestroy(gr);
+      gr = nullptr;
+    }
+    persist_invalidate(m);
+    LMB_CUDA(cudaMalloc(dst, keep * sizeof(float)));
+  }
   LMB_CUDA(cudaMemcpy(*dst, data + off, keep * sizeof(float), cudaMemcpyHostToDevice));
   return LMB_OK;
 }
@@ -481,6 +457,7 @@ int model_tie_head(lmb_model *m) {
     if (g) cudaGraphExecDestroy(g);
     g = nullptr;
   }
+  persist_invalidate(m);
   if (m->lm_head && !m->head_tied) lmb_weight_free(m->lm_head);
   m->lm_head = m->embed;
   m->head_tied = true;
@@ -549,7 +526,29 @@ int lmb_model_forward(lmb_model *m, const int *token_ids, const size_t *position
   }
 
   int st = LMB_OK;
-  const bool graphed = m->use_graph;
+  bool graphed = false;
+  if (batch == 1 && !m->capturing && persist_eligible(m)) {
+    // embedding and all layers as one persistent kernel, then the final norm inside the head's launch
+    st = persist_forward(m);
+    if (st == LMB_OK) {
+      Fuse fin;
+      fin.xmode = XMODE_RMSNORM;
+      fin.x2 = m->final_norm;
+      if (c.tp_size > 1) {
+        st = gemv1(m, m->lm_head, m->head_rot, m->hidden, h, m->logits_local, 1, fin);
+        if (st == LMB_OK) st = lmb_allgather(ctx, m->logits_local, m->logits, m->vocab_local);
+      } else {
+        st = gemv1(m, m->lm_head, m->head_rot, m->hidden, h, m->logits, 1, fin);
+      }
+      if (st == LMB_OK) st = persist_record_status(m);
+      if (st != LMB_OK) return st;
+      goto fetch;
+    }
+    if (st != LMB_ERR_STATE) return st;  // LMB_ERR_STATE: the model does not fit the persistent kernel's limits
+    m->persistent = false;
+    st = LMB_OK;
+  }
+  graphed = m->use_graph;
   if (graphed) {
     if (m->graphs.size() <= batch) {
       m->graphs.resize(batch + 1, nullptr);
@@ -693,6 +692,16 @@ fetch:
   if (h_logits) {
     LMB_CUDA(cudaMemcpyAsync(h_logits, m->logits, batch * c.vocab_size * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
     LMB_CUDA(cudaStreamSynchronize(ctx->stream));
+    {
+      unsigned expired = 0;
+      int ps = persist_take_status(m, &expired);
+      if (ps != LMB_OK) return ps;
+      if (expired) {
+        set_last_error("lmb_model_forward: a bounded wait between the phases of the decode step expired (phase " +
+                       std::to_string(expired - 1) + ")");
+        return LMB_ERR_TIMEOUT;
+      }
+    }
     if (c.tp_size > 1 && ctx->xchg.ready) {
       // a consumer that gave up waiting for another rank's partial vector has produced garbage:
       // the step reports it instead of returning the logits as if nothing had happened
@@ -704,6 +713,13 @@ fetch:
       }
     }
   }
+  return LMB_OK;
+}
+
+int lmb_debug_model_waits(lmb_model *m, int extra_arrivals, unsigned spin_limit) {
+  LMB_REQUIRE(m && extra_arrivals >= 0, "lmb_debug_model_waits: bad argument");
+  m->debug_extra_arrivals = extra_arrivals;
+  m->ctx->xchg.spin_limit = spin_limit ? spin_limit : (1u << 22);
   return LMB_OK;
 }
 

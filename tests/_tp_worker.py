@@ -21,6 +21,9 @@ CASES = (
     ("int4", "INT4", "1", SMALL, 2, STEPS2, (0, 1)),
     ("ternary", "TERNARY", "1", SMALL, 2, STEPS2, (0, 1)),
     ("int4_nccl", "INT4", "0", SMALL, 2, STEPS2, (0, 1)),
+    # batch 1: embedding, all layers and the exchanges between the ranks inside one persistent kernel
+    ("int4_batch_1", "INT4", "1", SMALL, 1, ((3,), (100,), (7,), (500,)), (0,)),
+    ("int2_batch_1", "INT2", "1", SMALL, 1, ((3,), (100,), (7,), (500,)), (0,)),
     ("ternary_hidden_8192", "TERNARY", "1", WIDE, 1, ((3,), (900,), (77,)), (0,)),
     ("ternary_batch_16", "TERNARY", "1", SMALL, 16, None, (0, 7, 15)),
 )

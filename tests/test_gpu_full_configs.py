@@ -36,6 +36,15 @@ def reference_steps(reference, spec, caches, tokens, position):
         return list(ex.map(one, range(len(caches))))
 
 
+def port_step(oracle, spec, cache, token, position):
+    """The same step through the plain-C restatement (no -ffast-math): how far two builds of the
+    SAME fp32 arithmetic drift apart on this model state is the reference's own noise floor."""
+    from oracle.oracle import OracleModel
+    om = OracleModel(oracle, spec, n_threads=8)
+    om.kv[:] = cache
+    return om.forward(int(token), position)
+
+
 def prefill(model, vocab, ctx_len, batch, seed):
     rng = np.random.default_rng(seed)
     for p in range(ctx_len):  # uniform-random token ids, as the configurations state
@@ -57,7 +66,7 @@ def test_config3_llama_1b_int4_context_512(ctx, reference):
     m.close()
 
 
-def test_config4_qwen_1p5b_rrq_context_1024_batch_1_and_8(ctx, reference):
+def test_config4_qwen_1p5b_rrq_context_1024_batch_1_and_8(ctx, reference, oracle):
     """28 layers, hidden 1536, 12/2 heads of 128, FFN 8960, vocab 151936, q/k/v bias, 2-bit RRQ
     projections (scale2 != 0), 1024 cached positions; batch 1, then batch 8 (two of the eight
     sequences are checked, each against a reference run of its own)."""
@@ -73,6 +82,8 @@ def test_config4_qwen_1p5b_rrq_context_1024_batch_1_and_8(ctx, reference):
     errs = {"batch 8, sequence 0": rel_l2(got8[0], want[0]), "batch 8, sequence 7": rel_l2(got8[7], want[1]),
             "batch 1": rel_l2(got1, want[0])}
     print("config 4 (28 layers, RRQ 2-bit): logits rel L2 vs reference " + ", ".join(f"{k} {v:.3e}" for k, v in errs.items()))
+    port = port_step(oracle, spec, caches[0], tok8[0], 1024)
+    print(f"config 4 noise floor: C restatement vs reference {rel_l2(port, want[0]):.3e}, GPU vs C restatement {rel_l2(got1, port):.3e}")
     for k, v in errs.items():
         assert v < TOL, (k, v)
     m.close()

@@ -280,3 +280,21 @@ def test_extreme_activation_ranges(ctx, oracle):
         y = run_linear(ctx, t, x)[0]
         want = oracle.gemv_f64(kind, t.blocks, x, 96, 1024)
         assert rel_l2(y, want) < TOL, KIND_NAMES[kind]
+
+
+@pytest.mark.parametrize("kind,M,K", [(TERNARY, 8192, 8192), (INT2, 8960, 1536), (INT2, 1536, 8960), (INT4, 2048, 8192),
+                                      (INT8, 4096, 2048)])
+def test_error_against_fp64_truth_is_not_above_the_reference_kernel(ctx, oracle, reference, kind, M, K):
+    """Both the CUDA path and the reference kernel are fp32 approximations of the same exact sum.
+    Against the fp64 evaluation of that sum the CUDA result must not be further off than the
+    reference's own scalar kernel (twice its error, or 3e-7, whichever is larger)."""
+    rng = np.random.default_rng(kind * 31 + M)
+    t = synth.tensor(rng, kind, M, K)
+    x = synth.activations(rng, K)
+    xr = reference.apply_hadamard_rotation(x) if t.needs_rotation() else x  # what lut_linear feeds its kernel
+    truth = oracle.gemv_f64(kind, t.blocks, xr, M, K)
+    got = api.lut_linear(t, None, x, None, 1, ctx=ctx)
+    ref = reference.lut_linear(kind, t.quant_bits, t.blocks, M, K, None, x)[0]
+    e_gpu, e_ref = rel_l2(got, truth), rel_l2(ref, truth)
+    print(f"kind {kind} {M}x{K}: rel L2 vs fp64 truth: CUDA {e_gpu:.3e}, reference kernel {e_ref:.3e}")
+    assert e_gpu <= max(2.0 * e_ref, 3e-7), (e_gpu, e_ref)

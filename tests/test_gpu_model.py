@@ -67,10 +67,13 @@ def test_batched_decode_equals_independent_sequences(ctx, oracle):
     m.close()
 
 
-@pytest.mark.parametrize("env", [{"LMB_MODEL_FUSED": "0"}, {"LMB_MODEL_GRAPH": "0"}, {"LMB_MODEL_FUSED": "0", "LMB_MODEL_GRAPH": "0"}])
+@pytest.mark.parametrize("env", [{}, {"LMB_MODEL_FUSED": "0"}, {"LMB_MODEL_GRAPH": "0"}, {"LMB_MODEL_FUSED": "0", "LMB_MODEL_GRAPH": "0"}])
 def test_unfused_and_ungraphed_steps_match_the_fixtures(ctx, env, monkeypatch):
-    """The step can run without norm/activation fusion (the sequence tensor-parallel runs use)
-    and without graph capture; the switches are read when the model is created."""
+    """Batch 1 normally runs as one persistent kernel; with LMB_MODEL_PERSISTENT=0 the step is one
+    launch per projection, which can in turn run without norm/activation fusion (the sequence
+    batched tensor-parallel runs use) and without graph capture.  The switches are read when the
+    model is created."""
+    env = dict(env, LMB_MODEL_PERSISTENT="0")
     for k, v in env.items():
         monkeypatch.setenv(k, v)
     g = np.load(os.path.join(GOLD, "model.npz"))
@@ -122,6 +125,27 @@ def test_batch_size_changes_on_a_graphed_model(oracle):
             pos[b] += 1
     m.close()
     own.close()
+
+
+def test_persistent_step_wait_expires_and_reports(ctx):
+    """The CTAs of the persistent decode step wait for each other through arrival counters.  Here
+    every wait expects one arrival more than there are CTAs and polls only 200 times: the first
+    wait runs out, the kernel records the phase and returns by itself, the step reports
+    LMB_ERR_TIMEOUT, and the same model decodes correctly again afterwards."""
+    from lutmac_b200 import _lib
+    from lutmac_b200._lib import LutmacError
+    g = np.load(os.path.join(GOLD, "model.npz"))
+    spec = synth.model_spec(synth.tiny_model_shape(), INT4, seed=11, max_seq=2048)
+    m = Model(spec, ctx)
+    assert rel_l2(m.forward(int(g["tokens"][0]), 0), g["int4_logits"][0]) < TOL
+    _lib.check(_lib.lib().lmb_debug_model_waits(m.h, 1, 200))
+    with pytest.raises(LutmacError) as e:
+        m.forward(int(g["tokens"][1]), 1)
+    assert e.value.status == _lib.ERR_TIMEOUT
+    _lib.check(_lib.lib().lmb_debug_model_waits(m.h, 0, 0))
+    for p, t in enumerate(g["tokens"]):  # the cache slots are rewritten with the same values
+        assert rel_l2(m.forward(int(t), p), g["int4_logits"][p]) < TOL, p
+    m.close()
 
 
 def test_model_errors(ctx):
