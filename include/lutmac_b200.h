@@ -43,7 +43,11 @@ enum {
   LMB_INT4 = 4,    /* Int4Block     132 B  types.hpp:174-181 */
   LMB_INT5 = 5,    /* Int5Block     164 B  types.hpp:296-301 */
   LMB_INT6 = 6,    /* Int6Block     196 B  types.hpp:344-349 */
-  LMB_INT8 = 8     /* Int8Block     260 B  types.hpp:434-438 */
+  LMB_INT8 = 8,    /* Int8Block     260 B  types.hpp:434-438 */
+  /* PackedTensor::raw_data of an unquantised tensor (is_quantized == false, types.hpp:470-492):
+   * `blocks` is then the row-major fp32 matrix [M][K] and lut_linear takes its plain dot-product
+   * branch (lut_gemm_scalar.cpp:157-171: no rotation, no padding).  lmb_linear* only. */
+  LMB_RAW_F32 = 32
 };
 /* sizeof the reference block struct of a kind (0 for an unknown kind). */
 size_t lmb_block_bytes(int kind);
@@ -212,7 +216,16 @@ typedef struct {
   float rope_theta, rope_scaling_factor, rms_norm_eps;
   size_t max_batch;  /* sequences decoded together (the reference decodes one) */
   int tp_rank, tp_size; /* tensor-parallel position of this process (0,1 = unsharded) */
+  /* model_type "gemma" (src/model.cpp:255-260,294-301,390-399,436-442): the embedding row is scaled
+   * by sqrt(hidden_size) and every RMSNorm multiplies by (1 + weight) (gemma_rms_norm,
+   * src/layers/norm.cpp:40-53).  0 = the llama-type path. */
+  int gemma;
+  /* FFN activation: LMB_ACT_SILU = silu(gate) * up (the reference's default branch,
+   * src/model.cpp:414-416), LMB_ACT_GELU = gelu(gate) * up with the tanh form of src/model.cpp:38-42
+   * (ActivationType::GELU, :409-412). */
+  int activation;
 } lmb_model_config;
+enum { LMB_ACT_SILU = 0, LMB_ACT_GELU = 1 };
 
 enum { /* tensor slots of lmb_model_set_weight */
   LMB_SLOT_EMBED = 0, LMB_SLOT_LM_HEAD = 1, LMB_SLOT_Q = 2, LMB_SLOT_K = 3, LMB_SLOT_V = 4,
@@ -246,6 +259,13 @@ int lmb_model_logits_dev(lmb_model *m, const float **d_logits);
  * wait runs out, the kernel records the phase and returns by itself, and the lmb_model_forward
  * call that fetches logits returns LMB_ERR_TIMEOUT; (0, 0) restores normal operation. */
 int lmb_debug_model_waits(lmb_model *m, int extra_arrivals, unsigned spin_limit);
+/* Per-phase timestamps of the persistent decode step (profiling aid).  The first call switches
+ * the recording on (and returns only *n_phases); later calls return the last step's record:
+ * out[2][n_phases][5] nanoseconds of the device's global timer for CTA 0 and for the last CTA at
+ * {phase descriptor read, dependency met, activations prepared, main loop done, phase done},
+ * types[i] = 0 embedding, 1 GEMV, 2 attention, 3 tensor-parallel reduce, kslices[i] = K split. */
+int lmb_debug_model_timeline(lmb_model *m, unsigned long long *out, int *types, int *kslices, size_t cap_phases,
+                             size_t *n_phases);
 int lmb_model_reset(lmb_model *m);
 /* KV cache exchange in the reference layout [layer][2][max_seq][kv_heads][head_dim]
  * (types.hpp:599-627) for sequence `seq`.  The host buffer always has the layout of the whole

@@ -30,7 +30,7 @@ class ModelConfig(C.Structure):
     _fields_ = [("vocab_size", sz), ("hidden_size", sz), ("intermediate_size", sz), ("num_hidden_layers", sz),
                 ("num_attention_heads", sz), ("num_key_value_heads", sz), ("head_dim", sz), ("max_seq_len", sz),
                 ("rope_theta", C.c_float), ("rope_scaling_factor", C.c_float), ("rms_norm_eps", C.c_float),
-                ("max_batch", sz), ("tp_rank", C.c_int), ("tp_size", C.c_int)]
+                ("max_batch", sz), ("tp_rank", C.c_int), ("tp_size", C.c_int), ("gemma", C.c_int), ("activation", C.c_int)]
 
 
 # name -> (restype, argtypes); every symbol include/lutmac_b200.h declares
@@ -89,6 +89,7 @@ SIGNATURES = {
     "lmb_model_tie_head": (C.c_int, [vp]),
     "lmb_model_set_vector": (C.c_int, [vp, C.c_int, C.c_int, vp, sz]),
     "lmb_model_forward": (C.c_int, [vp, C.POINTER(C.c_int), C.POINTER(sz), sz, vp]),
+    "lmb_debug_model_timeline": (C.c_int, [vp, C.POINTER(C.c_uint64), C.POINTER(C.c_int), C.POINTER(C.c_int), sz, C.POINTER(sz)]),
     "lmb_debug_model_waits": (C.c_int, [vp, C.c_int, C.c_uint]),
     "lmb_model_logits_dev": (C.c_int, [vp, C.POINTER(vp)]),
     "lmb_model_reset": (C.c_int, [vp]),

@@ -86,12 +86,45 @@ int launch_fwht256(lmb_ctx *ctx, float *d_x, size_t n) {
   return LMB_OK;
 }
 
+// Unquantised weights: the raw fp32 branch of lut_linear (lut_gemm_scalar.cpp:157-171), y = W x + bias
+// with W row-major [M][K].  One warp per row, 128-bit loads where the row is 16-byte aligned.
+__global__ void __launch_bounds__(256) k_gemv_raw(const float *__restrict__ W, const float *x, const float *bias, float *y, size_t M,
+                                                  size_t K, size_t x_len, size_t x_stride) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const size_t row = size_t(blockIdx.x) * 8 + warp;
+  if (row >= M) return;
+  const float *w = W + row * K, *xb = x + size_t(blockIdx.y) * x_stride;
+  const size_t n = x_len < K ? x_len : K;  // columns at or beyond x_len read as zero
+  float acc = 0.0f;
+  if ((K & 3) == 0 && ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(xb)) & 15) == 0) {
+    const size_t n4 = n / 4;
+    for (size_t i = lane; i < n4; i += 32) {
+      const float4 a = ld_stream_v4f(w + 4 * i), b = *reinterpret_cast<const float4 *>(xb + 4 * i);
+      acc += (a.x * b.x + a.y * b.y) + (a.z * b.z + a.w * b.w);
+    }
+    for (size_t i = 4 * n4 + lane; i < n; i += 32) acc += w[i] * xb[i];
+  } else {
+    for (size_t i = lane; i < n; i += 32) acc += w[i] * xb[i];
+  }
+#pragma unroll
+  for (int m = 16; m > 0; m >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
+  if (lane == 0) y[size_t(blockIdx.y) * M + row] = acc + (bias ? bias[row] : 0.0f);
+}
+
 static int linear_impl(lmb_ctx *ctx, const lmb_weight *w, const float *d_bias, const float *d_x, size_t x_len,
                        size_t x_stride, float *d_y, size_t batch, unsigned flags) {
   LMB_REQUIRE(ctx && w && d_x && d_y, "lmb_linear: null argument");
   LMB_REQUIRE(batch > 0 && batch <= 65535, "lmb_linear: batch must be in 1..65535");
   LMB_REQUIRE(w->device == ctx->device, "lmb_linear: weight lives on another device");
   LMB_REQUIRE(x_len <= w->bpr * size_t(BLK), "lmb_linear: x_len exceeds the padded input width");
+  if (w->kind == LMB_RAW_F32) {
+    LMB_REQUIRE(!(flags & LMB_ROTATE), "lmb_linear: the unquantised branch of lut_linear never rotates its input");
+    dim3 grid(unsigned((w->M + 7) / 8), unsigned(batch));
+    k_gemv_raw<<<grid, 256, 0, ctx->stream>>>(reinterpret_cast<const float *>(w->d_tiles), d_x, d_bias, d_y, w->M, w->K, x_len, x_stride);
+    ctx->launches++;
+    LMB_CUDA(cudaGetLastError());
+    return LMB_OK;
+  }
   LinearArgs a;
   a.w = w;
   a.bias = d_bias;
@@ -364,6 +397,31 @@ int lmb_graph_destroy(lmb_graph *g) {
 int lmb_weight_upload_shard(lmb_ctx *ctx, int kind, const void *blocks, size_t M, size_t K, size_t row0,
                             size_t row1, size_t blk0, size_t blk1, lmb_weight **out) {
   LMB_REQUIRE(ctx && blocks && out, "lmb_weight_upload: null argument");
+  if (kind == LMB_RAW_F32) {  // row-major fp32, kept as it is (rows [row0,row1) only; no column shards)
+    LMB_REQUIRE(M > 0 && K > 0 && row0 < row1 && row1 <= M && blk0 == 0 && blk1 == (K + BLK - 1) / BLK,
+                "lmb_weight_upload: an unquantised matrix can be sharded by rows only");
+    *out = nullptr;
+    lmb_weight *w = new (std::nothrow) lmb_weight();
+    if (!w) return LMB_ERR_ALLOC;
+    w->kind = w->ref_kind = LMB_RAW_F32;
+    w->device = ctx->device;
+    w->M = row1 - row0;
+    w->K = K;
+    w->bpr = blk1;
+    w->row_tiles = (w->M + TILE_ROWS - 1) / TILE_ROWS;
+    w->bytes = w->M * K * sizeof(float);
+    cudaError_t e = cudaSetDevice(ctx->device);
+    if (e == cudaSuccess) e = cudaMalloc(&w->d_tiles, w->bytes);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(w->d_tiles, static_cast<const float *>(blocks) + row0 * K, w->bytes, cudaMemcpyHostToDevice, ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) {
+      if (w->d_tiles) cudaFree(w->d_tiles);
+      delete w;
+      return cuda_fail(e, "lmb_weight_upload(raw)");
+    }
+    *out = w;
+    return LMB_OK;
+  }
   LMB_REQUIRE(kind_valid(kind), "lmb_weight_upload: unknown block kind");
   const size_t src_bpr = (K + BLK - 1) / BLK;
   LMB_REQUIRE(M > 0 && K > 0, "lmb_weight_upload: empty shape");
@@ -433,6 +491,11 @@ int lmb_weight_info(const lmb_weight *w, int *kind, size_t *M, size_t *K, size_t
 
 int lmb_weight_download(lmb_ctx *ctx, const lmb_weight *w, void *blocks_out) {
   LMB_REQUIRE(ctx && w && blocks_out, "lmb_weight_download: null argument");
+  if (w->kind == LMB_RAW_F32) {
+    LMB_CUDA(cudaMemcpyAsync(blocks_out, w->d_tiles, w->bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    LMB_CUDA(cudaStreamSynchronize(ctx->stream));
+    return LMB_OK;
+  }
   std::vector<uint8_t> h(w->bytes);
   LMB_CUDA(cudaMemcpyAsync(h.data(), w->d_tiles, w->bytes, cudaMemcpyDeviceToHost, ctx->stream));
   LMB_CUDA(cudaStreamSynchronize(ctx->stream));

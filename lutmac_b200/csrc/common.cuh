@@ -219,12 +219,12 @@ struct LinearArgs {
   size_t y_stride;
   size_t batch;
   bool rotate;
-  const float *x2 = nullptr;        // norm weight (XMODE_RMSNORM) or the vector multiplied in (XMODE_SILU_MUL)
+  const float *x2 = nullptr;        // norm weight (XMODE_RMSNORM) or the vector multiplied in (XMODE_SILU_MUL, XMODE_GELU_MUL)
   const float *residual = nullptr;  // added to the output (same layout as y; may alias y)
   bool to_peers = false;            // deliver y into every rank's exchange block instead (single-job launches)
 };
 // How the GEMV prologue forms its activations from x.
-enum { XMODE_PLAIN = 0, XMODE_RMSNORM = 1, XMODE_SILU_MUL = 2 };
+enum { XMODE_PLAIN = 0, XMODE_RMSNORM = 1, XMODE_SILU_MUL = 2, XMODE_GELU_MUL = 3 };
 int configure_gemv(lmb_ctx *ctx);
 int launch_gemv(lmb_ctx *ctx, const LinearArgs *args, int njobs, bool rotate, int xmode = XMODE_PLAIN, float eps = 0.0f);
 int launch_fwht256(lmb_ctx *ctx, float *d_x, size_t n);

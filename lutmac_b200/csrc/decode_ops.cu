@@ -3,19 +3,21 @@
 // model.cpp:385-399), GQA decode attention with bias + RoPE + KV-cache write folded in
 // (model.cpp:312-372, src/layers/embedding.cpp:36-75, src/layers/attention.cpp:23-42) and SiLU(gate)*up (model.cpp:36,414-416).
 #include "decode_device.cuh"
+#include "device_utils.cuh"
 
 namespace lmb {
 
 namespace {
 
 __global__ void k_embed_rows(const int *tokens, int kind, const uint8_t *tiles, size_t bpr, size_t vocab, size_t h,
-                             float *hidden) {
+                             float scale, float *hidden) {
   asm volatile("griddepcontrol.launch_dependents;");  // a following GEMV may prefetch its weights
   const size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= h) return;
   const int tok = tokens[blockIdx.y];
   // rows beyond the table read as zero (model.cpp:95-104)
-  hidden[size_t(blockIdx.y) * h + i] = (tok >= 0 && size_t(tok) < vocab) ? tile_elem(kind, tiles, bpr, size_t(tok), i) : 0.0f;
+  // gemma-type models scale the row by sqrt(hidden size) (model.cpp:255-260); scale = 1 otherwise
+  hidden[size_t(blockIdx.y) * h + i] = (tok >= 0 && size_t(tok) < vocab) ? tile_elem(kind, tiles, bpr, size_t(tok), i) * scale : 0.0f;
 }
 
 // hidden += add (if given); out = hidden * rsqrt(mean(hidden^2) + eps) * w.  One CTA per sequence.
@@ -101,21 +103,21 @@ __global__ void __launch_bounds__(ATT_THREADS) k_decode_attn(const AttnArgs a, c
   attn_item<false>(a, d, blockIdx.x, blockIdx.y, blockIdx.z, sm, &is_last);
 }
 
-__global__ void k_silu_mul(const float *gate, const float *up, float *out, size_t n) {
+__global__ void k_silu_mul(const float *gate, const float *up, float *out, size_t n, int gelu) {
   asm volatile("griddepcontrol.launch_dependents;");  // a following GEMV may prefetch its weights
   const size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i < n) {
     const float g = gate[i];
-    out[i] = (g / (1.0f + expf(-g))) * up[i];
+    out[i] = (gelu ? gelu_tanh(g) : g / (1.0f + expf(-g))) * up[i];
   }
 }
 
 }  // namespace
 
 int launch_embed_rows(lmb_ctx *ctx, const int *d_tokens, const lmb_weight *embed, size_t vocab, size_t h, size_t batch,
-                      float *d_hidden) {
+                      float scale, float *d_hidden) {
   dim3 grid(unsigned((h + 255) / 256), unsigned(batch));
-  k_embed_rows<<<grid, 256, 0, ctx->stream>>>(d_tokens, embed->kind, embed->d_tiles, embed->bpr, vocab, h, d_hidden);
+  k_embed_rows<<<grid, 256, 0, ctx->stream>>>(d_tokens, embed->kind, embed->d_tiles, embed->bpr, vocab, h, scale, d_hidden);
   ctx->launches++;
   LMB_CUDA(cudaGetLastError());
   return LMB_OK;
@@ -174,8 +176,8 @@ int launch_decode_attn(lmb_ctx *ctx, const float *q, const float *k, const float
   return LMB_OK;
 }
 
-int launch_silu_mul(lmb_ctx *ctx, const float *gate, const float *up, float *out, size_t n) {
-  k_silu_mul<<<unsigned((n + 255) / 256), 256, 0, ctx->stream>>>(gate, up, out, n);
+int launch_silu_mul(lmb_ctx *ctx, const float *gate, const float *up, float *out, size_t n, bool gelu) {
+  k_silu_mul<<<unsigned((n + 255) / 256), 256, 0, ctx->stream>>>(gate, up, out, n, gelu ? 1 : 0);
   ctx->launches++;
   LMB_CUDA(cudaGetLastError());
   return LMB_OK;

@@ -17,6 +17,11 @@ __device__ __forceinline__ uint4 ld_stream_v4(const void *p) {
                : "l"(p));
   return v;
 }
+__device__ __forceinline__ float4 ld_stream_v4f(const void *p) {
+  float4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+  return v;
+}
 __device__ __forceinline__ float ld_stream_f32(const void *p) {
   float v;
   asm volatile("ld.global.nc.L1::no_allocate.f32 %0, [%1];" : "=f"(v) : "l"(p));
@@ -36,6 +41,11 @@ __device__ __forceinline__ float2 add2(const float2 a, const float2 b) {
       : "=l"(reinterpret_cast<unsigned long long &>(r))
       : "l"(reinterpret_cast<const unsigned long long &>(a)), "l"(reinterpret_cast<const unsigned long long &>(b)));
   return r;
+}
+
+// gelu(x) of src/model.cpp:38-42 (tanh form)
+__device__ __forceinline__ float gelu_tanh(float x) {
+  return 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
 }
 
 // Loads the lane's 8 consecutive activations of 256-block `b` (elements b*256 + lane*8 + j);

@@ -196,7 +196,7 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
 #pragma unroll
       for (int e = 0; e < 8; ++e) v[e] = nv[e];
       if (p.xmode == XMODE_RMSNORM) load_x8(job.x2, job.x_len, size_t(b0 + bl), lane, w8);
-      if (p.xmode == XMODE_SILU_MUL) load_x8(job.x2 + size_t(batch0 + q) * job.x_stride, job.x_len, size_t(b0 + bl), lane, w8);
+      if (p.xmode == XMODE_SILU_MUL || p.xmode == XMODE_GELU_MUL) load_x8(job.x2 + size_t(batch0 + q) * job.x_stride, job.x_len, size_t(b0 + bl), lane, w8);
       if (it + WARPS < items) {
         const int nq = NSEQ == 1 ? 0 : (it + WARPS) / ns;
         load_x8(x + size_t(nq) * job.x_stride, job.x_len, size_t(b0 + (it + WARPS) - nq * ns), lane, nv);
@@ -208,6 +208,9 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
       } else if (p.xmode == XMODE_SILU_MUL) {
 #pragma unroll
         for (int e = 0; e < 8; ++e) v[e] = (v[e] / (1.0f + expf(-v[e]))) * w8[e];  // silu(gate) * up, model.cpp:36,414-416
+      } else if (p.xmode == XMODE_GELU_MUL) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = gelu_tanh(v[e]) * w8[e];  // gelu(gate) * up, model.cpp:38-42,409-412
       }
       if (p.rotate) fwht256_warp(v, lane);
       if constexpr (kind_is_mma(KIND)) {
@@ -371,10 +374,10 @@ __global__ void __launch_bounds__(THREADS) k_prepare_x(const float *x, const flo
     load_x8(x2, x_len, size_t(bl), lane, w8);
 #pragma unroll
     for (int e = 0; e < 8; ++e) v[e] = v[e] * inv_rms * w8[e];
-  } else if (xmode == XMODE_SILU_MUL) {
+  } else if (xmode == XMODE_SILU_MUL || xmode == XMODE_GELU_MUL) {
     load_x8(x2 + size_t(q) * x_stride, x_len, size_t(bl), lane, w8);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) v[e] = (v[e] / (1.0f + expf(-v[e]))) * w8[e];
+    for (int e = 0; e < 8; ++e) v[e] = (xmode == XMODE_GELU_MUL ? gelu_tanh(v[e]) : v[e] / (1.0f + expf(-v[e]))) * w8[e];
   }
   if (rotate) fwht256_warp(v, lane);
   mma_prologue(v, lane, stage[warp], &bsc[warp], aux2[warp]);

@@ -213,6 +213,8 @@ int lmb_file_config(const lmb_file *f, lmb_model_config *cfg) {
   cfg->max_batch = 1;
   cfg->tp_rank = 0;
   cfg->tp_size = 1;
+  cfg->gemma = f->model_type == "gemma" ? 1 : 0;                 // model.cpp:255,294,390,436
+  cfg->activation = f->activation == 1 ? LMB_ACT_GELU : LMB_ACT_SILU;  // ActivationType::GELU = 1; everything else takes the SiLU branch (model.cpp:409-417)
   return LMB_OK;
 }
 
@@ -275,11 +277,6 @@ int lmb_model_load(lmb_ctx *ctx, const char *path, size_t max_batch, size_t max_
   if (st != LMB_OK) return st;
   lmb_model_config cfg;
   lmb_file_config(f, &cfg);
-  if (f->model_type == "gemma" || f->activation == 1) {
-    set_last_error("lmb_model_load: only the llama-type path (RMSNorm, SiLU) is implemented on the device");
-    lmb_file_close(f);
-    return LMB_ERR_FORMAT;
-  }
   cfg.max_batch = max_batch ? max_batch : 1;
   if (max_seq) cfg.max_seq_len = max_seq;
   cfg.tp_rank = tp_rank;

@@ -320,7 +320,9 @@ int lmb_model_create(lmb_ctx *ctx, const lmb_model_config *c, lmb_model **out) {
         cs[pos * hd + d] = std::cos(angle);
         cs[pos * hd + half + d] = std::sin(angle);
       }
-    std::vector<float> ones(h, 1.0f);  // norm weights default to identity (model.hpp:96-104)
+    // norm weights default to one (model.hpp:96-104).  For gemma-type models the device keeps the
+    // multiplier 1 + weight of gemma_rms_norm (norm.cpp:40-53), so every norm kernel stays x * inv * w.
+    std::vector<float> ones(h, c->gemma ? 2.0f : 1.0f);
     cudaError_t e = cudaMemcpy(m->cs_table, cs.data(), cs.size() * 4, cudaMemcpyHostToDevice);
     if (e == cudaSuccess) e = cudaMemcpy(m->final_norm, ones.data(), h * 4, cudaMemcpyHostToDevice);
     for (auto &L : m->layers) {
@@ -365,6 +367,8 @@ int lmb_model_destroy(lmb_model *m) {
 int lmb_model_set_weight(lmb_model *m, int layer, int slot, int kind, int quant_bits, const void *blocks, size_t M, size_t K) {
   LMB_REQUIRE(m && blocks, "lmb_model_set_weight: null argument");
   LMB_REQUIRE(slot >= LMB_SLOT_EMBED && slot <= LMB_SLOT_DOWN, "lmb_model_set_weight: unknown slot");
+  LMB_REQUIRE(kind != LMB_RAW_F32, "lmb_model_set_weight: the device decoder takes quantised tensors only "
+                                   "(unquantised matrices go through lmb_linear)");
   for (auto &g : m->graphs) {  // captured steps hold the old pointers
     if (g) cudaGraphExecDestroy(g);
     g = nullptr;
@@ -432,6 +436,12 @@ int lmb_model_set_vector(lmb_model *m, int layer, int which, const float *data, 
     }
   }
   LMB_REQUIRE(n == want, "lmb_model_set_vector: length does not match the model config");
+  std::vector<float> plus_one;
+  if (c.gemma && (which == LMB_VEC_FINAL_NORM || which == LMB_VEC_INPUT_NORM || which == LMB_VEC_POST_NORM)) {
+    plus_one.resize(n);
+    for (size_t i = 0; i < n; ++i) plus_one[i] = 1.0f + data[i];  // gemma_rms_norm's (1.0f + weight[i]), same fp32 rounding
+    data = plus_one.data();
+  }
   if (!*dst) {
     for (auto &gr : m->graphs) {  // a bias that did not exist when a step was captured or planned
       if (gr) cudaGraphExecDestroy(gr);
@@ -598,7 +608,7 @@ int lmb_model_forward(lmb_model *m, const int *token_ids, const size_t *position
       goto fetch;
     }
   }
-  st = launch_embed_rows(ctx, m->d_tokens, m->embed, c.vocab_size, h, batch, m->hidden);
+  st = launch_embed_rows(ctx, m->d_tokens, m->embed, c.vocab_size, h, batch, c.gemma ? std::sqrt(float(h)) : 1.0f, m->hidden);
   {
   if (c.tp_size == 1 && m->fused) {
     // Fused form: RMSNorm rides in the prologue of the projections that consume it, SiLU*up in
@@ -610,7 +620,7 @@ int lmb_model_forward(lmb_model *m, const int *token_ids, const size_t *position
       norm1.xmode = XMODE_RMSNORM; norm1.x2 = L.in_norm;
       norm2.xmode = XMODE_RMSNORM; norm2.x2 = L.post_norm;
       res.residual = m->hidden;
-      act.xmode = XMODE_SILU_MUL; act.x2 = m->up; act.residual = m->hidden;
+      act.xmode = c.activation == LMB_ACT_GELU ? XMODE_GELU_MUL : XMODE_SILU_MUL; act.x2 = m->up; act.residual = m->hidden;
       float *qkv[3] = {m->q, m->k, m->v};
       st = gemv_group(m, 3, &L.w[0], &L.rot[0], m->hidden, h, qkv, batch, norm1);
       if (st != LMB_OK) break;
@@ -671,7 +681,7 @@ int lmb_model_forward(lmb_model *m, const int *token_ids, const size_t *position
     st = gemv_group(m, 2, &L.w[4], &L.rot[4], m->normed, h, gu, batch);
     if (st != LMB_OK) break;
     Fuse act;  // SiLU(gate) * up in the prologue of down_proj (element-wise, so a column shard needs no exchange)
-    act.xmode = XMODE_SILU_MUL;
+    act.xmode = c.activation == LMB_ACT_GELU ? XMODE_GELU_MUL : XMODE_SILU_MUL;
     act.x2 = m->up;
     st = row_reduce(L.w[6], L.rot[6], m->gate, m->inter, act);
   }
@@ -714,6 +724,11 @@ fetch:
     }
   }
   return LMB_OK;
+}
+
+int lmb_debug_model_timeline(lmb_model *m, unsigned long long *out, int *types, int *kslices, size_t cap_phases, size_t *n_phases) {
+  LMB_REQUIRE(m && n_phases && (cap_phases == 0 || (out && types && kslices)), "lmb_debug_model_timeline: null argument");
+  return persist_timeline(m, out, types, kslices, cap_phases, n_phases);
 }
 
 int lmb_debug_model_waits(lmb_model *m, int extra_arrivals, unsigned spin_limit) {

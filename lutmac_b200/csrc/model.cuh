@@ -60,4 +60,5 @@ int persist_record_status(lmb_model *m);  // after the launches that follow the 
 void persist_invalidate(lmb_model *m);  // weights or vectors changed: plan again at the next step
 // whether a bounded wait of a persistent step expired since the last call (the flag is cleared)
 int persist_take_status(lmb_model *m, unsigned *status);
+int persist_timeline(lmb_model *m, unsigned long long *out, int *types, int *kslices, size_t cap_phases, size_t *n_phases);
 }  // namespace lmb

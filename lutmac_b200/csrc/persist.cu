@@ -24,6 +24,7 @@
 // one-GEMV kernels; only the integer tensor-core layouts take this path, and only models whose
 // seven projections per layer share one layout.  Cooperative launch guarantees co-residency.
 #include <algorithm>
+#include <cmath>
 #include <cstdlib>
 #include <cstring>
 #include <new>
@@ -71,6 +72,7 @@ struct PsPhase {
   const uint8_t *embed_tiles;
   int embed_kind;
   unsigned embed_bpr, vocab, h;
+  float embed_scale;  // 1, or sqrt(hidden size) for gemma-type models (model.cpp:255-260)
   float *hidden;
 };
 
@@ -86,6 +88,9 @@ struct PsParams {
   PeerOut peer;  // peer.n > 0: tensor parallel
   XchgHeader *hdr;
   const unsigned long long *xchg_data;  // this rank's exchange block
+  // optional (null: off): nanosecond timestamps of CTA 0 and of the last CTA at five points of every
+  // phase -- descriptor read, dependency met, activations prepared, main loop done, phase done
+  unsigned long long *timeline;  // [2][n_phases][5]
 };
 
 __device__ __forceinline__ unsigned ld_acquire_u32(const unsigned *p) {
@@ -136,6 +141,12 @@ __device__ __forceinline__ bool ps_wait(const PsParams &p, int ph, int *flag) {
   return ok;
 }
 
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
 // load_x8 for vectors written earlier in the same launch: around the (incoherent) L1
 __device__ __forceinline__ void load_x8_cg(const float *x, size_t x_len, size_t b, int lane, float v[8]) {
   const size_t i0 = b * 256 + size_t(lane) * 8;
@@ -176,8 +187,14 @@ __global__ void __launch_bounds__(PS_THREADS, 2) k_decode_step(const __grid_cons
   const int G = int(gridDim.x), c = int(blockIdx.x);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, t = threadIdx.x;
   const unsigned epoch0 = p.peer.n ? ld_volatile_u32(&p.hdr->epoch) : 0u;
+  unsigned long long *tl = nullptr;
+  if (p.timeline && t == 0 && (c == 0 || c == G - 1)) tl = p.timeline + size_t(c == 0 ? 0 : 1) * p.n_phases * 5;
+  auto stamp = [&](int ph, int k) {
+    if (tl) tl[ph * 5 + k] = global_ns();
+  };
 
   for (int ph = 0; ph < p.n_phases; ++ph) {
+    stamp(ph, 0);
     {  // the phase descriptor: constant for the launch, so it can be read ahead of the dependency
       const uint32_t *src = reinterpret_cast<const uint32_t *>(p.phases + ph);
       uint32_t *dst = reinterpret_cast<uint32_t *>(&P);
@@ -226,6 +243,7 @@ __global__ void __launch_bounds__(PS_THREADS, 2) k_decode_step(const __grid_cons
 
       // ---- the activations exist once every CTA has finished the previous phase --------------------------
       if (ph > 0 && !ps_wait(p, ph - 1, &flag)) return;
+      stamp(ph, 1);
 
       float inv_rms = 1.0f;
       if (P.xmode == XMODE_RMSNORM) {  // src/layers/norm.cpp:18-34, the sum of squares from the producer's partials
@@ -241,10 +259,15 @@ __global__ void __launch_bounds__(PS_THREADS, 2) k_decode_step(const __grid_cons
           load_x8(P.x2, P.x_len, size_t(b0 + it), lane, w8);
 #pragma unroll
           for (int e = 0; e < 8; ++e) v[e] = v[e] * inv_rms * w8[e];
-        } else if (P.xmode == XMODE_SILU_MUL) {
+        } else if (P.xmode == XMODE_SILU_MUL || P.xmode == XMODE_GELU_MUL) {
           load_x8_cg(P.x2, P.x_len, size_t(b0 + it), lane, w8);
+          if (P.xmode == XMODE_SILU_MUL) {
 #pragma unroll
-          for (int e = 0; e < 8; ++e) v[e] = (v[e] / (1.0f + expf(-v[e]))) * w8[e];  // silu(gate) * up, model.cpp:36,414-416
+            for (int e = 0; e < 8; ++e) v[e] = (v[e] / (1.0f + expf(-v[e]))) * w8[e];  // silu(gate) * up, model.cpp:36,414-416
+          } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = gelu_tanh(v[e]) * w8[e];  // gelu(gate) * up, model.cpp:38-42,409-412
+          }
         }
         if (P.rotate) fwht256_warp(v, lane);
         int *aux = xaux + 4 * it;
@@ -252,6 +275,7 @@ __global__ void __launch_bounds__(PS_THREADS, 2) k_decode_step(const __grid_cons
         if (lane == 0) aux[2] = aux[3] = 0;
       }
       __syncthreads();
+      stamp(ph, 2);
 
       // ---- main loop: evaluate a slot, refill it with the unit NSLOT ahead ------------------------------
       typename U::Acc accs[1];
@@ -284,6 +308,7 @@ __global__ void __launch_bounds__(PS_THREADS, 2) k_decode_step(const __grid_cons
         }
       }
       __syncthreads();
+      stamp(ph, 3);
 
       // ---- rows: add the warps' parts in warp order; split K goes through scratch ------------------------
       const unsigned epoch = epoch0 + unsigned(P.xchg_seq);
@@ -346,6 +371,7 @@ __global__ void __launch_bounds__(PS_THREADS, 2) k_decode_step(const __grid_cons
       }
     } else {
       if (ph > 0 && !ps_wait(p, ph - 1, &flag)) return;
+      stamp(ph, 1);
       if (P.type == PH_ATTN) {
         // model.cpp:312-372: one (query head, KV split) item at a time
         const int items = int(P.rd.nh) * P.at.n_splits;
@@ -359,7 +385,7 @@ __global__ void __launch_bounds__(PS_THREADS, 2) k_decode_step(const __grid_cons
         const int tok = P.tokens[0];
         float ss = 0.0f;
         for (int i = i0 + t; i < i1; i += PS_THREADS) {
-          const float v = (tok >= 0 && unsigned(tok) < P.vocab) ? tile_elem(P.embed_kind, P.embed_tiles, P.embed_bpr, size_t(tok), size_t(i)) : 0.0f;
+          const float v = (tok >= 0 && unsigned(tok) < P.vocab) ? tile_elem(P.embed_kind, P.embed_tiles, P.embed_bpr, size_t(tok), size_t(i)) * P.embed_scale : 0.0f;
           P.hidden[i] = v;
           ss += v * v;
         }
@@ -399,6 +425,7 @@ __global__ void __launch_bounds__(PS_THREADS, 2) k_decode_step(const __grid_cons
       }
     }
     ps_arrive(p, ph);
+    stamp(ph, 4);
   }
   // tensor parallel: the exchange block's epoch advances once every CTA is past its last use of it
   if (p.peer.n && c == 0 && p.n_phases > 0) {
@@ -415,8 +442,11 @@ __global__ void __launch_bounds__(PS_THREADS, 2) k_decode_step(const __grid_cons
 int choose_k_slices(int grid, int rt_total, int bpr, size_t tile_b) {
   int best = 0;
   double best_cost = 1e30;
+  const char *force = std::getenv("LMB_PERSIST_KSLICES");  // tuning: largest K split allowed
+  const int cap = force ? std::max(1, std::atoi(force)) : 16;
   for (int n_ks = 1; n_ks <= 16 && n_ks <= bpr; ++n_ks) {
     if (grid % n_ks) continue;
+    if (n_ks > cap && best > 0) continue;
     const int S = (bpr + n_ks - 1) / n_ks;
     if (S > PS_S_MAX) continue;
     const int n_rg = grid / n_ks;
@@ -487,12 +517,14 @@ struct PersistPlan {
   float *d_scratch = nullptr, *d_sumsq = nullptr;
   unsigned *h_status = nullptr;  // pinned copy of the status word of the last step
   bool status_pending = false;
+  unsigned long long *d_timeline = nullptr;  // debug timeline (persist_timeline), allocated on first request
   ~PersistPlan() {
     if (d_phases) cudaFree(d_phases);
     if (d_sync) cudaFree(d_sync);
     if (d_scratch) cudaFree(d_scratch);
     if (d_sumsq) cudaFree(d_sumsq);
     if (h_status) cudaFreeHost(h_status);
+    if (d_timeline) cudaFree(d_timeline);
   }
 };
 
@@ -562,6 +594,7 @@ static int build_plan(lmb_model *m) {
   e.embed_bpr = unsigned(m->embed->bpr);
   e.vocab = unsigned(c.vocab_size);
   e.h = unsigned(h);
+  e.embed_scale = c.gemma ? std::sqrt(float(h)) : 1.0f;
   e.hidden = m->hidden;
   e.sumsq_out = ss[cur];
   ph.push_back(e);
@@ -622,7 +655,10 @@ static int build_plan(lmb_model *m) {
     ph.push_back(g);
   };
 
-  const int n_splits = decode_attn_splits(ctx, m->nh, 1, c.max_seq_len);
+  // KV splits: every (head, split) item gets a CTA of its own (a second round of a few left-over
+  // items would double the phase's time)
+  int n_splits = std::max(1, std::min(decode_attn_splits(ctx, m->nh, 1, c.max_seq_len), grid / int(m->nh)));
+  if (const char *as = std::getenv("LMB_PERSIST_ATTN_SPLITS")) n_splits = std::max(1, std::min(32, std::atoi(as)));
   RopeDims rd{m->nh, m->nkv, hd, c.max_seq_len, m->seq_stride, 0};
   rd.split_len = ((c.max_seq_len + n_splits - 1) / n_splits + 15) / 16 * 16;
   if ((rd.split_len + 3 * hd + 32 + ATT_THREADS) * sizeof(float) > PS_SMEM || hd > size_t(ATT_THREADS) || ATT_THREADS % hd != 0) ok = false;
@@ -642,7 +678,7 @@ static int build_plan(lmb_model *m) {
     float *gu[2] = {m->gate, m->up};
     gemv(2, &L.w[4], gu, m->hidden, h, XMODE_RMSNORM, L.post_norm, L.rot[4], nullptr, false);
     float *d[1] = {tp ? m->proj : m->hidden};
-    gemv(1, &L.w[6], d, m->gate, m->inter, XMODE_SILU_MUL, m->up, L.rot[6], m->hidden, true);
+    gemv(1, &L.w[6], d, m->gate, m->inter, c.activation == LMB_ACT_GELU ? XMODE_GELU_MUL : XMODE_SILU_MUL, m->up, L.rot[6], m->hidden, true);
   }
   if (!ok) {
     set_last_error("persistent step: a projection shape does not fit the kernel's per-CTA limits");
@@ -683,6 +719,7 @@ int persist_forward(lmb_model *m) {
   p.spin_limit = ctx->xchg.spin_limit;
   p.extra_arrivals = unsigned(m->debug_extra_arrivals);
   p.eps = m->cfg.rms_norm_eps;
+  p.timeline = pl->d_timeline;
   if (m->cfg.tp_size > 1) {
     p.peer.n = ctx->tp_size;
     p.peer.rank = ctx->tp_rank;
@@ -703,6 +740,33 @@ int persist_record_status(lmb_model *m) {
   if (!pl) return LMB_OK;
   LMB_CUDA(cudaMemcpyAsync(pl->h_status, pl->d_sync, sizeof(unsigned), cudaMemcpyDeviceToHost, m->ctx->stream));
   pl->status_pending = true;
+  return LMB_OK;
+}
+
+// Debug view: turns the per-phase timestamps on (first call) and returns those of the last step:
+// out[2][n_phases][5] nanoseconds, phase types in types[n_phases], K slices in kslices[n_phases].
+int persist_timeline(lmb_model *m, unsigned long long *out, int *types, int *kslices, size_t cap_phases, size_t *n_phases) {
+  PersistPlan *pl = m->ps;
+  if (!pl) {
+    set_last_error("persistent step: no plan yet (run one batch-1 step first)");
+    return LMB_ERR_STATE;
+  }
+  *n_phases = size_t(pl->n_phases);
+  const size_t words = size_t(2) * pl->n_phases * 5;
+  LMB_CUDA(cudaStreamSynchronize(m->ctx->stream));
+  if (!pl->d_timeline) {
+    LMB_CUDA(cudaMalloc(&pl->d_timeline, words * sizeof(unsigned long long)));
+    LMB_CUDA(cudaMemset(pl->d_timeline, 0, words * sizeof(unsigned long long)));
+    return LMB_OK;  // recorded from the next step on
+  }
+  if (cap_phases < size_t(pl->n_phases)) return LMB_OK;
+  LMB_CUDA(cudaMemcpy(out, pl->d_timeline, words * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+  std::vector<PsPhase> ph(size_t(pl->n_phases));
+  LMB_CUDA(cudaMemcpy(ph.data(), pl->d_phases, ph.size() * sizeof(PsPhase), cudaMemcpyDeviceToHost));
+  for (int i = 0; i < pl->n_phases; ++i) {
+    types[i] = ph[size_t(i)].type;
+    kslices[i] = ph[size_t(i)].n_ks;
+  }
   return LMB_OK;
 }
 

@@ -29,7 +29,7 @@ class Model:
         self.max_batch = max_batch
         cfg = _lib.ModelConfig(c["vocab"], c["hidden"], c["inter"], c["n_layers"], c["n_heads"], c["n_kv_heads"],
                                c["head_dim"], c["max_seq"], c["rope_theta"], c["rope_factor"], c["eps"], max_batch,
-                               tp_rank, tp_size)
+                               tp_rank, tp_size, int(bool(c.get("gemma"))), 1 if c.get("gelu") else 0)
         h = C.c_void_p()
         check(lib().lmb_model_create(self.ctx.h, C.byref(cfg), C.byref(h)))
         self.h = h

@@ -144,7 +144,7 @@ float orc_block_get(int kind, const void *block, size_t i) {
     ACC acc = 0;                                                            \
     for (size_t b = 0; b < bpr; ++b) {                                      \
       const T *blk = (const T *)blocks + row * bpr + b;                     \
-      const float *x = act + b * BLK;                                       \
+      const XT *x = act + b * BLK;                                          \
       ACC s = 0;
 #define ROW_LOOP_END(scale_expr)                                            \
       acc += s * (ACC)(scale_expr);                                         \
@@ -152,17 +152,17 @@ float orc_block_get(int kind, const void *block, size_t i) {
     out[row] = acc;                                                         \
   }
 
-#define DEFINE_GEMVS(SUFFIX, ACCTYPE)                                                              \
+#define DEFINE_GEMVS(SUFFIX, ACCTYPE, XTYPE)                                                             \
   /* lut_gemm_scalar.cpp:7-61 */                                                                   \
-  static void gemv_ternary_##SUFFIX(const void *blocks, const float *act, ACCTYPE *out, size_t M, size_t K) { \
-    typedef ACCTYPE ACC;                                                                           \
+  static void gemv_ternary_##SUFFIX(const void *blocks, const XTYPE *act, ACCTYPE *out, size_t M, size_t K) { \
+    typedef ACCTYPE ACC; typedef XTYPE XT;                                                                         \
     ROW_LOOP_BEGIN(orc_ternary_block)                                                              \
     for (size_t i = 0; i < BLK; ++i) { int t = ternary_at(blk, i); if (t > 0) s += x[i]; else if (t < 0) s -= x[i]; } \
     ROW_LOOP_END(blk->scale)                                                                       \
   }                                                                                                \
   /* lut_gemm_scalar.cpp:228-259 */                                                                \
-  static void gemv_binary_##SUFFIX(const void *blocks, const float *act, ACCTYPE *out, size_t M, size_t K) { \
-    typedef ACCTYPE ACC;                                                                           \
+  static void gemv_binary_##SUFFIX(const void *blocks, const XTYPE *act, ACCTYPE *out, size_t M, size_t K) { \
+    typedef ACCTYPE ACC; typedef XTYPE XT;                                                                         \
     ROW_LOOP_BEGIN(orc_binary_block)                                                               \
     for (size_t i = 0; i < BLK; ++i) s += (binary_at(blk, i) > 0) ? x[i] : -x[i];                  \
     ROW_LOOP_END(blk->scale)                                                                       \
@@ -170,14 +170,14 @@ float orc_block_get(int kind, const void *block, size_t i) {
   /* lut_gemm_scalar.cpp:298-321: sum of get(i)*x/scale, times scale.  Restated in the     */      \
   /* algebraically equal RRQ form of lut_gemm_simd.cpp:326-328 (primary sum * scale +      */      \
   /* residual sum * scale2), which is also defined when scale == 0.                        */      \
-  static void gemv_int2_##SUFFIX(const void *blocks, const float *act, ACCTYPE *out, size_t M, size_t K) { \
-    typedef ACCTYPE ACC;                                                                           \
+  static void gemv_int2_##SUFFIX(const void *blocks, const XTYPE *act, ACCTYPE *out, size_t M, size_t K) { \
+    typedef ACCTYPE ACC;                                                                                           \
     const size_t bpr = (K + BLK - 1) / BLK;                                                        \
     for (size_t row = 0; row < M; ++row) {                                                         \
       ACC acc = 0;                                                                                 \
       for (size_t b = 0; b < bpr; ++b) {                                                           \
         const orc_int2_block *blk = (const orc_int2_block *)blocks + row * bpr + b;                \
-        const float *x = act + b * BLK;                                                            \
+        const XTYPE *x = act + b * BLK;                                                            \
         ACC p = 0, r = 0;                                                                          \
         for (size_t i = 0; i < BLK; ++i) {                                                         \
           unsigned c = int2_code(blk, i);                                                          \
@@ -190,41 +190,41 @@ float orc_block_get(int kind, const void *block, size_t i) {
     }                                                                                              \
   }                                                                                                \
   /* lut_gemm_scalar.cpp:327-350 */                                                                \
-  static void gemv_int3_##SUFFIX(const void *blocks, const float *act, ACCTYPE *out, size_t M, size_t K) { \
-    typedef ACCTYPE ACC;                                                                           \
+  static void gemv_int3_##SUFFIX(const void *blocks, const XTYPE *act, ACCTYPE *out, size_t M, size_t K) { \
+    typedef ACCTYPE ACC; typedef XTYPE XT;                                                                         \
     ROW_LOOP_BEGIN(orc_int3_block)                                                                 \
     for (size_t i = 0; i < BLK; ++i) s += (ACC)((int)bitstream_get(blk->data, 96, i, 3) - 4) * x[i]; \
     ROW_LOOP_END(blk->scale)                                                                       \
   }                                                                                                \
   /* lut_gemm_scalar.cpp:186-222 */                                                                \
-  static void gemv_int4_##SUFFIX(const void *blocks, const float *act, ACCTYPE *out, size_t M, size_t K) { \
-    typedef ACCTYPE ACC;                                                                           \
+  static void gemv_int4_##SUFFIX(const void *blocks, const XTYPE *act, ACCTYPE *out, size_t M, size_t K) { \
+    typedef ACCTYPE ACC; typedef XTYPE XT;                                                                         \
     ROW_LOOP_BEGIN(orc_int4_block)                                                                 \
     for (size_t i = 0; i < BLK; ++i) s += (ACC)int4_at(blk, i) * x[i];                             \
     ROW_LOOP_END(blk->scale)                                                                       \
   }                                                                                                \
   /* lut_gemm_scalar.cpp:356-389 */                                                                \
-  static void gemv_int5_##SUFFIX(const void *blocks, const float *act, ACCTYPE *out, size_t M, size_t K) { \
-    typedef ACCTYPE ACC;                                                                           \
+  static void gemv_int5_##SUFFIX(const void *blocks, const XTYPE *act, ACCTYPE *out, size_t M, size_t K) { \
+    typedef ACCTYPE ACC; typedef XTYPE XT;                                                                         \
     ROW_LOOP_BEGIN(orc_int5_block)                                                                 \
     for (size_t i = 0; i < BLK; ++i) s += (ACC)((int)bitstream_get(blk->data, 160, i, 5) - 16) * x[i]; \
     ROW_LOOP_END(blk->scale)                                                                       \
   }                                                                                                \
   /* lut_gemm_scalar.cpp:395-428 */                                                                \
-  static void gemv_int6_##SUFFIX(const void *blocks, const float *act, ACCTYPE *out, size_t M, size_t K) { \
-    typedef ACCTYPE ACC;                                                                           \
+  static void gemv_int6_##SUFFIX(const void *blocks, const XTYPE *act, ACCTYPE *out, size_t M, size_t K) { \
+    typedef ACCTYPE ACC; typedef XTYPE XT;                                                                         \
     ROW_LOOP_BEGIN(orc_int6_block)                                                                 \
     for (size_t i = 0; i < BLK; ++i) s += (ACC)((int)bitstream_get(blk->data, 192, i, 6) - 32) * x[i]; \
     ROW_LOOP_END(blk->scale)                                                                       \
   }                                                                                                \
   /* lut_gemm_scalar.cpp:265-292 */                                                                \
-  static void gemv_int8_##SUFFIX(const void *blocks, const float *act, ACCTYPE *out, size_t M, size_t K) { \
-    typedef ACCTYPE ACC;                                                                           \
+  static void gemv_int8_##SUFFIX(const void *blocks, const XTYPE *act, ACCTYPE *out, size_t M, size_t K) { \
+    typedef ACCTYPE ACC; typedef XTYPE XT;                                                                         \
     ROW_LOOP_BEGIN(orc_int8_block)                                                                 \
     for (size_t i = 0; i < BLK; ++i) s += (ACC)blk->data[i] * x[i];                                \
     ROW_LOOP_END(blk->scale)                                                                       \
   }                                                                                                \
-  static void gemv_dispatch_##SUFFIX(int kind, const void *blocks, const float *act, ACCTYPE *out, size_t M, size_t K) { \
+  static void gemv_dispatch_##SUFFIX(int kind, const void *blocks, const XTYPE *act, ACCTYPE *out, size_t M, size_t K) { \
     switch (kind) {                                                                                \
     case ORC_TERNARY: gemv_ternary_##SUFFIX(blocks, act, out, M, K); break;                        \
     case ORC_BINARY: gemv_binary_##SUFFIX(blocks, act, out, M, K); break;                          \
@@ -238,8 +238,9 @@ float orc_block_get(int kind, const void *block, size_t i) {
     }                                                                                              \
   }
 
-DEFINE_GEMVS(f32, float)
-DEFINE_GEMVS(f64, double)
+DEFINE_GEMVS(f32, float, float)
+DEFINE_GEMVS(f64, double, float)
+DEFINE_GEMVS(d64, double, double) /* double activations too: the fp64 evaluation of a whole decode step */
 
 void orc_gemv(int kind, const void *blocks, const float *act, float *out, size_t M, size_t K) {
   gemv_dispatch_f32(kind, blocks, act, out, M, K);
@@ -497,6 +498,15 @@ void orc_rms_norm(const float *in, const float *w, float *out, size_t n, float e
   for (size_t i = 0; i < n; ++i) out[i] = in[i] * inv * w[i];
 }
 
+/* src/layers/norm.cpp:40-53: the weights are offsets from one */
+void orc_gemma_rms_norm(const float *in, const float *w, float *out, size_t n, float eps) {
+  float ss = 0.0f;
+  for (size_t i = 0; i < n; ++i) ss += in[i] * in[i];
+  float rms = sqrtf(ss / (float)n + eps);
+  float inv = 1.0f / rms;
+  for (size_t i = 0; i < n; ++i) out[i] = in[i] * inv * (1.0f + w[i]);
+}
+
 /* src/layers/embedding.cpp:36-75: pairs (d, d + head_dim/2); angle = (pos/factor)*freq,
  * freq = 1/pow(theta, 2d/head_dim), all in float. */
 void orc_apply_rope(float *q, float *k, size_t position, size_t nh, size_t nkv, size_t hd,
@@ -571,6 +581,10 @@ static void linear_mt(const orc_tensor *w, const float *in, float *out, int nt) 
 }
 
 static inline float silu(float x) { return x / (1.0f + expf(-x)); } /* model.cpp:36 */
+/* model.cpp:38-42: the constant and the tanh are evaluated in double (M_PI is a double) */
+static inline float gelu(float x) {
+  return (float)(0.5f * x * (1.0f + tanh(sqrt(2.0f / 3.14159265358979323846) * (x + 0.044715f * x * x * x))));
+}
 
 void orc_model_forward(const orc_model *m, int token_id, size_t position, float *logits) {
   const size_t h = m->hidden, nh = m->n_heads, nkv = m->n_kv_heads, hd = m->head_dim, inter = m->inter;
@@ -594,11 +608,16 @@ void orc_model_forward(const orc_model *m, int token_id, size_t position, float 
       const char *blk = (const char *)m->embed.blocks + ((size_t)token_id * bpr + i / BLK) * bb;
       hidden[i] = orc_block_get(m->embed.kind, blk, i % BLK);
     }
+    if (m->gemma) { /* model.cpp:255-260 */
+      float scale = sqrtf((float)h);
+      for (size_t i = 0; i < h; ++i) hidden[i] *= scale;
+    }
   }
+  void (*norm)(const float *, const float *, float *, size_t, float) = m->gemma ? orc_gemma_rms_norm : orc_rms_norm;
 
   for (size_t l = 0; l < m->n_layers; ++l) {
     const orc_layer *L = &m->layers[l];
-    orc_rms_norm(hidden, L->input_norm, normed, h, m->eps); /* model.cpp:297-301 */
+    norm(hidden, L->input_norm, normed, h, m->eps); /* model.cpp:294-301 */
     linear_mt(&L->q, normed, q, nt);                       /* :307-309 */
     linear_mt(&L->k, normed, k, nt);
     linear_mt(&L->v, normed, v, nt);
@@ -633,15 +652,135 @@ void orc_model_forward(const orc_model *m, int token_id, size_t position, float 
     }
     linear_mt(&L->o, att, proj, nt);                              /* :380-381 */
     for (size_t j = 0; j < h; ++j) hidden[j] += proj[j];          /* :385-387 */
-    orc_rms_norm(hidden, L->post_norm, normed, h, m->eps);        /* :395-399 */
+    norm(hidden, L->post_norm, normed, h, m->eps);                /* :390-399 */
     linear_mt(&L->gate, normed, gate, nt);                        /* :402-403 */
     linear_mt(&L->up, normed, up, nt);
-    for (size_t j = 0; j < inter; ++j) gate[j] = silu(gate[j]) * up[j]; /* :414-416 */
+    if (m->gelu) for (size_t j = 0; j < inter; ++j) gate[j] = gelu(gate[j]) * up[j]; /* :409-412 */
+    else for (size_t j = 0; j < inter; ++j) gate[j] = silu(gate[j]) * up[j];          /* :414-416 */
     linear_mt(&L->down, gate, proj, nt);                          /* :419-420 */
     for (size_t j = 0; j < h; ++j) hidden[j] += proj[j];          /* :424-426 */
   }
-  orc_rms_norm(hidden, m->final_norm, normed, h, m->eps);         /* :441-442 */
+  norm(hidden, m->final_norm, normed, h, m->eps);                 /* :436-442 */
   linear_mt(&m->lm_head, normed, logits, nt);                     /* :447 */
 
+  free(hidden); free(normed); free(q); free(k); free(v); free(att); free(w); free(proj); free(gate); free(up);
+}
+
+
+/* ---------------------------------------------------------------------------------------
+ * The same decode step evaluated in fp64 throughout (weights are the exact real values of the
+ * codes and scales, activations, norms, softmax and sums in double; cos/sin of the float angle
+ * the reference forms).  Not a restatement of reference code: the arbiter for "how far is an
+ * fp32 implementation from the exact result" when two fp32 implementations disagree.
+ * The KV cache (fp32, shared layout) is read as given and NOT updated.
+ * ------------------------------------------------------------------------------------- */
+typedef struct {
+  int kind; const void *blocks; const double *act; double *out; size_t M, K;
+} gemv_job_d;
+
+static void *gemv_thread_d(void *p) {
+  gemv_job_d *j = (gemv_job_d *)p;
+  gemv_dispatch_d64(j->kind, j->blocks, j->act, j->out, j->M, j->K);
+  return NULL;
+}
+
+static void linear_d(const orc_tensor *w, const double *in, double *out, int nt) {
+  const size_t k_aligned = (w->K + 255) / 256 * 256, bpr = k_aligned / 256, bb = orc_block_bytes(w->kind);
+  const int rotate = (w->quant_bits <= 2 && w->quant_bits > 0) || (w->kind == ORC_TERNARY);
+  double *buf = (double *)calloc(k_aligned, sizeof(double));
+  memcpy(buf, in, w->K * sizeof(double));
+  if (rotate)
+    for (size_t b = 0; b < bpr; ++b) {
+      double *d = buf + b * 256;
+      for (size_t h = 1; h < 256; h <<= 1)
+        for (size_t i = 0; i < 256; i += 2 * h)
+          for (size_t j = i; j < i + h; ++j) { double x = d[j], y = d[j + h]; d[j] = x + y; d[j + h] = x - y; }
+      for (size_t i = 0; i < 256; ++i) d[i] *= 0.0625;
+    }
+  if (nt < 1) nt = 1;
+  if ((size_t)nt > w->M) nt = (int)w->M;
+  pthread_t *th = (pthread_t *)malloc(sizeof(pthread_t) * (size_t)nt);
+  gemv_job_d *jobs = (gemv_job_d *)malloc(sizeof(gemv_job_d) * (size_t)nt);
+  for (int t = 0; t < nt; ++t) {
+    size_t r0 = w->M * (size_t)t / (size_t)nt, r1 = w->M * (size_t)(t + 1) / (size_t)nt;
+    jobs[t] = (gemv_job_d){w->kind, (const char *)w->blocks + r0 * bpr * bb, buf, out + r0, r1 - r0, w->K};
+    pthread_create(&th[t], NULL, gemv_thread_d, &jobs[t]);
+  }
+  for (int t = 0; t < nt; ++t) pthread_join(th[t], NULL);
+  free(th); free(jobs); free(buf);
+}
+
+static void norm_d(const double *in, const float *w, double *out, size_t n, float eps, int gemma) {
+  double ss = 0.0;
+  for (size_t i = 0; i < n; ++i) ss += in[i] * in[i];
+  double inv = 1.0 / sqrt(ss / (double)n + (double)eps);
+  for (size_t i = 0; i < n; ++i) out[i] = in[i] * inv * (gemma ? 1.0 + (double)w[i] : (double)w[i]);
+}
+
+void orc_model_forward_f64(const orc_model *m, int token_id, size_t position, double *logits) {
+  const size_t h = m->hidden, nh = m->n_heads, nkv = m->n_kv_heads, hd = m->head_dim, inter = m->inter;
+  const size_t attn_dim = nh * hd, kv_dim = nkv * hd, half = hd / 2;
+  const int nt = m->n_threads > 0 ? m->n_threads : 1;
+  double *hidden = calloc(h, 8), *normed = calloc(h, 8), *q = calloc(attn_dim, 8), *k = calloc(kv_dim, 8), *v = calloc(kv_dim, 8);
+  double *att = calloc(attn_dim, 8), *w = calloc(m->max_seq, 8), *proj = calloc(h, 8), *gate = calloc(inter, 8), *up = calloc(inter, 8);
+  {
+    const size_t bpr = (h + BLK - 1) / BLK, bb = orc_block_bytes(m->embed.kind);
+    for (size_t i = 0; i < h; ++i) {
+      const char *blk = (const char *)m->embed.blocks + ((size_t)token_id * bpr + i / BLK) * bb;
+      hidden[i] = (double)orc_block_get(m->embed.kind, blk, i % BLK); /* int8 embedding: code * scale, exact enough in float */
+    }
+    if (m->gemma) { double scale = sqrt((double)h); for (size_t i = 0; i < h; ++i) hidden[i] *= scale; }
+  }
+  for (size_t l = 0; l < m->n_layers; ++l) {
+    const orc_layer *L = &m->layers[l];
+    norm_d(hidden, L->input_norm, normed, h, m->eps, m->gemma);
+    linear_d(&L->q, normed, q, nt); linear_d(&L->k, normed, k, nt); linear_d(&L->v, normed, v, nt);
+    if (L->q_bias) for (size_t j = 0; j < attn_dim; ++j) q[j] += (double)L->q_bias[j];
+    if (L->k_bias) for (size_t j = 0; j < kv_dim; ++j) k[j] += (double)L->k_bias[j];
+    if (L->v_bias) for (size_t j = 0; j < kv_dim; ++j) v[j] += (double)L->v_bias[j];
+    for (int pass = 0; pass < 2; ++pass) { /* rotary embedding on the float angle of embedding.cpp:45-46 */
+      double *base = pass == 0 ? q : k;
+      size_t heads = pass == 0 ? nh : nkv;
+      for (size_t hh = 0; hh < heads; ++hh)
+        for (size_t d = 0; d < half; ++d) {
+          float freq = 1.0f / powf(m->rope_theta, (2.0f * (float)d) / (float)hd);
+          float angle = ((float)position / m->rope_factor) * freq;
+          double c = cos((double)angle), s = sin((double)angle), a = base[hh * hd + d], b = base[hh * hd + d + half];
+          base[hh * hd + d] = a * c - b * s;
+          base[hh * hd + d + half] = a * s + b * c;
+        }
+    }
+    const float *kc = m->kv_cache + (l * 2) * m->max_seq * kv_dim, *vc = m->kv_cache + (l * 2 + 1) * m->max_seq * kv_dim;
+    const size_t seq = position + 1, group = nh / nkv;
+    const double scale = 1.0 / sqrt((double)hd);
+    memset(att, 0, attn_dim * 8);
+    for (size_t head = 0; head < nh; ++head) {
+      const size_t kvh = head / group;
+      const double *qh = q + head * hd;
+      double mx = -1e300, sum = 0.0;
+      for (size_t t = 0; t < seq; ++t) {
+        double s = 0.0;
+        for (size_t d = 0; d < hd; ++d) s += qh[d] * (t == position ? k[kvh * hd + d] : (double)kc[t * kv_dim + kvh * hd + d]);
+        w[t] = s * scale;
+        if (w[t] > mx) mx = w[t];
+      }
+      for (size_t t = 0; t < seq; ++t) { w[t] = exp(w[t] - mx); sum += w[t]; }
+      for (size_t t = 0; t < seq; ++t)
+        for (size_t d = 0; d < hd; ++d)
+          att[head * hd + d] += w[t] / sum * (t == position ? v[kvh * hd + d] : (double)vc[t * kv_dim + kvh * hd + d]);
+    }
+    linear_d(&L->o, att, proj, nt);
+    for (size_t j = 0; j < h; ++j) hidden[j] += proj[j];
+    norm_d(hidden, L->post_norm, normed, h, m->eps, m->gemma);
+    linear_d(&L->gate, normed, gate, nt); linear_d(&L->up, normed, up, nt);
+    for (size_t j = 0; j < inter; ++j) {
+      double g = gate[j];
+      gate[j] = (m->gelu ? 0.5 * g * (1.0 + tanh(sqrt(2.0 / 3.14159265358979323846) * (g + 0.044715 * g * g * g))) : g / (1.0 + exp(-g))) * up[j];
+    }
+    linear_d(&L->down, gate, proj, nt);
+    for (size_t j = 0; j < h; ++j) hidden[j] += proj[j];
+  }
+  norm_d(hidden, m->final_norm, normed, h, m->eps, m->gemma);
+  linear_d(&m->lm_head, normed, logits, nt);
   free(hidden); free(normed); free(q); free(k); free(v); free(att); free(w); free(proj); free(gate); free(up);
 }

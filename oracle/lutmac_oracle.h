@@ -109,9 +109,14 @@ typedef struct {
   const orc_layer *layers;
   float *kv_cache; /* [layer][2][max_seq][n_kv_heads][head_dim] fp32 */
   int n_threads;   /* rows of each GEMV are split over this many threads (1 = as shipped) */
+  int gemma;       /* model_type "gemma": embedding x sqrt(hidden), norms scale by (1 + weight) */
+  int gelu;        /* ActivationType::GELU: gelu(gate) * up instead of silu(gate) * up */
 } orc_model;
 
 void orc_model_forward(const orc_model *m, int token_id, size_t position, float *logits);
+/* The same step in fp64 throughout (exact weight values, double activations); reads the KV cache
+ * without updating it.  Not reference arithmetic: the yardstick for two fp32 implementations. */
+void orc_model_forward_f64(const orc_model *m, int token_id, size_t position, double *logits);
 
 #ifdef __cplusplus
 }

@@ -25,10 +25,26 @@ _u8p = C.POINTER(C.c_uint8)
 _i8p = C.POINTER(C.c_int8)
 
 
+def reference_dir() -> str:
+    """The reference checkout: $LUTMAC_REFERENCE_DIR, else `reference_path` of the BASELINE.json beside
+    this package; "" when neither names a directory that holds the reference's headers."""
+    cands = [os.environ.get("LUTMAC_REFERENCE_DIR", "")]
+    try:
+        import json
+        with open(os.path.join(os.path.dirname(_HERE), "BASELINE.json")) as f:
+            cands.append(json.load(f).get("reference_path", ""))
+    except (OSError, ValueError):
+        pass
+    for c in cands:
+        if c and os.path.exists(os.path.join(c, "include", "lutmac", "types.hpp")):
+            return c
+    return ""
+
+
 def build(force: bool = False) -> None:
     """Compile the oracle (and the reference library when its sources are present)."""
-    ref_dir = os.environ.get("LUTMAC_REFERENCE_DIR", "/root/reference")
-    ref_present = os.path.exists(os.path.join(ref_dir, "include", "lutmac", "types.hpp"))
+    ref_dir = reference_dir()
+    ref_present = bool(ref_dir)
     need = force or not os.path.exists(ORACLE_SO) or (ref_present and not os.path.exists(REF_SO))
     if not need:
         src_m = max(os.path.getmtime(os.path.join(_HERE, f)) for f in ("lutmac_oracle.c", "lutmac_oracle.h"))
@@ -64,7 +80,8 @@ class OrcModel(C.Structure):
                 ("n_heads", C.c_size_t), ("n_kv_heads", C.c_size_t), ("head_dim", C.c_size_t), ("max_seq", C.c_size_t),
                 ("rope_theta", C.c_float), ("rope_factor", C.c_float), ("eps", C.c_float),
                 ("embed", OrcTensor), ("lm_head", OrcTensor), ("final_norm", _f32p),
-                ("layers", C.POINTER(OrcLayer)), ("kv_cache", _f32p), ("n_threads", C.c_int)]
+                ("layers", C.POINTER(OrcLayer)), ("kv_cache", _f32p), ("n_threads", C.c_int), ("gemma", C.c_int),
+                ("gelu", C.c_int)]
 
 
 class Oracle:
@@ -94,6 +111,7 @@ class Oracle:
         L.orc_apply_rope.argtypes = [_f32p, _f32p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t, C.c_float, C.c_float]
         L.orc_softmax.argtypes = [_f32p, C.c_size_t]
         L.orc_model_forward.argtypes = [C.POINTER(OrcModel), C.c_int, C.c_size_t, _f32p]
+        L.orc_model_forward_f64.argtypes = [C.POINTER(OrcModel), C.c_int, C.c_size_t, _f64p]
         self.prefix = "orc"
 
     # -- kernel API ---------------------------------------------------------------------
@@ -248,11 +266,17 @@ class OracleModel:
         self.m = OrcModel(cfg["vocab"], cfg["hidden"], cfg["inter"], n_layers, cfg["n_heads"], cfg["n_kv_heads"],
                           cfg["head_dim"], cfg["max_seq"], cfg["rope_theta"], cfg["rope_factor"], cfg["eps"],
                           tens(spec.embed), tens(spec.lm_head), vec(spec.final_norm), self.layers,
-                          _ptr(self.kv, _f32p), n_threads)
+                          _ptr(self.kv, _f32p), n_threads, int(bool(cfg.get("gemma"))), int(bool(cfg.get("gelu"))))
 
     def forward(self, token, position):
         logits = np.empty(self.spec.cfg["vocab"], np.float32)
         self.o.lib.orc_model_forward(C.byref(self.m), int(token), int(position), _ptr(logits, _f32p))
+        return logits
+
+    def forward_f64(self, token, position):
+        """The step evaluated in fp64 throughout over the current cache (which it does not update)."""
+        logits = np.empty(self.spec.cfg["vocab"], np.float64)
+        self.o.lib.orc_model_forward_f64(C.byref(self.m), int(token), int(position), _ptr(logits, _f64p))
         return logits
 
 
@@ -293,6 +317,7 @@ class Reference:
         L.ref_model_create.argtypes = [C.c_size_t] * 8 + [C.c_float] * 3
         L.ref_model_create.restype = C.c_void_p
         L.ref_model_free.argtypes = [C.c_void_p]
+        L.ref_model_set_variant.argtypes = [C.c_void_p, C.c_int, C.c_int]
         L.ref_model_set_tensor.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_size_t, C.c_size_t]
         L.ref_model_set_vector.argtypes = [C.c_void_p, C.c_int, C.c_int, _f32p, C.c_size_t]
         L.ref_model_forward.argtypes = [C.c_void_p, C.c_int, C.c_size_t]
@@ -314,9 +339,10 @@ class Reference:
             nb = name.encode()
             keep.append((nb, data))
             arr[i] = RefFileTensor(nb, kind, qb, data.ctypes.data, M, K)
-        self.lib.ref_save_lutmac.argtypes = [C.c_char_p] + [C.c_size_t] * 7 + [C.c_float] * 3 + [C.POINTER(RefFileTensor), C.c_size_t]
+        self.lib.ref_save_lutmac.argtypes = [C.c_char_p] + [C.c_size_t] * 7 + [C.c_float] * 3 + [C.POINTER(RefFileTensor), C.c_size_t, C.c_int, C.c_int]
         rc = self.lib.ref_save_lutmac(path.encode(), c["vocab"], c["hidden"], c["inter"], c["n_layers"], c["n_heads"],
-                                      c["n_kv_heads"], c["head_dim"], c["rope_theta"], c["rope_factor"], c["eps"], arr, len(ents))
+                                      c["n_kv_heads"], c["head_dim"], c["rope_theta"], c["rope_factor"], c["eps"], arr, len(ents),
+                                      int(bool(c.get("gemma"))), int(bool(c.get("gelu"))))
         assert rc == 0, "save_lutmac failed"
 
     def load_model_logits(self, path, tokens, vocab):
@@ -490,6 +516,7 @@ class ReferenceModel:
         L = ref.lib
         self.h = L.ref_model_create(c["vocab"], c["hidden"], c["inter"], c["n_layers"], c["n_heads"], c["n_kv_heads"],
                                     c["head_dim"], c["max_seq"], c["rope_theta"], c["rope_factor"], c["eps"])
+        L.ref_model_set_variant(self.h, int(bool(c.get("gemma"))), int(bool(c.get("gelu"))))
 
         def st(layer, slot, t):
             L.ref_model_set_tensor(self.h, layer, slot, t.kind, t.quant_bits, _blocks_ptr(t.blocks), t.M, t.K)

@@ -182,6 +182,12 @@ void *ref_model_create(size_t vocab, size_t hidden, size_t inter, size_t n_layer
   m->allocate();
   return m;
 }
+// model_type "gemma" (embedding scale, (1 + w) norms) and / or ActivationType::GELU
+void ref_model_set_variant(void *mp, int gemma, int gelu) {
+  auto *m = static_cast<Model *>(mp);
+  m->config.model_type = gemma ? "gemma" : "llama";
+  m->config.activation = gelu ? ActivationType::GELU : ActivationType::SILU;
+}
 void ref_model_free(void *m) { delete static_cast<Model *>(m); }
 
 // slot: 0 embed, 1 lm_head, 2 q, 3 k, 4 v, 5 o, 6 gate, 7 up, 8 down
@@ -233,9 +239,10 @@ struct ref_file_tensor {
 
 int ref_save_lutmac(const char *path, size_t vocab, size_t hidden, size_t inter, size_t n_layers,
                     size_t n_heads, size_t n_kv_heads, size_t head_dim, float rope_theta, float rope_factor,
-                    float eps, const ref_file_tensor *tensors, size_t n_tensors) {
+                    float eps, const ref_file_tensor *tensors, size_t n_tensors, int gemma, int gelu) {
   ModelConfig c;
-  c.model_type = "llama";
+  c.model_type = gemma ? "gemma" : "llama";
+  c.activation = gelu ? ActivationType::GELU : ActivationType::SILU;
   c.vocab_size = vocab;
   c.hidden_size = hidden;
   c.intermediate_size = inter;
