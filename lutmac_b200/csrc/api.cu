@@ -216,6 +216,11 @@ int lmb_ctx_create(int device, lmb_ctx **out) {
   ctx->pdl = !(pdl_env && pdl_env[0] == '0');
   int st = configure_gemv(ctx);
   if (st == LMB_OK) st = ensure_scratch(ctx, size_t(4) << 20, size_t(1) << 16);
+  if (st == LMB_OK) {
+    e = cudaMalloc(&ctx->d_fault, sizeof(unsigned));
+    if (e == cudaSuccess) e = cudaMemset(ctx->d_fault, 0, sizeof(unsigned));
+    if (e != cudaSuccess) st = cuda_fail(e, "lmb_ctx_create");
+  }
   if (st != LMB_OK) {
     lmb_ctx_destroy(ctx);
     return st;
@@ -231,6 +236,7 @@ int lmb_ctx_destroy(lmb_ctx *ctx) {
   if (ctx->scratch) cudaFree(ctx->scratch);
   if (ctx->counters) cudaFree(ctx->counters);
   if (ctx->xprep) cudaFree(ctx->xprep);
+  if (ctx->d_fault) cudaFree(ctx->d_fault);
   if (ctx->h_stage) cudaFreeHost(ctx->h_stage);
   if (ctx->d_stage) cudaFree(ctx->d_stage);
   if (ctx->ev0) cudaEventDestroy(ctx->ev0);

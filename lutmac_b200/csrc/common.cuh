@@ -189,6 +189,8 @@ struct lmb_ctx {
   // activations prepared once per launch for batched GEMVs (digits, block scales, digit sums)
   uint32_t *xprep = nullptr;
   size_t xprep_blocks = 0;  // capacity in (sequence, block) pairs
+  // set by a kernel whose bounded wait (for its own asynchronous copies) ran out; read with the logits
+  unsigned *d_fault = nullptr;
   // staging buffers of the host-pointer entry points
   void *h_stage = nullptr;
   size_t h_stage_bytes = 0;

@@ -347,6 +347,278 @@ __device__ __forceinline__ void attn_item(const AttnArgs &a, const RopeDims &d, 
   if (threadIdx.x == 0) *ctr = 0u;
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Group attention: one CTA per (KV head, KV split, sequence) serves ALL query heads of the KV
+// group, so the keys and values of the slice are read once instead of once per query head
+// (grouped-query attention, model.cpp:338-372, reads the same cache rows for every head of a
+// group).  The slice's cache rows are fetched with bulk asynchronous copies (cp.async.bulk,
+// completion on an mbarrier): every row of the slice is in flight at once instead of a few
+// loads per thread, which is what bounds a latency-limited decode attention.  The new position's
+// key / value come from the fresh projections (bias and rotary embedding applied here) and are
+// written to the cache by this CTA.  Partial (max, sum, vector) records go to scratch; the last
+// split of a KV head to arrive merges the records of the group's heads in split order.
+// ---------------------------------------------------------------------------------------------
+constexpr int ATT_MAX_GROUP = 8;    // query heads per KV head the group form handles
+constexpr int ATT_MAX_SPLITS = 64;  // KV splits the merge handles
+constexpr int ATT_REC_PAD = 4;      // a partial record is head_dim + 4 floats: {vector, max, sum, -, -} (16-byte aligned)
+
+__host__ __device__ inline size_t attn_group_smem_floats(size_t split_len, size_t hd, size_t group) {
+  return 2 * split_len * hd + group * hd + group * split_len + size_t(ATT_MAX_GROUP) * ATT_MAX_SPLITS + 2 * ATT_MAX_GROUP;
+}
+
+__device__ __forceinline__ uint32_t smem_addr_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbar_init(uint64_t *bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr_u32(bar)), "r"(count) : "memory");
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_addr_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Plain (not multicast) bulk copy from this GPU's global memory into this CTA's shared memory:
+// both addresses 16-byte aligned, the size a multiple of 16.
+__device__ __forceinline__ void bulk_copy_g2s(void *dst, const void *src, unsigned bytes, uint64_t *bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_addr_u32(dst)),
+               "l"(src), "r"(bytes), "r"(smem_addr_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+template <int PER> struct LaneVec { float v[PER]; };
+template <int PER> __device__ __forceinline__ LaneVec<PER> ld_lane_vec(const float *row, int lane) {
+  LaneVec<PER> r;
+  if constexpr (PER == 4) {
+    const float4 x = reinterpret_cast<const float4 *>(row)[lane];
+    r.v[0] = x.x; r.v[1] = x.y; r.v[2] = x.z; r.v[3] = x.w;
+  } else {
+    const float2 x = reinterpret_cast<const float2 *>(row)[lane];
+    r.v[0] = x.x; r.v[1] = x.y;
+  }
+  return r;
+}
+template <int PER> __device__ __forceinline__ void st_lane_vec(float *row, int lane, const LaneVec<PER> &r) {
+  if constexpr (PER == 4) reinterpret_cast<float4 *>(row)[lane] = make_float4(r.v[0], r.v[1], r.v[2], r.v[3]);
+  else reinterpret_cast<float2 *>(row)[lane] = make_float2(r.v[0], r.v[1]);
+}
+template <int PER> __device__ __forceinline__ LaneVec<PER> ldcg_lane_vec(const float *row, int lane) {
+  LaneVec<PER> r;
+  if constexpr (PER == 4) {
+    const float4 x = __ldcg(reinterpret_cast<const float4 *>(row) + lane);
+    r.v[0] = x.x; r.v[1] = x.y; r.v[2] = x.z; r.v[3] = x.w;
+  } else {
+    const float2 x = __ldcg(reinterpret_cast<const float2 *>(row) + lane);
+    r.v[0] = x.x; r.v[1] = x.y;
+  }
+  return r;
+}
+
+// One (KV head, split, sequence) item.  head_dim = 32 * PER.  `parity` is the phase of `bar` this
+// item waits for (flipped here).  False when the bounded wait for the copies ran out (*timed_out
+// is then set): the caller leaves the kernel.  All ATT_THREADS threads of the CTA take part.
+template <bool FRESH_CG, int PER>
+__device__ __forceinline__ bool attn_group_item(const AttnArgs &a, const RopeDims &d, size_t kvh, size_t split, size_t b, float *sm,
+                                                uint64_t *bar, unsigned &parity, unsigned spin_limit, int *flag) {
+  const size_t hd = d.hd, g = d.nh / d.nkv, kv_dim = d.nkv * hd, half = hd / 2, sl = d.split_len;
+  float *Ks = sm, *Vs = Ks + sl * hd, *qs = Vs + sl * hd, *sc = qs + g * hd, *wk = sc + g * sl, *stat = wk + ATT_MAX_GROUP * ATT_MAX_SPLITS;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nw = ATT_THREADS / 32;
+  const size_t pos = a.positions[b], seq = pos + 1;
+  const int n_splits = a.n_splits;
+  size_t len = (seq + n_splits - 1) / n_splits;
+  len = (len + 7) / 8 * 8;  // <= split_len, which was sized for the longest context
+  const size_t t0 = min(split * len, seq), t1 = min(t0 + len, seq), n = t1 - t0;
+  const bool has_new = (pos >= t0 && pos < t1);  // the new position is the last one of its slice
+  const size_t n_old = has_new ? n - 1 : n;
+  float *kc = a.kv + b * d.seq_stride + (a.layer * 2) * d.max_seq * kv_dim + kvh * hd;
+  float *vc = kc + d.max_seq * kv_dim;
+  const unsigned row_bytes = unsigned(hd * sizeof(float));
+
+  __syncthreads();  // whatever used this shared memory before is done
+  // cached rows of the slice: all in flight at once
+  if (tid == 0) mbar_arrive_expect_tx(bar, unsigned(2 * n_old) * row_bytes);
+  fence_proxy_async_smem();  // earlier generic-proxy accesses of this memory precede the asynchronous writes
+  for (size_t t = tid; t < n_old; t += ATT_THREADS) {
+    bulk_copy_g2s(Ks + t * hd, kc + (t0 + t) * kv_dim, row_bytes, bar);
+    bulk_copy_g2s(Vs + t * hd, vc + (t0 + t) * kv_dim, row_bytes, bar);
+  }
+  // meanwhile: the group's rotated queries, and the new position's key / value (pairs (i, i + hd/2))
+  const float *cs = a.cs_table + pos * hd;
+  for (size_t i = tid; i < g * half; i += ATT_THREADS) {
+    const size_t h = i / half, j = i - h * half, head = kvh * g + h;
+    const float c = cs[j], sn = cs[half + j];
+    const size_t i0 = (b * d.nh + head) * hd + j;
+    float x0 = ld_fresh<FRESH_CG>(a.q + i0), x1 = ld_fresh<FRESH_CG>(a.q + i0 + half);
+    if (a.qb) {
+      x0 += a.qb[head * hd + j];
+      x1 += a.qb[head * hd + j + half];
+    }
+    qs[h * hd + j] = x0 * c - x1 * sn;
+    qs[h * hd + j + half] = x0 * sn + x1 * c;
+  }
+  if (has_new) {
+    for (size_t j = tid; j < half; j += ATT_THREADS) {
+      const float c = cs[j], sn = cs[half + j];
+      const size_t k0 = (b * d.nkv + kvh) * hd + j;
+      float y0 = ld_fresh<FRESH_CG>(a.k + k0), y1 = ld_fresh<FRESH_CG>(a.k + k0 + half);
+      float v0 = ld_fresh<FRESH_CG>(a.v + k0), v1 = ld_fresh<FRESH_CG>(a.v + k0 + half);
+      if (a.kb) {
+        y0 += a.kb[kvh * hd + j];
+        y1 += a.kb[kvh * hd + j + half];
+      }
+      if (a.vb) {
+        v0 += a.vb[kvh * hd + j];
+        v1 += a.vb[kvh * hd + j + half];
+      }
+      const float r0 = y0 * c - y1 * sn, r1 = y0 * sn + y1 * c;
+      float *kr = Ks + n_old * hd, *vr = Vs + n_old * hd;
+      kr[j] = r0; kr[j + half] = r1;
+      vr[j] = v0; vr[j + half] = v1;
+      kc[pos * kv_dim + j] = r0; kc[pos * kv_dim + j + half] = r1;  // this CTA is the only one that holds the position
+      vc[pos * kv_dim + j] = v0; vc[pos * kv_dim + j + half] = v1;
+    }
+  }
+  {  // bounded wait for the copies
+    unsigned spins = 0;
+    bool ok = true;
+    while (!mbar_try_wait(bar, parity)) {
+      if (++spins > spin_limit) {
+        ok = false;
+        break;
+      }
+    }
+    parity ^= 1u;
+    if (tid == 0) *flag = 1;
+    __syncthreads();
+    if (!ok) *flag = 0;  // any thread that gave up
+    __syncthreads();
+    if (*flag == 0) return false;
+  }
+  // scores: a warp per timestep, a lane per PER dimensions
+  const float scale = 1.0f / sqrtf(float(hd));
+  for (size_t t = warp; t < n; t += nw) {
+    const LaneVec<PER> kk = ld_lane_vec<PER>(Ks + t * hd, lane);
+    float s[ATT_MAX_GROUP];
+#pragma unroll
+    for (int h = 0; h < ATT_MAX_GROUP; ++h) {
+      s[h] = 0.0f;
+      if (size_t(h) < g) {
+        const LaneVec<PER> qv = ld_lane_vec<PER>(qs + h * hd, lane);
+#pragma unroll
+        for (int e = 0; e < PER; ++e) s[h] += qv.v[e] * kk.v[e];
+      }
+    }
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) {
+#pragma unroll
+      for (int h = 0; h < ATT_MAX_GROUP; ++h) s[h] += __shfl_xor_sync(0xffffffffu, s[h], m);
+    }
+#pragma unroll
+    for (int h = 0; h < ATT_MAX_GROUP; ++h)
+      if (lane == h && size_t(h) < g) sc[h * sl + t] = s[h] * scale;
+  }
+  __syncthreads();
+  // softmax of the slice (attention.cpp:23-42 per head), a warp per head
+  for (size_t h = warp; h < g; h += nw) {
+    float mx = -INFINITY;
+    for (size_t t = lane; t < n; t += 32) mx = fmaxf(mx, sc[h * sl + t]);
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, m));
+    float sum = 0.0f;
+    for (size_t t = lane; t < n; t += 32) {
+      const float e = expf(sc[h * sl + t] - mx);
+      sc[h * sl + t] = e;
+      sum += e;
+    }
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, m);
+    if (lane == 0) {
+      stat[2 * h] = mx;
+      stat[2 * h + 1] = sum;
+    }
+  }
+  __syncthreads();
+  // weighted values, a warp per head; the partial record of (head, split)
+  const size_t rec = hd + ATT_REC_PAD;
+  for (size_t h = warp; h < g; h += nw) {
+    LaneVec<PER> acc;
+#pragma unroll
+    for (int e = 0; e < PER; ++e) acc.v[e] = 0.0f;
+    for (size_t t = 0; t < n; ++t) {
+      const float pt = sc[h * sl + t];
+      const LaneVec<PER> vv = ld_lane_vec<PER>(Vs + t * hd, lane);
+#pragma unroll
+      for (int e = 0; e < PER; ++e) acc.v[e] += pt * vv.v[e];
+    }
+    float *prt = a.partial + ((b * d.nh + kvh * g + h) * n_splits + split) * rec;
+    st_lane_vec<PER>(prt, lane, acc);
+    if (lane == 0) {
+      prt[hd] = stat[2 * h];
+      prt[hd + 1] = stat[2 * h + 1];
+    }
+  }
+  __syncthreads();
+  unsigned *ctr = a.counters + b * d.nkv + kvh;
+  if (tid == 0) {
+    __threadfence();
+    *flag = (atomicAdd(ctr, 1u) == unsigned(n_splits - 1));
+    __threadfence();
+  }
+  __syncthreads();
+  if (*flag == 0) return true;
+  // merge by the last split of the KV head: a warp per query head of the group
+  for (size_t h = warp; h < g; h += nw) {
+    const size_t head = kvh * g + h;
+    const float *all = a.partial + ((b * d.nh + head) * n_splits) * rec;
+    float *w = wk + h * ATT_MAX_SPLITS;
+    float gmx = -INFINITY;
+    for (int s2 = lane; s2 < n_splits; s2 += 32) gmx = fmaxf(gmx, __ldcg(all + s2 * rec + hd));
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) gmx = fmaxf(gmx, __shfl_xor_sync(0xffffffffu, gmx, m));
+    float den = 0.0f;
+    for (int s2 = lane; s2 < n_splits; s2 += 32) {
+      const float sm2 = __ldcg(all + s2 * rec + hd + 1);
+      const float ws = sm2 > 0.0f ? expf(__ldcg(all + s2 * rec + hd) - gmx) : 0.0f;  // empty slices (short contexts) weigh nothing
+      w[s2] = ws;
+      den += ws * sm2;
+    }
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) den += __shfl_xor_sync(0xffffffffu, den, m);
+    __syncwarp();
+    LaneVec<PER> tot;
+#pragma unroll
+    for (int e = 0; e < PER; ++e) tot.v[e] = 0.0f;
+    int s2 = 0;
+    for (; s2 + 3 < n_splits; s2 += 4) {
+      LaneVec<PER> pv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) pv[i] = ldcg_lane_vec<PER>(all + (s2 + i) * rec, lane);
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int e = 0; e < PER; ++e) tot.v[e] += w[s2 + i] * pv[i].v[e];
+    }
+    for (; s2 < n_splits; ++s2) {
+      const LaneVec<PER> pv = ldcg_lane_vec<PER>(all + s2 * rec, lane);
+#pragma unroll
+      for (int e = 0; e < PER; ++e) tot.v[e] += w[s2] * pv.v[e];
+    }
+    const float inv = 1.0f / den;
+#pragma unroll
+    for (int e = 0; e < PER; ++e) tot.v[e] *= inv;
+    st_lane_vec<PER>(a.out + (b * d.nh + head) * hd, lane, tot);
+  }
+  if (tid == 0) *ctr = 0u;
+  return true;
+}
+
 }  // namespace
 
 }  // namespace lmb

@@ -5,6 +5,8 @@
 #include "decode_device.cuh"
 #include "device_utils.cuh"
 
+#include <algorithm>
+
 namespace lmb {
 
 namespace {
@@ -103,6 +105,22 @@ __global__ void __launch_bounds__(ATT_THREADS) k_decode_attn(const AttnArgs a, c
   attn_item<false>(a, d, blockIdx.x, blockIdx.y, blockIdx.z, sm, &is_last);
 }
 
+// Group attention as a kernel of its own: grid = (KV heads x splits, sequences).
+template <int PER>
+__global__ void __launch_bounds__(ATT_THREADS) k_decode_attn_group(const AttnArgs a, const RopeDims d, unsigned spin_limit,
+                                                                    unsigned *timed_out) {
+  asm volatile("griddepcontrol.launch_dependents;");
+  extern __shared__ __align__(16) float sm[];
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ int flag;
+  if (threadIdx.x == 0) mbar_init(&bar, 1);
+  __syncthreads();
+  unsigned parity = 0;
+  const size_t kvh = blockIdx.x % d.nkv, split = blockIdx.x / d.nkv;
+  if (!attn_group_item<false, PER>(a, d, kvh, split, blockIdx.y, sm, &bar, parity, spin_limit, &flag) && threadIdx.x == 0 && timed_out)
+    *timed_out = 1u;
+}
+
 __global__ void k_silu_mul(const float *gate, const float *up, float *out, size_t n, int gelu) {
   asm volatile("griddepcontrol.launch_dependents;");  // a following GEMV may prefetch its weights
   const size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -176,6 +194,48 @@ int launch_decode_attn(lmb_ctx *ctx, const float *q, const float *k, const float
   return LMB_OK;
 }
 
+size_t attn_partial_floats(size_t batch, size_t nh, size_t hd) { return batch * nh * ATT_MAX_SPLITS * (hd + ATT_REC_PAD); }
+
+AttnGroupPlan plan_attn_group(size_t nh, size_t nkv, size_t hd, size_t max_seq, size_t batch, size_t want_items, size_t smem_bytes) {
+  AttnGroupPlan pl{false, 1, 0, 0, 0};
+  if (nkv == 0 || nh % nkv != 0) return pl;
+  const size_t g = nh / nkv;
+  if (g > size_t(ATT_MAX_GROUP) || (hd != 64 && hd != 128)) return pl;
+  pl.per = int(hd / 32);
+  // longest slice whose rows, queries and scores fit
+  const size_t fixed = g * hd + size_t(ATT_MAX_GROUP) * ATT_MAX_SPLITS + 2 * ATT_MAX_GROUP, budget = smem_bytes / sizeof(float);
+  if (budget <= fixed + 8 * (2 * hd + g)) return pl;
+  const size_t cap = (budget - fixed) / (2 * hd + g) / 8 * 8;
+  const size_t min_splits = (max_seq + cap - 1) / cap;
+  size_t want = (want_items + nkv * batch - 1) / (nkv * batch);
+  size_t n = std::max(min_splits, std::max<size_t>(want, 1));
+  n = std::min<size_t>(n, ATT_MAX_SPLITS);
+  n = std::min<size_t>(n, std::max<size_t>(1, (max_seq + 7) / 8));  // no slice shorter than 8 positions at full context
+  if (n < min_splits) return pl;
+  pl.n_splits = int(n);
+  pl.split_len = ((max_seq + n - 1) / n + 7) / 8 * 8;
+  if (pl.split_len > cap) return pl;
+  pl.smem_bytes = attn_group_smem_floats(pl.split_len, hd, g) * sizeof(float);
+  pl.ok = true;
+  return pl;
+}
+
+int launch_decode_attn_group(lmb_ctx *ctx, const float *q, const float *k, const float *v, const float *qb, const float *kb,
+                             const float *vb, const float *cs_table, const size_t *positions, float *kv, float *out,
+                             float *partial, unsigned *counters, const AttnGroupPlan &plan, size_t layer, const RopeDims &d0,
+                             size_t batch) {
+  RopeDims d = d0;
+  d.split_len = plan.split_len;
+  AttnArgs a{q, k, v, qb, kb, vb, cs_table, positions, kv, out, partial, counters, plan.n_splits, layer};
+  dim3 grid(unsigned(d.nkv * size_t(plan.n_splits)), unsigned(batch));
+  unsigned *flag = ctx->d_fault;  // set when a bounded wait for the bulk copies runs out
+  if (plan.per == 4) k_decode_attn_group<4><<<grid, ATT_THREADS, plan.smem_bytes, ctx->stream>>>(a, d, ctx->xchg.spin_limit, flag);
+  else k_decode_attn_group<2><<<grid, ATT_THREADS, plan.smem_bytes, ctx->stream>>>(a, d, ctx->xchg.spin_limit, flag);
+  ctx->launches++;
+  LMB_CUDA(cudaGetLastError());
+  return LMB_OK;
+}
+
 int launch_silu_mul(lmb_ctx *ctx, const float *gate, const float *up, float *out, size_t n, bool gelu) {
   k_silu_mul<<<unsigned((n + 255) / 256), 256, 0, ctx->stream>>>(gate, up, out, n, gelu ? 1 : 0);
   ctx->launches++;
@@ -185,6 +245,8 @@ int launch_silu_mul(lmb_ctx *ctx, const float *gate, const float *up, float *out
 
 int configure_decode_ops(lmb_ctx *ctx) {
   LMB_CUDA(cudaFuncSetAttribute(k_decode_attn, cudaFuncAttributeMaxDynamicSharedMemorySize, int(ctx->smem_optin) - 1024));
+  LMB_CUDA(cudaFuncSetAttribute(k_decode_attn_group<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(ATTN_GROUP_SMEM)));
+  LMB_CUDA(cudaFuncSetAttribute(k_decode_attn_group<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(ATTN_GROUP_SMEM)));
   return LMB_OK;
 }
 

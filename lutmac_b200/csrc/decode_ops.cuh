@@ -23,6 +23,23 @@ int decode_attn_splits(const lmb_ctx *ctx, size_t nh, size_t batch, size_t max_s
 int launch_decode_attn(lmb_ctx *ctx, const float *q, const float *k, const float *v, const float *qb, const float *kb,
                        const float *vb, const float *cs_table, const size_t *positions, float *kv, float *out,
                        float *partial, unsigned *counters, int n_splits, size_t layer, const RopeDims &d, size_t batch);
+// Group form of the decode attention (one CTA per KV head, split and sequence; keys and values of a
+// slice fetched once with bulk asynchronous copies).  plan_attn_group sizes the KV splits so that a
+// slice's rows fit `smem_bytes` of shared memory and about `want_items` CTAs result; ok = false
+// when the shape is outside what the group form handles (more than 8 query heads per KV head, a
+// head_dim other than 64 or 128, a context that needs more than 64 splits).
+constexpr size_t ATTN_GROUP_SMEM = 72 * 1024;  // shared memory a group-attention CTA may use (two CTAs per SM)
+struct AttnGroupPlan {
+  bool ok;
+  int n_splits, per;  // per = head_dim / 32
+  size_t split_len, smem_bytes;
+};
+AttnGroupPlan plan_attn_group(size_t nh, size_t nkv, size_t hd, size_t max_seq, size_t batch, size_t want_items, size_t smem_bytes);
+int launch_decode_attn_group(lmb_ctx *ctx, const float *q, const float *k, const float *v, const float *qb, const float *kb,
+                             const float *vb, const float *cs_table, const size_t *positions, float *kv, float *out,
+                             float *partial, unsigned *counters, const AttnGroupPlan &plan, size_t layer, const RopeDims &d,
+                             size_t batch);
+size_t attn_partial_floats(size_t batch, size_t nh, size_t hd);  // scratch both attention forms fit in
 int launch_silu_mul(lmb_ctx *ctx, const float *gate, const float *up, float *out, size_t n, bool gelu = false);
 
 }  // namespace lmb

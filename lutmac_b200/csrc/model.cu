@@ -289,6 +289,8 @@ int lmb_model_create(lmb_ctx *ctx, const lmb_model_config *c, lmb_model **out) {
     m->tp_peers = !(pv && pv[0] == '0');
     const char *sv = std::getenv("LMB_MODEL_PERSISTENT");
     m->persistent = !(sv && sv[0] == '0');
+    const char *av = std::getenv("LMB_ATTN_GROUP");
+    m->attn_group = !(av && av[0] == '0');
   }
   const size_t B = c->max_batch, h = c->hidden_size, hd = c->head_dim;
   m->seq_stride = c->num_hidden_layers * 2 * c->max_seq_len * m->nkv * hd;
@@ -298,7 +300,7 @@ int lmb_model_create(lmb_ctx *ctx, const lmb_model_config *c, lmb_model **out) {
   A(&m->v, B * m->nkv * hd); A(&m->att, B * m->nh * hd); A(&m->proj, B * h); A(&m->gate, B * m->inter);
   A(&m->up, B * m->inter); A(&m->act, B * m->inter); A(&m->logits, B * c->vocab_size);
   if (g > 1) A(&m->logits_local, B * m->vocab_local);
-  A(&m->att_partial, B * m->nh * 32 * (hd + 2));
+  A(&m->att_partial, attn_partial_floats(B, m->nh, hd));
   A(reinterpret_cast<float **>(&m->att_counters), B * m->nh);
   A(&m->kv, B * m->seq_stride); A(&m->final_norm, h); A(&m->cs_table, c->max_seq_len * hd);
   for (auto &L : m->layers) { A(&L.in_norm, h); A(&L.post_norm, h); }
@@ -306,6 +308,7 @@ int lmb_model_create(lmb_ctx *ctx, const lmb_model_config *c, lmb_model **out) {
     cudaError_t e = cudaMalloc(&m->d_tokens, B * sizeof(int));
     if (e == cudaSuccess) e = cudaMalloc(&m->d_pos, B * sizeof(size_t));
     if (e == cudaSuccess) e = cudaMallocHost(&m->h_io, B * (sizeof(int) + sizeof(size_t)));
+    if (e == cudaSuccess) e = cudaMallocHost(&m->h_status, 4 * sizeof(unsigned));
     if (e != cudaSuccess) st = cuda_fail(e, "lmb_model_create");
   }
   if (st == LMB_OK) {
@@ -360,6 +363,7 @@ int lmb_model_destroy(lmb_model *m) {
   if (m->d_tokens) cudaFree(m->d_tokens);
   if (m->d_pos) cudaFree(m->d_pos);
   if (m->h_io) cudaFreeHost(m->h_io);
+  if (m->h_status) cudaFreeHost(m->h_status);
   delete m;
   return LMB_OK;
 }
@@ -524,6 +528,17 @@ int lmb_model_forward(lmb_model *m, const int *token_ids, const size_t *position
   const size_t h = c.hidden_size, hd = c.head_dim;
   const RopeDims rd{m->nh, m->nkv, hd, c.max_seq_len, m->seq_stride, 0};
   const int n_splits = decode_attn_splits(ctx, m->nh, batch, c.max_seq_len);
+  // attention of one layer: the group form (keys / values of a slice read once for all query heads of
+  // a KV head, bulk asynchronous copies) where the shape allows it, else one CTA per query head
+  const AttnGroupPlan agp = m->attn_group ? plan_attn_group(m->nh, m->nkv, hd, c.max_seq_len, batch, size_t(2) * ctx->sm_count, ATTN_GROUP_SMEM)
+                                          : AttnGroupPlan{false, 1, 0, 0, 0};
+  auto attention = [&](LayerW &L, size_t l) {
+    if (agp.ok)
+      return launch_decode_attn_group(ctx, m->q, m->k, m->v, L.qb, L.kb, L.vb, m->cs_table, m->d_pos, m->kv, m->att, m->att_partial,
+                                      m->att_counters, agp, l, rd, batch);
+    return launch_decode_attn(ctx, m->q, m->k, m->v, L.qb, L.kb, L.vb, m->cs_table, m->d_pos, m->kv, m->att, m->att_partial,
+                              m->att_counters, n_splits, l, rd, batch);
+  };
 
   int *ht = static_cast<int *>(m->h_io);
   size_t *hp = reinterpret_cast<size_t *>(static_cast<char *>(m->h_io) + c.max_batch * sizeof(int));
@@ -624,8 +639,7 @@ int lmb_model_forward(lmb_model *m, const int *token_ids, const size_t *position
       float *qkv[3] = {m->q, m->k, m->v};
       st = gemv_group(m, 3, &L.w[0], &L.rot[0], m->hidden, h, qkv, batch, norm1);
       if (st != LMB_OK) break;
-      st = launch_decode_attn(ctx, m->q, m->k, m->v, L.qb, L.kb, L.vb, m->cs_table, m->d_pos, m->kv, m->att, m->att_partial,
-                              m->att_counters, n_splits, l, rd, batch);
+      st = attention(L, l);
       if (st != LMB_OK) break;
       st = gemv1(m, L.w[3], L.rot[3], m->att, m->nh * hd, m->hidden, batch, res);
       if (st != LMB_OK) break;
@@ -670,8 +684,7 @@ int lmb_model_forward(lmb_model *m, const int *token_ids, const size_t *position
     float *qkv[3] = {m->q, m->k, m->v};
     st = gemv_group(m, 3, &L.w[0], &L.rot[0], m->normed, h, qkv, batch);
     if (st != LMB_OK) break;
-    st = launch_decode_attn(ctx, m->q, m->k, m->v, L.qb, L.kb, L.vb, m->cs_table, m->d_pos, m->kv, m->att, m->att_partial,
-                            m->att_counters, n_splits, l, rd, batch);
+    st = attention(L, l);
     if (st != LMB_OK) break;
     st = row_reduce(L.w[3], L.rot[3], m->att, m->nh * hd, Fuse());
     if (st != LMB_OK) break;
@@ -700,27 +713,34 @@ int lmb_model_forward(lmb_model *m, const int *token_ids, const size_t *position
   }
 fetch:
   if (h_logits) {
+    // the logits and, behind them in the same stream, the three status words a step can leave: the
+    // context's fault flag, the exchange block's time-out flag, the persistent step's status
+    unsigned *hs = static_cast<unsigned *>(m->h_status);
+    hs[0] = hs[1] = 0;
     LMB_CUDA(cudaMemcpyAsync(h_logits, m->logits, batch * c.vocab_size * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
+    LMB_CUDA(cudaMemcpyAsync(&hs[0], ctx->d_fault, sizeof(unsigned), cudaMemcpyDeviceToHost, ctx->stream));
+    if (c.tp_size > 1 && ctx->xchg.ready)
+      LMB_CUDA(cudaMemcpyAsync(&hs[1], &static_cast<XchgHeader *>(ctx->xchg.local)->timed_out, sizeof(unsigned),
+                               cudaMemcpyDeviceToHost, ctx->stream));
     LMB_CUDA(cudaStreamSynchronize(ctx->stream));
-    {
-      unsigned expired = 0;
-      int ps = persist_take_status(m, &expired);
-      if (ps != LMB_OK) return ps;
-      if (expired) {
-        set_last_error("lmb_model_forward: a bounded wait between the phases of the decode step expired (phase " +
-                       std::to_string(expired - 1) + ")");
-        return LMB_ERR_TIMEOUT;
-      }
+    if (hs[0]) {  // a kernel's bounded wait for its own asynchronous copies ran out
+      LMB_CUDA(cudaMemset(ctx->d_fault, 0, sizeof(unsigned)));
+      set_last_error("lmb_model_forward: a bounded wait for asynchronous copies expired in the attention kernel");
+      return LMB_ERR_TIMEOUT;
     }
-    if (c.tp_size > 1 && ctx->xchg.ready) {
+    unsigned expired = 0;
+    int ps = persist_take_status(m, &expired);
+    if (ps != LMB_OK) return ps;
+    if (expired) {
+      set_last_error("lmb_model_forward: a bounded wait between the phases of the decode step expired (phase " +
+                     std::to_string(expired - 1) + ")");
+      return LMB_ERR_TIMEOUT;
+    }
+    if (hs[1]) {
       // a consumer that gave up waiting for another rank's partial vector has produced garbage:
       // the step reports it instead of returning the logits as if nothing had happened
-      unsigned flag = 0;
-      LMB_CUDA(cudaMemcpy(&flag, &static_cast<XchgHeader *>(ctx->xchg.local)->timed_out, sizeof flag, cudaMemcpyDeviceToHost));
-      if (flag) {
-        set_last_error("lmb_model_forward: a bounded wait for another rank's partial vector expired");
-        return LMB_ERR_TIMEOUT;
-      }
+      set_last_error("lmb_model_forward: a bounded wait for another rank's partial vector expired");
+      return LMB_ERR_TIMEOUT;
     }
   }
   return LMB_OK;

@@ -34,6 +34,7 @@ struct lmb_model {
   int *d_tokens = nullptr;
   size_t *d_pos = nullptr;
   void *h_io = nullptr;  // pinned staging for tokens + positions
+  void *h_status = nullptr;  // pinned: status words copied back with the logits
   size_t seq_stride = 0;
   // one instantiated CUDA graph of the whole step per batch size (token ids and positions are
   // read from device buffers, so the graph never changes)
@@ -46,6 +47,7 @@ struct lmb_model {
   // batch-1 steps of models whose layer projections share one integer-MMA kind run as one
   // persistent kernel over all layers (persist.cu); LMB_MODEL_PERSISTENT=0 disables it
   bool persistent = true;
+  bool attn_group = true;  // LMB_ATTN_GROUP=0: one attention CTA per query head instead of per KV head
   lmb::PersistPlan *ps = nullptr;
   int debug_extra_arrivals = 0;  // failure-path test: every grid barrier waits for this many arrivals that never come
 };

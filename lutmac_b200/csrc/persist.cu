@@ -67,6 +67,7 @@ struct PsPhase {
   // PH_ATTN
   AttnArgs at;
   RopeDims rd;
+  int attn_per;  // 0: one item per (query head, split); 2 or 4: group form, head_dim / 32
   // PH_EMBED (tokens, embed_*) and PH_REDUCE (hidden += sum over ranks of exchange xchg_seq)
   const int *tokens;
   const uint8_t *embed_tiles;
@@ -91,6 +92,7 @@ struct PsParams {
   // optional (null: off): nanosecond timestamps of CTA 0 and of the last CTA at five points of every
   // phase -- descriptor read, dependency met, activations prepared, main loop done, phase done
   unsigned long long *timeline;  // [2][n_phases][5]
+  int l2_prefetch_units;         // row-blocks per warp pulled into L2 beyond the register ring before a wait
 };
 
 __device__ __forceinline__ unsigned ld_acquire_u32(const unsigned *p) {
@@ -168,6 +170,32 @@ __device__ __forceinline__ int job_of(const PsPhase &P, int vrt) {
   return j;
 }
 
+// Pulls `bytes` (a multiple of 16, from a 16-byte aligned address) of this GPU's memory into L2.
+__device__ __forceinline__ void l2_prefetch(const void *ptr, unsigned bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(ptr), "r"(bytes) : "memory");
+}
+
+// L2 prefetch of units [first, first + count) of this warp's share of GEMV phase Q (the share is
+// computed exactly as the phase itself computes it).  Weights never change, so this may run
+// any time ahead of the phase: HBM keeps streaming while the CTA waits for a dependency.
+template <size_t TB> __device__ __forceinline__ void prefetch_share(const PsPhase &Q, int c, int warp, int lane, int first, int count) {
+  if (Q.type != PH_GEMV || count <= 0) return;
+  const int ks = c % Q.n_ks, rg = c / Q.n_ks;
+  const int rt_a = int((long long)(rg)*Q.rt_total / Q.n_rg), rt_b = int((long long)(rg + 1) * Q.rt_total / Q.n_rg);
+  const int nrt = rg < Q.n_rg ? rt_b - rt_a : 0;
+  const int b0 = ks * Q.bpr / Q.n_ks, S = (ks + 1) * Q.bpr / Q.n_ks - b0;
+  const int N = nrt * S;
+  const int u0 = warp * N / PS_WARPS, u1 = (warp + 1) * N / PS_WARPS;
+  int u = u0 + first;
+  const int end = min(u1, u + count);
+  while (u < end) {  // one prefetch per run of row-blocks that are contiguous in memory (same row-tile)
+    const int rtl = u / S, b = u - rtl * S, run = min(S - b, end - u);
+    const int vrt = rt_a + rtl, j = job_of(Q, vrt);
+    if (lane == 0) l2_prefetch(Q.job[j].tiles + (size_t(vrt - Q.job[j].rt_begin) * Q.bpr + b0 + b) * TB, unsigned(run * TB));
+    u += run;
+  }
+}
+
 // warp that evaluates unit u when N units are dealt to 8 warps as [w*N/8, (w+1)*N/8)
 __device__ __forceinline__ int warp_of_unit(int u, int N) { return ((u + 1) * PS_WARPS - 1) / N; }
 
@@ -184,6 +212,10 @@ __global__ void __launch_bounds__(PS_THREADS, 2) k_decode_step(const __grid_cons
   __shared__ __align__(16) int xaux[64 * 4];
   __shared__ float red[32];
   __shared__ int flag;
+  __shared__ __align__(8) uint64_t bar;  // completion of the attention phase's bulk copies
+  unsigned bar_parity = 0;
+  if (threadIdx.x == 0) mbar_init(&bar, 1);
+  __syncthreads();
   const int G = int(gridDim.x), c = int(blockIdx.x);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, t = threadIdx.x;
   const unsigned epoch0 = p.peer.n ? ld_volatile_u32(&p.hdr->epoch) : 0u;
@@ -240,6 +272,8 @@ __global__ void __launch_bounds__(PS_THREADS, 2) k_decode_step(const __grid_cons
           slot[sl].load(l_ptr, lane);
           advance_load();
         }
+      // beyond the ring: into L2, so that HBM keeps streaming through the wait and the prologue
+      prefetch_share<TB>(P, c, warp, lane, NSLOT, p.l2_prefetch_units);
 
       // ---- the activations exist once every CTA has finished the previous phase --------------------------
       if (ph > 0 && !ps_wait(p, ph - 1, &flag)) return;
@@ -370,14 +404,30 @@ __global__ void __launch_bounds__(PS_THREADS, 2) k_decode_step(const __grid_cons
         P.sumsq_out[rg] = 0.0f;  // a row group without rows (fewer row-tiles than groups): the slot may hold an older phase's value
       }
     } else {
+      // a phase without weights of its own: start pulling the next GEMV phase's first row-blocks into L2
+      if (ph + 1 < p.n_phases) prefetch_share<TB>(p.phases[ph + 1], c, warp, lane, 0, NSLOT + p.l2_prefetch_units);
       if (ph > 0 && !ps_wait(p, ph - 1, &flag)) return;
       stamp(ph, 1);
       if (P.type == PH_ATTN) {
-        // model.cpp:312-372: one (query head, KV split) item at a time
-        const int items = int(P.rd.nh) * P.at.n_splits;
-        for (int it = c; it < items; it += G) {
-          attn_item<true>(P.at, P.rd, size_t(it % int(P.rd.nh)), size_t(it / int(P.rd.nh)), 0, smem, &flag);
-          __syncthreads();
+        // model.cpp:312-372
+        if (P.attn_per) {  // one (KV head, KV split) item at a time, all query heads of the group together
+          const int items = int(P.rd.nkv) * P.at.n_splits;
+          for (int it = c; it < items; it += G) {
+            const size_t kvh = size_t(it % int(P.rd.nkv)), split = size_t(it / int(P.rd.nkv));
+            const bool ok = P.attn_per == 4 ? attn_group_item<true, 4>(P.at, P.rd, kvh, split, 0, smem, &bar, bar_parity, p.spin_limit, &flag)
+                                            : attn_group_item<true, 2>(P.at, P.rd, kvh, split, 0, smem, &bar, bar_parity, p.spin_limit, &flag);
+            if (!ok) {
+              if (t == 0) atomicCAS(p.status, 0u, unsigned(ph) + 1u);
+              return;
+            }
+            __syncthreads();
+          }
+        } else {  // one (query head, KV split) item at a time
+          const int items = int(P.rd.nh) * P.at.n_splits;
+          for (int it = c; it < items; it += G) {
+            attn_item<true>(P.at, P.rd, size_t(it % int(P.rd.nh)), size_t(it / int(P.rd.nh)), 0, smem, &flag);
+            __syncthreads();
+          }
         }
       } else if (P.type == PH_EMBED) {
         // model.cpp:58-252: the token's embedding row, and the sum of squares of this CTA's part
@@ -655,13 +705,23 @@ static int build_plan(lmb_model *m) {
     ph.push_back(g);
   };
 
-  // KV splits: every (head, split) item gets a CTA of its own (a second round of a few left-over
-  // items would double the phase's time)
-  int n_splits = std::max(1, std::min(decode_attn_splits(ctx, m->nh, 1, c.max_seq_len), grid / int(m->nh)));
-  if (const char *as = std::getenv("LMB_PERSIST_ATTN_SPLITS")) n_splits = std::max(1, std::min(32, std::atoi(as)));
+  // Attention: the group form where the shape allows it (every (KV head, split) item gets a CTA of
+  // its own: a second round of a few left-over items would double the phase's time), else one item
+  // per (query head, split).
   RopeDims rd{m->nh, m->nkv, hd, c.max_seq_len, m->seq_stride, 0};
-  rd.split_len = ((c.max_seq_len + n_splits - 1) / n_splits + 15) / 16 * 16;
-  if ((rd.split_len + 3 * hd + 32 + ATT_THREADS) * sizeof(float) > PS_SMEM || hd > size_t(ATT_THREADS) || ATT_THREADS % hd != 0) ok = false;
+  int n_splits = 1, attn_per = 0;
+  // as many items as fit the grid in one round (more only when the context needs that many slices)
+  const AttnGroupPlan agp = m->attn_group ? plan_attn_group(m->nh, m->nkv, hd, c.max_seq_len, 1, (size_t(grid) / m->nkv) * m->nkv, PS_SMEM)
+                                          : AttnGroupPlan{false, 1, 0, 0, 0};
+  if (agp.ok) {
+    n_splits = agp.n_splits;
+    attn_per = agp.per;
+    rd.split_len = agp.split_len;
+  } else {
+    n_splits = std::max(1, std::min(decode_attn_splits(ctx, m->nh, 1, c.max_seq_len), grid / int(m->nh)));
+    rd.split_len = ((c.max_seq_len + n_splits - 1) / n_splits + 15) / 16 * 16;
+    if ((rd.split_len + 3 * hd + 32 + ATT_THREADS) * sizeof(float) > PS_SMEM || hd > size_t(ATT_THREADS) || ATT_THREADS % hd != 0) ok = false;
+  }
 
   for (size_t l = 0; l < m->layers.size(); ++l) {
     LayerW &L = m->layers[l];
@@ -672,6 +732,7 @@ static int build_plan(lmb_model *m) {
     a.type = PH_ATTN;
     a.at = AttnArgs{m->q, m->k, m->v, L.qb, L.kb, L.vb, m->cs_table, m->d_pos, m->kv, m->att, m->att_partial, m->att_counters, n_splits, l};
     a.rd = rd;
+    a.attn_per = attn_per;
     ph.push_back(a);
     float *o[1] = {tp ? m->proj : m->hidden};
     gemv(1, &L.w[3], o, m->att, m->nh * hd, XMODE_PLAIN, nullptr, L.rot[3], m->hidden, true);
@@ -720,6 +781,10 @@ int persist_forward(lmb_model *m) {
   p.extra_arrivals = unsigned(m->debug_extra_arrivals);
   p.eps = m->cfg.rms_norm_eps;
   p.timeline = pl->d_timeline;
+  {
+    const char *pf = std::getenv("LMB_PERSIST_L2_PREFETCH");  // tuning: row-blocks per warp (default 8)
+    p.l2_prefetch_units = pf ? std::max(0, std::atoi(pf)) : 8;
+  }
   if (m->cfg.tp_size > 1) {
     p.peer.n = ctx->tp_size;
     p.peer.rank = ctx->tp_rank;

@@ -67,13 +67,16 @@ def test_batched_decode_equals_independent_sequences(ctx, oracle):
     m.close()
 
 
-@pytest.mark.parametrize("env", [{}, {"LMB_MODEL_FUSED": "0"}, {"LMB_MODEL_GRAPH": "0"}, {"LMB_MODEL_FUSED": "0", "LMB_MODEL_GRAPH": "0"}])
+@pytest.mark.parametrize("env", [{"LMB_MODEL_PERSISTENT": "0"}, {"LMB_MODEL_PERSISTENT": "0", "LMB_MODEL_FUSED": "0"},
+                                 {"LMB_MODEL_PERSISTENT": "0", "LMB_MODEL_GRAPH": "0"},
+                                 {"LMB_MODEL_PERSISTENT": "0", "LMB_MODEL_FUSED": "0", "LMB_MODEL_GRAPH": "0"},
+                                 {"LMB_ATTN_GROUP": "0"}, {"LMB_MODEL_PERSISTENT": "0", "LMB_ATTN_GROUP": "0"}])
 def test_unfused_and_ungraphed_steps_match_the_fixtures(ctx, env, monkeypatch):
     """Batch 1 normally runs as one persistent kernel; with LMB_MODEL_PERSISTENT=0 the step is one
     launch per projection, which can in turn run without norm/activation fusion (the sequence
-    batched tensor-parallel runs use) and without graph capture.  The switches are read when the
-    model is created."""
-    env = dict(env, LMB_MODEL_PERSISTENT="0")
+    batched tensor-parallel runs use) and without graph capture.  LMB_ATTN_GROUP=0 selects the
+    attention form with one CTA per query head instead of one per KV head, in either kind of step.
+    The switches are read when the model is created."""
     for k, v in env.items():
         monkeypatch.setenv(k, v)
     g = np.load(os.path.join(GOLD, "model.npz"))
