@@ -174,9 +174,11 @@ int lmb_group_destroy(lmb_group *g);
 
 /* ---- kernel API on host pointers: replaces the dispatchers lut_gemv, lut_gemv_binary,
  * int2_gemv ... int8_gemv (include/lutmac/lut_gemm.hpp:172-408) -----------------------------------
- * Same arguments as the reference: activations must be readable for ceil(K/256)*256 floats,
- * num_blocks is ignored, output receives M floats.  Each call uploads the blocks, runs the
- * CUDA kernel on the default context of the current device and copies the result back. */
+ * Same arguments as the reference: num_blocks is ignored, output receives M floats.  Only the
+ * first K activations are read; the columns that pad the last 256-block count as zero (the
+ * reference reads them, but they only meet the zero weights its quantizers pad with, and its own
+ * tests pass arrays of exactly K floats).  Each call uploads the blocks, runs the CUDA kernel on
+ * the default context of the current device and copies the result back. */
 int lmb_gemv_host(int kind, const void *blocks, size_t num_blocks, const float *activations, float *output,
                   size_t M, size_t K);
 /* Layer API on host pointers: lut_linear for a weight already resident (lmb_weight_upload),
@@ -263,6 +265,9 @@ int lmb_debug_model_waits(lmb_model *m, int extra_arrivals, unsigned spin_limit)
  * the recording on (and returns only *n_phases); later calls return the last step's record:
  * out[2][n_phases][5] nanoseconds of the device's global timer for CTA 0 and for the last CTA at
  * {phase descriptor read, dependency met, activations prepared, main loop done, phase done},
+ * followed by out[10 n_phases + 2 i] = the last CTA's arrival at the end of phase i and
+ * out[10 n_phases + 2 i + 1] = the bitwise complement of the first CTA's arrival
+ * (so `out` holds 12 * n_phases words),
  * types[i] = 0 embedding, 1 GEMV, 2 attention, 3 tensor-parallel reduce, kslices[i] = K split. */
 int lmb_debug_model_timeline(lmb_model *m, unsigned long long *out, int *types, int *kslices, size_t cap_phases,
                              size_t *n_phases);

@@ -581,15 +581,20 @@ int lmb_gemv_host(int kind, const void *blocks, size_t num_blocks, const float *
   lmb_weight *w = nullptr;
   st = lmb_weight_upload(ctx, kind, blocks, M, K, &w);
   if (st != LMB_OK) return st;
-  // The reference kernels read whole 256-blocks of the activation vector.
+  // The reference kernels read whole 256-blocks of the activation vector, but what lies beyond
+  // column K only ever meets the zero weights the quantizers pad a row's last block with
+  // (quantize.hpp:262-273): the reference's own tests pass arrays of exactly K floats
+  // (tests/test_lut_gemm.cpp:108-118,150-158).  So only K activations are read here and the rest of
+  // the last block counts as zero, which is the same result without touching the caller's memory
+  // beyond K (and without letting whatever lies there disturb the block's fixed-point scale).
   const size_t kp = w->bpr * BLK;
   st = ensure_stage(ctx, (kp + M) * sizeof(float));
   if (st == LMB_OK) {
     float *h = static_cast<float *>(ctx->h_stage), *d = ctx->d_stage;
-    std::memcpy(h, activations, kp * sizeof(float));
-    cudaError_t e = cudaMemcpyAsync(d, h, kp * sizeof(float), cudaMemcpyHostToDevice, ctx->stream);
+    std::memcpy(h, activations, K * sizeof(float));
+    cudaError_t e = cudaMemcpyAsync(d, h, K * sizeof(float), cudaMemcpyHostToDevice, ctx->stream);
     if (e != cudaSuccess) st = cuda_fail(e, "lmb_gemv_host h2d");
-    if (st == LMB_OK) st = linear_impl(ctx, w, nullptr, d, kp, kp, d + kp, 1, 0);
+    if (st == LMB_OK) st = linear_impl(ctx, w, nullptr, d, K, kp, d + kp, 1, 0);
     if (st == LMB_OK) {
       e = cudaMemcpyAsync(h + kp, d + kp, M * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream);
       if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);

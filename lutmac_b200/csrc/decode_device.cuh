@@ -156,8 +156,10 @@ __device__ __forceinline__ void attn_item(const AttnArgs &a, const RopeDims &d, 
   float *acc = red + 32;             // [ATT_THREADS]
   const size_t pos = a.positions[b], seq = pos + 1;
   const size_t group = d.nh / d.nkv, kvh = head / group, kv_dim = d.nkv * d.hd, half = d.hd / 2;
-  float *kc_w = a.kv + b * d.seq_stride + (a.layer * 2) * d.max_seq * kv_dim + kvh * d.hd;
+  // cache layout on the device: [sequence][layer][K|V][kv head][position][head_dim]
+  float *kc_w = a.kv + b * d.seq_stride + (a.layer * 2) * d.max_seq * kv_dim + kvh * d.max_seq * d.hd;
   float *vc_w = kc_w + d.max_seq * kv_dim;
+  const size_t rs = d.hd;  // floats between consecutive positions of one head
   const float *kc = kc_w, *vc = vc_w;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = ATT_THREADS / 32;
   const int n_splits = a.n_splits;
@@ -194,10 +196,10 @@ __device__ __forceinline__ void attn_item(const AttnArgs &a, const RopeDims &d, 
       vn[i] = v0;
       vn[i + half] = v1;
       if (head % group == 0) {  // one writer per KV head
-        kc_w[pos * kv_dim + i] = r0;
-        kc_w[pos * kv_dim + i + half] = r1;
-        vc_w[pos * kv_dim + i] = v0;
-        vc_w[pos * kv_dim + i + half] = v1;
+        kc_w[pos * rs + i] = r0;
+        kc_w[pos * rs + i + half] = r1;
+        vc_w[pos * rs + i] = v0;
+        vc_w[pos * rs + i + half] = v1;
       }
     }
   }
@@ -218,7 +220,7 @@ __device__ __forceinline__ void attn_item(const AttnArgs &a, const RopeDims &d, 
         const size_t t = tb + i;
         kk[i] = (t >= n) ? make_float4(0, 0, 0, 0)
                 : (t == tnew) ? reinterpret_cast<const float4 *>(kn)[lane]
-                              : reinterpret_cast<const float4 *>(kc + (t0 + t) * kv_dim)[lane];
+                              : reinterpret_cast<const float4 *>(kc + (t0 + t) * rs)[lane];
       }
 #pragma unroll
       for (int i = 0; i < TS; ++i) s[i] = qv.x * kk[i].x + qv.y * kk[i].y + qv.z * kk[i].z + qv.w * kk[i].w;
@@ -230,7 +232,7 @@ __device__ __forceinline__ void attn_item(const AttnArgs &a, const RopeDims &d, 
         const size_t t = tb + i;
         kk[i] = (t >= n) ? make_float2(0, 0)
                 : (t == tnew) ? reinterpret_cast<const float2 *>(kn)[lane]
-                              : reinterpret_cast<const float2 *>(kc + (t0 + t) * kv_dim)[lane];
+                              : reinterpret_cast<const float2 *>(kc + (t0 + t) * rs)[lane];
       }
 #pragma unroll
       for (int i = 0; i < TS; ++i) s[i] = qv.x * kk[i].x + qv.y * kk[i].y;
@@ -239,7 +241,7 @@ __device__ __forceinline__ void attn_item(const AttnArgs &a, const RopeDims &d, 
       for (int i = 0; i < TS; ++i) {
         const size_t t = tb + i;
         if (t < n)
-          for (size_t c = lane; c < d.hd; c += 32) s[i] += qs[c] * (t == tnew ? kn[c] : kc[(t0 + t) * kv_dim + c]);
+          for (size_t c = lane; c < d.hd; c += 32) s[i] += qs[c] * (t == tnew ? kn[c] : kc[(t0 + t) * rs + c]);
       }
     }
 #pragma unroll
@@ -273,18 +275,18 @@ __device__ __forceinline__ void attn_item(const AttnArgs &a, const RopeDims &d, 
     for (; t + 15 * groups < n_old; t += 16 * groups) {
       float vv[16];
 #pragma unroll
-      for (int i = 0; i < 16; ++i) vv[i] = vc[(t0 + t + i * groups) * kv_dim + dd];
+      for (int i = 0; i < 16; ++i) vv[i] = vc[(t0 + t + i * groups) * rs + dd];
 #pragma unroll
       for (int i = 0; i < 16; ++i) av += sc[t + i * groups] * vv[i];
     }
     for (; t + 3 * groups < n_old; t += 4 * groups) {
       float vv[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) vv[i] = vc[(t0 + t + i * groups) * kv_dim + dd];
+      for (int i = 0; i < 4; ++i) vv[i] = vc[(t0 + t + i * groups) * rs + dd];
 #pragma unroll
       for (int i = 0; i < 4; ++i) av += sc[t + i * groups] * vv[i];
     }
-    for (; t < n_old; t += groups) av += sc[t] * vc[(t0 + t) * kv_dim + dd];
+    for (; t < n_old; t += groups) av += sc[t] * vc[(t0 + t) * rs + dd];
     if (has_new && g == 0) av += sc[n - 1] * vn[dd];
   }
   acc[threadIdx.x] = av;
@@ -352,9 +354,9 @@ __device__ __forceinline__ void attn_item(const AttnArgs &a, const RopeDims &d, 
 // Group attention: one CTA per (KV head, KV split, sequence) serves ALL query heads of the KV
 // group, so the keys and values of the slice are read once instead of once per query head
 // (grouped-query attention, model.cpp:338-372, reads the same cache rows for every head of a
-// group).  The slice's cache rows are fetched with bulk asynchronous copies (cp.async.bulk,
-// completion on an mbarrier): every row of the slice is in flight at once instead of a few
-// loads per thread, which is what bounds a latency-limited decode attention.  The new position's
+// group).  The slice's keys and its values are each fetched with ONE bulk asynchronous copy
+// (cp.async.bulk, completion on an mbarrier): the whole slice is in flight at once instead of a
+// few loads per thread, which is what bounds a latency-limited decode attention.  The new position's
 // key / value come from the fresh projections (bias and rotary embedding applied here) and are
 // written to the cache by this CTA.  Partial (max, sum, vector) records go to scratch; the last
 // split of a KV head to arrive merges the records of the group's heads in split order.
@@ -437,17 +439,21 @@ __device__ __forceinline__ bool attn_group_item(const AttnArgs &a, const RopeDim
   const size_t t0 = min(split * len, seq), t1 = min(t0 + len, seq), n = t1 - t0;
   const bool has_new = (pos >= t0 && pos < t1);  // the new position is the last one of its slice
   const size_t n_old = has_new ? n - 1 : n;
-  float *kc = a.kv + b * d.seq_stride + (a.layer * 2) * d.max_seq * kv_dim + kvh * hd;
+  // cache layout on the device: [sequence][layer][K|V][kv head][position][head_dim]: the slice of one
+  // head is contiguous, so it takes ONE bulk copy for the keys and one for the values
+  float *kc = a.kv + b * d.seq_stride + (a.layer * 2) * d.max_seq * kv_dim + kvh * d.max_seq * hd;
   float *vc = kc + d.max_seq * kv_dim;
   const unsigned row_bytes = unsigned(hd * sizeof(float));
 
   __syncthreads();  // whatever used this shared memory before is done
   // cached rows of the slice: all in flight at once
-  if (tid == 0) mbar_arrive_expect_tx(bar, unsigned(2 * n_old) * row_bytes);
-  fence_proxy_async_smem();  // earlier generic-proxy accesses of this memory precede the asynchronous writes
-  for (size_t t = tid; t < n_old; t += ATT_THREADS) {
-    bulk_copy_g2s(Ks + t * hd, kc + (t0 + t) * kv_dim, row_bytes, bar);
-    bulk_copy_g2s(Vs + t * hd, vc + (t0 + t) * kv_dim, row_bytes, bar);
+  if (tid == 0) {
+    fence_proxy_async_smem();  // earlier generic-proxy accesses of this memory precede the asynchronous writes
+    mbar_arrive_expect_tx(bar, unsigned(2 * n_old) * row_bytes);
+    if (n_old) {
+      bulk_copy_g2s(Ks, kc + t0 * hd, unsigned(n_old) * row_bytes, bar);
+      bulk_copy_g2s(Vs, vc + t0 * hd, unsigned(n_old) * row_bytes, bar);
+    }
   }
   // meanwhile: the group's rotated queries, and the new position's key / value (pairs (i, i + hd/2))
   const float *cs = a.cs_table + pos * hd;
@@ -481,8 +487,8 @@ __device__ __forceinline__ bool attn_group_item(const AttnArgs &a, const RopeDim
       float *kr = Ks + n_old * hd, *vr = Vs + n_old * hd;
       kr[j] = r0; kr[j + half] = r1;
       vr[j] = v0; vr[j + half] = v1;
-      kc[pos * kv_dim + j] = r0; kc[pos * kv_dim + j + half] = r1;  // this CTA is the only one that holds the position
-      vc[pos * kv_dim + j] = v0; vc[pos * kv_dim + j + half] = v1;
+      kc[pos * hd + j] = r0; kc[pos * hd + j + half] = r1;  // this CTA is the only one that holds the position
+      vc[pos * hd + j] = v0; vc[pos * hd + j + half] = v1;
     }
   }
   {  // bounded wait for the copies

@@ -770,28 +770,36 @@ int lmb_model_reset(lmb_model *m) {
   return LMB_OK;
 }
 
-// The host side always sees the reference layout of the WHOLE model, [layer][2][max_seq][kv_heads][head_dim];
-// a tensor-parallel rank holds kv_heads / tp_size consecutive heads of every row: a strided copy.
-int lmb_model_kv_export(lmb_model *m, size_t seq, float *h_out) {
-  LMB_REQUIRE(m && h_out && seq < m->cfg.max_batch, "lmb_model_kv_export: bad argument");
+// The host side always sees the reference layout of the WHOLE model, [layer][2][max_seq][kv_heads][head_dim]
+// (types.hpp:599-627).  On the device a sequence's cache is [layer][2][local kv head][max_seq][head_dim]
+// (the positions of one head contiguous); a tensor-parallel rank holds kv_heads / tp_size consecutive
+// heads.  One strided copy per (layer, K|V, head).
+static int kv_transfer(lmb_model *m, size_t seq, float *h, bool to_host) {
   const lmb_model_config &c = m->cfg;
-  const size_t rows = c.num_hidden_layers * 2 * c.max_seq_len, full = c.num_key_value_heads * c.head_dim * sizeof(float),
-               mine = m->nkv * c.head_dim * sizeof(float);
-  LMB_CUDA(cudaMemcpy2DAsync(reinterpret_cast<char *>(h_out) + size_t(c.tp_rank) * mine, full, m->kv + seq * m->seq_stride, mine,
-                             mine, rows, cudaMemcpyDeviceToHost, m->ctx->stream));
+  const size_t hd = c.head_dim, full = c.num_key_value_heads * hd, S = c.max_seq_len;
+  for (size_t lk = 0; lk < c.num_hidden_layers * 2; ++lk)
+    for (size_t kh = 0; kh < m->nkv; ++kh) {
+      float *dev = m->kv + seq * m->seq_stride + (lk * m->nkv + kh) * S * hd;
+      float *host = h + lk * S * full + (size_t(c.tp_rank) * m->nkv + kh) * hd;
+      if (to_host)
+        LMB_CUDA(cudaMemcpy2DAsync(host, full * sizeof(float), dev, hd * sizeof(float), hd * sizeof(float), S, cudaMemcpyDeviceToHost,
+                                   m->ctx->stream));
+      else
+        LMB_CUDA(cudaMemcpy2DAsync(dev, hd * sizeof(float), host, full * sizeof(float), hd * sizeof(float), S, cudaMemcpyHostToDevice,
+                                   m->ctx->stream));
+    }
   LMB_CUDA(cudaStreamSynchronize(m->ctx->stream));
   return LMB_OK;
 }
 
+int lmb_model_kv_export(lmb_model *m, size_t seq, float *h_out) {
+  LMB_REQUIRE(m && h_out && seq < m->cfg.max_batch, "lmb_model_kv_export: bad argument");
+  return kv_transfer(m, seq, h_out, true);
+}
+
 int lmb_model_kv_import(lmb_model *m, size_t seq, const float *h_in) {
   LMB_REQUIRE(m && h_in && seq < m->cfg.max_batch, "lmb_model_kv_import: bad argument");
-  const lmb_model_config &c = m->cfg;
-  const size_t rows = c.num_hidden_layers * 2 * c.max_seq_len, full = c.num_key_value_heads * c.head_dim * sizeof(float),
-               mine = m->nkv * c.head_dim * sizeof(float);
-  LMB_CUDA(cudaMemcpy2DAsync(m->kv + seq * m->seq_stride, mine, reinterpret_cast<const char *>(h_in) + size_t(c.tp_rank) * mine, full,
-                             mine, rows, cudaMemcpyHostToDevice, m->ctx->stream));
-  LMB_CUDA(cudaStreamSynchronize(m->ctx->stream));
-  return LMB_OK;
+  return kv_transfer(m, seq, const_cast<float *>(h_in), false);
 }
 
 int lmb_model_step_bytes(lmb_model *m, size_t position, uint64_t *bytes_out) {

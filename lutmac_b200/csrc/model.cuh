@@ -29,7 +29,7 @@ struct lmb_model {
         *gate = nullptr, *up = nullptr, *act = nullptr, *logits = nullptr, *logits_local = nullptr;
   float *att_partial = nullptr;      // [max_batch][nh][32 splits][hd + 2]
   unsigned *att_counters = nullptr;  // [max_batch][nh]
-  float *kv = nullptr;        // [max_batch][L][2][max_seq][nkv][hd]
+  float *kv = nullptr;        // [max_batch][L][2][nkv][max_seq][hd]: the positions of one head contiguous
   float *cs_table = nullptr;  // [max_seq][hd/2 cos | hd/2 sin]
   int *d_tokens = nullptr;
   size_t *d_pos = nullptr;

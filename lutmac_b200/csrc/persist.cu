@@ -44,7 +44,10 @@ constexpr int PS_MAX_JOBS = 3;
 constexpr int PS_S_MAX = 48;     // 256-column blocks of activations a CTA prepares (1 KiB of digits each)
 constexpr int PS_MAX_SEG = 160;  // (row-tile, contributing warp) partial rows a CTA can hold (128 B each)
 constexpr int PS_NRT_MAX = 80;   // row-tiles per CTA and phase
-constexpr size_t PS_SMEM = size_t(PS_S_MAX) * 1024 + size_t(PS_MAX_SEG) * 128;
+// digits of the CTA's K slice, then either the staged second operand of the prologue (norm weight
+// or `up` slice, as large as the digits) or, later, the warps' partial rows
+constexpr size_t PS_SMEM = size_t(PS_S_MAX) * 1024 * 2;
+static_assert(size_t(PS_MAX_SEG) * 128 <= size_t(PS_S_MAX) * 1024, "partial rows must fit behind the digits");
 
 enum { PH_EMBED = 0, PH_GEMV = 1, PH_ATTN = 2, PH_REDUCE = 3 };
 
@@ -90,8 +93,9 @@ struct PsParams {
   XchgHeader *hdr;
   const unsigned long long *xchg_data;  // this rank's exchange block
   // optional (null: off): nanosecond timestamps of CTA 0 and of the last CTA at five points of every
-  // phase -- descriptor read, dependency met, activations prepared, main loop done, phase done
-  unsigned long long *timeline;  // [2][n_phases][5]
+  // phase -- descriptor read, dependency met, activations prepared, main loop done, phase done --
+  // then per phase the last arrival and the complement of the first arrival over all CTAs
+  unsigned long long *timeline;  // [2][n_phases][5] + [n_phases][2]
   int l2_prefetch_units;         // row-blocks per warp pulled into L2 beyond the register ring before a wait
 };
 
@@ -106,12 +110,24 @@ __device__ __forceinline__ unsigned ld_volatile_u32(const unsigned *p) {
   return v;
 }
 
-// This CTA has finished phase `ph` (all its global writes are ordered before the arrival).
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+// This CTA has finished phase `ph`: one release-ordered reduction (the CTA's global writes, ordered
+// before it by the block barrier, become visible to whoever observes the count with an acquire).
 __device__ __forceinline__ void ps_arrive(const PsParams &p, int ph) {
   __syncthreads();
   if (threadIdx.x == 0) {
-    __threadfence();
-    atomicAdd(p.barrier + ph, 1u);
+    if (p.timeline) {
+      const unsigned long long now = global_ns();
+      unsigned long long *skew = p.timeline + size_t(2) * p.n_phases * 5 + size_t(ph) * 2;
+      atomicMax(skew, now);       // last arrival
+      atomicMax(skew + 1, ~now);  // first arrival, complemented
+    }
+    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.barrier + ph) : "memory");
   }
 }
 
@@ -123,30 +139,23 @@ __device__ __forceinline__ bool ps_wait(const PsParams &p, int ph, int *flag) {
     unsigned spins = 0;
     int ok = 1;
     while (ld_acquire_u32(p.barrier + ph) < target) {
-      if (ld_volatile_u32(p.status) != 0u) {
+      ++spins;
+      if ((spins & 63u) == 0u && ld_volatile_u32(p.status) != 0u) {  // somebody else gave up
         ok = 0;
         break;
       }
-      if (++spins > p.spin_limit) {
+      if (spins > p.spin_limit) {
         atomicCAS(p.status, 0u, unsigned(ph) + 1u);
         ok = 0;
         break;
       }
-      __nanosleep(20);
     }
-    __threadfence();
     *flag = ok;
   }
   __syncthreads();
   const bool ok = *flag != 0;
   __syncthreads();
   return ok;
-}
-
-__device__ __forceinline__ unsigned long long global_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
 }
 
 // load_x8 for vectors written earlier in the same launch: around the (incoherent) L1
@@ -279,6 +288,19 @@ __global__ void __launch_bounds__(PS_THREADS, 2) k_decode_step(const __grid_cons
       if (ph > 0 && !ps_wait(p, ph - 1, &flag)) return;
       stamp(ph, 1);
 
+      // Activations of the K slice.  Whole 256-blocks (every decoder shape): ONE bulk asynchronous
+      // copy brings the slice into shared memory (a second one the norm weights or the `up` slice)
+      // while the RMSNorm statistics are summed; each warp then converts its blocks in place, from
+      // shared memory, instead of paying a global-memory round trip per block.
+      const bool staged = (P.x_len % BLK == 0) && S > 0;
+      float *stage2 = smem + size_t(S) * FPB;
+      if (staged && t == 0) {
+        asm volatile("fence.proxy.async;" ::: "memory");  // the producers' writes, acquired above, precede the asynchronous reads
+        const unsigned bytes = unsigned(S) * BLK * 4u;
+        mbar_arrive_expect_tx(&bar, P.xmode == XMODE_PLAIN ? bytes : 2u * bytes);
+        bulk_copy_g2s(smem, P.x + size_t(b0) * BLK, bytes, &bar);
+        if (P.xmode != XMODE_PLAIN) bulk_copy_g2s(stage2, P.x2 + size_t(b0) * BLK, bytes, &bar);
+      }
       float inv_rms = 1.0f;
       if (P.xmode == XMODE_RMSNORM) {  // src/layers/norm.cpp:18-34, the sum of squares from the producer's partials
         float ss = 0.0f;
@@ -286,22 +308,45 @@ __global__ void __launch_bounds__(PS_THREADS, 2) k_decode_step(const __grid_cons
         ss = block_sum(ss, red);
         inv_rms = 1.0f / sqrtf(ss / float(P.x_len) + p.eps);
       }
+      if (staged) {  // bounded wait for the copies
+        unsigned spins = 0;
+        bool ok = true;
+        while (!mbar_try_wait(&bar, bar_parity)) {
+          if (++spins > p.spin_limit) {
+            ok = false;
+            break;
+          }
+        }
+        bar_parity ^= 1u;
+        if (!ok) atomicCAS(p.status, 0u, unsigned(ph) + 1u);
+        if (__syncthreads_or(!ok)) return;
+      }
       for (int it = warp; it < S; it += PS_WARPS) {
         float v[8], w8[8];
-        load_x8_cg(P.x, P.x_len, size_t(b0 + it), lane, v);
+        if (staged) {
+          const float4 a0 = reinterpret_cast<const float4 *>(smem + size_t(it) * FPB)[2 * lane];
+          const float4 a1 = reinterpret_cast<const float4 *>(smem + size_t(it) * FPB)[2 * lane + 1];
+          v[0] = a0.x; v[1] = a0.y; v[2] = a0.z; v[3] = a0.w; v[4] = a1.x; v[5] = a1.y; v[6] = a1.z; v[7] = a1.w;
+          if (P.xmode != XMODE_PLAIN) {
+            const float4 c0 = reinterpret_cast<const float4 *>(stage2 + size_t(it) * BLK)[2 * lane];
+            const float4 c1 = reinterpret_cast<const float4 *>(stage2 + size_t(it) * BLK)[2 * lane + 1];
+            w8[0] = c0.x; w8[1] = c0.y; w8[2] = c0.z; w8[3] = c0.w; w8[4] = c1.x; w8[5] = c1.y; w8[6] = c1.z; w8[7] = c1.w;
+          }
+          __syncwarp();  // the block is overwritten with its digits below
+        } else {
+          load_x8_cg(P.x, P.x_len, size_t(b0 + it), lane, v);
+          if (P.xmode == XMODE_RMSNORM) load_x8(P.x2, P.x_len, size_t(b0 + it), lane, w8);
+          else if (P.xmode != XMODE_PLAIN) load_x8_cg(P.x2, P.x_len, size_t(b0 + it), lane, w8);
+        }
         if (P.xmode == XMODE_RMSNORM) {
-          load_x8(P.x2, P.x_len, size_t(b0 + it), lane, w8);
 #pragma unroll
           for (int e = 0; e < 8; ++e) v[e] = v[e] * inv_rms * w8[e];
-        } else if (P.xmode == XMODE_SILU_MUL || P.xmode == XMODE_GELU_MUL) {
-          load_x8_cg(P.x2, P.x_len, size_t(b0 + it), lane, w8);
-          if (P.xmode == XMODE_SILU_MUL) {
+        } else if (P.xmode == XMODE_SILU_MUL) {
 #pragma unroll
-            for (int e = 0; e < 8; ++e) v[e] = (v[e] / (1.0f + expf(-v[e]))) * w8[e];  // silu(gate) * up, model.cpp:36,414-416
-          } else {
+          for (int e = 0; e < 8; ++e) v[e] = (v[e] / (1.0f + expf(-v[e]))) * w8[e];  // silu(gate) * up, model.cpp:36,414-416
+        } else if (P.xmode == XMODE_GELU_MUL) {
 #pragma unroll
-            for (int e = 0; e < 8; ++e) v[e] = gelu_tanh(v[e]) * w8[e];  // gelu(gate) * up, model.cpp:38-42,409-412
-          }
+          for (int e = 0; e < 8; ++e) v[e] = gelu_tanh(v[e]) * w8[e];  // gelu(gate) * up, model.cpp:38-42,409-412
         }
         if (P.rotate) fwht256_warp(v, lane);
         int *aux = xaux + 4 * it;
@@ -379,9 +424,11 @@ __global__ void __launch_bounds__(PS_THREADS, 2) k_decode_step(const __grid_cons
       if (P.n_ks > 1 && nrt > 0) {
         __syncthreads();
         if (t == 0) {
-          __threadfence();  // cumulative: publishes the CTA's partial sums (ordered before it by the barrier)
-          flag = (atomicAdd(p.counters + rg, 1u) == unsigned(P.n_ks - 1));
-          __threadfence();
+          // release: publishes the CTA's partial sums (ordered before it by the block barrier);
+          // acquire: the last arriver sees the other slices' sums
+          unsigned before;
+          asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(before) : "l"(p.counters + rg) : "memory");
+          flag = (before == unsigned(P.n_ks - 1));
         }
         __syncthreads();
         final_writer = flag != 0;
@@ -795,6 +842,8 @@ int persist_forward(lmb_model *m) {
     for (int r = 0; r < ctx->tp_size; ++r)
       p.peer.data[r] = reinterpret_cast<unsigned long long *>(static_cast<char *>(ctx->xchg.peer[r]) + XCHG_HEADER_BYTES);
   }
+  if (pl->d_timeline)
+    LMB_CUDA(cudaMemsetAsync(pl->d_timeline + size_t(2) * pl->n_phases * 5, 0, size_t(pl->n_phases) * 2 * sizeof(unsigned long long), ctx->stream));
   return launch_step_kind(pl->kind, ctx, pl->grid, p);
 }
 
@@ -817,7 +866,7 @@ int persist_timeline(lmb_model *m, unsigned long long *out, int *types, int *ksl
     return LMB_ERR_STATE;
   }
   *n_phases = size_t(pl->n_phases);
-  const size_t words = size_t(2) * pl->n_phases * 5;
+  const size_t words = size_t(2) * pl->n_phases * 5 + size_t(pl->n_phases) * 2;
   LMB_CUDA(cudaStreamSynchronize(m->ctx->stream));
   if (!pl->d_timeline) {
     LMB_CUDA(cudaMalloc(&pl->d_timeline, words * sizeof(unsigned long long)));
