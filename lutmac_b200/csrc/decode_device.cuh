@@ -426,9 +426,12 @@ template <int PER> __device__ __forceinline__ LaneVec<PER> ldcg_lane_vec(const f
 // One (KV head, split, sequence) item.  head_dim = 32 * PER.  `parity` is the phase of `bar` this
 // item waits for (flipped here).  False when the bounded wait for the copies ran out (*timed_out
 // is then set): the caller leaves the kernel.  All ATT_THREADS threads of the CTA take part.
+// `dbg` (profiling aid, usually null): thread 0 records the device's nanosecond timer after the wait
+// for the copies (dbg[0]) and after the partial records are written (dbg[1]).
 template <bool FRESH_CG, int PER>
 __device__ __forceinline__ bool attn_group_item(const AttnArgs &a, const RopeDims &d, size_t kvh, size_t split, size_t b, float *sm,
-                                                uint64_t *bar, unsigned &parity, unsigned spin_limit, int *flag) {
+                                                uint64_t *bar, unsigned &parity, unsigned spin_limit, int *flag,
+                                                unsigned long long *dbg = nullptr) {
   const size_t hd = d.hd, g = d.nh / d.nkv, kv_dim = d.nkv * hd, half = hd / 2, sl = d.split_len;
   float *Ks = sm, *Vs = Ks + sl * hd, *qs = Vs + sl * hd, *sc = qs + g * hd, *wk = sc + g * sl, *stat = wk + ATT_MAX_GROUP * ATT_MAX_SPLITS;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nw = ATT_THREADS / 32;
@@ -507,6 +510,7 @@ __device__ __forceinline__ bool attn_group_item(const AttnArgs &a, const RopeDim
     __syncthreads();
     if (*flag == 0) return false;
   }
+  if (dbg && tid == 0) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(dbg[0]));
   // scores: a warp per timestep, a lane per PER dimensions
   const float scale = 1.0f / sqrtf(float(hd));
   for (size_t t = warp; t < n; t += nw) {
@@ -571,11 +575,12 @@ __device__ __forceinline__ bool attn_group_item(const AttnArgs &a, const RopeDim
     }
   }
   __syncthreads();
+  if (dbg && tid == 0) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(dbg[1]));
   unsigned *ctr = a.counters + b * d.nkv + kvh;
   if (tid == 0) {
-    __threadfence();
-    *flag = (atomicAdd(ctr, 1u) == unsigned(n_splits - 1));
-    __threadfence();
+    unsigned before;  // release: this CTA's partial records; acquire: the other splits' records
+    asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(before) : "l"(ctr) : "memory");
+    *flag = (before == unsigned(n_splits - 1));
   }
   __syncthreads();
   if (*flag == 0) return true;
@@ -602,12 +607,12 @@ __device__ __forceinline__ bool attn_group_item(const AttnArgs &a, const RopeDim
 #pragma unroll
     for (int e = 0; e < PER; ++e) tot.v[e] = 0.0f;
     int s2 = 0;
-    for (; s2 + 3 < n_splits; s2 += 4) {
-      LaneVec<PER> pv[4];
+    for (; s2 + 7 < n_splits; s2 += 8) {  // eight records in flight per lane
+      LaneVec<PER> pv[8];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) pv[i] = ldcg_lane_vec<PER>(all + (s2 + i) * rec, lane);
+      for (int i = 0; i < 8; ++i) pv[i] = ldcg_lane_vec<PER>(all + (s2 + i) * rec, lane);
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
+      for (int i = 0; i < 8; ++i)
 #pragma unroll
         for (int e = 0; e < PER; ++e) tot.v[e] += w[s2 + i] * pv[i].v[e];
     }

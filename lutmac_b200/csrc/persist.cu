@@ -397,8 +397,9 @@ __global__ void __launch_bounds__(PS_THREADS, 2) k_decode_step(const __grid_cons
           const int items = int(P.rd.nkv) * P.at.n_splits;
           for (int it = c; it < items; it += G) {
             const size_t kvh = size_t(it % int(P.rd.nkv)), split = size_t(it / int(P.rd.nkv));
-            const bool ok = P.attn_per == 4 ? attn_group_item<true, 4>(P.at, P.rd, kvh, split, 0, smem, &bar, bar_parity, p.spin_limit, &flag)
-                                            : attn_group_item<true, 2>(P.at, P.rd, kvh, split, 0, smem, &bar, bar_parity, p.spin_limit, &flag);
+            unsigned long long *dbg = tl ? tl + ph * 5 + 2 : nullptr;  // timeline slots 2 and 3 of the phase
+            const bool ok = P.attn_per == 4 ? attn_group_item<true, 4>(P.at, P.rd, kvh, split, 0, smem, &bar, bar_parity, p.spin_limit, &flag, dbg)
+                                            : attn_group_item<true, 2>(P.at, P.rd, kvh, split, 0, smem, &bar, bar_parity, p.spin_limit, &flag, dbg);
             if (!ok) {
               if (t == 0) atomicCAS(p.status, 0u, unsigned(ph) + 1u);
               return;
