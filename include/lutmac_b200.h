@@ -126,6 +126,19 @@ size_t lmb_tiled_bytes(int kind, size_t M, size_t K);
 int lmb_retile_host(int kind, const void *blocks, size_t M, size_t K, void *tiled);
 int lmb_untile_host(int kind, const void *tiled, size_t M, size_t K, void *blocks_out);
 
+/* ---- quantize + pack on the device: replaces quantize_tensor (ternary), quantize_tensor_binary,
+ * _int2, _int3, _int4, _int8 (include/lutmac/quantize.hpp:193-336, 725-823, 918-975, 982-1039,
+ * 387-495, 833-911) for a row-major fp32 matrix [M][K] -----------------------------------------------
+ * d_blocks_out receives M*ceil(K/256) blocks in the reference's struct layout (what a .lutmac file
+ * stores and lmb_weight_upload takes, from host memory).  Codes and bit planes are bit-exact with
+ * the reference's quantizers; scales agree to the last ulp or two of a -ffast-math build.  The
+ * Hadamard rotation the reference's quantize tool applies to the weights of its <= 2-bit formats
+ * (tools/lutmac-quantize.cpp:423-453) is lmb_fwht256 over the same buffer, called first;
+ * lmb_quantize_host does that when rotate_first is non-zero.  5- and 6-bit blocks are not
+ * produced on the device. */
+int lmb_quantize(lmb_ctx *ctx, int kind, const float *d_weights, size_t M, size_t K, void *d_blocks_out);
+int lmb_quantize_host(lmb_ctx *ctx, int kind, const float *weights, size_t M, size_t K, int rotate_first, void *blocks_out);
+
 /* ---- layer API on device pointers: replaces lut_linear (include/lutmac/lut_gemm.hpp:419,
  * src/kernels/lut_gemm_scalar.cpp:68-180) ---------------------------------------------------------
  * y[b] = W * rot?(pad(x[b])) + bias for b < batch.  d_x holds batch rows of x_stride floats of

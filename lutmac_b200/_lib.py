@@ -66,6 +66,8 @@ SIGNATURES = {
     "lmb_tiled_bytes": (sz, [C.c_int, sz, sz]),
     "lmb_retile_host": (C.c_int, [C.c_int, vp, sz, sz, vp]),
     "lmb_untile_host": (C.c_int, [C.c_int, vp, sz, sz, vp]),
+    "lmb_quantize": (C.c_int, [vp, C.c_int, vp, sz, sz, vp]),
+    "lmb_quantize_host": (C.c_int, [vp, C.c_int, vp, sz, sz, C.c_int, vp]),
     "lmb_linear": (C.c_int, [vp, vp, vp, vp, sz, sz, vp, sz, C.c_uint]),
     "lmb_linear_static_scratch": (C.c_int, [vp, vp, vp, sz, vp, C.c_uint, vp]),
     "lmb_group_create": (C.c_int, [vp, sz, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), C.c_uint, C.POINTER(vp)]),

@@ -376,6 +376,24 @@ def lut_linear_multi(weights: Sequence[PackedTensor], inputs: Sequence[np.ndarra
     return outs
 
 
+# ---- the reference's quantizers ---------------------------------------------------------------------------------
+
+def quantize_tensor(kind: int, weights: np.ndarray, rotate_first: bool = False, ctx: Optional[Context] = None,
+                    name: str = "") -> PackedTensor:
+    """quantize_tensor / quantize_tensor_binary / _int2 / _int3 / _int4 / _int8 of
+    include/lutmac/quantize.hpp on the device: a 2-D fp32 array to a PackedTensor of `kind`.
+    rotate_first applies the block-wise Hadamard rotation to the flat weight array before
+    quantizing, as the reference's quantize tool does for its ternary, binary and 2-bit formats
+    (tools/lutmac-quantize.cpp:423-453)."""
+    w = np.ascontiguousarray(weights, np.float32)
+    assert w.ndim == 2
+    M, K = w.shape
+    ctx = ctx or default_context()
+    blocks = np.zeros(M * blocks_per_row(K), BLOCK_DTYPES[kind])
+    check(lib().lmb_quantize_host(ctx.h, kind, _vp(w), M, K, 1 if rotate_first else 0, _vp(blocks)))
+    return PackedTensor(kind, blocks, M, K, name=name)
+
+
 # ---- the reference's transform API -------------------------------------------------------------------------
 
 def apply_hadamard_rotation(data: np.ndarray, n: Optional[int] = None) -> np.ndarray:
