@@ -525,14 +525,25 @@ __device__ __forceinline__ bool attn_group_item(const AttnArgs &a, const RopeDim
         for (int e = 0; e < PER; ++e) s[h] += qv.v[e] * kk.v[e];
       }
     }
+    // Eight sums per lane to reduce over the 32 lanes: each step halves the values a lane carries
+    // (it keeps one half of the heads and hands the other half to its partner), 4 + 2 + 1 + 1 + 1
+    // shuffles instead of 8 x 5.  Lane l ends with the total of head 4*bit4(l) + 2*bit3(l) + bit2(l).
+    float a4[4], a2[2];
 #pragma unroll
-    for (int m = 16; m > 0; m >>= 1) {
-#pragma unroll
-      for (int h = 0; h < ATT_MAX_GROUP; ++h) s[h] += __shfl_xor_sync(0xffffffffu, s[h], m);
+    for (int i = 0; i < 4; ++i) {
+      const float keep = (lane & 16) ? s[4 + i] : s[i], give = (lane & 16) ? s[i] : s[4 + i];
+      a4[i] = keep + __shfl_xor_sync(0xffffffffu, give, 16);
     }
 #pragma unroll
-    for (int h = 0; h < ATT_MAX_GROUP; ++h)
-      if (lane == h && size_t(h) < g) sc[h * sl + t] = s[h] * scale;
+    for (int i = 0; i < 2; ++i) {
+      const float keep = (lane & 8) ? a4[2 + i] : a4[i], give = (lane & 8) ? a4[i] : a4[2 + i];
+      a2[i] = keep + __shfl_xor_sync(0xffffffffu, give, 8);
+    }
+    float a1 = ((lane & 4) ? a2[1] : a2[0]) + __shfl_xor_sync(0xffffffffu, (lane & 4) ? a2[0] : a2[1], 4);
+    a1 += __shfl_xor_sync(0xffffffffu, a1, 2);
+    a1 += __shfl_xor_sync(0xffffffffu, a1, 1);
+    const int hsel = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
+    if ((lane & 3) == 0 && size_t(hsel) < g) sc[hsel * sl + t] = a1 * scale;
   }
   __syncthreads();
   // softmax of the slice (attention.cpp:23-42 per head), a warp per head

@@ -58,6 +58,12 @@ constexpr int NCCL_FLOAT = 7, NCCL_SUM = 0;
 
 using namespace lmb;
 
+// Whether batch-1 steps run as the persistent kernel when the environment does not say.  Measured
+// on B200 (Llama-3-70B-shaped ternary stack, 2048 positions): on one GPU the waits between its
+// phases cost about what the kernel boundaries of the launch-per-projection step cost, so it is
+// opt-in there.
+static constexpr bool PERSISTENT_BY_DEFAULT = false;
+
 static int dev_alloc(float **p, size_t n) {
   LMB_CUDA(cudaMalloc(p, (n ? n : 1) * sizeof(float)));
   LMB_CUDA(cudaMemset(*p, 0, (n ? n : 1) * sizeof(float)));
@@ -287,8 +293,9 @@ int lmb_model_create(lmb_ctx *ctx, const lmb_model_config *c, lmb_model **out) {
     m->fused = !(fv && fv[0] == '0');
     const char *pv = std::getenv("LMB_TP_PEERS");
     m->tp_peers = !(pv && pv[0] == '0');
+    // LMB_MODEL_PERSISTENT=1 / 0 forces the persistent batch-1 step on / off; unset: the default below
     const char *sv = std::getenv("LMB_MODEL_PERSISTENT");
-    m->persistent = !(sv && sv[0] == '0');
+    m->persistent = sv ? (sv[0] != '0') : PERSISTENT_BY_DEFAULT;
     const char *av = std::getenv("LMB_ATTN_GROUP");
     m->attn_group = !(av && av[0] == '0');
   }

@@ -10,20 +10,21 @@
 // (tensor parallel: o and down deliver their partial vectors to every rank's exchange block and a
 // short reduce phase after each adds the ranks' vectors in rank order).  Phases are ordered by
 // arrival counters in device memory; every wait is bounded and on expiry records the phase in a
-// status word and ends the kernel (no trap, no endless spin).  What makes it faster:
+// status word and ends the kernel (no trap, no endless spin).  Design points:
 //   * weights never depend on a predecessor, so every warp issues the loads of its first
 //     row-blocks of the NEXT phase into its register ring BEFORE it waits for the current phase
-//     to finish everywhere: about 140 KB per SM (20 MB per GPU) are in flight across every
-//     dependency, where separate launches cannot overlap at all while the SMs are full;
-//   * the work of a GEMV phase is cut by warp, not by CTA slot: every CTA serves one K slice, and
-//     the slice's row-tiles (each a contiguous chunk of memory) are dealt round-robin over all warps
-//     that serve it; a warp completes its rows itself, so nothing waits for a partial wave or for
-//     the slowest warp of a CTA;
+//     to finish everywhere (about 140 KB per SM in flight across every dependency);
+//   * the work of a GEMV phase is cut by SM, not by CTA slot: K slices x row groups = grid size
+//     exactly, row groups differ by at most one row-tile, and the warps of a CTA split its
+//     (row-tile, block) units evenly;
 //   * the activations of a K slice arrive by ONE bulk asynchronous copy (cp.async.bulk + mbarrier)
 //     and are converted in place from shared memory; attention fetches a slice's keys and values
 //     the same way;
 //   * RMSNorm statistics are computed once by the phase that produces the hidden state (one
-//     partial sum of squares per row-tile) instead of by every CTA of the consuming phase.
+//     partial sum of squares per row group) instead of by every CTA of the consuming phase.
+// Measured on B200 the step is not faster than the launch-per-projection step on one GPU (the
+// spread of the CTAs' arrivals at each wait, 6 to 14 us, costs more than a kernel boundary under
+// programmatic dependent launch), so models take this path only on request.
 // The evaluation units (weights x fixed-point digits on the integer MMA) are those of the
 // one-GEMV kernels; only the integer tensor-core layouts take this path, and only models whose
 // seven projections per layer share one layout.  Cooperative launch guarantees co-residency.
@@ -46,9 +47,12 @@ constexpr int PS_THREADS = 256;
 constexpr int PS_WARPS = PS_THREADS / 32;
 constexpr int PS_MAX_JOBS = 3;
 constexpr int PS_S_MAX = 48;     // 256-column blocks of activations a CTA prepares (1 KiB of digits each)
-// digits of the CTA's K slice, then the staged second operand of the prologue (norm weight or `up`
-// slice, as large as the digits); the attention phase uses the same memory for its slice
+constexpr int PS_MAX_SEG = 160;  // (row-tile, contributing warp) partial rows a CTA can hold (128 B each)
+constexpr int PS_NRT_MAX = 80;   // row-tiles per CTA and phase
+// digits of the CTA's K slice, then either the staged second operand of the prologue (norm weight
+// or `up` slice, as large as the digits) or, later, the warps' partial rows
 constexpr size_t PS_SMEM = size_t(PS_S_MAX) * 1024 * 2;
+static_assert(size_t(PS_MAX_SEG) * 128 <= size_t(PS_S_MAX) * 1024, "partial rows must fit behind the digits");
 
 enum { PH_EMBED = 0, PH_GEMV = 1, PH_ATTN = 2, PH_REDUCE = 3 };
 
@@ -67,7 +71,7 @@ struct PsPhase {
   int n_sumsq_in;
   PsJob job[PS_MAX_JOBS];
   const float *x, *x2, *residual, *sumsq_in;
-  float *sumsq_out;  // one partial sum of squares of the output per row-tile (PH_GEMV), per CTA (PH_EMBED, PH_REDUCE)
+  float *sumsq_out;  // one partial sum of squares of the output per row group (PH_GEMV), per CTA (PH_EMBED, PH_REDUCE)
   // PH_ATTN
   AttnArgs at;
   RopeDims rd;
@@ -85,7 +89,7 @@ struct PsParams {
   const PsPhase *phases;
   int n_phases, n_xchg;
   unsigned *barrier;   // [n_phases] arrival counters, zeroed before the launch
-  unsigned *counters;  // [row-tiles of the largest phase] split-K arrival counters, zeroed before the launch
+  unsigned *counters;  // [grid] split-K arrival counters, zeroed before the launch
   float *scratch;      // split-K partial sums [K slice][row of the phase]
   unsigned *status;    // 0, or 1 + the phase whose wait expired
   unsigned spin_limit, extra_arrivals;
@@ -179,6 +183,9 @@ __device__ __forceinline__ int job_of(const PsPhase &P, int vrt) {
   return j;
 }
 
+// warp that evaluates unit u when N units are dealt to 8 warps as [w*N/8, (w+1)*N/8)
+__device__ __forceinline__ int warp_of_unit(int u, int N) { return ((u + 1) * PS_WARPS - 1) / N; }
+
 template <int KIND>
 __global__ void __launch_bounds__(PS_THREADS, 2) k_decode_step(const __grid_constant__ PsParams p) {
   using U = Unit<KIND>;
@@ -215,34 +222,40 @@ __global__ void __launch_bounds__(PS_THREADS, 2) k_decode_step(const __grid_cons
     __syncthreads();
 
     if (P.type == PH_GEMV) {
-      // ---- work: this CTA serves K slice ks; a warp evaluates whole chunks = (row-tile, K slice), which
-      // are contiguous in memory.  Chunks are dealt round-robin over the warps that serve the slice
-      // (warp-major, so that a phase with fewer chunks than warps still keeps every SM busy).
-      const int ks = c % P.n_ks, n_rg = G / P.n_ks, rg = c / P.n_ks;
+      // ---- this CTA's share: K slice ks, row-tiles [rt_a, rt_b) of the concatenated jobs -----------------
+      const int ks = c % P.n_ks, rg = c / P.n_ks;
+      const int rt_a = int((long long)(rg)*P.rt_total / P.n_rg), rt_b = int((long long)(rg + 1) * P.rt_total / P.n_rg);
+      const int nrt = rg < P.n_rg ? rt_b - rt_a : 0;
       const int b0 = ks * P.bpr / P.n_ks, S = (ks + 1) * P.bpr / P.n_ks - b0;
-      const int wps = n_rg * PS_WARPS, wslice = warp * n_rg + rg;
-      const int RT = P.rt_total;
-      auto chunk_ptr = [&](int vrt) {
-        const int j = job_of(P, vrt);
-        return P.job[j].tiles + (size_t(vrt - P.job[j].rt_begin) * P.bpr + b0) * TB;
+      const int N = nrt * S;
+      const int u0 = warp * N / PS_WARPS, u1 = (warp + 1) * N / PS_WARPS;
+      const int seg_slots = N > 0 ? min(PS_WARPS, (S * PS_WARPS + N - 1) / N + 1) : 1;
+      float *seg = smem + size_t(S) * FPB;
+
+      auto tile_ptr = [&](int rtl, int b) {
+        const int vrt = rt_a + rtl, j = job_of(P, vrt);
+        return P.job[j].tiles + (size_t(vrt - P.job[j].rt_begin) * P.bpr + b0 + b) * TB;
       };
-      // load cursor: runs NSLOT row-blocks ahead of the evaluation, across chunk boundaries
-      int l_rt = (rg < n_rg && wslice < RT) ? wslice : -1, l_b = 0;
-      const uint8_t *l_ptr = l_rt >= 0 ? chunk_ptr(l_rt) : nullptr;
+      // load cursor (runs NSLOT units ahead of the evaluation)
+      int l_rtl = 0, l_b = 0;
+      const uint8_t *l_ptr = nullptr;
+      if (u0 < u1) {
+        l_rtl = u0 / S;
+        l_b = u0 - l_rtl * S;
+        l_ptr = tile_ptr(l_rtl, l_b);
+      }
       auto advance_load = [&]() {
         l_ptr += TB;
         if (++l_b == S) {
           l_b = 0;
-          l_rt += wps;
-          if (l_rt >= RT) l_rt = -1;
-          else l_ptr = chunk_ptr(l_rt);
+          ++l_rtl;
+          if (l_rtl < nrt) l_ptr = tile_ptr(l_rtl, 0);
         }
       };
-      int e_rt = l_rt, e_b = 0;
       U slot[NSLOT];
 #pragma unroll
       for (int sl = 0; sl < NSLOT; ++sl)
-        if (l_rt >= 0) {
+        if (u0 + sl < u1) {
           slot[sl].load(l_ptr, lane);
           advance_load();
         }
@@ -319,75 +332,100 @@ __global__ void __launch_bounds__(PS_THREADS, 2) k_decode_step(const __grid_cons
       __syncthreads();
       stamp(ph, 2);
 
-      // ---- main loop: evaluate a slot, refill it with the row-block NSLOT ahead; a finished chunk's
-      // 32 rows (one per lane) are completed by the warp itself -------------------------------------------
-      const unsigned epoch = epoch0 + unsigned(P.xchg_seq);
-      const int mp = RT * TILE_ROWS;
-      auto finish_rows = [&](int vrt, float val) {  // bias-free epilogue of row vrt*32 + lane: residual, output, statistics
-        const int j = job_of(P, vrt);
-        const int row = (vrt - P.job[j].rt_begin) * TILE_ROWS + lane;
-        float o = 0.0f;
-        if (row < P.job[j].M) {
-          o = val;
-          if (P.residual) o += __ldcg(P.residual + row);
-          if (P.to_peers) {  // value and tag in one 8-byte store per rank: the reader needs no fence and no flag
-            const size_t at = (size_t(epoch & 1u) * p.peer.n + p.peer.rank) * p.peer.cap + row;
-            const unsigned long long word = (static_cast<unsigned long long>(epoch + 1u) << 32) | __float_as_uint(o);
-            for (int r = 0; r < p.peer.n; ++r) *reinterpret_cast<volatile unsigned long long *>(p.peer.data[r] + at) = word;
-          } else {
-            P.job[j].y[row] = o;
-          }
-        }
-        if (P.sumsq_out) {  // one partial sum of squares per row-tile, lanes added in a fixed tree
-          float ss = o * o;
-#pragma unroll
-          for (int m = 16; m > 0; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
-          if (lane == 0) P.sumsq_out[vrt] = ss;
-        }
-      };
+      // ---- main loop: evaluate a slot, refill it with the unit NSLOT ahead ------------------------------
       typename U::Acc accs[1];
       U::acc_init(accs[0]);
       const MmaX xo{smem, xsum, xaux, S * FPB};
-      while (e_rt >= 0) {
+      if (u0 < u1) {
+        int e_rtl = u0 / S, e_b = u0 - e_rtl * S;
+        for (int base = u0; base < u1; base += NSLOT) {
 #pragma unroll
-        for (int sl = 0; sl < NSLOT; ++sl) {
-          if (e_rt >= 0) {  // uniform over the warp
-            slot[sl].template eval<1, false>(xo, e_b, accs);
-            if (l_rt >= 0) {
-              slot[sl].load(l_ptr, lane);
-              advance_load();
-            }
-            if (++e_b == S) {  // the chunk is complete
-              const float v = U::acc_row(accs[0], lane);
-              U::acc_init(accs[0]);
-              if (P.n_ks == 1) {
-                finish_rows(e_rt, v);
-              } else {  // split K: the last slice to arrive for the row-tile adds all slices in slice order
-                p.scratch[size_t(ks) * mp + e_rt * TILE_ROWS + lane] = v;
-                __syncwarp();
-                int last = 0;
-                if (lane == 0) {
-                  unsigned before;  // release: this warp's partial sums; acquire: the other slices' sums
-                  asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(before) : "l"(p.counters + e_rt) : "memory");
-                  last = (before == unsigned(P.n_ks - 1));
-                  if (last) p.counters[e_rt] = 0u;  // ready for the next phase (which starts behind a grid-wide wait)
-                }
-                last = __shfl_sync(0xffffffffu, last, 0);
-                if (last) {
-                  const float *scr = p.scratch + e_rt * TILE_ROWS + lane;
-                  float tot = 0.0f;
-                  for (int k = 0; k < P.n_ks; ++k) tot += __ldcg(scr + size_t(k) * mp);
-                  finish_rows(e_rt, tot);
-                }
+          for (int sl = 0; sl < NSLOT; ++sl) {
+            const int u = base + sl;
+            if (u < u1) {
+              slot[sl].template eval<1, false>(xo, e_b, accs);
+              if (u + NSLOT < u1) {
+                slot[sl].load(l_ptr, lane);
+                advance_load();
               }
-              e_b = 0;
-              e_rt += wps;
-              if (e_rt >= RT) e_rt = -1;
+              if (e_b == S - 1 || u == u1 - 1) {  // this warp's part of the row-tile is complete
+                const float v = U::acc_row(accs[0], lane);
+                const int k = warp - warp_of_unit(e_rtl * S, N);
+                seg[(e_rtl * seg_slots + k) * 32 + lane] = v;
+                U::acc_init(accs[0]);
+              }
+              if (++e_b == S) {
+                e_b = 0;
+                ++e_rtl;
+              }
             }
           }
         }
       }
+      __syncthreads();
       stamp(ph, 3);
+
+      // ---- rows: add the warps' parts in warp order; split K goes through scratch ------------------------
+      const unsigned epoch = epoch0 + unsigned(P.xchg_seq);
+      float my_ss = 0.0f;
+      auto finish_row = [&](int rtl, int l, float val) {
+        const int vrt = rt_a + rtl, j = job_of(P, vrt);
+        const int row = (vrt - P.job[j].rt_begin) * TILE_ROWS + l;
+        if (row >= P.job[j].M) return;
+        float o = val;
+        if (P.residual) o += __ldcg(P.residual + row);
+        if (P.to_peers) {  // value and tag in one 8-byte store per rank: the reader needs no fence and no flag
+          const size_t at = (size_t(epoch & 1u) * p.peer.n + p.peer.rank) * p.peer.cap + row;
+          const unsigned long long word = (static_cast<unsigned long long>(epoch + 1u) << 32) | __float_as_uint(o);
+          for (int r = 0; r < p.peer.n; ++r) *reinterpret_cast<volatile unsigned long long *>(p.peer.data[r] + at) = word;
+        } else {
+          P.job[j].y[row] = o;
+        }
+        my_ss += o * o;
+      };
+      const int nrows = nrt * TILE_ROWS;
+      const int mp = P.rt_total * TILE_ROWS;
+      bool final_writer = (P.n_ks == 1);
+      for (int r = t; r < nrows; r += PS_THREADS) {
+        const int rtl = r >> 5, l = r & 31;
+        const int wf = warp_of_unit(rtl * S, N), wl = warp_of_unit(rtl * S + S - 1, N);
+        float s = 0.0f;
+        for (int k = 0; k <= wl - wf; ++k) {  // warps without a unit of this row-tile (fewer units than warps) wrote nothing
+          const int w = wf + k;
+          if (max(w * N / PS_WARPS, rtl * S) < min((w + 1) * N / PS_WARPS, (rtl + 1) * S)) s += seg[(rtl * seg_slots + k) * 32 + l];
+        }
+        if (P.n_ks == 1) finish_row(rtl, l, s);
+        else p.scratch[size_t(ks) * mp + (rt_a + rtl) * TILE_ROWS + l] = s;
+      }
+      if (P.n_ks > 1 && nrt > 0) {
+        __syncthreads();
+        if (t == 0) {
+          // release: publishes the CTA's partial sums (ordered before it by the block barrier);
+          // acquire: the last arriver sees the other slices' sums
+          unsigned before;
+          asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(before) : "l"(p.counters + rg) : "memory");
+          flag = (before == unsigned(P.n_ks - 1));
+        }
+        __syncthreads();
+        final_writer = flag != 0;
+        if (final_writer) {  // the last slice to arrive adds all slices in slice order
+          for (int r = t; r < nrows; r += PS_THREADS) {
+            const int rtl = r >> 5, l = r & 31;
+            const float *scr = p.scratch + (rt_a + rtl) * TILE_ROWS + l;
+            float tot = 0.0f;
+            for (int k = 0; k < P.n_ks; ++k) tot += __ldcg(scr + size_t(k) * mp);
+            finish_row(rtl, l, tot);
+          }
+          if (t == 0) p.counters[rg] = 0u;
+        }
+        __syncthreads();
+      }
+      if (P.sumsq_out && nrt > 0 && final_writer) {  // uniform over the CTA
+        my_ss = block_sum(my_ss, red);
+        if (t == 0) P.sumsq_out[rg] = my_ss;
+      } else if (P.sumsq_out && nrt == 0 && ks == 0 && t == 0) {
+        P.sumsq_out[rg] = 0.0f;  // a row group without rows (fewer row-tiles than groups): the slot may hold an older phase's value
+      }
     } else {
       if (ph > 0 && !ps_wait(p, ph - 1, &flag)) return;
       stamp(ph, 1);
@@ -470,29 +508,27 @@ __global__ void __launch_bounds__(PS_THREADS, 2) k_decode_step(const __grid_cons
 
 // ---- host side ------------------------------------------------------------------------------------------
 
-// K slices of a GEMV phase: a divisor of the grid size (every CTA serves one slice, the warps that
-// serve a slice take its row-tiles round-robin), chosen by a cost estimate in microseconds:
-// staging and converting the slice's activations + streaming at the HBM rate, or at the rate the
-// busy warps' register rings sustain when there are fewer chunks than warps, stretched by the
-// round-robin's quantisation + the trip through scratch when K is split.
-int choose_k_slices(int grid, int rt_total, int bpr, size_t tile_b, int nslot) {
+// K slices of a GEMV phase: a divisor of the grid size (so that K slices x row groups = grid),
+// chosen by a cost estimate in microseconds: prologue of the slice + the longest warp's units at
+// an SM's share of the HBM bandwidth + the trip through scratch when K is split.
+int choose_k_slices(int grid, int rt_total, int bpr, size_t tile_b) {
   int best = 0;
   double best_cost = 1e30;
   const char *force = std::getenv("LMB_PERSIST_KSLICES");  // tuning: largest K split allowed
   const int cap = force ? std::max(1, std::atoi(force)) : 16;
-  const double bytes = double(rt_total) * bpr * double(tile_b);
   for (int n_ks = 1; n_ks <= 16 && n_ks <= bpr; ++n_ks) {
     if (grid % n_ks) continue;
     if (n_ks > cap && best > 0) continue;
     const int S = (bpr + n_ks - 1) / n_ks;
     if (S > PS_S_MAX) continue;
-    const int wps = grid / n_ks * PS_WARPS;  // warps per slice
-    const double busy = double(std::min(wps, rt_total)) * n_ks;
-    const double per_warp_gbs = double(nslot) * double(tile_b) / 1.0e3;  // a ring of nslot row-blocks per microsecond of latency
-    const double rate = std::min(6.0e3, busy * per_warp_gbs / 1.0e3);    // GB/s -> bytes per microsecond / 1e3
-    const double rounds = double((rt_total + wps - 1) / wps), even = std::max(1.0, double(rt_total) / wps);
-    const double cost = 1.2 + 0.25 * double((S + PS_WARPS - 1) / PS_WARPS) + bytes / (rate * 1.0e3) * (rounds / even) +
-                        (n_ks > 1 ? 1.5 : 0.3) + 0.01 * n_ks;
+    const int n_rg = grid / n_ks;
+    const int nrt = (rt_total + n_rg - 1) / n_rg;
+    if (nrt > PS_NRT_MAX) continue;
+    const int slots = std::min(PS_WARPS, (PS_WARPS + std::max(1, rt_total / n_rg) - 1) / std::max(1, rt_total / n_rg) + 1);
+    if (nrt * slots > PS_MAX_SEG) continue;
+    const double per_warp = double((nrt * S + PS_WARPS - 1) / PS_WARPS);
+    const double cost = 0.4 + 0.35 * double((S + PS_WARPS - 1) / PS_WARPS) + per_warp * 0.79 * double(tile_b) / 2176.0 +
+                        (n_ks > 1 ? 1.5 : 0.0) + 0.01 * n_ks;
     if (cost < best_cost) {
       best_cost = cost;
       best = n_ks;
@@ -545,7 +581,7 @@ int configure_step_kind(int kind, int *ctas_per_sm) {
 struct PersistPlan {
   int kind = -1, grid = 0, n_phases = 0, n_xchg = 0;
   PsPhase *d_phases = nullptr;
-  // [status | barrier[n_phases] | split-K counters[row-tiles]]; everything but the status word is zeroed
+  // [status | barrier[n_phases] | split-K counters[grid]]; everything but the status word is zeroed
   // before each launch.  The status word stays set until the host has read it: steps launched in
   // between leave at their first wait.
   unsigned *d_sync = nullptr;
@@ -614,13 +650,9 @@ static int build_plan(lmb_model *m) {
   const size_t TB = tile_bytes(pl->kind);
   std::vector<PsPhase> ph;
   size_t scratch_floats = 1;
-  // statistics of the hidden state: one partial sum of squares per row-tile of the projection that
-  // produced it, or per CTA of the embedding / reduce phase; two buffers in alternation
-  const size_t ss_slots = std::max<size_t>(size_t(grid), (h + TILE_ROWS - 1) / TILE_ROWS);
-  LMB_CUDA(cudaMalloc(&pl->d_sumsq, size_t(2) * ss_slots * sizeof(float)));
-  LMB_CUDA(cudaMemset(pl->d_sumsq, 0, size_t(2) * ss_slots * sizeof(float)));
-  float *ss[2] = {pl->d_sumsq, pl->d_sumsq + ss_slots};
-  size_t max_rt = size_t(grid);
+  LMB_CUDA(cudaMalloc(&pl->d_sumsq, size_t(2) * grid * sizeof(float)));
+  LMB_CUDA(cudaMemset(pl->d_sumsq, 0, size_t(2) * grid * sizeof(float)));
+  float *ss[2] = {pl->d_sumsq, pl->d_sumsq + grid};
   int cur = 0;  // sumsq buffer that describes the current hidden state
   int n_cur = grid;
   bool ok = true;
@@ -653,7 +685,7 @@ static int build_plan(lmb_model *m) {
     }
     g.rt_total = rt;
     g.bpr = int(ws[0]->bpr);
-    g.n_ks = choose_k_slices(grid, rt, g.bpr, TB, prefetch_depth(pl->kind) + 1);
+    g.n_ks = choose_k_slices(grid, rt, g.bpr, TB);
     if (g.n_ks < 1) {
       ok = false;
       g.n_ks = 1;
@@ -670,7 +702,6 @@ static int build_plan(lmb_model *m) {
       g.n_sumsq_in = n_cur;
     }
     if (g.n_ks > 1) scratch_floats = std::max(scratch_floats, size_t(g.n_ks) * rt * TILE_ROWS);
-    max_rt = std::max(max_rt, size_t(rt));
     if (hidden_out && tp) {  // partial vector to every rank; the reduce phase makes the hidden state
       g.to_peers = 1;
       g.xchg_seq = pl->n_xchg;
@@ -691,7 +722,7 @@ static int build_plan(lmb_model *m) {
     if (hidden_out) {
       cur ^= 1;
       g.sumsq_out = ss[cur];
-      n_cur = rt;
+      n_cur = g.n_rg;
     }
     ph.push_back(g);
   };
@@ -737,7 +768,7 @@ static int build_plan(lmb_model *m) {
     return fail(LMB_ERR_STATE);
   }
   pl->n_phases = int(ph.size());
-  pl->sync_words = 1 + size_t(pl->n_phases) + max_rt;
+  pl->sync_words = 1 + size_t(pl->n_phases) + size_t(grid);
   cudaError_t err = cudaMalloc(&pl->d_phases, ph.size() * sizeof(PsPhase));
   if (err == cudaSuccess) err = cudaMemcpy(pl->d_phases, ph.data(), ph.size() * sizeof(PsPhase), cudaMemcpyHostToDevice);
   if (err == cudaSuccess) err = cudaMalloc(&pl->d_sync, pl->sync_words * sizeof(unsigned));

@@ -16,16 +16,20 @@ SMALL = dict(hidden=512, inter=2048, n_heads=16, n_kv_heads=8, head_dim=128, n_l
 WIDE = dict(hidden=8192, inter=8192, n_heads=64, n_kv_heads=8, head_dim=128, n_layers=1, vocab=1024)
 STEPS2 = ((3, 9), (100, 4), (7, 7), (500, 1))
 
-# name, kind name, LMB_TP_PEERS, shape overrides, batch, token ids per step, sequences rank 0 checks
+STEPS1 = ((3,), (100,), (7,), (500,))
+# name, kind name, LMB_TP_PEERS, LMB_MODEL_PERSISTENT, shape overrides, batch, token ids per step, sequences rank 0 checks
 CASES = (
-    ("int4", "INT4", "1", SMALL, 2, STEPS2, (0, 1)),
-    ("ternary", "TERNARY", "1", SMALL, 2, STEPS2, (0, 1)),
-    ("int4_nccl", "INT4", "0", SMALL, 2, STEPS2, (0, 1)),
+    ("int4", "INT4", "1", "0", SMALL, 2, STEPS2, (0, 1)),
+    ("ternary", "TERNARY", "1", "0", SMALL, 2, STEPS2, (0, 1)),
+    ("int4_nccl", "INT4", "0", "0", SMALL, 2, STEPS2, (0, 1)),
+    # batch 1, one launch per projection, partial vectors through peer memory
+    ("int4_batch_1", "INT4", "1", "0", SMALL, 1, STEPS1, (0,)),
     # batch 1: embedding, all layers and the exchanges between the ranks inside one persistent kernel
-    ("int4_batch_1", "INT4", "1", SMALL, 1, ((3,), (100,), (7,), (500,)), (0,)),
-    ("int2_batch_1", "INT2", "1", SMALL, 1, ((3,), (100,), (7,), (500,)), (0,)),
-    ("ternary_hidden_8192", "TERNARY", "1", WIDE, 1, ((3,), (900,), (77,)), (0,)),
-    ("ternary_batch_16", "TERNARY", "1", SMALL, 16, None, (0, 7, 15)),
+    ("int4_batch_1_persistent", "INT4", "1", "1", SMALL, 1, STEPS1, (0,)),
+    ("int2_batch_1_persistent", "INT2", "1", "1", SMALL, 1, STEPS1, (0,)),
+    ("ternary_hidden_8192", "TERNARY", "1", "0", WIDE, 1, ((3,), (900,), (77,)), (0,)),
+    ("ternary_hidden_8192_persistent", "TERNARY", "1", "1", WIDE, 1, ((3,), (900,), (77,)), (0,)),
+    ("ternary_batch_16", "TERNARY", "1", "0", SMALL, 16, None, (0, 7, 15)),
 )
 
 
@@ -39,9 +43,10 @@ def main():
     ctx = Context(local)
     tp.init_tp(ctx, dist, peer_floats=16 * 8192)
     out = {}
-    for name, kind_name, peers, over, batch, steps, check in CASES:
+    for name, kind_name, peers, persistent, over, batch, steps, check in CASES:
         kind = getattr(blocks, kind_name)
-        os.environ["LMB_TP_PEERS"] = peers  # read when the model is created
+        os.environ["LMB_TP_PEERS"] = peers  # both are read when the model is created
+        os.environ["LMB_MODEL_PERSISTENT"] = persistent
         spec = synth.model_spec(synth.tiny_model_shape(**over), kind, seed=7, max_seq=32)
         if steps is None:
             rng = np.random.default_rng(5)

@@ -18,8 +18,12 @@ CASES = [("int4", INT4, {}), ("ternary", TERNARY, {}), ("int2_bias", INT2, {"qkv
          ("int8", INT8, {"n_kv_heads": 1})]
 
 
+@pytest.mark.parametrize("persistent", ["0", "1"])
 @pytest.mark.parametrize("name,kind,over", CASES)
-def test_forward_matches_reference_fixtures(ctx, name, kind, over):
+def test_forward_matches_reference_fixtures(ctx, name, kind, over, persistent, monkeypatch):
+    """Both forms of the batch-1 step: one launch per projection (0) and embedding + all layers as
+    one persistent kernel (1)."""
+    monkeypatch.setenv("LMB_MODEL_PERSISTENT", persistent)
     g = np.load(os.path.join(GOLD, "model.npz"))
     spec = synth.model_spec(synth.tiny_model_shape(**over), kind, seed=11, max_seq=2048)
     m = Model(spec, ctx)
@@ -70,11 +74,11 @@ def test_batched_decode_equals_independent_sequences(ctx, oracle):
 @pytest.mark.parametrize("env", [{"LMB_MODEL_PERSISTENT": "0"}, {"LMB_MODEL_PERSISTENT": "0", "LMB_MODEL_FUSED": "0"},
                                  {"LMB_MODEL_PERSISTENT": "0", "LMB_MODEL_GRAPH": "0"},
                                  {"LMB_MODEL_PERSISTENT": "0", "LMB_MODEL_FUSED": "0", "LMB_MODEL_GRAPH": "0"},
-                                 {"LMB_ATTN_GROUP": "0"}, {"LMB_MODEL_PERSISTENT": "0", "LMB_ATTN_GROUP": "0"}])
+                                 {"LMB_MODEL_PERSISTENT": "1", "LMB_ATTN_GROUP": "0"}, {"LMB_MODEL_PERSISTENT": "0", "LMB_ATTN_GROUP": "0"}])
 def test_unfused_and_ungraphed_steps_match_the_fixtures(ctx, env, monkeypatch):
-    """Batch 1 normally runs as one persistent kernel; with LMB_MODEL_PERSISTENT=0 the step is one
-    launch per projection, which can in turn run without norm/activation fusion (the sequence
-    batched tensor-parallel runs use) and without graph capture.  LMB_ATTN_GROUP=0 selects the
+    """With LMB_MODEL_PERSISTENT=0 the step is one launch per projection, which can in turn run
+    without norm/activation fusion (the sequence batched tensor-parallel runs use) and without
+    graph capture; with 1, batch 1 runs as one persistent kernel.  LMB_ATTN_GROUP=0 selects the
     attention form with one CTA per query head instead of one per KV head, in either kind of step.
     The switches are read when the model is created."""
     for k, v in env.items():
@@ -130,13 +134,14 @@ def test_batch_size_changes_on_a_graphed_model(oracle):
     own.close()
 
 
-def test_persistent_step_wait_expires_and_reports(ctx):
+def test_persistent_step_wait_expires_and_reports(ctx, monkeypatch):
     """The CTAs of the persistent decode step wait for each other through arrival counters.  Here
     every wait expects one arrival more than there are CTAs and polls only 200 times: the first
     wait runs out, the kernel records the phase and returns by itself, the step reports
     LMB_ERR_TIMEOUT, and the same model decodes correctly again afterwards."""
     from lutmac_b200 import _lib
     from lutmac_b200._lib import LutmacError
+    monkeypatch.setenv("LMB_MODEL_PERSISTENT", "1")
     g = np.load(os.path.join(GOLD, "model.npz"))
     spec = synth.model_spec(synth.tiny_model_shape(), INT4, seed=11, max_seq=2048)
     m = Model(spec, ctx)

@@ -31,7 +31,8 @@ def test_tensor_parallel_decode_matches_oracle(world):
     line = [l for l in r.stdout.splitlines() if l.startswith("TP_RESULT ")][-1]
     res = json.loads(line[len("TP_RESULT "):])
     print(f"tensor parallel over {world} GPUs, logits rel L2 vs the oracle of the unsharded model: {res}")
-    assert set(res) == {"int4", "ternary", "int4_nccl", "int4_batch_1", "int2_batch_1", "ternary_hidden_8192", "ternary_batch_16"}
+    assert set(res) == {"int4", "ternary", "int4_nccl", "int4_batch_1", "int4_batch_1_persistent", "int2_batch_1_persistent",
+                        "ternary_hidden_8192", "ternary_hidden_8192_persistent", "ternary_batch_16"}
     for name, err in res.items():
         assert err < 1e-5, (name, err)
 
