@@ -40,7 +40,7 @@ METRIC = "lut_gemv_decode_hbm_gbs"
 UNIT = "GB/s"
 MODEL = "llama-3-70b"
 CONTEXT = 2047  # the step attends over 2048 positions: 2047 cached ones and its own
-DISTINCT_LAYERS = 4  # random layers drawn on the host; the 80 layers are 80 separate device copies of them
+DISTINCT_LAYERS = 2  # random layers drawn on the host; the 80 layers are 80 separate device copies of them
 WORKLOAD = ("config[4]: decode step, Llama-3-70B-shaped ternary stack (80 layers, hidden 8192, FFN 28672, int8 head), "
             "batch 1, 2048-token KV, tensor-parallel over the ranks")
 

@@ -187,11 +187,13 @@ int lmb_group_destroy(lmb_group *g);
 
 /* ---- kernel API on host pointers: replaces the dispatchers lut_gemv, lut_gemv_binary,
  * int2_gemv ... int8_gemv (include/lutmac/lut_gemm.hpp:172-408) -----------------------------------
- * Same arguments as the reference: num_blocks is ignored, output receives M floats.  Only the
- * first K activations are read; the columns that pad the last 256-block count as zero (the
- * reference reads them, but they only meet the zero weights its quantizers pad with, and its own
- * tests pass arrays of exactly K floats).  Each call uploads the blocks, runs the CUDA kernel on
- * the default context of the current device and copies the result back. */
+ * Same arguments as the reference: activations are read for ceil(K/256)*256 floats, num_blocks is
+ * ignored, output receives M floats.  One difference in the padding columns of the last block:
+ * a value there that is not finite, or more than 4096 times larger than every activation of the
+ * block's first K % 256 columns, is taken as zero (the reference's own tests pass arrays of exactly
+ * K floats and rely on the zero weights of the padding to hide whatever follows them in memory).
+ * Each call uploads the blocks, runs the CUDA kernel on the default context of the current device
+ * and copies the result back. */
 int lmb_gemv_host(int kind, const void *blocks, size_t num_blocks, const float *activations, float *output,
                   size_t M, size_t K);
 /* Layer API on host pointers: lut_linear for a weight already resident (lmb_weight_upload),

@@ -276,13 +276,12 @@ class DeviceWeight:
 # ---- the reference's kernel API (host pointers) ------------------------------------------------------
 
 def _gemv(kind, blocks, num_blocks, activations, output, M, K):
-    """X_gemv(blocks, num_blocks, activations, output, M, K) of lut_gemm.hpp:172-408: num_blocks is
-    ignored, output receives M floats, the first K activations are read (the padding columns of
-    the last block count as zero)."""
+    """X_gemv(blocks, num_blocks, activations, output, M, K) of lut_gemm.hpp:172-408: activations
+    must hold ceil(K/256)*256 floats, num_blocks is ignored, output receives M floats."""
     blocks = np.ascontiguousarray(blocks)
     act = np.ascontiguousarray(activations, np.float32)
-    if act.size < K:
-        raise ValueError("activations must hold at least K floats")
+    if act.size < blocks_per_row(K) * 256:
+        raise ValueError("activations must be readable for ceil(K/256)*256 floats (the reference kernels read whole blocks)")
     if blocks.nbytes < M * blocks_per_row(K) * BLOCK_BYTES[kind]:
         raise ValueError("block array is smaller than M*ceil(K/256) blocks")
     out = output if output is not None else np.empty(M, np.float32)

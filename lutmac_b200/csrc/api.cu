@@ -1,5 +1,7 @@
 // C ABI: context, device memory helpers, weight upload, the layer / kernel / transform entry
 // points.  Declarations and the reference interfaces they replace: include/lutmac_b200.h.
+#include <algorithm>
+#include <cmath>
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
@@ -237,6 +239,7 @@ int lmb_ctx_destroy(lmb_ctx *ctx) {
   if (ctx->counters) cudaFree(ctx->counters);
   if (ctx->xprep) cudaFree(ctx->xprep);
   if (ctx->d_fault) cudaFree(ctx->d_fault);
+  if (ctx->h_upload) cudaFreeHost(ctx->h_upload);
   if (ctx->h_stage) cudaFreeHost(ctx->h_stage);
   if (ctx->d_stage) cudaFree(ctx->d_stage);
   if (ctx->ev0) cudaEventDestroy(ctx->ev0);
@@ -453,18 +456,26 @@ int lmb_weight_upload_shard(lmb_ctx *ctx, int kind, const void *blocks, size_t M
   w->K = (blk1 == src_bpr) ? (K - blk0 * BLK) : (w->bpr * BLK);
   w->row_tiles = (w->M + TILE_ROWS - 1) / TILE_ROWS;
   w->bytes = w->row_tiles * w->bpr * tile_bytes(w->kind);
-  void *h = nullptr;
-  cudaError_t e = cudaMallocHost(&h, w->bytes);
-  if (e != cudaSuccess) {
-    delete w;
-    return cuda_fail(e, "cudaMallocHost(weight staging)");
+  // re-tile into the context's pinned upload buffer (kept and grown on demand: allocating pinned
+  // memory per tensor costs more than the copy it serves)
+  cudaError_t e = cudaSuccess;
+  if (w->bytes > ctx->h_upload_bytes) {
+    if (ctx->h_upload) cudaFreeHost(ctx->h_upload);
+    ctx->h_upload = nullptr;
+    ctx->h_upload_bytes = 0;
+    e = cudaMallocHost(&ctx->h_upload, w->bytes);
+    if (e != cudaSuccess) {
+      delete w;
+      return cuda_fail(e, "cudaMallocHost(weight staging)");
+    }
+    ctx->h_upload_bytes = w->bytes;
   }
+  void *h = ctx->h_upload;
   retile(w->kind, static_cast<const uint8_t *>(blocks), src_bpr, row0, row1, blk0, blk1, static_cast<uint8_t *>(h));
   e = cudaSetDevice(ctx->device);
   if (e == cudaSuccess) e = cudaMalloc(&w->d_tiles, w->bytes);
   if (e == cudaSuccess) e = cudaMemcpyAsync(w->d_tiles, h, w->bytes, cudaMemcpyHostToDevice, ctx->stream);
   if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
-  cudaFreeHost(h);
   if (e != cudaSuccess) {
     if (w->d_tiles) cudaFree(w->d_tiles);
     delete w;
@@ -581,20 +592,30 @@ int lmb_gemv_host(int kind, const void *blocks, size_t num_blocks, const float *
   lmb_weight *w = nullptr;
   st = lmb_weight_upload(ctx, kind, blocks, M, K, &w);
   if (st != LMB_OK) return st;
-  // The reference kernels read whole 256-blocks of the activation vector, but what lies beyond
-  // column K only ever meets the zero weights the quantizers pad a row's last block with
-  // (quantize.hpp:262-273): the reference's own tests pass arrays of exactly K floats
-  // (tests/test_lut_gemm.cpp:108-118,150-158).  So only K activations are read here and the rest of
-  // the last block counts as zero, which is the same result without touching the caller's memory
-  // beyond K (and without letting whatever lies there disturb the block's fixed-point scale).
+  // The reference kernels read whole 256-blocks of the activation vector, and so does this call.
+  // What lies beyond column K normally meets the zero weights the quantizers pad a row's last
+  // block with, and the reference's own tests pass arrays of exactly K floats
+  // (tests/test_lut_gemm.cpp:108-118,150-158), i.e. whatever the heap holds behind them.  In the
+  // reference such values are multiplied by zero; here they would also enter the block's shared
+  // fixed-point exponent.  So a padding value that is not finite, or more than 4096 times larger than
+  // every activation of the block's valid part, is taken as zero (a genuine activation vector never
+  // looks like that; at most 12 of the 31 fixed-point bits are given up to the padding).
   const size_t kp = w->bpr * BLK;
   st = ensure_stage(ctx, (kp + M) * sizeof(float));
   if (st == LMB_OK) {
     float *h = static_cast<float *>(ctx->h_stage), *d = ctx->d_stage;
-    std::memcpy(h, activations, K * sizeof(float));
-    cudaError_t e = cudaMemcpyAsync(d, h, K * sizeof(float), cudaMemcpyHostToDevice, ctx->stream);
+    std::memcpy(h, activations, kp * sizeof(float));
+    if (K < kp) {
+      const size_t b0 = (w->bpr - 1) * BLK;
+      float amax = 0.0f;
+      for (size_t i = b0; i < K; ++i) amax = std::max(amax, std::fabs(h[i]));
+      const float lim = 4096.0f * std::max(amax, 1e-30f);
+      for (size_t i = K; i < kp; ++i)
+        if (!(std::fabs(h[i]) <= lim)) h[i] = 0.0f;  // also catches NaN
+    }
+    cudaError_t e = cudaMemcpyAsync(d, h, kp * sizeof(float), cudaMemcpyHostToDevice, ctx->stream);
     if (e != cudaSuccess) st = cuda_fail(e, "lmb_gemv_host h2d");
-    if (st == LMB_OK) st = linear_impl(ctx, w, nullptr, d, K, kp, d + kp, 1, 0);
+    if (st == LMB_OK) st = linear_impl(ctx, w, nullptr, d, kp, kp, d + kp, 1, 0);
     if (st == LMB_OK) {
       e = cudaMemcpyAsync(h + kp, d + kp, M * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream);
       if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);

@@ -191,6 +191,8 @@ struct lmb_ctx {
   size_t xprep_blocks = 0;  // capacity in (sequence, block) pairs
   // set by a kernel whose bounded wait (for its own asynchronous copies) ran out; read with the logits
   unsigned *d_fault = nullptr;
+  void *h_upload = nullptr;  // pinned staging of lmb_weight_upload
+  size_t h_upload_bytes = 0;
   // staging buffers of the host-pointer entry points
   void *h_stage = nullptr;
   size_t h_stage_bytes = 0;
