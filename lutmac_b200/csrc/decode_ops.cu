@@ -121,6 +121,13 @@ __global__ void __launch_bounds__(ATT_THREADS) k_decode_attn_group(const AttnArg
     *timed_out = 1u;
 }
 
+__global__ void k_interleave_rows(const float *src, float *dst, size_t ranks, size_t batch, size_t n) {
+  const size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x, total = ranks * batch * n;
+  if (i >= total) return;
+  const size_t r = i / (batch * n), b = (i / n) % batch, j = i % n;
+  dst[b * ranks * n + r * n + j] = src[i];
+}
+
 __global__ void k_silu_mul(const float *gate, const float *up, float *out, size_t n, int gelu) {
   asm volatile("griddepcontrol.launch_dependents;");  // a following GEMV may prefetch its weights
   const size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -231,6 +238,14 @@ int launch_decode_attn_group(lmb_ctx *ctx, const float *q, const float *k, const
   unsigned *flag = ctx->d_fault;  // set when a bounded wait for the bulk copies runs out
   if (plan.per == 4) k_decode_attn_group<4><<<grid, ATT_THREADS, plan.smem_bytes, ctx->stream>>>(a, d, ctx->xchg.spin_limit, flag);
   else k_decode_attn_group<2><<<grid, ATT_THREADS, plan.smem_bytes, ctx->stream>>>(a, d, ctx->xchg.spin_limit, flag);
+  ctx->launches++;
+  LMB_CUDA(cudaGetLastError());
+  return LMB_OK;
+}
+
+int launch_interleave_rows(lmb_ctx *ctx, const float *src, float *dst, size_t ranks, size_t batch, size_t n) {
+  const size_t total = ranks * batch * n;
+  k_interleave_rows<<<unsigned((total + 255) / 256), 256, 0, ctx->stream>>>(src, dst, ranks, batch, n);
   ctx->launches++;
   LMB_CUDA(cudaGetLastError());
   return LMB_OK;

@@ -40,6 +40,8 @@ int launch_decode_attn_group(lmb_ctx *ctx, const float *q, const float *k, const
                              float *partial, unsigned *counters, const AttnGroupPlan &plan, size_t layer, const RopeDims &d,
                              size_t batch);
 size_t attn_partial_floats(size_t batch, size_t nh, size_t hd);  // scratch both attention forms fit in
+// dst[b][r * n + i] = src[r][b][i]: the gathered per-rank logits slabs into rows of the full vocabulary
+int launch_interleave_rows(lmb_ctx *ctx, const float *src, float *dst, size_t ranks, size_t batch, size_t n);
 int launch_silu_mul(lmb_ctx *ctx, const float *gate, const float *up, float *out, size_t n, bool gelu = false);
 
 }  // namespace lmb

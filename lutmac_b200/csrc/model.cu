@@ -307,6 +307,7 @@ int lmb_model_create(lmb_ctx *ctx, const lmb_model_config *c, lmb_model **out) {
   A(&m->v, B * m->nkv * hd); A(&m->att, B * m->nh * hd); A(&m->proj, B * h); A(&m->gate, B * m->inter);
   A(&m->up, B * m->inter); A(&m->act, B * m->inter); A(&m->logits, B * c->vocab_size);
   if (g > 1) A(&m->logits_local, B * m->vocab_local);
+  if (g > 1 && B > 1) A(&m->logits_gather, B * c->vocab_size);
   A(&m->att_partial, attn_partial_floats(B, m->nh, hd));
   A(reinterpret_cast<float **>(&m->att_counters), B * m->nh);
   A(&m->kv, B * m->seq_stride); A(&m->final_norm, h); A(&m->cs_table, c->max_seq_len * hd);
@@ -355,7 +356,7 @@ int lmb_model_destroy(lmb_model *m) {
   cudaSetDevice(m->ctx->device);
   cudaStreamSynchronize(m->ctx->stream);
   float *bufs[] = {m->hidden, m->normed, m->q, m->k, m->v, m->att, m->proj, m->gate, m->up, m->act, m->logits,
-                   m->logits_local, m->kv, m->final_norm, m->cs_table, m->att_partial,
+                   m->logits_local, m->logits_gather, m->kv, m->final_norm, m->cs_table, m->att_partial,
                    reinterpret_cast<float *>(m->att_counters)};
   for (float *b : bufs) if (b) cudaFree(b);
   for (auto &L : m->layers) {
@@ -710,8 +711,14 @@ int lmb_model_forward(lmb_model *m, const int *token_ids, const size_t *position
   if (st != LMB_OK) return st;
   if (c.tp_size > 1) {
     st = gemv1(m, m->lm_head, m->head_rot, m->normed, h, m->logits_local, batch);
-    for (size_t b = 0; b < batch && st == LMB_OK; ++b)
-      st = lmb_allgather(ctx, m->logits_local + b * m->vocab_local, m->logits + b * c.vocab_size, m->vocab_local);
+    if (st == LMB_OK && batch == 1) {
+      st = lmb_allgather(ctx, m->logits_local, m->logits, m->vocab_local);
+    } else if (st == LMB_OK) {
+      // ONE all-gather per step: every rank's [batch][vocab / ranks] slab into [rank][batch][vocab / ranks],
+      // then the rows are put in place ([batch][vocab]) by a copy kernel
+      st = lmb_allgather(ctx, m->logits_local, m->logits_gather, batch * m->vocab_local);
+      if (st == LMB_OK) st = launch_interleave_rows(ctx, m->logits_gather, m->logits, size_t(c.tp_size), batch, m->vocab_local);
+    }
   } else {
     st = gemv1(m, m->lm_head, m->head_rot, m->normed, h, m->logits, batch);
   }

@@ -26,7 +26,7 @@ struct lmb_model {
   std::vector<LayerW> layers;
   // activations [max_batch][...]
   float *hidden = nullptr, *normed = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *att = nullptr, *proj = nullptr,
-        *gate = nullptr, *up = nullptr, *act = nullptr, *logits = nullptr, *logits_local = nullptr;
+        *gate = nullptr, *up = nullptr, *act = nullptr, *logits = nullptr, *logits_local = nullptr, *logits_gather = nullptr;
   float *att_partial = nullptr;      // [max_batch][nh][32 splits][hd + 2]
   unsigned *att_counters = nullptr;  // [max_batch][nh]
   float *kv = nullptr;        // [max_batch][L][2][nkv][max_seq][hd]: the positions of one head contiguous
