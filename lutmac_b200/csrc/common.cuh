@@ -226,7 +226,20 @@ struct LinearArgs {
   const float *x2 = nullptr;        // norm weight (XMODE_RMSNORM) or the vector multiplied in (XMODE_SILU_MUL, XMODE_GELU_MUL)
   const float *residual = nullptr;  // added to the output (same layout as y; may alias y)
   bool to_peers = false;            // deliver y into every rank's exchange block instead (single-job launches)
+  // Hand-off of prepared activations between two batch-1 GEMVs (integer tensor-core kinds).  Producer
+  // side: next_prep / next_sumsq receive, per 256-block of this GEMV's output, the record the next
+  // GEMV's CTAs would otherwise each compute (output x next_w, rotated if next_rotate, as fixed-point
+  // digits) and the block's sum of squares.  Consumer side: prep_in / prep_sumsq_in (prep_sumsq_n
+  // blocks) replace x; with prep_sumsq_in the vector is RMS-normalised by the total.
+  uint32_t *next_prep = nullptr;
+  float *next_sumsq = nullptr;
+  const float *next_w = nullptr;
+  bool next_rotate = false;
+  const uint32_t *prep_in = nullptr;
+  const float *prep_sumsq_in = nullptr;
+  int prep_sumsq_n = 0;
 };
+constexpr int PREP_RECORD_WORDS = 256 + 4;  // one prepared 256-block: digits, block scale, two digit-pair sums, pad
 // How the GEMV prologue forms its activations from x.
 enum { XMODE_PLAIN = 0, XMODE_RMSNORM = 1, XMODE_SILU_MUL = 2, XMODE_GELU_MUL = 3 };
 int configure_gemv(lmb_ctx *ctx);

@@ -58,10 +58,18 @@ struct Job {
   int R, S, n_rg, n_ks;
   int cta_end;          // exclusive prefix of CTAs over the jobs of the launch
   unsigned x_len, x_stride, y_stride;
+  // Hand-off to the next projection (batch 1, R = 8: a row group is one 256-block of the output):
+  // the CTA that completes a row group also prepares that block as the NEXT GEMV's activation --
+  // times the next norm's weight, rotated, as fixed-point digits -- so that the consumer's CTAs copy
+  // records instead of each converting the whole vector.  next_prep null: off.
+  uint32_t *next_prep;      // [block] records of PREP_WORDS words
+  float *next_sumsq;        // [block] sum of squares of the block's outputs (the consumer's RMSNorm statistic)
+  const float *next_w;      // weight of the norm between this projection and the next (null: none)
+  int next_rotate;
 };
 
 // One prepared (sequence, block): 256 words of digits in B-operand order, block scale, two digit-pair sums, pad.
-constexpr int PREP_WORDS = 256 + 4;
+constexpr int PREP_WORDS = PREP_RECORD_WORDS;
 
 struct GemvParams {
   Job job[MAX_JOBS];
@@ -78,6 +86,10 @@ struct GemvParams {
   // activations already converted by k_prepare_x (batched launches whose jobs share one input):
   // [sequence][block] records of PREP_WORDS words; null: every CTA converts its own slice
   const uint32_t *prep;
+  // with `prep` from a producer's hand-off: the partial sums of squares whose total normalises the
+  // prepared vector (RMSNorm is linear in that scalar, so it is applied to the block scales); null: none
+  const float *prep_sumsq;
+  int prep_sumsq_n;
 };
 
 template <int KIND, int NSEQ>
@@ -166,19 +178,25 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
   }
   if constexpr (kind_is_mma(KIND)) {
     if (p.prep) {
-      // the launch's activations were converted once by k_prepare_x: copy this CTA's slice
+      float prep_scale = 1.0f;
+      if (p.prep_sumsq) {  // src/layers/norm.cpp:18-34 with the sum of squares from the producer's per-block partials
+        float tot = 0.0f;
+        for (int i = 0; i < p.prep_sumsq_n; ++i) tot += __ldcg(p.prep_sumsq + i);
+        prep_scale = 1.0f / sqrtf(tot / float(job.x_len) + p.eps);
+      }
+      // the launch's activations were converted once (k_prepare_x, or the producing GEMV): copy this CTA's slice
       const int items = ns * nb;
       for (int it = warp; it < items; it += WARPS) {
         const int q = NSEQ == 1 ? 0 : it / ns, bl = it - q * ns;
         const uint32_t *src = p.prep + (size_t(batch0 + q) * job.bpr + b0 + bl) * PREP_WORDS;
         uint4 *dst = reinterpret_cast<uint4 *>(smem + (size_t(q) * job.S + bl) * FPB);
         const uint4 *s4 = reinterpret_cast<const uint4 *>(src);
-        dst[lane] = __ldg(s4 + lane);
-        dst[lane + 32] = __ldg(s4 + lane + 32);
+        dst[lane] = __ldcg(s4 + lane);
+        dst[lane + 32] = __ldcg(s4 + lane + 32);
         if (lane == 0) {
-          const uint4 tail = __ldg(s4 + 64);  // {block scale, d01, d23, -}
+          const uint4 tail = __ldcg(s4 + 64);  // {block scale, d01, d23, -}
           int *aux = xaux + ((q >> 1) * 64 + bl) * 4;
-          xsum[q * 64 + bl] = __uint_as_float(tail.x);
+          xsum[q * 64 + bl] = __uint_as_float(tail.x) * prep_scale;
           aux[2 * (q & 1)] = int(tail.y);
           aux[2 * (q & 1) + 1] = int(tail.z);
           if ((q | 1) >= nb) aux[2] = aux[3] = 0;
@@ -293,6 +311,44 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
       for (int r = 0; r < p.peer.n; ++r) *reinterpret_cast<volatile unsigned long long *>(p.peer.data[r] + slot) = word;
     }
   };
+  // Hand-off (see Job::next_prep): thread t of the CTA that completes the row group holds output
+  // 256 * rg + t; one warp turns the block into the next GEMV's prepared activation record.
+  float handoff = 0.0f;  // this thread's finished output (first sequence), 0 beyond M
+  auto hand_off = [&]() {
+    if (NSEQ != 1 || !job.next_prep) return;  // uniform over the CTA
+    __syncthreads();
+    part[0][t] = handoff;
+    __syncthreads();
+    if (warp == 0) {
+      float v[8];
+      float ss = 0.0f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        v[e] = part[0][lane * 8 + e];
+        ss += v[e] * v[e];
+      }
+#pragma unroll
+      for (int m = 16; m > 0; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
+      if (job.next_w) {
+        float w8[8];
+        load_x8(job.next_w, size_t(job.M), size_t(rg), lane, w8);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] *= w8[e];
+      }
+      if (job.next_rotate) fwht256_warp(v, lane);
+      float *stage = smem;  // the activation digits of this launch are no longer needed by this CTA
+      mma_prologue(v, lane, stage, &xsum[0], &xaux[0]);
+      __syncwarp();
+      uint4 *dst = reinterpret_cast<uint4 *>(job.next_prep + size_t(rg) * PREP_WORDS);
+      const uint4 *src = reinterpret_cast<const uint4 *>(stage);
+      dst[lane] = src[lane];
+      dst[lane + 32] = src[lane + 32];
+      if (lane == 0) {
+        dst[64] = make_uint4(__float_as_uint(xsum[0]), uint32_t(xaux[0]), uint32_t(xaux[1]), 0u);
+        job.next_sumsq[rg] = ss;
+      }
+    }
+  };
   if (job.n_ks == 1) {
     if (owns_row && row < job.M) {
       const float bias = job.bias ? job.bias[row] : 0.0f;
@@ -303,8 +359,10 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
           if (job.bias) o += bias;
           if (job.residual) o += job.residual[size_t(batch0 + q) * job.y_stride + row];
           emit(q, o);
+          if (q == 0) handoff = o;
         }
     }
+    hand_off();
     return;
   }
   // split K: publish the partial sums, the last slice to arrive adds them in slice order
@@ -333,9 +391,11 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
         if (job.bias) tot += bias;
         if (job.residual) tot += job.residual[size_t(batch0 + q) * job.y_stride + row];
         emit(q, tot);
+        if (q == 0) handoff = tot;
       }
   }
   if (t == 0) *ctr = 0u;  // ready for the next launch
+  hand_off();
 }
 
 // Conversion pass for batched launches: the activations of every (sequence, block) of the shared
@@ -418,7 +478,8 @@ int ctas_per_sm(int kind) { return kind_info(kind).lut ? 3 : 2; }
 // of "one warp evaluates one 256-column block":
 //     waves of CTAs x (blocks per warp + prologue share + fixed CTA cost [+ split-K hand-off]).
 // `other_row_tiles` are the row-tiles of the other jobs of the same launch.
-Plan make_plan(int kind, size_t row_tiles, size_t bpr, size_t batch, int sm_count, size_t other_row_tiles = 0, int nseq = 1) {
+Plan make_plan(int kind, size_t row_tiles, size_t bpr, size_t batch, int sm_count, size_t other_row_tiles = 0, int nseq = 1,
+               bool whole_blocks = false) {
   const bool lut = kind_info(kind).lut;
   // 48 KiB of tables / activations per CTA (96 KiB when 4 or 8 sequences share a pass)
   const size_t s_cap = lut ? 12 : nseq == 1 ? 48 : nseq == 8 ? 12 : 24;
@@ -428,7 +489,8 @@ Plan make_plan(int kind, size_t row_tiles, size_t bpr, size_t batch, int sm_coun
   Plan best{};
   double best_cost = 1e30;
   for (int R = 8; R >= 1; R >>= 1) {
-    if (size_t(R) > row_tiles && R > 1) continue;
+    if (whole_blocks && R != 8) break;  // a row group must be one 256-block of the output (hand-off to the next GEMV)
+    if (size_t(R) > row_tiles && R > 1 && !whole_blocks) continue;
     const size_t n_rg = (row_tiles + R - 1) / R, wpr = size_t(8 / R);
     for (size_t n_ks = 1; n_ks <= bpr; ++n_ks) {
       const size_t S = (bpr + n_ks - 1) / n_ks;
@@ -478,7 +540,7 @@ int prepare_jobs(lmb_ctx *ctx, int kind, const LinearArgs *args, int njobs, Job 
   for (int j = 0; j < njobs; ++j) {
     const lmb_weight *w = args[j].w;
     const size_t others = total_rt - w->row_tiles;
-    plans[size_t(j)] = make_plan(kind, w->row_tiles, w->bpr, ny, ctx->sm_count, others, nseq);
+    plans[size_t(j)] = make_plan(kind, w->row_tiles, w->bpr, ny, ctx->sm_count, others, nseq, args[j].next_prep != nullptr);
     if (plans[size_t(j)].n_ks > 1) {
       scratch_need += batch * plans[size_t(j)].n_ks * w->row_tiles * TILE_ROWS;
       counter_need += ny * plans[size_t(j)].n_rg;
@@ -520,6 +582,10 @@ int prepare_jobs(lmb_ctx *ctx, int kind, const LinearArgs *args, int njobs, Job 
     jb.y_stride = unsigned(args[j].y_stride);
     jb.scratch = ctx->scratch + scratch_off;
     jb.counters = ctx->counters + counter_off;
+    jb.next_prep = args[j].next_prep;
+    jb.next_sumsq = args[j].next_sumsq;
+    jb.next_w = args[j].next_w;
+    jb.next_rotate = args[j].next_rotate ? 1 : 0;
     if (pl.n_ks > 1) {
       scratch_off += batch * pl.n_ks * jb.mp;
       counter_off += ny * pl.n_rg;
@@ -665,6 +731,18 @@ int launch_gemv(lmb_ctx *ctx, const LinearArgs *args, int njobs, bool rotate, in
   int ctas = 0, s_max = 1;
   int st = prepare_jobs(ctx, kind, args, njobs, p.job, &ctas, &s_max, nullptr);
   if (st != LMB_OK) return st;
+  p.prep_sumsq = nullptr;
+  p.prep_sumsq_n = 0;
+  if (args[0].prep_in) {  // the producing GEMV prepared the activations (batch 1)
+    if (args[0].batch != 1 || !kind_is_mma(kind)) {
+      set_last_error("launch_gemv: prepared activations need batch 1 and an integer tensor-core layout");
+      return LMB_ERR_ARG;
+    }
+    p.prep = args[0].prep_in;
+    p.prep_sumsq = args[0].prep_sumsq_in;
+    p.prep_sumsq_n = args[0].prep_sumsq_n;
+    return launch_params_kind(ctx, kind, p, ctas, s_max, 1);
+  }
   // Batches of three or more sequences whose jobs read one input: convert the activations once
   // for the whole launch instead of once per CTA.
   p.prep = nullptr;
@@ -790,6 +868,8 @@ int lmb_group_launch(lmb_ctx *ctx, lmb_group *g) {
   p.cta_map = g->d_map;
   p.peer.n = 0;
   p.prep = nullptr;
+  p.prep_sumsq = nullptr;
+  p.prep_sumsq_n = 0;
   return launch_params_kind(ctx, g->kind, p, g->ctas, g->s_max, 1);
 }
 
@@ -969,6 +1049,8 @@ int lmb_linear_static_scratch(const lmb_weight *w, const float *d_bias, const fl
   p.cta_map = nullptr;
   p.peer.n = 0;
   p.prep = nullptr;
+  p.prep_sumsq = nullptr;
+  p.prep_sumsq_n = 0;
   Job &jb = p.job[0];
   jb.tiles = w->d_tiles;
   jb.x = d_x;
@@ -976,6 +1058,10 @@ int lmb_linear_static_scratch(const lmb_weight *w, const float *d_bias, const fl
   jb.bias = d_bias;
   jb.x2 = nullptr;
   jb.residual = nullptr;
+  jb.next_prep = nullptr;
+  jb.next_sumsq = nullptr;
+  jb.next_w = nullptr;
+  jb.next_rotate = 0;
   jb.scratch = su.scratch;
   jb.counters = su.counters;
   jb.M = int(w->M);

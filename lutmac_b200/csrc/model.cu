@@ -298,6 +298,8 @@ int lmb_model_create(lmb_ctx *ctx, const lmb_model_config *c, lmb_model **out) {
     m->persistent = sv ? (sv[0] != '0') : PERSISTENT_BY_DEFAULT;
     const char *av = std::getenv("LMB_ATTN_GROUP");
     m->attn_group = !(av && av[0] == '0');
+    const char *hv = std::getenv("LMB_MODEL_HANDOFF");
+    m->handoff = !(hv && hv[0] == '0');
   }
   const size_t B = c->max_batch, h = c->hidden_size, hd = c->head_dim;
   m->seq_stride = c->num_hidden_layers * 2 * c->max_seq_len * m->nkv * hd;
@@ -309,6 +311,10 @@ int lmb_model_create(lmb_ctx *ctx, const lmb_model_config *c, lmb_model **out) {
   if (g > 1) A(&m->logits_local, B * m->vocab_local);
   if (g > 1 && B > 1) A(&m->logits_gather, B * c->vocab_size);
   A(&m->att_partial, attn_partial_floats(B, m->nh, hd));
+  for (int i = 0; i < 2; ++i) {  // hand-off records of the hidden state (batch 1) and their per-block sums of squares
+    A(reinterpret_cast<float **>(&m->prep[i]), (h + BLK - 1) / BLK * PREP_RECORD_WORDS);
+    A(&m->prep_ss[i], (h + BLK - 1) / BLK);
+  }
   A(reinterpret_cast<float **>(&m->att_counters), B * m->nh);
   A(&m->kv, B * m->seq_stride); A(&m->final_norm, h); A(&m->cs_table, c->max_seq_len * hd);
   for (auto &L : m->layers) { A(&L.in_norm, h); A(&L.post_norm, h); }
@@ -357,7 +363,8 @@ int lmb_model_destroy(lmb_model *m) {
   cudaStreamSynchronize(m->ctx->stream);
   float *bufs[] = {m->hidden, m->normed, m->q, m->k, m->v, m->att, m->proj, m->gate, m->up, m->act, m->logits,
                    m->logits_local, m->logits_gather, m->kv, m->final_norm, m->cs_table, m->att_partial,
-                   reinterpret_cast<float *>(m->att_counters)};
+                   reinterpret_cast<float *>(m->att_counters), reinterpret_cast<float *>(m->prep[0]),
+                   reinterpret_cast<float *>(m->prep[1]), m->prep_ss[0], m->prep_ss[1]};
   for (float *b : bufs) if (b) cudaFree(b);
   for (auto &L : m->layers) {
     for (auto *w : L.w) lmb_weight_free(w);
@@ -494,11 +501,30 @@ struct Fuse {
   int xmode = XMODE_PLAIN;
   const float *x2 = nullptr;        // norm weight / multiplied-in vector
   const float *residual = nullptr;  // added to the output
+  // hand-off of prepared activations (LinearArgs): producer side, consumer side
+  uint32_t *next_prep = nullptr;
+  float *next_sumsq = nullptr;
+  const float *next_w = nullptr;
+  bool next_rotate = false;
+  const uint32_t *prep_in = nullptr;
+  const float *prep_sumsq_in = nullptr;
+  int prep_sumsq_n = 0;
 };
+
+void apply_handoff(LinearArgs &a, const Fuse &f) {
+  a.next_prep = f.next_prep;
+  a.next_sumsq = f.next_sumsq;
+  a.next_w = f.next_w;
+  a.next_rotate = f.next_rotate;
+  a.prep_in = f.prep_in;
+  a.prep_sumsq_in = f.prep_sumsq_in;
+  a.prep_sumsq_n = f.prep_sumsq_n;
+}
 
 int gemv1(lmb_model *m, const lmb_weight *w, bool rot, const float *x, size_t x_len, float *y, size_t batch,
           const Fuse &f = Fuse()) {
   LinearArgs a{w, nullptr, x, x_len, x_len, y, w->M, batch, rot, f.x2, f.residual};
+  apply_handoff(a, f);
   return launch_gemv(m->ctx, &a, 1, rot, f.xmode, m->cfg.rms_norm_eps);
 }
 
@@ -509,7 +535,10 @@ int gemv_group(lmb_model *m, int n, lmb_weight *const *ws, const bool *rot, cons
   for (int i = 1; i < n; ++i) same = same && ws[i]->kind == ws[0]->kind && rot[i] == rot[0];
   if (same) {
     LinearArgs a[4];
-    for (int i = 0; i < n; ++i) a[i] = LinearArgs{ws[i], nullptr, x, x_len, x_len, ys[i], ws[i]->M, batch, rot[0], f.x2, nullptr};
+    for (int i = 0; i < n; ++i) {
+      a[i] = LinearArgs{ws[i], nullptr, x, x_len, x_len, ys[i], ws[i]->M, batch, rot[0], f.x2, nullptr};
+      apply_handoff(a[i], f);
+    }
     return launch_gemv(m->ctx, a, n, rot[0], f.xmode, m->cfg.rms_norm_eps);
   }
   for (int i = 0; i < n; ++i) {
@@ -517,6 +546,18 @@ int gemv_group(lmb_model *m, int n, lmb_weight *const *ws, const bool *rot, cons
     if (st != LMB_OK) return st;
   }
   return LMB_OK;
+}
+
+// Whether the producing projections of a batch-1 step may prepare the next projection's
+// activations: whole 256-blocks of hidden state, integer tensor-core layouts everywhere.
+bool handoff_possible(const lmb_model *m) {
+  if (!m->handoff || m->cfg.tp_size != 1 || m->cfg.hidden_size % BLK != 0 || !m->lm_head || !kind_is_mma(m->lm_head->kind)) return false;
+  for (const LayerW &L : m->layers) {
+    for (int i = 0; i < 7; ++i)
+      if (!L.w[i] || !kind_is_mma(L.w[i]->kind)) return false;
+    if (L.rot[0] != L.rot[1] || L.rot[0] != L.rot[2] || L.rot[4] != L.rot[5]) return false;
+  }
+  return true;
 }
 
 }  // namespace
@@ -637,6 +678,13 @@ int lmb_model_forward(lmb_model *m, const int *token_ids, const size_t *position
     // Fused form: RMSNorm rides in the prologue of the projections that consume it, SiLU*up in
     // the prologue of down_proj, the residual adds in the epilogues of o_proj and down_proj
     // (which write the hidden state in place): 6 launches per layer instead of 9.
+    // Hand-off (batch 1): o_proj and down_proj, which complete the hidden state, also prepare it --
+    // block by block, in the CTA that finishes the block -- as the next projections' activations, so
+    // that the CTAs of q/k/v, gate/up and the head copy 1 KiB records instead of each normalising,
+    // rotating and converting the whole vector.
+    const bool ho = batch == 1 && handoff_possible(m);
+    const int hb = int(h / BLK);
+    bool have = false;  // prep[1] holds the prepared hidden state left by the previous layer's down_proj
     for (size_t l = 0; l < m->layers.size() && st == LMB_OK; ++l) {
       LayerW &L = m->layers[l];
       Fuse norm1, norm2, res, act;
@@ -644,6 +692,16 @@ int lmb_model_forward(lmb_model *m, const int *token_ids, const size_t *position
       norm2.xmode = XMODE_RMSNORM; norm2.x2 = L.post_norm;
       res.residual = m->hidden;
       act.xmode = c.activation == LMB_ACT_GELU ? XMODE_GELU_MUL : XMODE_SILU_MUL; act.x2 = m->up; act.residual = m->hidden;
+      if (ho) {
+        if (have) { norm1.prep_in = m->prep[1]; norm1.prep_sumsq_in = m->prep_ss[1]; norm1.prep_sumsq_n = hb; }
+        res.next_prep = m->prep[0]; res.next_sumsq = m->prep_ss[0]; res.next_w = L.post_norm; res.next_rotate = L.rot[4];
+        norm2.prep_in = m->prep[0]; norm2.prep_sumsq_in = m->prep_ss[0]; norm2.prep_sumsq_n = hb;
+        const bool last = l + 1 == m->layers.size();
+        act.next_prep = m->prep[1]; act.next_sumsq = m->prep_ss[1];
+        act.next_w = last ? m->final_norm : m->layers[l + 1].in_norm;
+        act.next_rotate = last ? m->head_rot : m->layers[l + 1].rot[0];
+        have = true;
+      }
       float *qkv[3] = {m->q, m->k, m->v};
       st = gemv_group(m, 3, &L.w[0], &L.rot[0], m->hidden, h, qkv, batch, norm1);
       if (st != LMB_OK) break;
@@ -659,6 +717,7 @@ int lmb_model_forward(lmb_model *m, const int *token_ids, const size_t *position
     if (st != LMB_OK) return st;
     Fuse fin;
     fin.xmode = XMODE_RMSNORM; fin.x2 = m->final_norm;
+    if (ho && have) { fin.prep_in = m->prep[1]; fin.prep_sumsq_in = m->prep_ss[1]; fin.prep_sumsq_n = hb; }
     st = gemv1(m, m->lm_head, m->head_rot, m->hidden, h, m->logits, batch, fin);
     if (st != LMB_OK) return st;
   } else {

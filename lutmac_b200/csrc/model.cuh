@@ -47,6 +47,9 @@ struct lmb_model {
   // batch-1 steps of models whose layer projections share one integer-MMA kind run as one
   // persistent kernel over all layers (persist.cu); LMB_MODEL_PERSISTENT=0 disables it
   bool persistent = true;
+  bool handoff = true;  // LMB_MODEL_HANDOFF=0: every consumer CTA converts its own activations (batch 1, fused step)
+  uint32_t *prep[2] = {nullptr, nullptr};  // prepared hidden state after o_proj / after down_proj
+  float *prep_ss[2] = {nullptr, nullptr};
   bool attn_group = true;  // LMB_ATTN_GROUP=0: one attention CTA per query head instead of per KV head
   lmb::PersistPlan *ps = nullptr;
   int debug_extra_arrivals = 0;  // failure-path test: every grid barrier waits for this many arrivals that never come
