@@ -27,6 +27,20 @@ def test_library_exports_every_declared_symbol():
     assert declared == set(_lib.SIGNATURES), declared ^ set(_lib.SIGNATURES)
 
 
+def test_drop_in_defines_the_reference_entry_points():
+    """shim/lutmac_b200_dropin.cpp, compiled against the reference's headers (shim/Makefile), defines
+    the functions include/lutmac/lut_gemm.hpp and transform.hpp declare for the path."""
+    import subprocess
+    obj = os.path.join(ROOT, "shim", "_build", "dropin.o")
+    if not os.path.exists(obj):
+        pytest.skip("shim/_build/dropin.o not built (make -C shim REF=<reference checkout>)")
+    syms = subprocess.run(["nm", "-C", "--defined-only", obj], capture_output=True, text=True, check=True).stdout
+    for name in ("lut_gemv_scalar", "lut_gemv_avx2", "lut_gemv_binary_scalar", "lut_gemv_binary_avx2", "int2_gemv_scalar",
+                 "int2_gemv_avx2", "int3_gemv_scalar", "int3_gemv_avx2", "int4_gemv_scalar", "int4_gemv_avx2", "int5_gemv_scalar",
+                 "int6_gemv_scalar", "int8_gemv_scalar", "int8_gemv_avx2", "lut_linear", "fwht_256", "apply_hadamard_rotation"):
+        assert re.search(r" T lutmac::" + name + r"\(", syms), name
+
+
 def test_block_sizes_match_the_reference_structs():
     L = _lib.lib()
     for kind in ALL_KINDS:
