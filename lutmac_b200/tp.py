@@ -35,6 +35,22 @@ def shard(name: str, t: PackedTensor, rank: int, size: int) -> PackedTensor:
     return shard_rows(t, rank, size) if name in ROW_SHARDED else shard_blocks(t, rank, size)
 
 
+class RankLost(RuntimeError):
+    """A rank of the tensor-parallel group did not take part in a host-side exchange."""
+
+
+def exchange(dist, payload: bytes, what: str) -> list:
+    """All ranks' payloads, in rank order.  A rank that has left (or never joins) ends the
+    collective with the process group's timeout; that is reported as RankLost, so that the
+    caller stops before launching kernels that would wait for the missing rank."""
+    out = [None] * dist.get_world_size()
+    try:
+        dist.all_gather_object(out, payload)
+    except Exception as e:  # torch raises RuntimeError / DistBackendError, depending on the backend
+        raise RankLost(f"tensor-parallel {what}: a rank did not answer ({type(e).__name__}: {str(e)[:200]})") from e
+    return out
+
+
 def init_tp(ctx, dist, peer_floats: int = 32 * 8192) -> None:
     """Create the context's NCCL communicator: rank 0 makes the unique id, torch.distributed
     (any backend) carries it to the others.  peer_floats > 0 also sets up the exchange blocks of
@@ -52,8 +68,7 @@ def init_tp(ctx, dist, peer_floats: int = 32 * 8192) -> None:
         # exchange blocks for the all-reduce over peer memory: gather the IPC handles of all ranks
         handle = (C.c_char * 64)()
         check(lib().lmb_tp_peer_create(ctx.h, peer_floats, handle))
-        handles = [None] * size
-        dist.all_gather_object(handles, bytes(handle))
+        handles = exchange(dist, bytes(handle), "peer-memory set-up")
         allh = (C.c_char * (64 * size)).from_buffer_copy(b"".join(handles))
         check(lib().lmb_tp_peer_open(ctx.h, allh))
         dist.barrier()

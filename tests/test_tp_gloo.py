@@ -53,3 +53,38 @@ def test_tp2_gate_up_down_over_gloo(tmp_path):
     got, want = np.load(tmp_path / "got.npy"), np.load(tmp_path / "want.npy")
     err = np.linalg.norm(got - want) / np.linalg.norm(want)
     assert err < 1e-5, err
+
+
+def _leaver(rank, world, port, out_dir):
+    """Rank 1 takes part in the first exchange and then leaves, between steps and with nothing in
+    flight; rank 0's next exchange must end with RankLost within the group's timeout, not hang."""
+    sys.path.insert(0, ROOT)
+    import datetime
+    import time
+    import torch.distributed as dist
+    from lutmac_b200 import tp
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=3))
+    first = tp.exchange(dist, bytes([rank]) * 4, "step 0")
+    assert first == [bytes([r]) * 4 for r in range(world)]
+    if rank == 1:
+        os._exit(0)  # gone: no destroy, no further collective
+    t0 = time.time()
+    try:
+        tp.exchange(dist, b"step-1", "step 1")
+        outcome = "no error"
+    except tp.RankLost as e:
+        outcome = "RankLost: " + str(e)
+    with open(os.path.join(out_dir, "outcome.txt"), "w") as f:
+        f.write("%.1f\n%s\n" % (time.time() - t0, outcome))
+    os._exit(0)
+
+
+def test_a_rank_that_leaves_is_reported_on_the_host(tmp_path):
+    import torch.multiprocessing as mp
+    port = 31500 + os.getpid() % 2000
+    mp.spawn(_leaver, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    took, outcome = (tmp_path / "outcome.txt").read_text().splitlines()[:2]
+    assert outcome.startswith("RankLost"), outcome
+    assert float(took) < 30.0
