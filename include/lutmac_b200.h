@@ -220,6 +220,20 @@ int lmb_apply_hadamard_rotation_host(float *data, size_t n);         /* in place
 int lmb_debug_plan(int kind, size_t M, size_t K, size_t batch, size_t other_rows, int sm_count, int out5[5]);
 /* The same for a batch-1 launch of a resident weight alone (uses the weight's device layout kind). */
 int lmb_debug_plan_weight(const lmb_weight *w, int sm_count, int out5[5]);
+/* Tests and experiments: from now on every batch-1 launch whose shape can take this work split uses it
+ * (R row tiles per CTA, n_ks K slices, cr row groups per thread-block cluster -- cluster size
+ * cr * n_ks in {2, 4, 8}, cr = 0: no cluster); launches that cannot, plan as usual.  R = 0: off.
+ * Process-wide; graphs captured earlier keep their plans. */
+int lmb_debug_force_plan(int R, int n_ks, int cr);
+/* Launch timeline (debugging; no counterpart in the reference).  cap_launches > 0 on the first call
+ * switches recording on for the GEMV and attention launches issued (or captured into a graph) from
+ * then on, up to cap_launches per decode step.  Every call synchronises, copies the slots recorded
+ * since the previous call to `out` (8 words per launch, *n_launches of them, device global-timer
+ * nanoseconds: 0 first CTA started, 1 / 2 first / last CTA past the wait for the preceding kernel,
+ * 3 last CTA with its activations ready, 4 last CTA through its main loop, 5 / 6 last / first CTA
+ * done, 7 unused) and clears them; minima and maxima accumulate over the steps run in between,
+ * so run one step between two calls.  out may be null. */
+int lmb_debug_launch_timeline(lmb_ctx *ctx, size_t cap_launches, unsigned long long *out, size_t *n_launches);
 int lmb_debug_luts(lmb_ctx *ctx, const float *d_x, size_t x_len, unsigned flags, float *d_luts_out);
 /* Ternary LUT indices as the kernel consumes them: for every row and group of 4 weights the
  * (pos, neg) nibbles of extract_indices (lut_gemm.hpp:79-99); out = M*ceil(K/256)*64*2 bytes. */

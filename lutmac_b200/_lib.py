@@ -83,6 +83,8 @@ SIGNATURES = {
     "lmb_apply_hadamard_rotation_host": (C.c_int, [vp, sz]),
     "lmb_debug_plan": (C.c_int, [C.c_int, sz, sz, sz, sz, C.c_int, C.POINTER(C.c_int)]),
     "lmb_debug_plan_weight": (C.c_int, [vp, C.c_int, C.POINTER(C.c_int)]),
+    "lmb_debug_launch_timeline": (C.c_int, [vp, sz, vp, C.POINTER(sz)]),
+    "lmb_debug_force_plan": (C.c_int, [C.c_int, C.c_int, C.c_int]),
     "lmb_debug_luts": (C.c_int, [vp, vp, sz, C.c_uint, vp]),
     "lmb_debug_ternary_indices": (C.c_int, [vp, vp, vp]),
     "lmb_model_create": (C.c_int, [vp, C.POINTER(ModelConfig), C.POINTER(vp)]),

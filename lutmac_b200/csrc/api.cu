@@ -231,6 +231,25 @@ int lmb_ctx_create(int device, lmb_ctx **out) {
   return LMB_OK;
 }
 
+int lmb_debug_launch_timeline(lmb_ctx *ctx, size_t cap_launches, unsigned long long *out, size_t *n_launches) {
+  LMB_REQUIRE(ctx && n_launches, "lmb_debug_launch_timeline: null argument");
+  LMB_CUDA(cudaSetDevice(ctx->device));
+  LMB_CUDA(cudaStreamSynchronize(ctx->stream));
+  if (!ctx->d_timeline) {
+    LMB_REQUIRE(cap_launches > 0 && cap_launches < (size_t(1) << 20), "lmb_debug_launch_timeline: recording is off and no capacity was given");
+    LMB_CUDA(cudaMalloc(&ctx->d_timeline, cap_launches * 8 * sizeof(unsigned long long)));
+    ctx->timeline_cap = int(cap_launches);
+    ctx->timeline_cursor = 0;
+  }
+  const size_t n = size_t(ctx->timeline_cursor), words = size_t(ctx->timeline_cap) * 8;
+  if (out && n) LMB_CUDA(cudaMemcpy(out, ctx->d_timeline, n * 8 * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+  *n_launches = n;
+  std::vector<unsigned long long> init(words, 0ull);  // minima start at the largest value, maxima at 0
+  for (size_t i = 0; i < words; i += 8) init[i] = init[i + 1] = init[i + 6] = ~0ull;
+  LMB_CUDA(cudaMemcpy(ctx->d_timeline, init.data(), words * sizeof(unsigned long long), cudaMemcpyHostToDevice));
+  return LMB_OK;
+}
+
 int lmb_ctx_destroy(lmb_ctx *ctx) {
   if (!ctx) return LMB_OK;
   cudaSetDevice(ctx->device);
@@ -239,6 +258,7 @@ int lmb_ctx_destroy(lmb_ctx *ctx) {
   if (ctx->counters) cudaFree(ctx->counters);
   if (ctx->xprep) cudaFree(ctx->xprep);
   if (ctx->d_fault) cudaFree(ctx->d_fault);
+  if (ctx->d_timeline) cudaFree(ctx->d_timeline);
   if (ctx->h_upload) cudaFreeHost(ctx->h_upload);
   if (ctx->h_stage) cudaFreeHost(ctx->h_stage);
   if (ctx->d_stage) cudaFree(ctx->d_stage);

@@ -191,6 +191,9 @@ struct lmb_ctx {
   size_t xprep_blocks = 0;  // capacity in (sequence, block) pairs
   // set by a kernel whose bounded wait (for its own asynchronous copies) ran out; read with the logits
   unsigned *d_fault = nullptr;
+  // launch timeline (debugging, lmb_debug_launch_timeline): 8 time stamps per launch, null when off
+  unsigned long long *d_timeline = nullptr;
+  int timeline_cap = 0, timeline_cursor = 0;
   void *h_upload = nullptr;  // pinned staging of lmb_weight_upload
   size_t h_upload_bytes = 0;
   // staging buffers of the host-pointer entry points
@@ -199,6 +202,12 @@ struct lmb_ctx {
   float *d_stage = nullptr;
   size_t d_stage_bytes = 0;
 };
+
+// The next launch's slot of the launch timeline, or null (off / full).
+inline unsigned long long *timeline_slot(lmb_ctx *ctx) {
+  if (!ctx->d_timeline || ctx->timeline_cursor >= ctx->timeline_cap) return nullptr;
+  return ctx->d_timeline + size_t(8) * size_t(ctx->timeline_cursor++);
+}
 
 struct lmb_weight {
   int kind = 0;      // device layout kind (a reference kind, or DK_TERNARY_MMA)

@@ -6,6 +6,7 @@
 
 #include "common.cuh"
 #include "decode_ops.cuh"
+#include "device_utils.cuh"
 
 namespace lmb {
 
@@ -431,7 +432,7 @@ template <int PER> __device__ __forceinline__ LaneVec<PER> ldcg_lane_vec(const f
 template <bool FRESH_CG, int PER>
 __device__ __forceinline__ bool attn_group_item(const AttnArgs &a, const RopeDims &d, size_t kvh, size_t split, size_t b, float *sm,
                                                 uint64_t *bar, unsigned &parity, unsigned spin_limit, int *flag,
-                                                unsigned long long *dbg = nullptr) {
+                                                unsigned long long *dbg = nullptr, unsigned long long *tl = nullptr) {
   const size_t hd = d.hd, g = d.nh / d.nkv, kv_dim = d.nkv * hd, half = hd / 2, sl = d.split_len;
   float *Ks = sm, *Vs = Ks + sl * hd, *qs = Vs + sl * hd, *sc = qs + g * hd, *wk = sc + g * sl, *stat = wk + ATT_MAX_GROUP * ATT_MAX_SPLITS;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nw = ATT_THREADS / 32;
@@ -456,6 +457,15 @@ __device__ __forceinline__ bool attn_group_item(const AttnArgs &a, const RopeDim
     if (n_old) {
       bulk_copy_g2s(Ks, kc + t0 * hd, unsigned(n_old) * row_bytes, bar);
       bulk_copy_g2s(Vs, vc + t0 * hd, unsigned(n_old) * row_bytes, bar);
+    }
+  }
+  if constexpr (!FRESH_CG) {
+    // a kernel of its own: the cached rows do not depend on the preceding kernel (they were written by
+    // earlier steps), the fresh projections do
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (tid == 0) {
+      tl_min(tl, 1);
+      tl_max(tl, 2);
     }
   }
   // meanwhile: the group's rotated queries, and the new position's key / value (pairs (i, i + hd/2))
@@ -511,6 +521,7 @@ __device__ __forceinline__ bool attn_group_item(const AttnArgs &a, const RopeDim
     if (*flag == 0) return false;
   }
   if (dbg && tid == 0) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(dbg[0]));
+  if (tid == 0) tl_max(tl, 3);
   // scores: a warp per timestep, a lane per PER dimensions
   const float scale = 1.0f / sqrtf(float(hd));
   for (size_t t = warp; t < n; t += nw) {
@@ -587,6 +598,7 @@ __device__ __forceinline__ bool attn_group_item(const AttnArgs &a, const RopeDim
   }
   __syncthreads();
   if (dbg && tid == 0) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(dbg[1]));
+  if (tid == 0) tl_max(tl, 4);
   unsigned *ctr = a.counters + b * d.nkv + kvh;
   if (tid == 0) {
     unsigned before;  // release: this CTA's partial records; acquire: the other splits' records
@@ -594,7 +606,10 @@ __device__ __forceinline__ bool attn_group_item(const AttnArgs &a, const RopeDim
     *flag = (before == unsigned(n_splits - 1));
   }
   __syncthreads();
-  if (*flag == 0) return true;
+  if (*flag == 0) {
+    if (tid == 0) tl_min(tl, 6);
+    return true;
+  }
   // merge by the last split of the KV head: a warp per query head of the group
   for (size_t h = warp; h < g; h += nw) {
     const size_t head = kvh * g + h;
@@ -638,6 +653,7 @@ __device__ __forceinline__ bool attn_group_item(const AttnArgs &a, const RopeDim
     st_lane_vec<PER>(a.out + (b * d.nh + head) * hd, lane, tot);
   }
   if (tid == 0) *ctr = 0u;
+  if (tid == 0) tl_max(tl, 5);
   return true;
 }
 

@@ -108,8 +108,9 @@ __global__ void __launch_bounds__(ATT_THREADS) k_decode_attn(const AttnArgs a, c
 // Group attention as a kernel of its own: grid = (KV heads x splits, sequences).
 template <int PER>
 __global__ void __launch_bounds__(ATT_THREADS) k_decode_attn_group(const AttnArgs a, const RopeDims d, unsigned spin_limit,
-                                                                    unsigned *timed_out) {
+                                                                    unsigned *timed_out, unsigned long long *tl) {
   asm volatile("griddepcontrol.launch_dependents;");
+  if (threadIdx.x == 0) tl_min(tl, 0);
   extern __shared__ __align__(16) float sm[];
   __shared__ __align__(8) uint64_t bar;
   __shared__ int flag;
@@ -117,7 +118,8 @@ __global__ void __launch_bounds__(ATT_THREADS) k_decode_attn_group(const AttnArg
   __syncthreads();
   unsigned parity = 0;
   const size_t kvh = blockIdx.x % d.nkv, split = blockIdx.x / d.nkv;
-  if (!attn_group_item<false, PER>(a, d, kvh, split, blockIdx.y, sm, &bar, parity, spin_limit, &flag) && threadIdx.x == 0 && timed_out)
+  if (!attn_group_item<false, PER>(a, d, kvh, split, blockIdx.y, sm, &bar, parity, spin_limit, &flag, nullptr, tl) && threadIdx.x == 0 &&
+      timed_out)
     *timed_out = 1u;
 }
 
@@ -236,10 +238,22 @@ int launch_decode_attn_group(lmb_ctx *ctx, const float *q, const float *k, const
   AttnArgs a{q, k, v, qb, kb, vb, cs_table, positions, kv, out, partial, counters, plan.n_splits, layer};
   dim3 grid(unsigned(d.nkv * size_t(plan.n_splits)), unsigned(batch));
   unsigned *flag = ctx->d_fault;  // set when a bounded wait for the bulk copies runs out
-  if (plan.per == 4) k_decode_attn_group<4><<<grid, ATT_THREADS, plan.smem_bytes, ctx->stream>>>(a, d, ctx->xchg.spin_limit, flag);
-  else k_decode_attn_group<2><<<grid, ATT_THREADS, plan.smem_bytes, ctx->stream>>>(a, d, ctx->xchg.spin_limit, flag);
+  // programmatic dependent launch: the CTAs start fetching their cache slices while the q/k/v
+  // projections finish, and wait for those only before they read the fresh vectors
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(ATT_THREADS);
+  cfg.dynamicSmemBytes = plan.smem_bytes;
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = ctx->pdl ? 1 : 0;
+  unsigned long long *tl = timeline_slot(ctx);
+  if (plan.per == 4) LMB_CUDA(cudaLaunchKernelEx(&cfg, k_decode_attn_group<4>, a, d, ctx->xchg.spin_limit, flag, tl));
+  else LMB_CUDA(cudaLaunchKernelEx(&cfg, k_decode_attn_group<2>, a, d, ctx->xchg.spin_limit, flag, tl));
   ctx->launches++;
-  LMB_CUDA(cudaGetLastError());
   return LMB_OK;
 }
 

@@ -122,4 +122,20 @@ __device__ __forceinline__ void build_block_tables(const float *__restrict__ x, 
   if (lane == 0) *xsum = s;
 }
 
+
+// Launch timeline (debugging): word 0 first CTA start, 1 / 2 first / last CTA past the wait for the
+// preceding kernel, 3 last CTA with its activations ready, 4 last CTA through its main loop,
+// 5 / 6 last / first CTA done.  Called by one thread per CTA; dbg null: off.
+__device__ __forceinline__ unsigned long long tl_now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void tl_min(unsigned long long *dbg, int w) {
+  if (dbg) atomicMin(dbg + w, tl_now());
+}
+__device__ __forceinline__ void tl_max(unsigned long long *dbg, int w) {
+  if (dbg) atomicMax(dbg + w, tl_now());
+}
+
 }  // namespace lmb

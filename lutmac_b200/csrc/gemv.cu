@@ -44,6 +44,8 @@ namespace {
 constexpr int WARPS = 8;
 constexpr int THREADS = WARPS * 32;
 constexpr int MAX_JOBS = 4;
+constexpr int MAX_CLUSTER_BLOCKS = 384;  // longest input (in 256-blocks) of a launch that uses thread-block clusters
+constexpr int MAX_CLUSTER = 8;           // portable cluster size
 
 struct Job {
   const uint8_t *tiles;
@@ -90,6 +92,13 @@ struct GemvParams {
   // prepared vector (RMSNorm is linear in that scalar, so it is applied to the block scales); null: none
   const float *prep_sumsq;
   int prep_sumsq_n;
+  unsigned long long *dbg;  // this launch's slot of the launch timeline (debugging), or null
+  // Thread-block clusters (batch 1, integer-MMA kinds): cl_size consecutive CTAs = the n_ks K slices of
+  // cl_size / n_ks consecutive row groups of one job.  The CTAs that read the same K slice convert
+  // its activations together (each a share, written into the shared memory of all of them), and the
+  // K slices of a row group are added up through distributed shared memory instead of a scratch
+  // buffer and an arrival counter.  0 or 1: no clusters.
+  int cl_size;
 };
 
 template <int KIND, int NSEQ>
@@ -106,8 +115,10 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
   __shared__ float xsum[NSEQ * 64];
   __shared__ __align__(16) int xaux[NP * 64 * 4];
   __shared__ int is_last;
+  __shared__ float xss[MAX_CLUSTER_BLOCKS];  // cluster mode: sum of squares of every 256-block of the input
 
   pdl_launch_dependents();
+  if (threadIdx.x == 0) tl_min(p.dbg, 0);
 
   // work item of this CTA
   int j = 0, first = 0;
@@ -133,6 +144,8 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
   const int ns = min(job.S, job.bpr - b0);
   const bool active = rtl < nrt && sub < ns;
   const uint8_t *row_tiles = job.tiles + (size_t(rt0 + rtl) * job.bpr + b0) * TB;
+  const bool clustered = NSEQ == 1 && kind_is_mma(KIND) && p.cl_size > 1;  // uniform over the launch
+  const int crank = clustered ? local % p.cl_size : 0;                    // rank in the cluster (job starts are multiples of cl_size)
 
   // weights do not depend on the preceding kernel: fetch the first units before waiting for it
   constexpr int NSLOT = (NSEQ > 2 ? 1 : prefetch_depth(KIND)) + 1;  // a ring of row-blocks held in registers
@@ -144,12 +157,16 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
   }
 
   pdl_wait();
+  if (threadIdx.x == 0) {
+    tl_min(p.dbg, 1);
+    tl_max(p.dbg, 2);
+  }
 
   // tensor-parallel output: the epoch selects the parity of the exchange slot
   const unsigned epoch = p.peer.n ? *reinterpret_cast<volatile unsigned *>(p.peer.epoch) : 0u;
   const float *x = job.x + size_t(batch0) * job.x_stride;
   float *inv_rms = part[0];  // [sequence] after the block below (XMODE_RMSNORM)
-  if (p.xmode == XMODE_RMSNORM && !p.prep) {
+  if (p.xmode == XMODE_RMSNORM && !p.prep && !clustered) {
     // RMSNorm of the whole input vectors (src/layers/norm.cpp:18-34), recomputed by every CTA
     float ss[NSEQ];
 #pragma unroll
@@ -204,7 +221,75 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
       }
     }
   }
-  if (!(kind_is_mma(KIND) && p.prep)) {
+  if constexpr (NSEQ == 1 && kind_is_mma(KIND)) {
+    if (clustered) {
+      // The cr-th of the Cr CTAs that read this K slice converts blocks cr, cr + Cr, ... and writes each
+      // record into all Cr of them.  RMSNorm (src/layers/norm.cpp:18-34) is linear in 1 / rms: the
+      // digits are those of x * w, every converter publishes its blocks' sums of squares to the whole
+      // cluster (which covers all of K), and the block scales are multiplied by 1 / rms afterwards.
+      const int Cr = p.cl_size / job.n_ks, cr = crank / job.n_ks;
+      const int mine = ns > cr ? (ns - cr + Cr - 1) / Cr : 0;
+      float v[8], w8[8], nv[8];
+      if (warp < mine) load_x8(x, job.x_len, size_t(b0 + cr + warp * Cr), lane, nv);
+      for (int it = warp; it < mine; it += WARPS) {
+        const int bl = cr + it * Cr;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = nv[e];
+        if (p.xmode == XMODE_RMSNORM) load_x8(job.x2, job.x_len, size_t(b0 + bl), lane, w8);
+        if (p.xmode == XMODE_SILU_MUL || p.xmode == XMODE_GELU_MUL) load_x8(job.x2 + size_t(batch0) * job.x_stride, job.x_len, size_t(b0 + bl), lane, w8);
+        if (it + WARPS < mine) load_x8(x, job.x_len, size_t(b0 + cr + (it + WARPS) * Cr), lane, nv);
+        if (p.xmode == XMODE_RMSNORM) {
+          float ss = 0.0f;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            ss += v[e] * v[e];
+            v[e] *= w8[e];
+          }
+#pragma unroll
+          for (int m = 16; m > 0; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
+          if (lane < p.cl_size) st_cluster_f32(cluster_addr(&xss[b0 + bl], unsigned(lane)), ss);
+        } else if (p.xmode == XMODE_SILU_MUL) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[e] = (v[e] / (1.0f + expf(-v[e]))) * w8[e];  // silu(gate) * up, model.cpp:36,414-416
+        } else if (p.xmode == XMODE_GELU_MUL) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[e] = gelu_tanh(v[e]) * w8[e];  // gelu(gate) * up, model.cpp:38-42,409-412
+        }
+        if (p.rotate) fwht256_warp(v, lane);
+        float *blk = smem + size_t(bl) * FPB;
+        int *aux = xaux + bl * 4;
+        U::prologue(v, lane, blk, xsum + bl, aux);
+        if (lane == 0) aux[2] = aux[3] = 0;  // no second sequence
+        __syncwarp();
+        if (Cr > 1) {
+          const uint4 *src = reinterpret_cast<const uint4 *>(blk);
+          const uint4 d0 = src[lane], d1 = src[lane + 32];
+          const float bs = xsum[bl];
+          const uint4 ax = *reinterpret_cast<const uint4 *>(aux);
+          for (int c2 = 0; c2 < Cr; ++c2) {
+            if (c2 == cr) continue;
+            const unsigned peer = unsigned(c2 * job.n_ks + ks);
+            st_cluster_v4(cluster_addr(src + lane, peer), d0);
+            st_cluster_v4(cluster_addr(src + lane + 32, peer), d1);
+            if (lane == 0) {
+              st_cluster_f32(cluster_addr(xsum + bl, peer), bs);
+              st_cluster_v4(cluster_addr(aux, peer), ax);
+            }
+          }
+        }
+      }
+      cluster_sync_all();
+      if (p.xmode == XMODE_RMSNORM) {
+        float tot = 0.0f;
+        for (int i = lane; i < job.bpr; i += 32) tot += xss[i];
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, m);
+        const float ir = 1.0f / sqrtf(tot / float(job.x_len) + p.eps);
+        if (int(threadIdx.x) < ns) xsum[threadIdx.x] *= ir;
+      }
+    }
+  }
+  if (!(kind_is_mma(KIND) && p.prep) && !clustered) {
     // one warp per (sequence, block); the next item's activations are fetched while this one is converted
     float v[8], w8[8], nv[8];
     const int items = ns * nb;
@@ -241,6 +326,7 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
     }
   }
   __syncthreads();
+  if (threadIdx.x == 0) tl_max(p.dbg, 3);
 
   // each slot is evaluated and at once refilled with the row-block NSLOT steps ahead, so that
   // NSLOT-1 loads are in flight during every evaluation
@@ -283,7 +369,8 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
   }
 
   // combine the warps that share a row-tile, in warp order: thread t ends up with row rt0*32 + t
-  if (p.xmode == XMODE_RMSNORM && !p.prep) __syncthreads();  // inv_rms (in part[0]) has been read by everyone
+  if (threadIdx.x == 0) tl_max(p.dbg, 4);
+  if (p.xmode == XMODE_RMSNORM && !p.prep && !clustered) __syncthreads();  // inv_rms (in part[0]) has been read by everyone
 #pragma unroll
   for (int q = 0; q < NSEQ; ++q) part[q][threadIdx.x] = acc[q];
   __syncthreads();
@@ -362,7 +449,33 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
           if (q == 0) handoff = o;
         }
     }
-    hand_off();
+    if (rg < job.n_rg) hand_off();
+    if (t == 0) {
+      tl_max(p.dbg, 5);
+      tl_min(p.dbg, 6);
+    }
+    return;
+  }
+  if (clustered) {
+    // split K inside a cluster: slice 0 of the row group adds the partial sums of the others, in slice
+    // order, out of their shared memory
+    __syncthreads();  // part[] has been read
+    if (owns_row) part[0][t] = s[0];
+    cluster_sync_all();
+    if (ks == 0 && owns_row && row < job.M) {
+      float tot = s[0];
+      for (int k = 1; k < job.n_ks; ++k) tot += ld_cluster_f32(cluster_addr(&part[0][t], unsigned(crank + k)));
+      if (job.bias) tot += job.bias[row];
+      if (job.residual) tot += job.residual[size_t(batch0) * job.y_stride + row];
+      emit(0, tot);
+      handoff = tot;
+    }
+    cluster_sync_all();  // the other slices' shared memory stays alive until it has been read
+    if (ks == 0 && rg < job.n_rg) hand_off();
+    if (t == 0) {
+      tl_max(p.dbg, 5);
+      tl_min(p.dbg, 6);
+    }
     return;
   }
   // split K: publish the partial sums, the last slice to arrive adds them in slice order
@@ -379,7 +492,10 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
     __threadfence();
   }
   __syncthreads();
-  if (!is_last) return;  // uniform over the CTA
+  if (!is_last) {  // uniform over the CTA
+    if (t == 0) tl_min(p.dbg, 6);
+    return;
+  }
   if (owns_row && row < job.M) {
     const float bias = job.bias ? job.bias[row] : 0.0f;
 #pragma unroll
@@ -396,6 +512,7 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
   }
   if (t == 0) *ctr = 0u;  // ready for the next launch
   hand_off();
+  if (t == 0) tl_max(p.dbg, 5);
 }
 
 // Conversion pass for batched launches: the activations of every (sequence, block) of the shared
@@ -467,26 +584,68 @@ __global__ void k_debug_luts(const float *x, size_t x_len, int nblocks, int rota
 
 struct Plan {
   int R, S, n_rg, n_ks, ctas;
+  int cr;  // thread-block clusters: row groups per cluster (cluster size = cr * n_ks); 0: no cluster
 };
+
+// LMB_PLAN_FORCE="R,n_ks,cr" or lmb_debug_force_plan (experiments and tests): every batch-1 plan
+// that can take these values does.
+struct PlanForce {
+  bool on = false;
+  int R = 0, n_ks = 0, cr = 0;
+  PlanForce() {
+    const char *e = std::getenv("LMB_PLAN_FORCE");
+    on = e && std::sscanf(e, "%d,%d,%d", &R, &n_ks, &cr) == 3;
+  }
+};
+PlanForce g_plan_force;
+// LMB_GEMV_CLUSTER=0: no thread-block clusters in any plan.
+inline bool clusters_allowed() {
+  static const bool ok = [] {
+    const char *e = std::getenv("LMB_GEMV_CLUSTER");
+    return !(e && e[0] == '0');
+  }();
+  return ok;
+}
 
 // Resident CTAs per SM of k_gemv<kind> (register limited), used to count waves.
 int ctas_per_sm(int kind) { return kind_info(kind).lut ? 3 : 2; }
 
 // Chooses R (row-tiles per CTA: 8, 4, 2 or 1; the 8 warps of a CTA then share a row-tile
-// 1, 2, 4 or 8 ways along K, which costs only a shared-memory reduction) and the K split over
-// CTAs (which costs a trip through global scratch) by minimising a makespan estimate in units
-// of "one warp evaluates one 256-column block":
+// 1, 2, 4 or 8 ways along K, which costs only a shared-memory reduction), the K split over CTAs
+// and whether the CTAs form thread-block clusters (K slices added up through distributed shared
+// memory, and the conversion of the activations shared by the row groups of a cluster) or pass
+// their partial sums through global scratch, by minimising a makespan estimate in units of "one
+// warp evaluates one 256-column block":
 //     waves of CTAs x (blocks per warp + prologue share + fixed CTA cost [+ split-K hand-off]).
 // `other_row_tiles` are the row-tiles of the other jobs of the same launch.
+// Work split of one GEMV.  `cluster`: -1 free choice (none or 2 / 4 / 8 CTAs), 0 none, else exactly this
+// cluster size (the other jobs of the launch use it).
 Plan make_plan(int kind, size_t row_tiles, size_t bpr, size_t batch, int sm_count, size_t other_row_tiles = 0, int nseq = 1,
-               bool whole_blocks = false) {
+               bool whole_blocks = false, int cluster = 0) {
+  const PlanForce force = g_plan_force;
   const bool lut = kind_info(kind).lut;
   // 48 KiB of tables / activations per CTA (96 KiB when 4 or 8 sequences share a pass)
   const size_t s_cap = lut ? 12 : nseq == 1 ? 48 : nseq == 8 ? 12 : 24;
   const size_t slots = size_t(sm_count) * (min_ctas(kind, nseq) == 1 ? 1 : ctas_per_sm(kind));
-  const double prologue_per_block = 1.5 * nseq, fixed = 1.5, split_cost = 2.5;
+  const double prologue_per_block = 1.5 * nseq, fixed = 1.5, split_cost = 2.5, cluster_sync = 0.5, cluster_split = 0.8;
   const bool throughput = (other_row_tiles + 7) / 8 * batch >= 2 * slots;
+  const bool may_cluster = cluster != 0 && kind_is_mma(kind) && nseq == 1 && batch == 1 && bpr <= size_t(MAX_CLUSTER_BLOCKS) &&
+                           clusters_allowed();
   Plan best{};
+  if (force.on && batch == 1 && nseq == 1 && force.n_ks >= 1 && size_t(force.n_ks) <= bpr) {
+    const size_t fS = (bpr + size_t(force.n_ks) - 1) / size_t(force.n_ks), fc = size_t(force.cr) * size_t(force.n_ks);
+    const bool shape_ok = fS <= s_cap && (bpr + fS - 1) / fS == size_t(force.n_ks) &&
+                          (force.R == 8 || force.R == 4 || force.R == 2 || force.R == 1) && (size_t(force.R) <= row_tiles || force.R == 1) &&
+                          (!whole_blocks || force.R == 8);
+    const bool cluster_ok = force.cr == 0 ? cluster <= 0
+                                          : (may_cluster && fc >= 2 && fc <= size_t(MAX_CLUSTER) && !(fc & (fc - 1)) &&
+                                             (cluster < 0 || fc == size_t(cluster)));
+    if (shape_ok && cluster_ok) {
+      const size_t n_rg = (row_tiles + size_t(force.R) - 1) / size_t(force.R);
+      const size_t n_rgp = force.cr ? (n_rg + size_t(force.cr) - 1) / size_t(force.cr) * size_t(force.cr) : n_rg;
+      return Plan{force.R, int(fS), int(n_rg), force.n_ks, int(n_rgp) * force.n_ks, force.cr};
+    }
+  }
   double best_cost = 1e30;
   for (int R = 8; R >= 1; R >>= 1) {
     if (whole_blocks && R != 8) break;  // a row group must be one 256-block of the output (hand-off to the next GEMV)
@@ -496,26 +655,36 @@ Plan make_plan(int kind, size_t row_tiles, size_t bpr, size_t batch, int sm_coun
       const size_t S = (bpr + n_ks - 1) / n_ks;
       if (S > s_cap) continue;
       if ((bpr + S - 1) / S != n_ks) continue;  // not a distinct split
-      const size_t own = n_rg * n_ks * batch;
-      // other jobs of the launch are assumed to be cut the same way
-      const size_t other_ctas = (other_row_tiles + R - 1) / R * n_ks * batch;
-      const double per_warp = double((S + wpr - 1) / wpr);
-      const double cta_time = per_warp + prologue_per_block * double((S + 7) / 8) + fixed + (n_ks > 1 ? split_cost : 0.0);
-      // with plenty of work from other jobs (even cut 8 row-tiles per CTA) the GPU is busy anyway:
-      // minimise this job's total CTA time; otherwise minimise the time until its last CTA finishes
-      const double cost = (throughput ? double(own) * cta_time / double(slots)
-                                                   : double((own + other_ctas + slots - 1) / slots) * cta_time) +
-                          1e-3 * double(n_ks) + 1e-4 * double(8 / R);
-      if (cost < best_cost) {
-        best_cost = cost;
-        best.R = R;
-        best.S = int(S);
-        best.n_rg = int(n_rg);
-        best.n_ks = int(n_ks);
+      for (int cr = 0; cr <= MAX_CLUSTER; cr = cr ? cr * 2 : 1) {
+        const size_t csize = size_t(cr) * n_ks;  // 0: no cluster
+        if (cr && (!may_cluster || csize < 2 || csize > size_t(MAX_CLUSTER) || (csize & (csize - 1)))) continue;
+        if (cluster > 0 && may_cluster && csize != size_t(cluster)) continue;
+        if (cluster > 0 && !may_cluster) continue;
+        const size_t n_rgp = cr ? (n_rg + size_t(cr) - 1) / size_t(cr) * size_t(cr) : n_rg;
+        const size_t own = n_rgp * n_ks * batch;
+        // other jobs of the launch are assumed to be cut the same way
+        const size_t other_ctas = (other_row_tiles + R - 1) / R * n_ks * batch;
+        const double per_warp = double((S + wpr - 1) / wpr);
+        const size_t converted = cr ? (S + size_t(cr) - 1) / size_t(cr) : S;  // blocks this CTA converts itself
+        const double cta_time = per_warp + prologue_per_block * double((converted + 7) / 8) + fixed + (cr ? cluster_sync : 0.0) +
+                                (n_ks > 1 ? (cr ? cluster_split : split_cost) : 0.0);
+        // with plenty of work from other jobs (even cut 8 row-tiles per CTA) the GPU is busy anyway:
+        // minimise this job's total CTA time; otherwise minimise the time until its last CTA finishes
+        const double cost = (throughput ? double(own) * cta_time / double(slots)
+                                        : double((own + other_ctas + slots - 1) / slots) * cta_time) +
+                            1e-3 * double(n_ks) + 1e-4 * double(8 / R);
+        if (cost < best_cost) {
+          best_cost = cost;
+          best.R = R;
+          best.S = int(S);
+          best.n_rg = int(n_rg);
+          best.n_ks = int(n_ks);
+          best.cr = cr;
+          best.ctas = int(n_rgp * n_ks);
+        }
       }
     }
   }
-  best.ctas = best.n_rg * best.n_ks;
   return best;
 }
 
@@ -529,7 +698,7 @@ int seqs_per_pass(int kind, size_t batch) {
 // Plans every job of a launch and fills the job descriptors (scratch regions are carved out of
 // the context's scratch buffer, which is grown here when the stream is not capturing).
 int prepare_jobs(lmb_ctx *ctx, int kind, const LinearArgs *args, int njobs, Job *jobs, int *ctas_out, int *s_max_out,
-                 std::vector<int2> *cta_map) {
+                 std::vector<int2> *cta_map, bool allow_cluster, int *cluster_out) {
   const size_t batch = args[0].batch;
   const int nseq = seqs_per_pass(kind, batch);
   const size_t ny = (batch + size_t(nseq) - 1) / size_t(nseq);  // grid.y
@@ -537,11 +706,32 @@ int prepare_jobs(lmb_ctx *ctx, int kind, const LinearArgs *args, int njobs, Job 
   size_t scratch_need = 0, counter_need = 0;
   size_t total_rt = 0;
   for (int j = 0; j < njobs; ++j) total_rt += args[j].w->row_tiles;
+  // One cluster size per launch: the job with the most rows chooses (clusters only for direct batch-1
+  // launches whose CTAs convert their own activations), the others follow.
+  int cluster = 0;
+  if (allow_cluster && !cta_map && batch == 1 && !args[0].prep_in) {
+    int big = 0;
+    for (int j = 1; j < njobs; ++j)
+      if (args[j].w->row_tiles > args[big].w->row_tiles) big = j;
+    const Plan lead = make_plan(kind, args[big].w->row_tiles, args[big].w->bpr, ny, ctx->sm_count, total_rt - args[big].w->row_tiles, nseq,
+                                args[big].next_prep != nullptr, -1);
+    cluster = lead.cr * lead.n_ks;
+    for (int j = 0; j < njobs && cluster; ++j)  // every job must be able to follow
+      if (make_plan(kind, args[j].w->row_tiles, args[j].w->bpr, ny, ctx->sm_count, total_rt - args[j].w->row_tiles, nseq,
+                    args[j].next_prep != nullptr, cluster).ctas == 0)
+        cluster = 0;
+  }
+  *cluster_out = cluster;
   for (int j = 0; j < njobs; ++j) {
     const lmb_weight *w = args[j].w;
     const size_t others = total_rt - w->row_tiles;
-    plans[size_t(j)] = make_plan(kind, w->row_tiles, w->bpr, ny, ctx->sm_count, others, nseq, args[j].next_prep != nullptr);
-    if (plans[size_t(j)].n_ks > 1) {
+    plans[size_t(j)] = make_plan(kind, w->row_tiles, w->bpr, ny, ctx->sm_count, others, nseq, args[j].next_prep != nullptr, cluster);
+    static const bool print_plans = std::getenv("LMB_PLAN_PRINT") != nullptr;  // debugging: the work split of every launch
+    if (print_plans)
+      std::fprintf(stderr, "lmb plan: kind %d job %d/%d rows %zu blocks/row %zu batch %zu: R %d S %d K slices %d, row groups per cluster %d, %d CTAs\n",
+                   kind, j, njobs, size_t(w->M), size_t(w->bpr), batch, plans[size_t(j)].R, plans[size_t(j)].S, plans[size_t(j)].n_ks,
+                   plans[size_t(j)].cr, plans[size_t(j)].ctas);
+    if (plans[size_t(j)].n_ks > 1 && !cluster) {
       scratch_need += batch * plans[size_t(j)].n_ks * w->row_tiles * TILE_ROWS;
       counter_need += ny * plans[size_t(j)].n_rg;
     }
@@ -586,7 +776,7 @@ int prepare_jobs(lmb_ctx *ctx, int kind, const LinearArgs *args, int njobs, Job 
     jb.next_sumsq = args[j].next_sumsq;
     jb.next_w = args[j].next_w;
     jb.next_rotate = args[j].next_rotate ? 1 : 0;
-    if (pl.n_ks > 1) {
+    if (pl.n_ks > 1 && !cluster) {
       scratch_off += batch * pl.n_ks * jb.mp;
       counter_off += ny * pl.n_rg;
     }
@@ -621,11 +811,25 @@ template <int KIND, int NSEQ> int launch_params(lmb_ctx *ctx, GemvParams &p, int
   cfg.blockDim = dim3(THREADS);
   cfg.dynamicSmemBytes = size_t(s_max) * Unit<KIND>::FPB * sizeof(float) * NSEQ;
   cfg.stream = ctx->stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (ctx->pdl) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  if (NSEQ == 1 && p.cl_size > 1) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = unsigned(p.cl_size);
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  } else {
+    p.cl_size = 0;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = ctx->pdl ? 1 : 0;
+  cfg.numAttrs = unsigned(na);
+  p.dbg = timeline_slot(ctx);
   LMB_CUDA(cudaLaunchKernelEx(&cfg, k_gemv<KIND, NSEQ>, p));
   ctx->launches++;
   return LMB_OK;
@@ -729,8 +933,10 @@ int launch_gemv(lmb_ctx *ctx, const LinearArgs *args, int njobs, bool rotate, in
       p.peer.data[r] = reinterpret_cast<unsigned long long *>(static_cast<char *>(ctx->xchg.peer[r]) + XCHG_HEADER_BYTES);
   }
   int ctas = 0, s_max = 1;
-  int st = prepare_jobs(ctx, kind, args, njobs, p.job, &ctas, &s_max, nullptr);
+  int cluster = 0;
+  int st = prepare_jobs(ctx, kind, args, njobs, p.job, &ctas, &s_max, nullptr, true, &cluster);
   if (st != LMB_OK) return st;
+  p.cl_size = cluster;
   p.prep_sumsq = nullptr;
   p.prep_sumsq_n = 0;
   if (args[0].prep_in) {  // the producing GEMV prepared the activations (batch 1)
@@ -820,7 +1026,8 @@ int lmb_group_create(lmb_ctx *ctx, size_t n, const lmb_weight *const *ws, const 
   g->kind = kind;
   g->njobs = int(n);
   g->rotate = (flags & LMB_ROTATE) || ((flags & LMB_AUTO_ROTATE) && auto_rot);
-  int st = prepare_jobs(ctx, kind, args.data(), int(n), jobs.data(), &g->ctas, &g->s_max, &map);
+  int no_cluster = 0;
+  int st = prepare_jobs(ctx, kind, args.data(), int(n), jobs.data(), &g->ctas, &g->s_max, &map, false, &no_cluster);
   g->scratch_gen = ctx->scratch_gen;
   g->args = args;
   g->map_entries = map.size();
@@ -847,7 +1054,8 @@ int lmb_group_launch(lmb_ctx *ctx, lmb_group *g) {
     std::vector<Job> jobs(g->args.size());
     std::vector<int2> map;
     int ctas = 0, s_max = 1;
-    int st = prepare_jobs(ctx, g->kind, g->args.data(), g->njobs, jobs.data(), &ctas, &s_max, &map);
+    int no_cluster = 0;
+    int st = prepare_jobs(ctx, g->kind, g->args.data(), g->njobs, jobs.data(), &ctas, &s_max, &map, false, &no_cluster);
     if (st != LMB_OK) return st;
     if (ctas != g->ctas || map.size() != g->map_entries) {
       set_last_error("lmb_group_launch: the group's plan changed; create the group again");
@@ -870,6 +1078,7 @@ int lmb_group_launch(lmb_ctx *ctx, lmb_group *g) {
   p.prep = nullptr;
   p.prep_sumsq = nullptr;
   p.prep_sumsq_n = 0;
+  p.cl_size = 0;
   return launch_params_kind(ctx, g->kind, p, g->ctas, g->s_max, 1);
 }
 
@@ -965,6 +1174,15 @@ int lmb_debug_plan(int kind, size_t M, size_t K, size_t batch, size_t other_rows
   return LMB_OK;
 }
 
+int lmb_debug_force_plan(int R, int n_ks, int cr) {
+  using namespace lmb;
+  g_plan_force.on = R > 0;
+  g_plan_force.R = R;
+  g_plan_force.n_ks = n_ks;
+  g_plan_force.cr = cr;
+  return LMB_OK;
+}
+
 int lmb_debug_plan_weight(const lmb_weight *w, int sm_count, int out5[5]) {
   using namespace lmb;
   LMB_REQUIRE(w && out5 && sm_count > 0, "lmb_debug_plan_weight: bad argument");
@@ -1051,6 +1269,7 @@ int lmb_linear_static_scratch(const lmb_weight *w, const float *d_bias, const fl
   p.prep = nullptr;
   p.prep_sumsq = nullptr;
   p.prep_sumsq_n = 0;
+  p.cl_size = 0;
   Job &jb = p.job[0];
   jb.tiles = w->d_tiles;
   jb.x = d_x;

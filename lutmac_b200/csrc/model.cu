@@ -574,6 +574,7 @@ int lmb_model_forward(lmb_model *m, const int *token_ids, const size_t *position
   for (size_t b = 0; b < batch; ++b)
     LMB_REQUIRE(positions[b] < c.max_seq_len, "lmb_model_forward: position beyond the KV cache");
   lmb_ctx *ctx = m->ctx;
+  ctx->timeline_cursor = 0;  // launch timeline (debugging): slots are counted from the start of a step
   const size_t h = c.hidden_size, hd = c.head_dim;
   const RopeDims rd{m->nh, m->nkv, hd, c.max_seq_len, m->seq_stride, 0};
   const int n_splits = decode_attn_splits(ctx, m->nh, batch, c.max_seq_len);

@@ -110,6 +110,41 @@ def test_gemv_vs_oracle_config_shapes(ctx, oracle, kind, M, K):
     assert rel_l2(y, truth) < TOL
 
 
+# (R row tiles per CTA, K slices, row groups per cluster): clusters of 2 / 4 / 8 CTAs that share the
+# conversion of the activations and / or add up their K slices through distributed shared memory;
+# (8, 2, 0) and (2, 4, 0) are the same splits through the global scratch buffer
+FORCED_PLANS = ((8, 1, 2), (8, 1, 8), (4, 1, 4), (8, 2, 1), (8, 2, 2), (8, 4, 2), (4, 2, 4), (2, 8, 1), (1, 4, 1), (1, 1, 8), (8, 2, 0), (2, 4, 0))
+
+
+@pytest.mark.parametrize("kind", (TERNARY, INT2, INT4, INT8, BINARY, INT3, INT5, INT6))
+def test_every_work_split_gives_the_same_result(ctx, oracle, kind):
+    """Thread-block clusters change where partial sums and converted activations travel, not the
+    arithmetic: K slices are added in slice order either way, so a cluster split is bit-identical
+    to the same split through global scratch, and all of them match the oracle."""
+    rng = np.random.default_rng(300 + kind)
+    L = _lib.lib()
+    try:
+        for (M, K) in ((1000, 2048), (70, 2300), (4096, 8192)):
+            t = synth.tensor(rng, kind, M, K)
+            x = synth.activations(rng, blocks_per_row(K) * 256)
+            want = oracle.gemv_rows_parallel(kind, t.blocks, x, M, K, 8)
+            got = {}
+            for plan in FORCED_PLANS:
+                _lib.check(L.lmb_debug_force_plan(*plan))
+                y = run_linear(ctx, t, x, x_len=x.size)[0]
+                got[plan] = y
+                assert rel_l2(y, want) < TOL, (KIND_NAMES[kind], M, K, plan, rel_l2(y, want))
+                if K % 256 == 0 and kind in (TERNARY, INT2, BINARY):  # lut_linear rotates these (lut_gemm_scalar.cpp:92-93)
+                    yr = run_linear(ctx, t, x, x_len=x.size, flags=_lib.AUTO_ROTATE)[0]
+                    wr = oracle.lut_linear(kind, t.quant_bits, t.blocks, M, K, None, x)[0]
+                    assert rel_l2(yr, wr) < TOL, (KIND_NAMES[kind], M, K, plan, "rotated", rel_l2(yr, wr))
+            if K == 8192:  # both splits are feasible for 32 blocks per row
+                assert np.array_equal(got[(8, 2, 1)], got[(8, 2, 0)]), (KIND_NAMES[kind], "cluster split-K differs from scratch split-K")
+                assert np.array_equal(got[(8, 2, 2)], got[(8, 2, 0)]), KIND_NAMES[kind]
+    finally:
+        _lib.check(L.lmb_debug_force_plan(0, 0, 0))
+
+
 def test_config1_ternary_gemv_and_linear(ctx, oracle):
     t, x = synth.config1(seed=0)
     y = run_linear(ctx, t, x)[0]

@@ -33,6 +33,29 @@ def test_forward_matches_reference_fixtures(ctx, name, kind, over, persistent, m
     m.close()
 
 
+@pytest.mark.parametrize("plan", [(8, 1, 2), (2, 2, 2), (1, 4, 2), (4, 2, 1), (1, 1, 8), (8, 2, 0)])
+@pytest.mark.parametrize("kind,over", [(TERNARY, {}), (INT2, {"qkv_bias": True})])
+def test_decode_step_with_clustered_projections(ctx, oracle, kind, over, plan, monkeypatch):
+    """Forced work splits for every projection that can take them (R row tiles per CTA, K slices, row
+    groups per thread-block cluster): the CTAs of a cluster convert the activations together, RMSNorm
+    comes from the per-block sums of squares they publish to each other, and K slices are added
+    through distributed shared memory.  (8, 2, 0) is a split through global scratch."""
+    from lutmac_b200 import _lib
+    from oracle.oracle import OracleModel
+    monkeypatch.setenv("LMB_MODEL_PERSISTENT", "0")
+    spec = synth.model_spec(synth.tiny_model_shape(hidden=1024, inter=2048, n_heads=16, n_kv_heads=4, **over), kind, seed=21, max_seq=32)
+    L = _lib.lib()
+    _lib.check(L.lmb_debug_force_plan(*plan))
+    try:
+        m = Model(spec, ctx)
+        o = OracleModel(oracle, spec)
+        for p, t in enumerate((3, 77, 200, 5)):
+            assert rel_l2(m.forward(t, p), o.forward(t, p)) < TOL, (plan, p)
+        m.close()
+    finally:
+        _lib.check(L.lmb_debug_force_plan(0, 0, 0))
+
+
 def test_forward_vs_oracle_longer_context_and_kv(ctx, oracle):
     from oracle.oracle import OracleModel
     spec = synth.model_spec(synth.tiny_model_shape(n_layers=3, hidden=512, inter=768, n_heads=8, n_kv_heads=2), INT4,
