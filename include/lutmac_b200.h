@@ -225,6 +225,17 @@ int lmb_debug_plan_weight(const lmb_weight *w, int sm_count, int out5[5]);
  * cr * n_ks in {2, 4, 8}, cr = 0: no cluster); launches that cannot, plan as usual.  R = 0: off.
  * Process-wide; graphs captured earlier keep their plans. */
 int lmb_debug_force_plan(int R, int n_ks, int cr);
+/* Range-checking build (liblutmac_b200_dbg.so, compiled with -DLMB_DEBUG_BOUNDS; the reference has no
+ * sanitizer set-up to mirror): the GEMV kernels check every weight-tile load, output store and
+ * split-K scratch store against the extent of its buffer, the attention kernel its cache slices; an
+ * access that would leave its buffer is skipped and recorded, nothing traps.  lmb_debug_bounds
+ * synchronises, returns the first violation since the last call -- out4 = {code (0: none; 1 weight
+ * tile, 2 output, 3 scratch, 4 KV slice), offending offset, block | thread << 32, number of
+ * violations} -- and clears the record.  lmb_debug_bounds_shrink makes later launches claim their
+ * weight buffers `bytes` shorter than they are (a test hook: the check trips, every access that does
+ * run is inside the real buffer).  In the ordinary library both return LMB_ERR_STATE. */
+int lmb_debug_bounds(lmb_ctx *ctx, unsigned long long out4[4]);
+int lmb_debug_bounds_shrink(size_t bytes);
 /* Launch timeline (debugging; no counterpart in the reference).  cap_launches > 0 on the first call
  * switches recording on for the GEMV and attention launches issued (or captured into a graph) from
  * then on, up to cap_launches per decode step.  Every call synchronises, copies the slots recorded

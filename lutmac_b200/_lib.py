@@ -10,7 +10,8 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "liblutmac_b200.so")
+# LMB_DEBUG_BOUNDS=1 selects the range-checking build (python -m lutmac_b200.build --debug-bounds)
+LIB_PATH = os.path.join(HERE, "liblutmac_b200_dbg.so" if os.environ.get("LMB_DEBUG_BOUNDS") == "1" else "liblutmac_b200.so")
 
 OK = 0
 ERR_ARG, ERR_CUDA, ERR_ALLOC, ERR_TIMEOUT, ERR_FORMAT, ERR_LIMIT, ERR_STATE = 1, 2, 3, 4, 5, 6, 7
@@ -85,6 +86,8 @@ SIGNATURES = {
     "lmb_debug_plan_weight": (C.c_int, [vp, C.c_int, C.POINTER(C.c_int)]),
     "lmb_debug_launch_timeline": (C.c_int, [vp, sz, vp, C.POINTER(sz)]),
     "lmb_debug_force_plan": (C.c_int, [C.c_int, C.c_int, C.c_int]),
+    "lmb_debug_bounds": (C.c_int, [vp, C.POINTER(C.c_ulonglong)]),
+    "lmb_debug_bounds_shrink": (C.c_int, [sz]),
     "lmb_debug_luts": (C.c_int, [vp, vp, sz, C.c_uint, vp]),
     "lmb_debug_ternary_indices": (C.c_int, [vp, vp, vp]),
     "lmb_model_create": (C.c_int, [vp, C.POINTER(ModelConfig), C.POINTER(vp)]),

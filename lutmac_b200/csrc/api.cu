@@ -163,6 +163,19 @@ static int default_ctx(lmb_ctx **out) {
 
 using namespace lmb;
 
+#ifdef LMB_DEBUG_BOUNDS
+namespace lmb {
+size_t g_bounds_shrink = 0;
+namespace {
+std::vector<BoundsReader> &bounds_readers() {
+  static std::vector<BoundsReader> v;
+  return v;
+}
+}  // namespace
+void register_bounds_reader(BoundsReader fn) { bounds_readers().push_back(fn); }
+}  // namespace lmb
+#endif
+
 extern "C" {
 
 const char *lmb_strerror(int status) {
@@ -229,6 +242,40 @@ int lmb_ctx_create(int device, lmb_ctx **out) {
   }
   *out = ctx;
   return LMB_OK;
+}
+
+int lmb_debug_bounds(lmb_ctx *ctx, unsigned long long out4[4]) {
+  LMB_REQUIRE(ctx && out4, "lmb_debug_bounds: null argument");
+#ifdef LMB_DEBUG_BOUNDS
+  LMB_CUDA(cudaSetDevice(ctx->device));
+  LMB_CUDA(cudaStreamSynchronize(ctx->stream));
+  out4[0] = out4[1] = out4[2] = out4[3] = 0;
+  for (lmb::BoundsReader fn : lmb::bounds_readers()) {
+    unsigned long long r[4] = {0, 0, 0, 0};
+    LMB_CUDA(static_cast<cudaError_t>(fn(r, true)));
+    if (r[0] && !out4[0]) {
+      out4[0] = r[0];
+      out4[1] = r[1];
+      out4[2] = r[2];
+    }
+    out4[3] += r[3];
+  }
+  return LMB_OK;
+#else
+  set_last_error("lmb_debug_bounds: this library was built without -DLMB_DEBUG_BOUNDS (python -m lutmac_b200.build --debug-bounds)");
+  return LMB_ERR_STATE;
+#endif
+}
+
+int lmb_debug_bounds_shrink(size_t bytes) {
+#ifdef LMB_DEBUG_BOUNDS
+  lmb::g_bounds_shrink = bytes;
+  return LMB_OK;
+#else
+  (void)bytes;
+  set_last_error("lmb_debug_bounds_shrink: this library was built without -DLMB_DEBUG_BOUNDS");
+  return LMB_ERR_STATE;
+#endif
 }
 
 int lmb_debug_launch_timeline(lmb_ctx *ctx, size_t cap_launches, unsigned long long *out, size_t *n_launches) {

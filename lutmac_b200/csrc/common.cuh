@@ -209,6 +209,15 @@ inline unsigned long long *timeline_slot(lmb_ctx *ctx) {
   return ctx->d_timeline + size_t(8) * size_t(ctx->timeline_cursor++);
 }
 
+#ifdef LMB_DEBUG_BOUNDS
+namespace lmb {
+// test hook of the range-checking build: launches claim their weight buffers this many bytes shorter
+// than they are, so that the check of the last tiles trips (and skips the loads) while every access
+// that does run stays inside the real buffer
+extern size_t g_bounds_shrink;
+}
+#endif
+
 struct lmb_weight {
   int kind = 0;      // device layout kind (a reference kind, or DK_TERNARY_MMA)
   int ref_kind = 0;  // reference block kind

@@ -140,6 +140,9 @@ struct AttnArgs {
   unsigned *counters;
   int n_splits;
   size_t layer;
+#ifdef LMB_DEBUG_BOUNDS
+  size_t kv_floats;  // extent of `kv`
+#endif
 };
 
 // FRESH_CG: the fresh projections were written earlier in the SAME kernel launch (persistent
@@ -453,8 +456,13 @@ __device__ __forceinline__ bool attn_group_item(const AttnArgs &a, const RopeDim
   // cached rows of the slice: all in flight at once
   if (tid == 0) {
     fence_proxy_async_smem();  // earlier generic-proxy accesses of this memory precede the asynchronous writes
-    mbar_arrive_expect_tx(bar, unsigned(2 * n_old) * row_bytes);
-    if (n_old) {
+#ifdef LMB_DEBUG_BOUNDS
+    const bool slice_ok = LMB_IN_BOUNDS(size_t(vc - a.kv) + (t0 + n_old) * hd <= a.kv_floats, BOUNDS_KV_SLICE, size_t(vc - a.kv) + (t0 + n_old) * hd);
+#else
+    const bool slice_ok = true;
+#endif
+    mbar_arrive_expect_tx(bar, slice_ok ? unsigned(2 * n_old) * row_bytes : 0u);  // a refused slice is not copied
+    if (n_old && slice_ok) {
       bulk_copy_g2s(Ks, kc + t0 * hd, unsigned(n_old) * row_bytes, bar);
       bulk_copy_g2s(Vs, vc + t0 * hd, unsigned(n_old) * row_bytes, bar);
     }

@@ -236,6 +236,9 @@ int launch_decode_attn_group(lmb_ctx *ctx, const float *q, const float *k, const
   RopeDims d = d0;
   d.split_len = plan.split_len;
   AttnArgs a{q, k, v, qb, kb, vb, cs_table, positions, kv, out, partial, counters, plan.n_splits, layer};
+#ifdef LMB_DEBUG_BOUNDS
+  a.kv_floats = d.seq_stride * batch;  // the cache holds at least the sequences of this launch
+#endif
   dim3 grid(unsigned(d.nkv * size_t(plan.n_splits)), unsigned(batch));
   unsigned *flag = ctx->d_fault;  // set when a bounded wait for the bulk copies runs out
   // programmatic dependent launch: the CTAs start fetching their cache slices while the q/k/v

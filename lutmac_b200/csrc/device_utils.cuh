@@ -138,4 +138,50 @@ __device__ __forceinline__ void tl_max(unsigned long long *dbg, int w) {
   if (dbg) atomicMax(dbg + w, tl_now());
 }
 
+
+// Range-checking build (-DLMB_DEBUG_BOUNDS, liblutmac_b200_dbg.so): LMB_IN_BOUNDS(cond, code, value)
+// is `cond`, and a false one records the first violation of this translation unit -- code, value,
+// block and thread -- instead of letting the access run: the caller skips it, nothing traps.  In
+// the ordinary build the macro is `true` and the checks cost nothing.
+enum BoundsCode : unsigned { BOUNDS_WEIGHT_TILE = 1, BOUNDS_OUTPUT = 2, BOUNDS_SCRATCH = 3, BOUNDS_KV_SLICE = 4, BOUNDS_PREP = 5 };
+#ifdef LMB_DEBUG_BOUNDS
+namespace {
+__device__ unsigned long long tu_bounds[4];  // {code (0: clean), value, block | thread << 32, count}
+}
+__device__ __forceinline__ bool bounds_ok(bool ok, unsigned code, unsigned long long value) {
+  if (!ok) {
+    if (atomicCAS(&tu_bounds[0], 0ull, static_cast<unsigned long long>(code)) == 0ull) {
+      tu_bounds[1] = value;
+      tu_bounds[2] = static_cast<unsigned long long>(blockIdx.x) | (static_cast<unsigned long long>(threadIdx.x) << 32);
+    }
+    atomicAdd(&tu_bounds[3], 1ull);
+  }
+  return ok;
+}
+#define LMB_IN_BOUNDS(cond, code, value) (::lmb::bounds_ok((cond), (code), static_cast<unsigned long long>(value)))
+#else
+#define LMB_IN_BOUNDS(cond, code, value) (true)
+#endif
+
 }  // namespace lmb
+
+#ifdef LMB_DEBUG_BOUNDS
+// every translation unit with checked kernels registers a reader of its record (see api.cu)
+namespace lmb {
+using BoundsReader = int (*)(unsigned long long out[4], bool clear);
+void register_bounds_reader(BoundsReader fn);
+namespace {
+inline int read_tu_bounds(unsigned long long out[4], bool clear) {
+  cudaError_t e = cudaMemcpyFromSymbol(out, tu_bounds, 4 * sizeof(unsigned long long));
+  if (e == cudaSuccess && clear) {
+    const unsigned long long zero[4] = {0, 0, 0, 0};
+    e = cudaMemcpyToSymbol(tu_bounds, zero, sizeof(zero));
+  }
+  return int(e);
+}
+const struct BoundsRegistrar {
+  BoundsRegistrar() { register_bounds_reader(&read_tu_bounds); }
+} bounds_registrar;
+}  // namespace
+}  // namespace lmb
+#endif

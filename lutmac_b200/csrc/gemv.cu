@@ -68,6 +68,11 @@ struct Job {
   float *next_sumsq;        // [block] sum of squares of the block's outputs (the consumer's RMSNorm statistic)
   const float *next_w;      // weight of the norm between this projection and the next (null: none)
   int next_rotate;
+#ifdef LMB_DEBUG_BOUNDS
+  size_t tiles_bytes;   // extent of `tiles`
+  size_t y_floats;      // extent of `y`
+  size_t scratch_floats;  // extent of `scratch`
+#endif
 };
 
 // One prepared (sequence, block): 256 words of digits in B-operand order, block scale, two digit-pair sums, pad.
@@ -150,10 +155,15 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
   // weights do not depend on the preceding kernel: fetch the first units before waiting for it
   constexpr int NSLOT = (NSEQ > 2 ? 1 : prefetch_depth(KIND)) + 1;  // a ring of row-blocks held in registers
   U slot[NSLOT];
+#ifdef LMB_DEBUG_BOUNDS
+  auto tile_ok = [&](const uint8_t *tp) { return LMB_IN_BOUNDS(size_t(tp - job.tiles) + TB <= job.tiles_bytes, BOUNDS_WEIGHT_TILE, tp - job.tiles); };
+#else
+  auto tile_ok = [](const uint8_t *) { return true; };
+#endif
   if (active) {
 #pragma unroll
     for (int sl = 0; sl < NSLOT; ++sl)
-      if (sub + sl * wpr < ns) slot[sl].load(row_tiles + size_t(sub + sl * wpr) * TB, lane);
+      if (sub + sl * wpr < ns && tile_ok(row_tiles + size_t(sub + sl * wpr) * TB)) slot[sl].load(row_tiles + size_t(sub + sl * wpr) * TB, lane);
   }
 
   pdl_wait();
@@ -343,7 +353,7 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
           const int bl = base + sl * wpr;
           if (bl < ns) {
             slot[sl].template eval<NP, (NSEQ > 1)>(xo, bl, accs);
-            if (bl + NSLOT * wpr < ns) slot[sl].load(row_tiles + size_t(bl + NSLOT * wpr) * TB, lane);
+            if (bl + NSLOT * wpr < ns && tile_ok(row_tiles + size_t(bl + NSLOT * wpr) * TB)) slot[sl].load(row_tiles + size_t(bl + NSLOT * wpr) * TB, lane);
           }
         }
       }
@@ -360,7 +370,7 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
           const int bl = base + sl * wpr;
           if (bl < ns) {
             slot[sl].eval(smem + size_t(bl) * FPB, xsum[bl], xaux + 4 * bl, accs);
-            if (bl + NSLOT * wpr < ns) slot[sl].load(row_tiles + size_t(bl + NSLOT * wpr) * TB, lane);
+            if (bl + NSLOT * wpr < ns && tile_ok(row_tiles + size_t(bl + NSLOT * wpr) * TB)) slot[sl].load(row_tiles + size_t(bl + NSLOT * wpr) * TB, lane);
           }
         }
       }
@@ -389,6 +399,9 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
   // one output element; with tensor parallelism it goes to this rank's slot in every rank's block
   auto emit = [&](int q, float o) {
     const size_t at = size_t(batch0 + q) * job.y_stride + row;
+#ifdef LMB_DEBUG_BOUNDS
+    if (!LMB_IN_BOUNDS(at < job.y_floats, BOUNDS_OUTPUT, at)) return;
+#endif
     if (p.peer.n == 0) {
       job.y[at] = o;
     } else {
@@ -482,7 +495,13 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
   if (owns_row) {
 #pragma unroll
     for (int q = 0; q < NSEQ; ++q)
-      if (q < nb) job.scratch[(size_t(batch0 + q) * job.n_ks + ks) * job.mp + row] = s[q];
+      if (q < nb) {
+        const size_t at = (size_t(batch0 + q) * job.n_ks + ks) * job.mp + row;
+#ifdef LMB_DEBUG_BOUNDS
+        if (!LMB_IN_BOUNDS(at < job.scratch_floats, BOUNDS_SCRATCH, at)) continue;
+#endif
+        job.scratch[at] = s[q];
+      }
   }
   __syncthreads();
   unsigned *ctr = job.counters + size_t(blockIdx.y) * job.n_rg + rg;
@@ -776,6 +795,11 @@ int prepare_jobs(lmb_ctx *ctx, int kind, const LinearArgs *args, int njobs, Job 
     jb.next_sumsq = args[j].next_sumsq;
     jb.next_w = args[j].next_w;
     jb.next_rotate = args[j].next_rotate ? 1 : 0;
+#ifdef LMB_DEBUG_BOUNDS
+    jb.tiles_bytes = w->bytes > g_bounds_shrink ? w->bytes - g_bounds_shrink : 0;
+    jb.y_floats = (batch - 1) * args[j].y_stride + w->M;
+    jb.scratch_floats = pl.n_ks > 1 && !cluster ? batch * size_t(pl.n_ks) * size_t(jb.mp) : 0;
+#endif
     if (pl.n_ks > 1 && !cluster) {
       scratch_off += batch * pl.n_ks * jb.mp;
       counter_off += ny * pl.n_rg;
@@ -1295,6 +1319,11 @@ int lmb_linear_static_scratch(const lmb_weight *w, const float *d_bias, const fl
   jb.x_len = unsigned(x_len);
   jb.x_stride = unsigned(x_len);
   jb.y_stride = unsigned(w->M);
+#ifdef LMB_DEBUG_BOUNDS
+  jb.tiles_bytes = w->bytes;
+  jb.y_floats = w->M;
+  jb.scratch_floats = LMB_STATIC_SCRATCH_FLOATS;
+#endif
   lmb_ctx launch_ctx;  // plain launch on the caller's stream, no programmatic dependent launch
   launch_ctx.device = dev;
   launch_ctx.stream = stream;
