@@ -242,7 +242,7 @@ int lmb_debug_bounds_shrink(size_t bytes);
  * since the previous call to `out` (8 words per launch, *n_launches of them, device global-timer
  * nanoseconds: 0 first CTA started, 1 / 2 first / last CTA past the wait for the preceding kernel,
  * 3 last CTA with its activations ready, 4 last CTA through its main loop, 5 / 6 last / first CTA
- * done, 7 unused) and clears them; minima and maxima accumulate over the steps run in between,
+ * done, 7 last CTA with its activations fetched into shared memory, GEMV only) and clears them; minima and maxima accumulate over the steps run in between,
  * so run one step between two calls.  out may be null. */
 int lmb_debug_launch_timeline(lmb_ctx *ctx, size_t cap_launches, unsigned long long *out, size_t *n_launches);
 int lmb_debug_luts(lmb_ctx *ctx, const float *d_x, size_t x_len, unsigned flags, float *d_luts_out);

@@ -288,7 +288,7 @@ int lmb_debug_launch_timeline(lmb_ctx *ctx, size_t cap_launches, unsigned long l
     ctx->timeline_cap = int(cap_launches);
     ctx->timeline_cursor = 0;
   }
-  const size_t n = size_t(ctx->timeline_cursor), words = size_t(ctx->timeline_cap) * 8;
+  const size_t n = size_t(ctx->timeline_used), words = size_t(ctx->timeline_cap) * 8;
   if (out && n) LMB_CUDA(cudaMemcpy(out, ctx->d_timeline, n * 8 * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
   *n_launches = n;
   std::vector<unsigned long long> init(words, 0ull);  // minima start at the largest value, maxima at 0

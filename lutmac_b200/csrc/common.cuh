@@ -193,7 +193,7 @@ struct lmb_ctx {
   unsigned *d_fault = nullptr;
   // launch timeline (debugging, lmb_debug_launch_timeline): 8 time stamps per launch, null when off
   unsigned long long *d_timeline = nullptr;
-  int timeline_cap = 0, timeline_cursor = 0;
+  int timeline_cap = 0, timeline_cursor = 0, timeline_used = 0;  // used: most slots any step has taken (graph replays launch nothing)
   void *h_upload = nullptr;  // pinned staging of lmb_weight_upload
   size_t h_upload_bytes = 0;
   // staging buffers of the host-pointer entry points
@@ -206,7 +206,9 @@ struct lmb_ctx {
 // The next launch's slot of the launch timeline, or null (off / full).
 inline unsigned long long *timeline_slot(lmb_ctx *ctx) {
   if (!ctx->d_timeline || ctx->timeline_cursor >= ctx->timeline_cap) return nullptr;
-  return ctx->d_timeline + size_t(8) * size_t(ctx->timeline_cursor++);
+  unsigned long long *slot = ctx->d_timeline + size_t(8) * size_t(ctx->timeline_cursor++);
+  if (ctx->timeline_cursor > ctx->timeline_used) ctx->timeline_used = ctx->timeline_cursor;
+  return slot;
 }
 
 #ifdef LMB_DEBUG_BOUNDS

@@ -104,6 +104,15 @@ struct GemvParams {
   // K slices of a row group are added up through distributed shared memory instead of a scratch
   // buffer and an arrival counter.  0 or 1: no clusters.
   int cl_size;
+  // Batch 1, integer-MMA kinds: all threads first fetch the CTA's K slice of the activations into the
+  // (equally large) digit area of shared memory in one sweep -- with XMODE_RMSNORM the same sweep
+  // sums the squares of the whole vector -- and the warps then convert the blocks in place, so that
+  // the conversion rounds wait for no global load.  0: every warp fetches the blocks it converts.
+  int staged;
+  // CTAs that become resident while the preceding kernel is still running have nothing to do until
+  // it ends: with this set they ask for the rest of their weight range (beyond the register ring) to
+  // be brought into L2 meanwhile.  Hints only: no register or shared memory is tied up.
+  int l2_prefetch;
 };
 
 template <int KIND, int NSEQ>
@@ -150,6 +159,7 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
   const bool active = rtl < nrt && sub < ns;
   const uint8_t *row_tiles = job.tiles + (size_t(rt0 + rtl) * job.bpr + b0) * TB;
   const bool clustered = NSEQ == 1 && kind_is_mma(KIND) && p.cl_size > 1;  // uniform over the launch
+  const bool staged = NSEQ == 1 && kind_is_mma(KIND) && !clustered && !p.prep && p.staged;
   const int crank = clustered ? local % p.cl_size : 0;                    // rank in the cluster (job starts are multiples of cl_size)
 
   // weights do not depend on the preceding kernel: fetch the first units before waiting for it
@@ -166,6 +176,14 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
       if (sub + sl * wpr < ns && tile_ok(row_tiles + size_t(sub + sl * wpr) * TB)) slot[sl].load(row_tiles + size_t(sub + sl * wpr) * TB, lane);
   }
 
+  if (p.l2_prefetch && active) {
+    constexpr int LINES = int((TB + 127) / 128);
+    for (int bl = sub + NSLOT * wpr; bl < ns; bl += wpr) {
+      const uint8_t *tp = row_tiles + size_t(bl) * TB;
+      if (lane < LINES && tile_ok(tp)) asm volatile("prefetch.global.L2 [%0];" ::"l"(tp + size_t(lane) * 128));
+    }
+  }
+
   pdl_wait();
   if (threadIdx.x == 0) {
     tl_min(p.dbg, 1);
@@ -176,7 +194,7 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
   const unsigned epoch = p.peer.n ? *reinterpret_cast<volatile unsigned *>(p.peer.epoch) : 0u;
   const float *x = job.x + size_t(batch0) * job.x_stride;
   float *inv_rms = part[0];  // [sequence] after the block below (XMODE_RMSNORM)
-  if (p.xmode == XMODE_RMSNORM && !p.prep && !clustered) {
+  if (p.xmode == XMODE_RMSNORM && !p.prep && !clustered && !staged) {
     // RMSNorm of the whole input vectors (src/layers/norm.cpp:18-34), recomputed by every CTA
     float ss[NSEQ];
 #pragma unroll
@@ -299,7 +317,69 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
       }
     }
   }
-  if (!(kind_is_mma(KIND) && p.prep) && !clustered) {
+  if constexpr (NSEQ == 1 && kind_is_mma(KIND)) {
+    if (staged) {
+      float *stage = smem;  // ns * 256 floats, then (block by block, in place) their digits
+      const size_t g0 = size_t(b0) * BLK, x_len = job.x_len;
+      const int nslice = ns * BLK;
+      const bool vec = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(job.x2)) & 15) == 0 && (x_len & 3) == 0;
+      // four consecutive elements starting at i (a multiple of 4), zeros beyond the vector
+      auto ld4 = [&](const float *src, size_t i) {
+        if (vec) return i < x_len ? *reinterpret_cast<const float4 *>(src + i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        return make_float4(i < x_len ? src[i] : 0.0f, i + 1 < x_len ? src[i + 1] : 0.0f, i + 2 < x_len ? src[i + 2] : 0.0f,
+                           i + 3 < x_len ? src[i + 3] : 0.0f);
+      };
+      float ss = 0.0f;
+      for (int i = int(threadIdx.x) * 4; i < nslice; i += THREADS * 4) {
+        float4 v = ld4(x, g0 + size_t(i));
+        if (p.xmode == XMODE_RMSNORM) {
+          const float4 w = ld4(job.x2, g0 + size_t(i));
+          ss += (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
+          v = make_float4(v.x * w.x, v.y * w.y, v.z * w.z, v.w * w.w);
+        } else if (p.xmode == XMODE_SILU_MUL) {  // silu(gate) * up, model.cpp:36,414-416
+          const float4 u = ld4(job.x2 + size_t(batch0) * job.x_stride, g0 + size_t(i));
+          v = make_float4((v.x / (1.0f + expf(-v.x))) * u.x, (v.y / (1.0f + expf(-v.y))) * u.y, (v.z / (1.0f + expf(-v.z))) * u.z,
+                          (v.w / (1.0f + expf(-v.w))) * u.w);
+        } else if (p.xmode == XMODE_GELU_MUL) {  // gelu(gate) * up, model.cpp:38-42,409-412
+          const float4 u = ld4(job.x2 + size_t(batch0) * job.x_stride, g0 + size_t(i));
+          v = make_float4(gelu_tanh(v.x) * u.x, gelu_tanh(v.y) * u.y, gelu_tanh(v.z) * u.z, gelu_tanh(v.w) * u.w);
+        }
+        *reinterpret_cast<float4 *>(stage + i) = v;
+      }
+      float ir = 1.0f;
+      if (p.xmode == XMODE_RMSNORM) {
+        // src/layers/norm.cpp:18-34: the sum of squares runs over the whole vector, also outside this CTA's K slice
+        if (job.n_ks > 1) {
+          for (size_t i = size_t(threadIdx.x) * 4; i < x_len; i += size_t(THREADS) * 4) {
+            if (i >= g0 && i < g0 + size_t(nslice)) continue;
+            const float4 v = ld4(x, i);
+            ss += (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
+          }
+        }
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
+        if (lane == 0) xsum[warp] = ss;  // xsum is free until the conversion below
+        __syncthreads();
+        float t = 0.0f;
+#pragma unroll
+        for (int k = 0; k < WARPS; ++k) t += xsum[k];
+        ir = 1.0f / sqrtf(t / float(x_len) + p.eps);
+      }
+      __syncthreads();  // the slice is staged; xsum has been read
+      if (threadIdx.x == 0) tl_max(p.dbg, 7);
+      for (int bl = warp; bl < ns; bl += WARPS) {
+        float *blk = stage + size_t(bl) * BLK;
+        const float4 a = *reinterpret_cast<const float4 *>(blk + 8 * lane), c = *reinterpret_cast<const float4 *>(blk + 8 * lane + 4);
+        float v[8] = {a.x * ir, a.y * ir, a.z * ir, a.w * ir, c.x * ir, c.y * ir, c.z * ir, c.w * ir};
+        if (p.rotate) fwht256_warp(v, lane);
+        __syncwarp();  // every lane holds its eight values: the block's floats may be overwritten
+        int *aux = xaux + bl * 4;
+        U::prologue(v, lane, blk, xsum + bl, aux);
+        if (lane == 0) aux[2] = aux[3] = 0;  // no second sequence
+      }
+    }
+  }
+  if (!(kind_is_mma(KIND) && p.prep) && !clustered && !staged) {
     // one warp per (sequence, block); the next item's activations are fetched while this one is converted
     float v[8], w8[8], nv[8];
     const int items = ns * nb;
@@ -380,7 +460,7 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
 
   // combine the warps that share a row-tile, in warp order: thread t ends up with row rt0*32 + t
   if (threadIdx.x == 0) tl_max(p.dbg, 4);
-  if (p.xmode == XMODE_RMSNORM && !p.prep && !clustered) __syncthreads();  // inv_rms (in part[0]) has been read by everyone
+  if (p.xmode == XMODE_RMSNORM && !p.prep && !clustered && !staged) __syncthreads();  // inv_rms (in part[0]) has been read by everyone
 #pragma unroll
   for (int q = 0; q < NSEQ; ++q) part[q][threadIdx.x] = acc[q];
   __syncthreads();
@@ -506,9 +586,11 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
   __syncthreads();
   unsigned *ctr = job.counters + size_t(blockIdx.y) * job.n_rg + rg;
   if (t == 0) {
-    __threadfence();  // cumulative: publishes the CTA's partial sums (ordered before it by the barrier)
-    is_last = (atomicAdd(ctr, 1u) == unsigned(job.n_ks - 1));
-    __threadfence();
+    // release: this CTA's partial sums (ordered before the atomic by the barrier above, and release is
+    // cumulative); acquire: the partial sums of the slices that arrived earlier
+    unsigned before;
+    asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(before) : "l"(ctr) : "memory");
+    is_last = (before == unsigned(job.n_ks - 1));
   }
   __syncthreads();
   if (!is_last) {  // uniform over the CTA
@@ -617,7 +699,26 @@ struct PlanForce {
   }
 };
 PlanForce g_plan_force;
-// LMB_GEMV_CLUSTER=0: no thread-block clusters in any plan.
+// LMB_GEMV_STAGED=0: the warps of a CTA fetch the activation blocks they convert themselves.
+inline bool staged_prologue_enabled() {
+  static const bool on = [] {
+    const char *e = std::getenv("LMB_GEMV_STAGED");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+// LMB_GEMV_L2_PREFETCH=1: see GemvParams::l2_prefetch.
+inline bool l2_prefetch_enabled() {
+  static const bool on = [] {
+    const char *e = std::getenv("LMB_GEMV_L2_PREFETCH");
+    return e && e[0] == '1';
+  }();
+  return on;
+}
+// LMB_GEMV_CLUSTER=0: no thread-block clusters in any plan (a plan forced with lmb_debug_force_plan may
+// still use them).  A cluster starts only when all its CTAs find room at once, which costs part of the
+// overlap with the preceding kernel's tail (1.5 to 5 us measured on the 70B-shaped decode step): the
+// planner charges that, so clusters are chosen only where they save several conversion rounds.
 inline bool clusters_allowed() {
   static const bool ok = [] {
     const char *e = std::getenv("LMB_GEMV_CLUSTER");
@@ -646,10 +747,10 @@ Plan make_plan(int kind, size_t row_tiles, size_t bpr, size_t batch, int sm_coun
   // 48 KiB of tables / activations per CTA (96 KiB when 4 or 8 sequences share a pass)
   const size_t s_cap = lut ? 12 : nseq == 1 ? 48 : nseq == 8 ? 12 : 24;
   const size_t slots = size_t(sm_count) * (min_ctas(kind, nseq) == 1 ? 1 : ctas_per_sm(kind));
-  const double prologue_per_block = 1.5 * nseq, fixed = 1.5, split_cost = 2.5, cluster_sync = 0.5, cluster_split = 0.8;
+  const double prologue_per_block = 1.5 * nseq, fixed = 1.5, split_cost = 2.5, cluster_sync = 3.0, cluster_split = 0.8;
   const bool throughput = (other_row_tiles + 7) / 8 * batch >= 2 * slots;
   const bool may_cluster = cluster != 0 && kind_is_mma(kind) && nseq == 1 && batch == 1 && bpr <= size_t(MAX_CLUSTER_BLOCKS) &&
-                           clusters_allowed();
+                           (clusters_allowed() || (force.on && force.cr > 0));
   Plan best{};
   if (force.on && batch == 1 && nseq == 1 && force.n_ks >= 1 && size_t(force.n_ks) <= bpr) {
     const size_t fS = (bpr + size_t(force.n_ks) - 1) / size_t(force.n_ks), fc = size_t(force.cr) * size_t(force.n_ks);
@@ -961,6 +1062,8 @@ int launch_gemv(lmb_ctx *ctx, const LinearArgs *args, int njobs, bool rotate, in
   int st = prepare_jobs(ctx, kind, args, njobs, p.job, &ctas, &s_max, nullptr, true, &cluster);
   if (st != LMB_OK) return st;
   p.cl_size = cluster;
+  p.staged = staged_prologue_enabled() ? 1 : 0;
+  p.l2_prefetch = l2_prefetch_enabled() && ctx->pdl && args[0].batch == 1 ? 1 : 0;
   p.prep_sumsq = nullptr;
   p.prep_sumsq_n = 0;
   if (args[0].prep_in) {  // the producing GEMV prepared the activations (batch 1)
@@ -1103,6 +1206,8 @@ int lmb_group_launch(lmb_ctx *ctx, lmb_group *g) {
   p.prep_sumsq = nullptr;
   p.prep_sumsq_n = 0;
   p.cl_size = 0;
+  p.staged = staged_prologue_enabled() ? 1 : 0;
+  p.l2_prefetch = 0;
   return launch_params_kind(ctx, g->kind, p, g->ctas, g->s_max, 1);
 }
 
@@ -1294,6 +1399,8 @@ int lmb_linear_static_scratch(const lmb_weight *w, const float *d_bias, const fl
   p.prep_sumsq = nullptr;
   p.prep_sumsq_n = 0;
   p.cl_size = 0;
+  p.staged = 0;
+  p.l2_prefetch = 0;
   Job &jb = p.job[0];
   jb.tiles = w->d_tiles;
   jb.x = d_x;

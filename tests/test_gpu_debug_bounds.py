@@ -33,7 +33,7 @@ def report():
 
 def gemv(t, x):
     w = ctx.upload(t); dx = ctx.to_device(x); dy = ctx.malloc(t.M * 4)
-    ctx.linear(w, dx, dy, x_len=x.size, x_stride=x.size)
+    ctx.linear(w, dx, dy, flags=0, x_len=x.size, x_stride=x.size)
     y = dy.download(np.float32); w.free()
     return y
 
