@@ -6,6 +6,7 @@
 #include "device_utils.cuh"
 
 #include <algorithm>
+#include <cstdlib>
 
 namespace lmb {
 
@@ -252,7 +253,11 @@ int launch_decode_attn_group(lmb_ctx *ctx, const float *q, const float *k, const
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = ctx->pdl ? 1 : 0;
+  static const bool attn_pdl = [] {  // LMB_ATTN_PDL=0: the attention kernel starts only when the q/k/v projections have finished
+    const char *e = std::getenv("LMB_ATTN_PDL");
+    return !(e && e[0] == '0');
+  }();
+  cfg.numAttrs = ctx->pdl && attn_pdl ? 1 : 0;
   unsigned long long *tl = timeline_slot(ctx);
   if (plan.per == 4) LMB_CUDA(cudaLaunchKernelEx(&cfg, k_decode_attn_group<4>, a, d, ctx->xchg.spin_limit, flag, tl));
   else LMB_CUDA(cudaLaunchKernelEx(&cfg, k_decode_attn_group<2>, a, d, ctx->xchg.spin_limit, flag, tl));

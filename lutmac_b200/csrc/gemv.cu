@@ -104,19 +104,17 @@ struct GemvParams {
   // K slices of a row group are added up through distributed shared memory instead of a scratch
   // buffer and an arrival counter.  0 or 1: no clusters.
   int cl_size;
-  // Batch 1, integer-MMA kinds: all threads first fetch the CTA's K slice of the activations into the
-  // (equally large) digit area of shared memory in one sweep -- with XMODE_RMSNORM the same sweep
-  // sums the squares of the whole vector -- and the warps then convert the blocks in place, so that
-  // the conversion rounds wait for no global load.  0: every warp fetches the blocks it converts.
-  int staged;
-  // CTAs that become resident while the preceding kernel is still running have nothing to do until
-  // it ends: with this set they ask for the rest of their weight range (beyond the register ring) to
-  // be brought into L2 meanwhile.  Hints only: no register or shared memory is tied up.
-  int l2_prefetch;
+  // Row-blocks beyond the register ring that every warp asks to be brought into L2 before it waits for
+  // the preceding kernel (hints: no registers, no shared memory): the stream then starts from L2 while
+  // the CTAs convert their activations.  0: none.
+  int l2_tiles;
 };
 
-template <int KIND, int NSEQ>
+// CLUSTERED: the instantiation launched with thread-block clusters (GemvParams::cl_size); kept apart so
+// that the ordinary kernel carries none of its code.
+template <int KIND, int NSEQ, bool CLUSTERED = false>
 __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __grid_constant__ GemvParams p) {
+  static_assert(!CLUSTERED || (NSEQ == 1 && kind_is_mma(KIND)), "clusters: batch 1, integer-MMA kinds");
   // NSEQ sequences share one pass over the weights (integer-MMA kinds only: two sequences per
   // MMA); the other kinds run one sequence per CTA, blockIdx.y selecting it.
   static_assert(NSEQ == 1 || kind_is_mma(KIND), "several sequences per pass need an integer-MMA kind");
@@ -129,7 +127,7 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
   __shared__ float xsum[NSEQ * 64];
   __shared__ __align__(16) int xaux[NP * 64 * 4];
   __shared__ int is_last;
-  __shared__ float xss[MAX_CLUSTER_BLOCKS];  // cluster mode: sum of squares of every 256-block of the input
+  __shared__ float xss[CLUSTERED ? MAX_CLUSTER_BLOCKS : 1];  // cluster mode: sum of squares of every 256-block of the input
 
   pdl_launch_dependents();
   if (threadIdx.x == 0) tl_min(p.dbg, 0);
@@ -158,8 +156,7 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
   const int ns = min(job.S, job.bpr - b0);
   const bool active = rtl < nrt && sub < ns;
   const uint8_t *row_tiles = job.tiles + (size_t(rt0 + rtl) * job.bpr + b0) * TB;
-  const bool clustered = NSEQ == 1 && kind_is_mma(KIND) && p.cl_size > 1;  // uniform over the launch
-  const bool staged = NSEQ == 1 && kind_is_mma(KIND) && !clustered && !p.prep && p.staged;
+  constexpr bool clustered = CLUSTERED;
   const int crank = clustered ? local % p.cl_size : 0;                    // rank in the cluster (job starts are multiples of cl_size)
 
   // weights do not depend on the preceding kernel: fetch the first units before waiting for it
@@ -176,11 +173,11 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
       if (sub + sl * wpr < ns && tile_ok(row_tiles + size_t(sub + sl * wpr) * TB)) slot[sl].load(row_tiles + size_t(sub + sl * wpr) * TB, lane);
   }
 
-  if (p.l2_prefetch && active) {
+  if (p.l2_tiles > 0 && active) {
     constexpr int LINES = int((TB + 127) / 128);
-    for (int bl = sub + NSLOT * wpr; bl < ns; bl += wpr) {
-      const uint8_t *tp = row_tiles + size_t(bl) * TB;
-      if (lane < LINES && tile_ok(tp)) asm volatile("prefetch.global.L2 [%0];" ::"l"(tp + size_t(lane) * 128));
+    for (int k = 0; k < p.l2_tiles; ++k) {
+      const int bl = sub + (NSLOT + k) * wpr;
+      if (bl < ns && lane < LINES) asm volatile("prefetch.global.L2 [%0];" ::"l"(row_tiles + size_t(bl) * TB + size_t(lane) * 128));
     }
   }
 
@@ -194,7 +191,7 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
   const unsigned epoch = p.peer.n ? *reinterpret_cast<volatile unsigned *>(p.peer.epoch) : 0u;
   const float *x = job.x + size_t(batch0) * job.x_stride;
   float *inv_rms = part[0];  // [sequence] after the block below (XMODE_RMSNORM)
-  if (p.xmode == XMODE_RMSNORM && !p.prep && !clustered && !staged) {
+  if (p.xmode == XMODE_RMSNORM && !p.prep && !clustered) {
     // RMSNorm of the whole input vectors (src/layers/norm.cpp:18-34), recomputed by every CTA
     float ss[NSEQ];
 #pragma unroll
@@ -225,8 +222,12 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
     if (p.prep) {
       float prep_scale = 1.0f;
       if (p.prep_sumsq) {  // src/layers/norm.cpp:18-34 with the sum of squares from the producer's per-block partials
+        // all partials in one round trip: lane l of every warp takes l, l + 32, ... (a loop of dependent
+        // loads here cost 17 us per launch)
         float tot = 0.0f;
-        for (int i = 0; i < p.prep_sumsq_n; ++i) tot += __ldcg(p.prep_sumsq + i);
+        for (int i = lane; i < p.prep_sumsq_n; i += 32) tot += __ldcg(p.prep_sumsq + i);
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, m);
         prep_scale = 1.0f / sqrtf(tot / float(job.x_len) + p.eps);
       }
       // the launch's activations were converted once (k_prepare_x, or the producing GEMV): copy this CTA's slice
@@ -249,8 +250,8 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
       }
     }
   }
-  if constexpr (NSEQ == 1 && kind_is_mma(KIND)) {
-    if (clustered) {
+  if constexpr (CLUSTERED) {
+    {
       // The cr-th of the Cr CTAs that read this K slice converts blocks cr, cr + Cr, ... and writes each
       // record into all Cr of them.  RMSNorm (src/layers/norm.cpp:18-34) is linear in 1 / rms: the
       // digits are those of x * w, every converter publishes its blocks' sums of squares to the whole
@@ -317,69 +318,7 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
       }
     }
   }
-  if constexpr (NSEQ == 1 && kind_is_mma(KIND)) {
-    if (staged) {
-      float *stage = smem;  // ns * 256 floats, then (block by block, in place) their digits
-      const size_t g0 = size_t(b0) * BLK, x_len = job.x_len;
-      const int nslice = ns * BLK;
-      const bool vec = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(job.x2)) & 15) == 0 && (x_len & 3) == 0;
-      // four consecutive elements starting at i (a multiple of 4), zeros beyond the vector
-      auto ld4 = [&](const float *src, size_t i) {
-        if (vec) return i < x_len ? *reinterpret_cast<const float4 *>(src + i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        return make_float4(i < x_len ? src[i] : 0.0f, i + 1 < x_len ? src[i + 1] : 0.0f, i + 2 < x_len ? src[i + 2] : 0.0f,
-                           i + 3 < x_len ? src[i + 3] : 0.0f);
-      };
-      float ss = 0.0f;
-      for (int i = int(threadIdx.x) * 4; i < nslice; i += THREADS * 4) {
-        float4 v = ld4(x, g0 + size_t(i));
-        if (p.xmode == XMODE_RMSNORM) {
-          const float4 w = ld4(job.x2, g0 + size_t(i));
-          ss += (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
-          v = make_float4(v.x * w.x, v.y * w.y, v.z * w.z, v.w * w.w);
-        } else if (p.xmode == XMODE_SILU_MUL) {  // silu(gate) * up, model.cpp:36,414-416
-          const float4 u = ld4(job.x2 + size_t(batch0) * job.x_stride, g0 + size_t(i));
-          v = make_float4((v.x / (1.0f + expf(-v.x))) * u.x, (v.y / (1.0f + expf(-v.y))) * u.y, (v.z / (1.0f + expf(-v.z))) * u.z,
-                          (v.w / (1.0f + expf(-v.w))) * u.w);
-        } else if (p.xmode == XMODE_GELU_MUL) {  // gelu(gate) * up, model.cpp:38-42,409-412
-          const float4 u = ld4(job.x2 + size_t(batch0) * job.x_stride, g0 + size_t(i));
-          v = make_float4(gelu_tanh(v.x) * u.x, gelu_tanh(v.y) * u.y, gelu_tanh(v.z) * u.z, gelu_tanh(v.w) * u.w);
-        }
-        *reinterpret_cast<float4 *>(stage + i) = v;
-      }
-      float ir = 1.0f;
-      if (p.xmode == XMODE_RMSNORM) {
-        // src/layers/norm.cpp:18-34: the sum of squares runs over the whole vector, also outside this CTA's K slice
-        if (job.n_ks > 1) {
-          for (size_t i = size_t(threadIdx.x) * 4; i < x_len; i += size_t(THREADS) * 4) {
-            if (i >= g0 && i < g0 + size_t(nslice)) continue;
-            const float4 v = ld4(x, i);
-            ss += (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
-          }
-        }
-#pragma unroll
-        for (int m = 16; m > 0; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
-        if (lane == 0) xsum[warp] = ss;  // xsum is free until the conversion below
-        __syncthreads();
-        float t = 0.0f;
-#pragma unroll
-        for (int k = 0; k < WARPS; ++k) t += xsum[k];
-        ir = 1.0f / sqrtf(t / float(x_len) + p.eps);
-      }
-      __syncthreads();  // the slice is staged; xsum has been read
-      if (threadIdx.x == 0) tl_max(p.dbg, 7);
-      for (int bl = warp; bl < ns; bl += WARPS) {
-        float *blk = stage + size_t(bl) * BLK;
-        const float4 a = *reinterpret_cast<const float4 *>(blk + 8 * lane), c = *reinterpret_cast<const float4 *>(blk + 8 * lane + 4);
-        float v[8] = {a.x * ir, a.y * ir, a.z * ir, a.w * ir, c.x * ir, c.y * ir, c.z * ir, c.w * ir};
-        if (p.rotate) fwht256_warp(v, lane);
-        __syncwarp();  // every lane holds its eight values: the block's floats may be overwritten
-        int *aux = xaux + bl * 4;
-        U::prologue(v, lane, blk, xsum + bl, aux);
-        if (lane == 0) aux[2] = aux[3] = 0;  // no second sequence
-      }
-    }
-  }
-  if (!(kind_is_mma(KIND) && p.prep) && !clustered && !staged) {
+  if (!(kind_is_mma(KIND) && p.prep) && !clustered) {
     // one warp per (sequence, block); the next item's activations are fetched while this one is converted
     float v[8], w8[8], nv[8];
     const int items = ns * nb;
@@ -460,7 +399,7 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
 
   // combine the warps that share a row-tile, in warp order: thread t ends up with row rt0*32 + t
   if (threadIdx.x == 0) tl_max(p.dbg, 4);
-  if (p.xmode == XMODE_RMSNORM && !p.prep && !clustered && !staged) __syncthreads();  // inv_rms (in part[0]) has been read by everyone
+  if (p.xmode == XMODE_RMSNORM && !p.prep && !clustered) __syncthreads();  // inv_rms (in part[0]) has been read by everyone
 #pragma unroll
   for (int q = 0; q < NSEQ; ++q) part[q][threadIdx.x] = acc[q];
   __syncthreads();
@@ -549,7 +488,7 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
     }
     return;
   }
-  if (clustered) {
+  if constexpr (CLUSTERED) {
     // split K inside a cluster: slice 0 of the row group adds the partial sums of the others, in slice
     // order, out of their shared memory
     __syncthreads();  // part[] has been read
@@ -699,21 +638,13 @@ struct PlanForce {
   }
 };
 PlanForce g_plan_force;
-// LMB_GEMV_STAGED=0: the warps of a CTA fetch the activation blocks they convert themselves.
-inline bool staged_prologue_enabled() {
-  static const bool on = [] {
-    const char *e = std::getenv("LMB_GEMV_STAGED");
-    return !(e && e[0] == '0');
+// LMB_GEMV_L2_TILES=n: see GemvParams::l2_tiles.
+inline int l2_tiles_setting() {
+  static const int n = [] {
+    const char *e = std::getenv("LMB_GEMV_L2_TILES");
+    return e ? std::atoi(e) : 0;
   }();
-  return on;
-}
-// LMB_GEMV_L2_PREFETCH=1: see GemvParams::l2_prefetch.
-inline bool l2_prefetch_enabled() {
-  static const bool on = [] {
-    const char *e = std::getenv("LMB_GEMV_L2_PREFETCH");
-    return e && e[0] == '1';
-  }();
-  return on;
+  return n;
 }
 // LMB_GEMV_CLUSTER=0: no thread-block clusters in any plan (a plan forced with lmb_debug_force_plan may
 // still use them).  A cluster starts only when all its CTAs find room at once, which costs part of the
@@ -955,6 +886,13 @@ template <int KIND, int NSEQ> int launch_params(lmb_ctx *ctx, GemvParams &p, int
   cfg.attrs = attr;
   cfg.numAttrs = unsigned(na);
   p.dbg = timeline_slot(ctx);
+  if constexpr (NSEQ == 1 && kind_is_mma(KIND)) {
+    if (p.cl_size > 1) {
+      LMB_CUDA(cudaLaunchKernelEx(&cfg, k_gemv<KIND, 1, true>, p));
+      ctx->launches++;
+      return LMB_OK;
+    }
+  }
   LMB_CUDA(cudaLaunchKernelEx(&cfg, k_gemv<KIND, NSEQ>, p));
   ctx->launches++;
   return LMB_OK;
@@ -997,6 +935,7 @@ int launch_params_kind(lmb_ctx *ctx, int kind, GemvParams &p, int ctas, int s_ma
 template <int KIND> int configure_mma() {
   const int small = 64 * 1024, large = 100 * 1024;
   LMB_CUDA(cudaFuncSetAttribute(k_gemv<KIND, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, small));
+  LMB_CUDA(cudaFuncSetAttribute(k_gemv<KIND, 1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, small));
   LMB_CUDA(cudaFuncSetAttribute(k_gemv<KIND, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, small));
   if constexpr (max_seqs_per_pass(KIND) >= 4)
     LMB_CUDA(cudaFuncSetAttribute(k_gemv<KIND, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, large));
@@ -1062,8 +1001,7 @@ int launch_gemv(lmb_ctx *ctx, const LinearArgs *args, int njobs, bool rotate, in
   int st = prepare_jobs(ctx, kind, args, njobs, p.job, &ctas, &s_max, nullptr, true, &cluster);
   if (st != LMB_OK) return st;
   p.cl_size = cluster;
-  p.staged = staged_prologue_enabled() ? 1 : 0;
-  p.l2_prefetch = l2_prefetch_enabled() && ctx->pdl && args[0].batch == 1 ? 1 : 0;
+  p.l2_tiles = ctx->pdl && args[0].batch == 1 ? l2_tiles_setting() : 0;
   p.prep_sumsq = nullptr;
   p.prep_sumsq_n = 0;
   if (args[0].prep_in) {  // the producing GEMV prepared the activations (batch 1)
@@ -1206,8 +1144,7 @@ int lmb_group_launch(lmb_ctx *ctx, lmb_group *g) {
   p.prep_sumsq = nullptr;
   p.prep_sumsq_n = 0;
   p.cl_size = 0;
-  p.staged = staged_prologue_enabled() ? 1 : 0;
-  p.l2_prefetch = 0;
+  p.l2_tiles = 0;
   return launch_params_kind(ctx, g->kind, p, g->ctas, g->s_max, 1);
 }
 
@@ -1399,8 +1336,7 @@ int lmb_linear_static_scratch(const lmb_weight *w, const float *d_bias, const fl
   p.prep_sumsq = nullptr;
   p.prep_sumsq_n = 0;
   p.cl_size = 0;
-  p.staged = 0;
-  p.l2_prefetch = 0;
+  p.l2_tiles = 0;
   Job &jb = p.job[0];
   jb.tiles = w->d_tiles;
   jb.x = d_x;

@@ -299,7 +299,7 @@ int lmb_model_create(lmb_ctx *ctx, const lmb_model_config *c, lmb_model **out) {
     const char *av = std::getenv("LMB_ATTN_GROUP");
     m->attn_group = !(av && av[0] == '0');
     const char *hv = std::getenv("LMB_MODEL_HANDOFF");
-    m->handoff = hv && hv[0] == '1';  // opt-in: measured slower on the 70B-shaped stack (it forces 8 row tiles per CTA and more K slices on the producers)
+    m->handoff = !(hv && hv[0] == '0');  // LMB_MODEL_HANDOFF=0: every consumer CTA converts its own activations
   }
   const size_t B = c->max_batch, h = c->hidden_size, hd = c->head_dim;
   m->seq_stride = c->num_hidden_layers * 2 * c->max_seq_len * m->nkv * hd;
