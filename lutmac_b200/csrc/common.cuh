@@ -258,11 +258,6 @@ struct LinearArgs {
   const uint32_t *prep_in = nullptr;
   const float *prep_sumsq_in = nullptr;
   int prep_sumsq_n = 0;
-  // Look-ahead: a byte range (the weights of a LATER launch) that this launch's CTAs ask to be brought
-  // into L2 as they start -- each CTA an equal share, before it waits for the preceding kernel --
-  // for launches that leave the memory idle.  Hints only; null: none.
-  const void *ahead_ptr = nullptr;
-  size_t ahead_bytes = 0;
 };
 constexpr int PREP_RECORD_WORDS = 256 + 4;  // one prepared 256-block: digits, block scale, two digit-pair sums, pad
 // How the GEMV prologue forms its activations from x.

@@ -140,8 +140,6 @@ struct AttnArgs {
   unsigned *counters;
   int n_splits;
   size_t layer;
-  const unsigned char *ahead_ptr;  // L2 look-ahead range (LinearArgs::ahead_ptr) of the group kernel, in 128-byte lines
-  unsigned ahead_lines;
 #ifdef LMB_DEBUG_BOUNDS
   size_t kv_floats;  // extent of `kv`
 #endif

@@ -112,7 +112,6 @@ __global__ void __launch_bounds__(ATT_THREADS) k_decode_attn_group(const AttnArg
                                                                     unsigned *timed_out, unsigned long long *tl) {
   asm volatile("griddepcontrol.launch_dependents;");
   if (threadIdx.x == 0) tl_min(tl, 0);
-  if (a.ahead_lines) prefetch_share_l2(a.ahead_ptr, a.ahead_lines, blockIdx.y * gridDim.x + blockIdx.x, gridDim.x * gridDim.y, ATT_THREADS);
   extern __shared__ __align__(16) float sm[];
   __shared__ __align__(8) uint64_t bar;
   __shared__ int flag;
@@ -234,11 +233,10 @@ AttnGroupPlan plan_attn_group(size_t nh, size_t nkv, size_t hd, size_t max_seq, 
 int launch_decode_attn_group(lmb_ctx *ctx, const float *q, const float *k, const float *v, const float *qb, const float *kb,
                              const float *vb, const float *cs_table, const size_t *positions, float *kv, float *out,
                              float *partial, unsigned *counters, const AttnGroupPlan &plan, size_t layer, const RopeDims &d0,
-                             size_t batch, const void *ahead_ptr, size_t ahead_bytes) {
+                             size_t batch) {
   RopeDims d = d0;
   d.split_len = plan.split_len;
-  AttnArgs a{q, k, v, qb, kb, vb, cs_table, positions, kv, out, partial, counters, plan.n_splits, layer,
-             static_cast<const unsigned char *>(ahead_ptr), ahead_ptr ? unsigned(ahead_bytes / 128) : 0u};
+  AttnArgs a{q, k, v, qb, kb, vb, cs_table, positions, kv, out, partial, counters, plan.n_splits, layer};
 #ifdef LMB_DEBUG_BOUNDS
   a.kv_floats = d.seq_stride * batch;  // the cache holds at least the sequences of this launch
 #endif

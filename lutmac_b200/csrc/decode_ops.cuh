@@ -38,7 +38,7 @@ AttnGroupPlan plan_attn_group(size_t nh, size_t nkv, size_t hd, size_t max_seq, 
 int launch_decode_attn_group(lmb_ctx *ctx, const float *q, const float *k, const float *v, const float *qb, const float *kb,
                              const float *vb, const float *cs_table, const size_t *positions, float *kv, float *out,
                              float *partial, unsigned *counters, const AttnGroupPlan &plan, size_t layer, const RopeDims &d,
-                             size_t batch, const void *ahead_ptr = nullptr, size_t ahead_bytes = 0);
+                             size_t batch);
 size_t attn_partial_floats(size_t batch, size_t nh, size_t hd);  // scratch both attention forms fit in
 // dst[b][r * n + i] = src[r][b][i]: the gathered per-rank logits slabs into rows of the full vocabulary
 int launch_interleave_rows(lmb_ctx *ctx, const float *src, float *dst, size_t ranks, size_t batch, size_t n);

@@ -123,12 +123,6 @@ __device__ __forceinline__ void build_block_tables(const float *__restrict__ x, 
 }
 
 
-// This CTA's share of an L2 look-ahead range of `lines` 128-byte lines (see LinearArgs::ahead_ptr).
-__device__ __forceinline__ void prefetch_share_l2(const unsigned char *base, unsigned lines, unsigned cta, unsigned ctas, unsigned threads) {
-  const unsigned per = (lines + ctas - 1) / ctas, l0 = cta * per, l1 = min(l0 + per, lines);
-  for (unsigned l = l0 + threadIdx.x; l < l1; l += threads) asm volatile("prefetch.global.L2 [%0];" ::"l"(base + size_t(l) * 128));
-}
-
 // Launch timeline (debugging): word 0 first CTA start, 1 / 2 first / last CTA past the wait for the
 // preceding kernel, 3 last CTA with its activations ready, 4 last CTA through its main loop,
 // 5 / 6 last / first CTA done.  Called by one thread per CTA; dbg null: off.

@@ -108,8 +108,6 @@ struct GemvParams {
   // the preceding kernel (hints: no registers, no shared memory): the stream then starts from L2 while
   // the CTAs convert their activations.  0: none.
   int l2_tiles;
-  const unsigned char *ahead_ptr;  // L2 look-ahead range (LinearArgs::ahead_ptr), in 128-byte lines
-  unsigned ahead_lines;
 };
 
 // CLUSTERED: the instantiation launched with thread-block clusters (GemvParams::cl_size); kept apart so
@@ -175,7 +173,6 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
       if (sub + sl * wpr < ns && tile_ok(row_tiles + size_t(sub + sl * wpr) * TB)) slot[sl].load(row_tiles + size_t(sub + sl * wpr) * TB, lane);
   }
 
-  if (p.ahead_lines) prefetch_share_l2(p.ahead_ptr, p.ahead_lines, blockIdx.x, gridDim.x, THREADS);
   if (p.l2_tiles > 0 && active) {
     constexpr int LINES = int((TB + 127) / 128);
     for (int k = 0; k < p.l2_tiles; ++k) {
@@ -1005,8 +1002,6 @@ int launch_gemv(lmb_ctx *ctx, const LinearArgs *args, int njobs, bool rotate, in
   if (st != LMB_OK) return st;
   p.cl_size = cluster;
   p.l2_tiles = ctx->pdl && args[0].batch == 1 ? l2_tiles_setting() : 0;
-  p.ahead_ptr = static_cast<const unsigned char *>(args[0].ahead_ptr);
-  p.ahead_lines = args[0].ahead_ptr ? unsigned(args[0].ahead_bytes / 128) : 0u;
   p.prep_sumsq = nullptr;
   p.prep_sumsq_n = 0;
   if (args[0].prep_in) {  // the producing GEMV prepared the activations (batch 1)
@@ -1150,8 +1145,6 @@ int lmb_group_launch(lmb_ctx *ctx, lmb_group *g) {
   p.prep_sumsq_n = 0;
   p.cl_size = 0;
   p.l2_tiles = 0;
-  p.ahead_ptr = nullptr;
-  p.ahead_lines = 0;
   return launch_params_kind(ctx, g->kind, p, g->ctas, g->s_max, 1);
 }
 
@@ -1344,8 +1337,6 @@ int lmb_linear_static_scratch(const lmb_weight *w, const float *d_bias, const fl
   p.prep_sumsq_n = 0;
   p.cl_size = 0;
   p.l2_tiles = 0;
-  p.ahead_ptr = nullptr;
-  p.ahead_lines = 0;
   Job &jb = p.job[0];
   jb.tiles = w->d_tiles;
   jb.x = d_x;

@@ -509,14 +509,9 @@ struct Fuse {
   const uint32_t *prep_in = nullptr;
   const float *prep_sumsq_in = nullptr;
   int prep_sumsq_n = 0;
-  // L2 look-ahead range (LinearArgs::ahead_ptr)
-  const void *ahead_ptr = nullptr;
-  size_t ahead_bytes = 0;
 };
 
 void apply_handoff(LinearArgs &a, const Fuse &f) {
-  a.ahead_ptr = f.ahead_ptr;
-  a.ahead_bytes = f.ahead_bytes;
   a.next_prep = f.next_prep;
   a.next_sumsq = f.next_sumsq;
   a.next_w = f.next_w;
@@ -587,19 +582,10 @@ int lmb_model_forward(lmb_model *m, const int *token_ids, const size_t *position
   // a KV head, bulk asynchronous copies) where the shape allows it, else one CTA per query head
   const AttnGroupPlan agp = m->attn_group ? plan_attn_group(m->nh, m->nkv, hd, c.max_seq_len, batch, size_t(2) * ctx->sm_count, ATTN_GROUP_SMEM)
                                           : AttnGroupPlan{false, 1, 0, 0, 0};
-  // LMB_MODEL_L2_AHEAD (bit mask, batch-1 fused step): 1 the attention kernel's CTAs ask for the gate
-  // projection's weights to be brought into L2, 2 o_proj's CTAs for the up projection's: both
-  // kernels leave the memory mostly idle, and the gate/up launch that follows is the largest of a layer.
-  static const int l2_ahead = [] {
-    const char *e = std::getenv("LMB_MODEL_L2_AHEAD");
-    return e ? std::atoi(e) : 0;
-  }();
-  const bool ahead_ok = batch == 1 && c.tp_size == 1 && m->fused;
   auto attention = [&](LayerW &L, size_t l) {
     if (agp.ok)
       return launch_decode_attn_group(ctx, m->q, m->k, m->v, L.qb, L.kb, L.vb, m->cs_table, m->d_pos, m->kv, m->att, m->att_partial,
-                                      m->att_counters, agp, l, rd, batch, (ahead_ok && (l2_ahead & 1)) ? L.w[4]->d_tiles : nullptr,
-                                      L.w[4]->bytes);
+                                      m->att_counters, agp, l, rd, batch);
     return launch_decode_attn(ctx, m->q, m->k, m->v, L.qb, L.kb, L.vb, m->cs_table, m->d_pos, m->kv, m->att, m->att_partial,
                               m->att_counters, n_splits, l, rd, batch);
   };
@@ -706,7 +692,6 @@ int lmb_model_forward(lmb_model *m, const int *token_ids, const size_t *position
       norm1.xmode = XMODE_RMSNORM; norm1.x2 = L.in_norm;
       norm2.xmode = XMODE_RMSNORM; norm2.x2 = L.post_norm;
       res.residual = m->hidden;
-      if (ahead_ok && (l2_ahead & 2)) { res.ahead_ptr = L.w[5]->d_tiles; res.ahead_bytes = L.w[5]->bytes; }
       act.xmode = c.activation == LMB_ACT_GELU ? XMODE_GELU_MUL : XMODE_SILU_MUL; act.x2 = m->up; act.residual = m->hidden;
       if (ho) {
         if (have) { norm1.prep_in = m->prep[1]; norm1.prep_sumsq_in = m->prep_ss[1]; norm1.prep_sumsq_n = hb; }
