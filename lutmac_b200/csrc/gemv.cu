@@ -104,10 +104,6 @@ struct GemvParams {
   // K slices of a row group are added up through distributed shared memory instead of a scratch
   // buffer and an arrival counter.  0 or 1: no clusters.
   int cl_size;
-  // Row-blocks beyond the register ring that every warp asks to be brought into L2 before it waits for
-  // the preceding kernel (hints: no registers, no shared memory): the stream then starts from L2 while
-  // the CTAs convert their activations.  0: none.
-  int l2_tiles;
 };
 
 // CLUSTERED: the instantiation launched with thread-block clusters (GemvParams::cl_size); kept apart so
@@ -171,14 +167,6 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
 #pragma unroll
     for (int sl = 0; sl < NSLOT; ++sl)
       if (sub + sl * wpr < ns && tile_ok(row_tiles + size_t(sub + sl * wpr) * TB)) slot[sl].load(row_tiles + size_t(sub + sl * wpr) * TB, lane);
-  }
-
-  if (p.l2_tiles > 0 && active) {
-    constexpr int LINES = int((TB + 127) / 128);
-    for (int k = 0; k < p.l2_tiles; ++k) {
-      const int bl = sub + (NSLOT + k) * wpr;
-      if (bl < ns && lane < LINES) asm volatile("prefetch.global.L2 [%0];" ::"l"(row_tiles + size_t(bl) * TB + size_t(lane) * 128));
-    }
   }
 
   pdl_wait();
@@ -433,6 +421,8 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
   // Hand-off (see Job::next_prep): thread t of the CTA that completes the row group holds output
   // 256 * rg + t; one warp turns the block into the next GEMV's prepared activation record.
   float handoff = 0.0f;  // this thread's finished output (first sequence), 0 beyond M
+  float ho_w8[8];        // the next norm's weights of this row group's block: fetched before the split-K arrival, used after it
+  if (NSEQ == 1 && job.next_prep && job.next_w && warp == 0 && rg < job.n_rg) load_x8(job.next_w, size_t(job.M), size_t(rg), lane, ho_w8);
   auto hand_off = [&]() {
     if (NSEQ != 1 || !job.next_prep) return;  // uniform over the CTA
     __syncthreads();
@@ -449,10 +439,8 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
 #pragma unroll
       for (int m = 16; m > 0; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
       if (job.next_w) {
-        float w8[8];
-        load_x8(job.next_w, size_t(job.M), size_t(rg), lane, w8);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) v[e] *= w8[e];
+        for (int e = 0; e < 8; ++e) v[e] *= ho_w8[e];
       }
       if (job.next_rotate) fwht256_warp(v, lane);
       float *stage = smem;  // the activation digits of this launch are no longer needed by this CTA
@@ -542,10 +530,18 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
     for (int q = 0; q < NSEQ; ++q)
       if (q < nb) {
         const float *scr = job.scratch + size_t(batch0 + q) * job.n_ks * job.mp;
+        // eight partial sums per round trip (a loop of single loads serialises them), added in slice order
         float tot = 0.0f;
-        for (int k = 0; k < job.n_ks; ++k) tot += __ldcg(scr + size_t(k) * job.mp + row);
+        const float res = job.residual ? job.residual[size_t(batch0 + q) * job.y_stride + row] : 0.0f;
+        for (int k0 = 0; k0 < job.n_ks; k0 += 8) {
+          float v[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[i] = (k0 + i < job.n_ks) ? __ldcg(scr + size_t(k0 + i) * job.mp + row) : 0.0f;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) tot += v[i];
+        }
         if (job.bias) tot += bias;
-        if (job.residual) tot += job.residual[size_t(batch0 + q) * job.y_stride + row];
+        if (job.residual) tot += res;
         emit(q, tot);
         if (q == 0) handoff = tot;
       }
@@ -638,14 +634,6 @@ struct PlanForce {
   }
 };
 PlanForce g_plan_force;
-// LMB_GEMV_L2_TILES=n: see GemvParams::l2_tiles.
-inline int l2_tiles_setting() {
-  static const int n = [] {
-    const char *e = std::getenv("LMB_GEMV_L2_TILES");
-    return e ? std::atoi(e) : 0;
-  }();
-  return n;
-}
 // LMB_GEMV_CLUSTER=0: no thread-block clusters in any plan (a plan forced with lmb_debug_force_plan may
 // still use them).  A cluster starts only when all its CTAs find room at once, which costs part of the
 // overlap with the preceding kernel's tail (1.5 to 5 us measured on the 70B-shaped decode step): the
@@ -1001,7 +989,6 @@ int launch_gemv(lmb_ctx *ctx, const LinearArgs *args, int njobs, bool rotate, in
   int st = prepare_jobs(ctx, kind, args, njobs, p.job, &ctas, &s_max, nullptr, true, &cluster);
   if (st != LMB_OK) return st;
   p.cl_size = cluster;
-  p.l2_tiles = ctx->pdl && args[0].batch == 1 ? l2_tiles_setting() : 0;
   p.prep_sumsq = nullptr;
   p.prep_sumsq_n = 0;
   if (args[0].prep_in) {  // the producing GEMV prepared the activations (batch 1)
@@ -1144,7 +1131,6 @@ int lmb_group_launch(lmb_ctx *ctx, lmb_group *g) {
   p.prep_sumsq = nullptr;
   p.prep_sumsq_n = 0;
   p.cl_size = 0;
-  p.l2_tiles = 0;
   return launch_params_kind(ctx, g->kind, p, g->ctas, g->s_max, 1);
 }
 
@@ -1336,7 +1322,6 @@ int lmb_linear_static_scratch(const lmb_weight *w, const float *d_bias, const fl
   p.prep_sumsq = nullptr;
   p.prep_sumsq_n = 0;
   p.cl_size = 0;
-  p.l2_tiles = 0;
   Job &jb = p.job[0];
   jb.tiles = w->d_tiles;
   jb.x = d_x;

@@ -753,6 +753,9 @@ static int build_plan(lmb_model *m) {
     std::memset(&a, 0, sizeof a);
     a.type = PH_ATTN;
     a.at = AttnArgs{m->q, m->k, m->v, L.qb, L.kb, L.vb, m->cs_table, m->d_pos, m->kv, m->att, m->att_partial, m->att_counters, n_splits, l};
+#ifdef LMB_DEBUG_BOUNDS
+    a.at.kv_floats = m->seq_stride * m->cfg.max_batch;
+#endif
     a.rd = rd;
     a.attn_per = attn_per;
     ph.push_back(a);
