@@ -365,6 +365,9 @@ int lmb_tp_peer_status(lmb_ctx *ctx, int *timed_out);
  * counter afterwards, 1 if the hidden vector equals the sum of the posted partials}.  With
  * posted < ranks the wait runs out and the kernel returns by itself: nothing faults or hangs. */
 int lmb_debug_tp_wait(lmb_ctx *ctx, int ranks, int posted, size_t h, unsigned spin_limit, int out4[4]);
+/* The same for the consumer kernel of batch-1 steps with integer tensor-core layouts, which also leaves
+ * the hidden state as the next projections' prepared activations (h a multiple of 256). */
+int lmb_debug_tp_wait_prepare(lmb_ctx *ctx, int ranks, int posted, size_t h, unsigned spin_limit, int out4[4]);
 int lmb_allreduce_sum(lmb_ctx *ctx, float *d_buf, size_t n_floats);
 int lmb_allgather(lmb_ctx *ctx, const float *d_send, float *d_recv, size_t n_floats_per_rank);
 

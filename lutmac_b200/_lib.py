@@ -118,6 +118,7 @@ SIGNATURES = {
     "lmb_tp_peer_open": (C.c_int, [vp, vp]),
     "lmb_tp_peer_status": (C.c_int, [vp, C.POINTER(C.c_int)]),
     "lmb_debug_tp_wait": (C.c_int, [vp, C.c_int, C.c_int, sz, C.c_uint, C.POINTER(C.c_int)]),
+    "lmb_debug_tp_wait_prepare": (C.c_int, [vp, C.c_int, C.c_int, sz, C.c_uint, C.POINTER(C.c_int)]),
     "lmb_allreduce_sum": (C.c_int, [vp, vp, sz]),
     "lmb_allgather": (C.c_int, [vp, vp, vp, sz]),
 }

@@ -263,6 +263,7 @@ constexpr int PREP_RECORD_WORDS = 256 + 4;  // one prepared 256-block: digits, b
 // How the GEMV prologue forms its activations from x.
 enum { XMODE_PLAIN = 0, XMODE_RMSNORM = 1, XMODE_SILU_MUL = 2, XMODE_GELU_MUL = 3 };
 int configure_gemv(lmb_ctx *ctx);
+int launch_tp_sum_prepare(lmb_ctx *ctx, float *d_hidden, const float *d_w, bool rotate, uint32_t *prep, float *sumsq, size_t h);
 int launch_gemv(lmb_ctx *ctx, const LinearArgs *args, int njobs, bool rotate, int xmode = XMODE_PLAIN, float eps = 0.0f);
 int launch_fwht256(lmb_ctx *ctx, float *d_x, size_t n);
 int launch_debug_luts(lmb_ctx *ctx, const float *d_x, size_t x_len, bool rotate, float *d_out);

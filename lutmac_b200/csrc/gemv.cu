@@ -618,6 +618,81 @@ __global__ void k_debug_luts(const float *x, size_t x_len, int nblocks, int rota
   }
 }
 
+// Tensor-parallel sum as a producer of prepared activations (batch 1, integer-MMA consumers): one CTA
+// per 256-block of the hidden state adds the ranks' partial vectors out of this rank's exchange block
+// (words {value, epoch tag}, polled with a bound: all ranks' words of an element are requested at once)
+// and the residual, writes the new hidden state, and leaves the block as the next GEMV's activation
+// record -- times the norm weight, rotated, as fixed-point digits -- with its sum of squares; the
+// consumers normalise by the total (src/layers/norm.cpp:18-34 is linear in 1 / rms).  Replaces
+// k_tp_sum_add_rmsnorm plus the conversion in every consumer CTA.
+__global__ void __launch_bounds__(BLK) k_tp_sum_prepare(float *hidden, XchgHeader *hdr, const unsigned long long *data, int tp, unsigned cap,
+                                                        const float *w, int rotate, uint32_t *prep, float *sumsq, unsigned spin_limit) {
+  pdl_launch_dependents();
+  __shared__ __align__(16) float vals[BLK];
+  __shared__ __align__(16) float stage[BLK];
+  __shared__ float red[BLK / 32];
+  __shared__ float xs[1];
+  __shared__ __align__(16) int xa[4];
+  pdl_wait();  // the epoch below is advanced by the previous consumer of the exchange block, the residual written by earlier kernels
+  const int t = threadIdx.x, warp = t >> 5, lane = t & 31, blk = blockIdx.x;
+  const size_t i = size_t(blk) * BLK + t;
+  const unsigned epoch = *reinterpret_cast<volatile unsigned *>(&hdr->epoch), tag = epoch + 1u;
+  const unsigned long long *part = data + size_t(epoch & 1u) * tp * cap + i;
+  unsigned long long word[MAX_TP];
+#pragma unroll
+  for (int r = 0; r < MAX_TP; ++r)
+    if (r < tp) asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(word[r]) : "l"(part + size_t(r) * cap));
+  bool gave_up = *reinterpret_cast<volatile unsigned *>(&hdr->timed_out) != 0u;
+  float add = 0.0f;
+#pragma unroll
+  for (int r = 0; r < MAX_TP; ++r) {
+    if (r < tp) {
+      unsigned spins = 0;
+      while (unsigned(word[r] >> 32) != tag && !gave_up) {
+        if (++spins > spin_limit) {  // give up, report, carry on with what is there
+          hdr->timed_out = 1u;
+          gave_up = true;
+          break;
+        }
+        __nanosleep(40);
+        asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(word[r]) : "l"(part + size_t(r) * cap));
+      }
+      add += __uint_as_float(unsigned(word[r]));  // rank order: every rank computes the same bits
+    }
+  }
+  const float v = hidden[i] + add;
+  hidden[i] = v;
+  float ss = v * v;
+#pragma unroll
+  for (int m = 16; m > 0; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
+  if (lane == 0) red[warp] = ss;
+  vals[t] = v * w[i];
+  __syncthreads();
+  if (warp == 0) {
+    float tot = lane < BLK / 32 ? red[lane] : 0.0f;
+#pragma unroll
+    for (int m = 4; m > 0; m >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, m);
+    const float4 a = *reinterpret_cast<const float4 *>(vals + 8 * lane), c = *reinterpret_cast<const float4 *>(vals + 8 * lane + 4);
+    float v8[8] = {a.x, a.y, a.z, a.w, c.x, c.y, c.z, c.w};
+    if (rotate) fwht256_warp(v8, lane);
+    mma_prologue(v8, lane, stage, &xs[0], &xa[0]);
+    __syncwarp();
+    uint4 *dst = reinterpret_cast<uint4 *>(prep + size_t(blk) * PREP_WORDS);
+    const uint4 *src = reinterpret_cast<const uint4 *>(stage);
+    dst[lane] = src[lane];
+    dst[lane + 32] = src[lane + 32];
+    if (lane == 0) {
+      dst[64] = make_uint4(__float_as_uint(xs[0]), uint32_t(xa[0]), uint32_t(xa[1]), 0u);
+      sumsq[blk] = tot;
+    }
+  }
+  __syncthreads();
+  if (t == 0 && atomicAdd(&hdr->done, 1u) == gridDim.x - 1u) {
+    hdr->done = 0u;
+    *reinterpret_cast<volatile unsigned *>(&hdr->epoch) = tag;  // read by the next producer, a later kernel
+  }
+}
+
 struct Plan {
   int R, S, n_rg, n_ks, ctas;
   int cr;  // thread-block clusters: row groups per cluster (cluster size = cr * n_ks); 0: no cluster
@@ -949,6 +1024,30 @@ int configure_gemv(lmb_ctx *ctx) {
   if (st == LMB_OK) st = configure_mma<DK_INT8_MMA>();
   if (st == LMB_OK) st = configure_mma<DK_INT3_MMA>();
   return st;
+}
+
+// See k_tp_sum_prepare.  h must be a multiple of 256; prep holds h / 256 records, sumsq h / 256 floats.
+int launch_tp_sum_prepare(lmb_ctx *ctx, float *d_hidden, const float *d_w, bool rotate, uint32_t *prep, float *sumsq, size_t h) {
+  if (!ctx->xchg.ready || h % BLK != 0 || h > ctx->xchg.cap) {
+    set_last_error("launch_tp_sum_prepare: no exchange block, or hidden size not a multiple of 256 within its capacity");
+    return LMB_ERR_STATE;
+  }
+  XchgHeader *hdr = static_cast<XchgHeader *>(ctx->xchg.local);
+  const unsigned long long *data =
+      reinterpret_cast<const unsigned long long *>(static_cast<const char *>(ctx->xchg.local) + XCHG_HEADER_BYTES);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(unsigned(h / BLK));
+  cfg.blockDim = dim3(BLK);
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = ctx->pdl ? 1 : 0;
+  LMB_CUDA(cudaLaunchKernelEx(&cfg, k_tp_sum_prepare, d_hidden, hdr, data, ctx->tp_size, unsigned(ctx->xchg.cap), d_w, rotate ? 1 : 0, prep,
+                              sumsq, ctx->xchg.spin_limit));
+  ctx->launches++;
+  return LMB_OK;
 }
 
 // Up to MAX_JOBS independent GEMVs of one kind and one batch size in a single launch.

@@ -152,7 +152,7 @@ int lmb_tp_peer_status(lmb_ctx *ctx, int *timed_out) {
   return LMB_OK;
 }
 
-int lmb_debug_tp_wait(lmb_ctx *ctx, int ranks, int posted, size_t h, unsigned spin_limit, int out4[4]) {
+static int tp_wait_selftest(lmb_ctx *ctx, int ranks, int posted, size_t h, unsigned spin_limit, int out4[4], bool prepare) {
   LMB_REQUIRE(ctx && out4 && ranks >= 2 && ranks <= MAX_TP && posted >= 0 && posted <= ranks && h > 0 && spin_limit > 0,
               "lmb_debug_tp_wait: bad argument");
   LMB_REQUIRE(!ctx->xchg.local, "lmb_debug_tp_wait: the context already has an exchange block");
@@ -176,7 +176,7 @@ int lmb_debug_tp_wait(lmb_ctx *ctx, int ranks, int posted, size_t h, unsigned sp
   if (e == cudaSuccess) e = cudaMemcpy(static_cast<char *>(blk) + XCHG_HEADER_BYTES, words.data(), words.size() * 8, cudaMemcpyHostToDevice);
   if (e == cudaSuccess) e = cudaMalloc(&hidden, h * 4);
   if (e == cudaSuccess) e = cudaMalloc(&w, h * 4);
-  if (e == cudaSuccess) e = cudaMalloc(&out, h * 4);
+  if (e == cudaSuccess) e = cudaMalloc(&out, (h + h / BLK * (PREP_RECORD_WORDS + 1) + 64) * 4);
   if (e == cudaSuccess) e = cudaMemset(hidden, 0, h * 4);
   if (e == cudaSuccess) e = cudaMemcpy(w, ones.data(), h * 4, cudaMemcpyHostToDevice);
   int st = e == cudaSuccess ? LMB_OK : cuda_fail(e, "lmb_debug_tp_wait setup");
@@ -189,7 +189,9 @@ int lmb_debug_tp_wait(lmb_ctx *ctx, int ranks, int posted, size_t h, unsigned sp
     ctx->xchg.ready = true;
     ctx->xchg.spin_limit = spin_limit;
     ctx->tp_size = ranks;
-    st = launch_tp_sum_add_rmsnorm(ctx, hidden, w, out, h, 1, 1e-5f);
+    // the prepared form writes h / 256 records and as many sums of squares into `out` (it is large enough: 260 + 1 words per 256)
+    st = prepare ? launch_tp_sum_prepare(ctx, hidden, w, false, reinterpret_cast<uint32_t *>(out), out + h / BLK * PREP_RECORD_WORDS, h)
+                 : launch_tp_sum_add_rmsnorm(ctx, hidden, w, out, h, 1, 1e-5f);
     ctx->xchg = saved;
     ctx->tp_size = saved_size;
     if (st == LMB_OK) e = cudaStreamSynchronize(ctx->stream);
@@ -211,6 +213,15 @@ int lmb_debug_tp_wait(lmb_ctx *ctx, int ranks, int posted, size_t h, unsigned sp
   if (w) cudaFree(w);
   if (out) cudaFree(out);
   return st;
+}
+
+int lmb_debug_tp_wait(lmb_ctx *ctx, int ranks, int posted, size_t h, unsigned spin_limit, int out4[4]) {
+  return tp_wait_selftest(ctx, ranks, posted, h, spin_limit, out4, false);
+}
+
+int lmb_debug_tp_wait_prepare(lmb_ctx *ctx, int ranks, int posted, size_t h, unsigned spin_limit, int out4[4]) {
+  LMB_REQUIRE(h % lmb::BLK == 0, "lmb_debug_tp_wait_prepare: h must be a multiple of 256");
+  return tp_wait_selftest(ctx, ranks, posted, h, spin_limit, out4, true);
 }
 
 int lmb_tp_destroy(lmb_ctx *ctx) {
@@ -548,6 +559,18 @@ int gemv_group(lmb_model *m, int n, lmb_weight *const *ws, const bool *rot, cons
   return LMB_OK;
 }
 
+// Whether the tensor-parallel sum may leave the hidden state as prepared activations: whole 256-blocks,
+// integer tensor-core layouts in every consumer, one rotation setting per group of consumers.
+bool tp_prepare_possible(const lmb_model *m) {
+  if (!m->handoff || m->cfg.hidden_size % BLK != 0 || !m->lm_head || !kind_is_mma(m->lm_head->kind)) return false;
+  for (const LayerW &L : m->layers) {
+    for (int i : {0, 1, 2, 4, 5})
+      if (!L.w[i] || !kind_is_mma(L.w[i]->kind)) return false;
+    if (L.rot[0] != L.rot[1] || L.rot[0] != L.rot[2] || L.rot[4] != L.rot[5]) return false;
+  }
+  return true;
+}
+
 // Whether the producing projections of a batch-1 step may prepare the next projection's
 // activations: whole 256-blocks of hidden state, integer tensor-core layouts everywhere.
 bool handoff_possible(const lmb_model *m) {
@@ -727,9 +750,24 @@ int lmb_model_forward(lmb_model *m, const int *token_ids, const size_t *position
   // into every rank's exchange block; the next normalisation waits for all ranks and adds them.
   const bool peers = c.tp_size > 1 && ctx->xchg.ready && batch * h <= ctx->xchg.cap && m->tp_peers;
   bool in_flight = false;  // a partial vector is on its way through the exchange block
-  auto norm = [&](const float *w) {
-    int r = in_flight ? launch_tp_sum_add_rmsnorm(ctx, m->hidden, w, m->normed, h, batch, c.rms_norm_eps)
-                      : launch_add_rmsnorm(ctx, m->hidden, pending, w, m->normed, h, batch, c.rms_norm_eps);
+  // Batch 1 with integer tensor-core layouts everywhere: the kernel that adds the ranks' partial vectors
+  // also leaves the hidden state as the next projections' prepared activations (k_tp_sum_prepare), one
+  // CTA per 256-block, instead of one CTA normalising the whole vector and every consumer CTA converting it.
+  const bool prepare = peers && batch == 1 && tp_prepare_possible(m);
+  Fuse consumer;  // how the projections after the latest `norm` read their input
+  auto norm = [&](const float *w, bool rot) {
+    int r;
+    consumer = Fuse();
+    if (in_flight && prepare) {
+      r = launch_tp_sum_prepare(ctx, m->hidden, w, rot, m->prep[0], m->prep_ss[0], h);
+      consumer.xmode = XMODE_RMSNORM;
+      consumer.prep_in = m->prep[0];
+      consumer.prep_sumsq_in = m->prep_ss[0];
+      consumer.prep_sumsq_n = int(h / BLK);
+    } else {
+      r = in_flight ? launch_tp_sum_add_rmsnorm(ctx, m->hidden, w, m->normed, h, batch, c.rms_norm_eps)
+                    : launch_add_rmsnorm(ctx, m->hidden, pending, w, m->normed, h, batch, c.rms_norm_eps);
+    }
     in_flight = false;
     pending = nullptr;
     return r;
@@ -747,19 +785,19 @@ int lmb_model_forward(lmb_model *m, const int *token_ids, const size_t *position
   };
   for (size_t l = 0; l < m->layers.size() && st == LMB_OK; ++l) {
     LayerW &L = m->layers[l];
-    st = norm(L.in_norm);
+    st = norm(L.in_norm, L.rot[0]);
     if (st != LMB_OK) break;
     float *qkv[3] = {m->q, m->k, m->v};
-    st = gemv_group(m, 3, &L.w[0], &L.rot[0], m->normed, h, qkv, batch);
+    st = gemv_group(m, 3, &L.w[0], &L.rot[0], m->normed, h, qkv, batch, consumer);
     if (st != LMB_OK) break;
     st = attention(L, l);
     if (st != LMB_OK) break;
     st = row_reduce(L.w[3], L.rot[3], m->att, m->nh * hd, Fuse());
     if (st != LMB_OK) break;
-    st = norm(L.post_norm);
+    st = norm(L.post_norm, L.rot[4]);
     if (st != LMB_OK) break;
     float *gu[2] = {m->gate, m->up};
-    st = gemv_group(m, 2, &L.w[4], &L.rot[4], m->normed, h, gu, batch);
+    st = gemv_group(m, 2, &L.w[4], &L.rot[4], m->normed, h, gu, batch, consumer);
     if (st != LMB_OK) break;
     Fuse act;  // SiLU(gate) * up in the prologue of down_proj (element-wise, so a column shard needs no exchange)
     act.xmode = c.activation == LMB_ACT_GELU ? XMODE_GELU_MUL : XMODE_SILU_MUL;
@@ -767,10 +805,10 @@ int lmb_model_forward(lmb_model *m, const int *token_ids, const size_t *position
     st = row_reduce(L.w[6], L.rot[6], m->gate, m->inter, act);
   }
   if (st != LMB_OK) return st;
-  st = norm(m->final_norm);
+  st = norm(m->final_norm, m->head_rot);
   if (st != LMB_OK) return st;
   if (c.tp_size > 1) {
-    st = gemv1(m, m->lm_head, m->head_rot, m->normed, h, m->logits_local, batch);
+    st = gemv1(m, m->lm_head, m->head_rot, m->normed, h, m->logits_local, batch, consumer);
     if (st == LMB_OK && batch == 1) {
       st = lmb_allgather(ctx, m->logits_local, m->logits, m->vocab_local);
     } else if (st == LMB_OK) {

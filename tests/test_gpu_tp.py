@@ -55,6 +55,15 @@ def test_bounded_peer_wait_expires_and_reports(ctx):
     # nobody posts at all (two ranks)
     _lib.check(_lib.lib().lmb_debug_tp_wait(ctx.h, 2, 0, 8192, 16, out))
     assert list(out) == [1, 1, 0, 1]
+    # the same three cases for the consumer that also prepares the next projections' activations
+    # (batch-1 steps with integer tensor-core layouts): one CTA per 256-block of the hidden state
+    L = _lib.lib()
+    _lib.check(L.lmb_debug_tp_wait_prepare(ctx.h, 4, 4, 1024, 64, out))
+    assert list(out) == [0, 1, 0, 1]
+    _lib.check(L.lmb_debug_tp_wait_prepare(ctx.h, 4, 3, 1024, 64, out))
+    assert list(out) == [1, 1, 0, 1]
+    _lib.check(L.lmb_debug_tp_wait_prepare(ctx.h, 8, 0, 8192, 16, out))
+    assert list(out) == [1, 1, 0, 1]
     # the context is still usable afterwards
     import numpy as np
     x = ctx.to_device(np.arange(256, dtype=np.float32))
