@@ -421,8 +421,6 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
   // Hand-off (see Job::next_prep): thread t of the CTA that completes the row group holds output
   // 256 * rg + t; one warp turns the block into the next GEMV's prepared activation record.
   float handoff = 0.0f;  // this thread's finished output (first sequence), 0 beyond M
-  float ho_w8[8];        // the next norm's weights of this row group's block: fetched before the split-K arrival, used after it
-  if (NSEQ == 1 && job.next_prep && job.next_w && warp == 0 && rg < job.n_rg) load_x8(job.next_w, size_t(job.M), size_t(rg), lane, ho_w8);
   auto hand_off = [&]() {
     if (NSEQ != 1 || !job.next_prep) return;  // uniform over the CTA
     __syncthreads();
@@ -439,8 +437,10 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
 #pragma unroll
       for (int m = 16; m > 0; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
       if (job.next_w) {
+        float w8[8];
+        load_x8(job.next_w, size_t(job.M), size_t(rg), lane, w8);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) v[e] *= ho_w8[e];
+        for (int e = 0; e < 8; ++e) v[e] *= w8[e];
       }
       if (job.next_rotate) fwht256_warp(v, lane);
       float *stage = smem;  // the activation digits of this launch are no longer needed by this CTA
@@ -530,18 +530,10 @@ __global__ void __launch_bounds__(THREADS, min_ctas(KIND, NSEQ)) k_gemv(const __
     for (int q = 0; q < NSEQ; ++q)
       if (q < nb) {
         const float *scr = job.scratch + size_t(batch0 + q) * job.n_ks * job.mp;
-        // eight partial sums per round trip (a loop of single loads serialises them), added in slice order
         float tot = 0.0f;
-        const float res = job.residual ? job.residual[size_t(batch0 + q) * job.y_stride + row] : 0.0f;
-        for (int k0 = 0; k0 < job.n_ks; k0 += 8) {
-          float v[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) v[i] = (k0 + i < job.n_ks) ? __ldcg(scr + size_t(k0 + i) * job.mp + row) : 0.0f;
-#pragma unroll
-          for (int i = 0; i < 8; ++i) tot += v[i];
-        }
+        for (int k = 0; k < job.n_ks; ++k) tot += __ldcg(scr + size_t(k) * job.mp + row);
         if (job.bias) tot += bias;
-        if (job.residual) tot += res;
+        if (job.residual) tot += job.residual[size_t(batch0 + q) * job.y_stride + row];
         emit(q, tot);
         if (q == 0) handoff = tot;
       }
@@ -709,14 +701,15 @@ struct PlanForce {
   }
 };
 PlanForce g_plan_force;
-// LMB_GEMV_CLUSTER=0: no thread-block clusters in any plan (a plan forced with lmb_debug_force_plan may
-// still use them).  A cluster starts only when all its CTAs find room at once, which costs part of the
-// overlap with the preceding kernel's tail (1.5 to 5 us measured on the 70B-shaped decode step): the
-// planner charges that, so clusters are chosen only where they save several conversion rounds.
+// LMB_GEMV_CLUSTER=1: the planner may choose thread-block clusters (a plan forced with
+// lmb_debug_force_plan may use them either way).  Off by default: a cluster starts only when all its
+// CTAs find room at once, which costs part of the overlap with the preceding kernel's tail (1.5 to
+// 5 us measured on the 70B-shaped decode step), and with the hand-off of prepared activations the
+// conversion work they would share is gone; on the 1B / 1.5B-shaped steps they measured 5 % slower.
 inline bool clusters_allowed() {
   static const bool ok = [] {
     const char *e = std::getenv("LMB_GEMV_CLUSTER");
-    return !(e && e[0] == '0');
+    return e && e[0] == '1';
   }();
   return ok;
 }

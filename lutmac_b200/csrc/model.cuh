@@ -48,6 +48,7 @@ struct lmb_model {
   // persistent kernel over all layers (persist.cu); LMB_MODEL_PERSISTENT=0 disables it
   bool persistent = true;
   bool handoff = true;  // LMB_MODEL_HANDOFF=0: every consumer CTA converts its own activations (batch 1, fused step)
+  int handoff_forced = 0;  // hand-off requested explicitly: also for models narrower than 16 blocks
   uint32_t *prep[2] = {nullptr, nullptr};  // prepared hidden state after o_proj / after down_proj
   float *prep_ss[2] = {nullptr, nullptr};
   bool attn_group = true;  // LMB_ATTN_GROUP=0: one attention CTA per query head instead of per KV head

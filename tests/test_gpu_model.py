@@ -98,13 +98,14 @@ def test_batched_decode_equals_independent_sequences(ctx, oracle):
                                  {"LMB_MODEL_PERSISTENT": "0", "LMB_MODEL_GRAPH": "0"},
                                  {"LMB_MODEL_PERSISTENT": "0", "LMB_MODEL_FUSED": "0", "LMB_MODEL_GRAPH": "0"},
                                  {"LMB_MODEL_PERSISTENT": "1", "LMB_ATTN_GROUP": "0"}, {"LMB_MODEL_PERSISTENT": "0", "LMB_ATTN_GROUP": "0"},
-                                 {"LMB_MODEL_PERSISTENT": "0", "LMB_MODEL_HANDOFF": "0"}])
+                                 {"LMB_MODEL_PERSISTENT": "0", "LMB_MODEL_HANDOFF": "0"}, {"LMB_MODEL_PERSISTENT": "0", "LMB_MODEL_HANDOFF": "1"}])
 def test_unfused_and_ungraphed_steps_match_the_fixtures(ctx, env, monkeypatch):
     """With LMB_MODEL_PERSISTENT=0 the step is one launch per projection, which can in turn run
     without norm/activation fusion (the sequence batched tensor-parallel runs use) and without
-    graph capture; with 1, batch 1 runs as one persistent kernel.  By default o_proj and down_proj
-    prepare the hidden state for the next projections, whose CTAs then copy those records;
-    LMB_MODEL_HANDOFF=0 makes every consumer CTA convert its own activations instead.  LMB_ATTN_GROUP=0 selects the
+    graph capture; with 1, batch 1 runs as one persistent kernel.  In models at least 4096 wide
+    (and with LMB_MODEL_HANDOFF=1 in any model, as here) o_proj and down_proj prepare the hidden
+    state for the next projections, whose CTAs then copy those records; LMB_MODEL_HANDOFF=0 makes
+    every consumer CTA convert its own activations instead.  LMB_ATTN_GROUP=0 selects the
     attention form with one CTA per query head instead of one per KV head, in either kind of step.
     The switches are read when the model is created."""
     for k, v in env.items():
