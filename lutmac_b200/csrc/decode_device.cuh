@@ -432,7 +432,10 @@ template <int PER> __device__ __forceinline__ LaneVec<PER> ldcg_lane_vec(const f
 // is then set): the caller leaves the kernel.  All ATT_THREADS threads of the CTA take part.
 // `dbg` (profiling aid, usually null): thread 0 records the device's nanosecond timer after the wait
 // for the copies (dbg[0]) and after the partial records are written (dbg[1]).
-template <bool FRESH_CG, int PER>
+// WIDE: the form for batch 1, where the kernel is one wave of CTAs and bound by their latency: queries
+// kept in registers, the value pass by timestep with all heads per lane, merge statistics in one round
+// trip and 16 partial records in flight.  With several sequences (many waves) the plain form is faster.
+template <bool FRESH_CG, int PER, bool WIDE = false>
 __device__ __forceinline__ bool attn_group_item(const AttnArgs &a, const RopeDims &d, size_t kvh, size_t split, size_t b, float *sm,
                                                 uint64_t *bar, unsigned &parity, unsigned spin_limit, int *flag,
                                                 unsigned long long *dbg = nullptr, unsigned long long *tl = nullptr) {
@@ -532,13 +535,28 @@ __device__ __forceinline__ bool attn_group_item(const AttnArgs &a, const RopeDim
   if (tid == 0) tl_max(tl, 3);
   // scores: a warp per timestep, a lane per PER dimensions
   const float scale = 1.0f / sqrtf(float(hd));
+  LaneVec<PER> qreg[WIDE ? ATT_MAX_GROUP : 1];
+  if constexpr (WIDE) {
+#pragma unroll
+    for (int h = 0; h < ATT_MAX_GROUP; ++h) {
+      if (size_t(h) < g) {
+        qreg[h] = ld_lane_vec<PER>(qs + h * hd, lane);
+      } else {
+#pragma unroll
+        for (int e = 0; e < PER; ++e) qreg[h].v[e] = 0.0f;
+      }
+    }
+  }
   for (size_t t = warp; t < n; t += nw) {
     const LaneVec<PER> kk = ld_lane_vec<PER>(Ks + t * hd, lane);
     float s[ATT_MAX_GROUP];
 #pragma unroll
     for (int h = 0; h < ATT_MAX_GROUP; ++h) {
       s[h] = 0.0f;
-      if (size_t(h) < g) {
+      if constexpr (WIDE) {
+#pragma unroll
+        for (int e = 0; e < PER; ++e) s[h] += qreg[h].v[e] * kk.v[e];
+      } else if (size_t(h) < g) {
         const LaneVec<PER> qv = ld_lane_vec<PER>(qs + h * hd, lane);
 #pragma unroll
         for (int e = 0; e < PER; ++e) s[h] += qv.v[e] * kk.v[e];
@@ -585,23 +603,72 @@ __device__ __forceinline__ bool attn_group_item(const AttnArgs &a, const RopeDim
     }
   }
   __syncthreads();
-  // weighted values, a warp per head; the partial record of (head, split)
+  // weighted values; the partial record of (head, split)
   const size_t rec = hd + ATT_REC_PAD;
-  for (size_t h = warp; h < g; h += nw) {
-    LaneVec<PER> acc;
+  if (WIDE && sl >= size_t(nw - 1) * g && nw == 8) {
+    // A warp per timestep (w, w + 8, ...), every lane keeping its dimensions of all heads: a value row is
+    // read once for the whole group.  The eight warps' sums meet in the key area, which is free now:
+    // warp w keeps head w for itself and leaves the other heads where their warps add them up.
+    LaneVec<PER> acc[ATT_MAX_GROUP];
 #pragma unroll
-    for (int e = 0; e < PER; ++e) acc.v[e] = 0.0f;
-    for (size_t t = 0; t < n; ++t) {
-      const float pt = sc[h * sl + t];
+    for (int h = 0; h < ATT_MAX_GROUP; ++h)
+#pragma unroll
+      for (int e = 0; e < PER; ++e) acc[h].v[e] = 0.0f;
+    for (size_t t = warp; t < n; t += nw) {
       const LaneVec<PER> vv = ld_lane_vec<PER>(Vs + t * hd, lane);
 #pragma unroll
-      for (int e = 0; e < PER; ++e) acc.v[e] += pt * vv.v[e];
+      for (int h = 0; h < ATT_MAX_GROUP; ++h) {
+        if (size_t(h) < g) {
+          const float pt = sc[h * sl + t];
+#pragma unroll
+          for (int e = 0; e < PER; ++e) acc[h].v[e] += pt * vv.v[e];
+        }
+      }
     }
-    float *prt = a.partial + ((b * d.nh + kvh * g + h) * n_splits + split) * rec;
-    st_lane_vec<PER>(prt, lane, acc);
-    if (lane == 0) {
-      prt[hd] = stat[2 * h];
-      prt[hd + 1] = stat[2 * h + 1];
+    float *red = Ks;  // [head][7 other warps][hd]
+#pragma unroll
+    for (int h = 0; h < ATT_MAX_GROUP; ++h)
+      if (size_t(h) < g && h != warp) st_lane_vec<PER>(red + (size_t(h) * (nw - 1) + size_t(warp - (warp > h ? 1 : 0))) * hd, lane, acc[h]);
+    __syncthreads();
+    if (size_t(warp) < g) {
+      LaneVec<PER> tot;
+#pragma unroll
+      for (int h = 0; h < ATT_MAX_GROUP; ++h)
+        if (h == warp) tot = acc[h];
+      // warps in index order, as a sequential sum over the timesteps of each warp would give
+      LaneVec<PER> sum;
+#pragma unroll
+      for (int e = 0; e < PER; ++e) sum.v[e] = 0.0f;
+      for (int w = 0; w < nw; ++w) {
+        const LaneVec<PER> part = w == warp ? tot : ld_lane_vec<PER>(red + (size_t(warp) * (nw - 1) + size_t(w - (w > warp ? 1 : 0))) * hd, lane);
+#pragma unroll
+        for (int e = 0; e < PER; ++e) sum.v[e] += part.v[e];
+      }
+      float *prt = a.partial + ((b * d.nh + kvh * g + size_t(warp)) * n_splits + split) * rec;
+      st_lane_vec<PER>(prt, lane, sum);
+      if (lane == 0) {
+        prt[hd] = stat[2 * warp];
+        prt[hd + 1] = stat[2 * warp + 1];
+      }
+    }
+  } else {
+    // short slices: a warp per head walks the timesteps
+    for (size_t h = warp; h < g; h += nw) {
+      LaneVec<PER> acc;
+#pragma unroll
+      for (int e = 0; e < PER; ++e) acc.v[e] = 0.0f;
+      for (size_t t = 0; t < n; ++t) {
+        const float pt = sc[h * sl + t];
+        const LaneVec<PER> vv = ld_lane_vec<PER>(Vs + t * hd, lane);
+#pragma unroll
+        for (int e = 0; e < PER; ++e) acc.v[e] += pt * vv.v[e];
+      }
+      float *prt = a.partial + ((b * d.nh + kvh * g + h) * n_splits + split) * rec;
+      st_lane_vec<PER>(prt, lane, acc);
+      if (lane == 0) {
+        prt[hd] = stat[2 * h];
+        prt[hd + 1] = stat[2 * h + 1];
+      }
     }
   }
   __syncthreads();
@@ -623,37 +690,70 @@ __device__ __forceinline__ bool attn_group_item(const AttnArgs &a, const RopeDim
     const size_t head = kvh * g + h;
     const float *all = a.partial + ((b * d.nh + head) * n_splits) * rec;
     float *w = wk + h * ATT_MAX_SPLITS;
-    float gmx = -INFINITY;
-    for (int s2 = lane; s2 < n_splits; s2 += 32) gmx = fmaxf(gmx, __ldcg(all + s2 * rec + hd));
-#pragma unroll
-    for (int m = 16; m > 0; m >>= 1) gmx = fmaxf(gmx, __shfl_xor_sync(0xffffffffu, gmx, m));
-    float den = 0.0f;
-    for (int s2 = lane; s2 < n_splits; s2 += 32) {
-      const float sm2 = __ldcg(all + s2 * rec + hd + 1);
-      const float ws = sm2 > 0.0f ? expf(__ldcg(all + s2 * rec + hd) - gmx) : 0.0f;  // empty slices (short contexts) weigh nothing
-      w[s2] = ws;
-      den += ws * sm2;
-    }
-#pragma unroll
-    for (int m = 16; m > 0; m >>= 1) den += __shfl_xor_sync(0xffffffffu, den, m);
-    __syncwarp();
+    float den;
     LaneVec<PER> tot;
 #pragma unroll
     for (int e = 0; e < PER; ++e) tot.v[e] = 0.0f;
-    int s2 = 0;
-    for (; s2 + 7 < n_splits; s2 += 8) {  // eight records in flight per lane
-      LaneVec<PER> pv[8];
+    if constexpr (WIDE) {
+      // statistics of all slices in one round trip: lane l holds slices l and l + 32 (ATT_MAX_SPLITS = 64)
+      const bool h0 = lane < n_splits, h1 = lane + 32 < n_splits;
+      const float2 st0 = h0 ? __ldcg(reinterpret_cast<const float2 *>(all + lane * rec + hd)) : make_float2(-INFINITY, 0.0f);
+      const float2 st1 = h1 ? __ldcg(reinterpret_cast<const float2 *>(all + (lane + 32) * rec + hd)) : make_float2(-INFINITY, 0.0f);
+      float gmx = fmaxf(st0.x, st1.x);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) pv[i] = ldcg_lane_vec<PER>(all + (s2 + i) * rec, lane);
+      for (int m = 16; m > 0; m >>= 1) gmx = fmaxf(gmx, __shfl_xor_sync(0xffffffffu, gmx, m));
+      const float w0 = st0.y > 0.0f ? expf(st0.x - gmx) : 0.0f;  // empty slices (short contexts) weigh nothing
+      const float w1 = st1.y > 0.0f ? expf(st1.x - gmx) : 0.0f;
+      if (h0) w[lane] = w0;
+      if (h1) w[lane + 32] = w1;
+      den = w0 * st0.y + w1 * st1.y;
 #pragma unroll
-      for (int i = 0; i < 8; ++i)
+      for (int m = 16; m > 0; m >>= 1) den += __shfl_xor_sync(0xffffffffu, den, m);
+      __syncwarp();
+      int s2 = 0;
+      constexpr int FLY = PER == 4 ? 16 : 24;  // records in flight per lane
+      for (; s2 < n_splits; s2 += FLY) {  // the last round is partly empty: its loads are skipped, not serialised
+        LaneVec<PER> pv[FLY];
 #pragma unroll
-        for (int e = 0; e < PER; ++e) tot.v[e] += w[s2 + i] * pv[i].v[e];
-    }
-    for (; s2 < n_splits; ++s2) {
-      const LaneVec<PER> pv = ldcg_lane_vec<PER>(all + s2 * rec, lane);
+        for (int i = 0; i < FLY; ++i)
+          if (s2 + i < n_splits) pv[i] = ldcg_lane_vec<PER>(all + (s2 + i) * rec, lane);
 #pragma unroll
-      for (int e = 0; e < PER; ++e) tot.v[e] += w[s2] * pv.v[e];
+        for (int i = 0; i < FLY; ++i)
+          if (s2 + i < n_splits) {
+#pragma unroll
+            for (int e = 0; e < PER; ++e) tot.v[e] += w[s2 + i] * pv[i].v[e];
+          }
+      }
+    } else {
+      float gmx = -INFINITY;
+      for (int s2 = lane; s2 < n_splits; s2 += 32) gmx = fmaxf(gmx, __ldcg(all + s2 * rec + hd));
+#pragma unroll
+      for (int m = 16; m > 0; m >>= 1) gmx = fmaxf(gmx, __shfl_xor_sync(0xffffffffu, gmx, m));
+      den = 0.0f;
+      for (int s2 = lane; s2 < n_splits; s2 += 32) {
+        const float sm2 = __ldcg(all + s2 * rec + hd + 1);
+        const float ws = sm2 > 0.0f ? expf(__ldcg(all + s2 * rec + hd) - gmx) : 0.0f;  // empty slices (short contexts) weigh nothing
+        w[s2] = ws;
+        den += ws * sm2;
+      }
+#pragma unroll
+      for (int m = 16; m > 0; m >>= 1) den += __shfl_xor_sync(0xffffffffu, den, m);
+      __syncwarp();
+      int s2 = 0;
+      for (; s2 + 7 < n_splits; s2 += 8) {  // eight records in flight per lane
+        LaneVec<PER> pv[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) pv[i] = ldcg_lane_vec<PER>(all + (s2 + i) * rec, lane);
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+          for (int e = 0; e < PER; ++e) tot.v[e] += w[s2 + i] * pv[i].v[e];
+      }
+      for (; s2 < n_splits; ++s2) {
+        const LaneVec<PER> pv = ldcg_lane_vec<PER>(all + s2 * rec, lane);
+#pragma unroll
+        for (int e = 0; e < PER; ++e) tot.v[e] += w[s2] * pv.v[e];
+      }
     }
     const float inv = 1.0f / den;
 #pragma unroll

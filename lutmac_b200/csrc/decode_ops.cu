@@ -107,7 +107,7 @@ __global__ void __launch_bounds__(ATT_THREADS) k_decode_attn(const AttnArgs a, c
 }
 
 // Group attention as a kernel of its own: grid = (KV heads x splits, sequences).
-template <int PER>
+template <int PER, bool WIDE>
 __global__ void __launch_bounds__(ATT_THREADS) k_decode_attn_group(const AttnArgs a, const RopeDims d, unsigned spin_limit,
                                                                     unsigned *timed_out, unsigned long long *tl) {
   asm volatile("griddepcontrol.launch_dependents;");
@@ -119,7 +119,7 @@ __global__ void __launch_bounds__(ATT_THREADS) k_decode_attn_group(const AttnArg
   __syncthreads();
   unsigned parity = 0;
   const size_t kvh = blockIdx.x % d.nkv, split = blockIdx.x / d.nkv;
-  if (!attn_group_item<false, PER>(a, d, kvh, split, blockIdx.y, sm, &bar, parity, spin_limit, &flag, nullptr, tl) && threadIdx.x == 0 &&
+  if (!attn_group_item<false, PER, WIDE>(a, d, kvh, split, blockIdx.y, sm, &bar, parity, spin_limit, &flag, nullptr, tl) && threadIdx.x == 0 &&
       timed_out)
     *timed_out = 1u;
 }
@@ -259,8 +259,14 @@ int launch_decode_attn_group(lmb_ctx *ctx, const float *q, const float *k, const
   }();
   cfg.numAttrs = ctx->pdl && attn_pdl ? 1 : 0;
   unsigned long long *tl = timeline_slot(ctx);
-  if (plan.per == 4) LMB_CUDA(cudaLaunchKernelEx(&cfg, k_decode_attn_group<4>, a, d, ctx->xchg.spin_limit, flag, tl));
-  else LMB_CUDA(cudaLaunchKernelEx(&cfg, k_decode_attn_group<2>, a, d, ctx->xchg.spin_limit, flag, tl));
+  // one sequence: one wave of CTAs, bound by their latency (the WIDE form); several: many waves, bound by throughput
+  if (batch == 1) {
+    if (plan.per == 4) LMB_CUDA(cudaLaunchKernelEx(&cfg, k_decode_attn_group<4, true>, a, d, ctx->xchg.spin_limit, flag, tl));
+    else LMB_CUDA(cudaLaunchKernelEx(&cfg, k_decode_attn_group<2, true>, a, d, ctx->xchg.spin_limit, flag, tl));
+  } else {
+    if (plan.per == 4) LMB_CUDA(cudaLaunchKernelEx(&cfg, k_decode_attn_group<4, false>, a, d, ctx->xchg.spin_limit, flag, tl));
+    else LMB_CUDA(cudaLaunchKernelEx(&cfg, k_decode_attn_group<2, false>, a, d, ctx->xchg.spin_limit, flag, tl));
+  }
   ctx->launches++;
   return LMB_OK;
 }
@@ -282,8 +288,10 @@ int launch_silu_mul(lmb_ctx *ctx, const float *gate, const float *up, float *out
 
 int configure_decode_ops(lmb_ctx *ctx) {
   LMB_CUDA(cudaFuncSetAttribute(k_decode_attn, cudaFuncAttributeMaxDynamicSharedMemorySize, int(ctx->smem_optin) - 1024));
-  LMB_CUDA(cudaFuncSetAttribute(k_decode_attn_group<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(ATTN_GROUP_SMEM)));
-  LMB_CUDA(cudaFuncSetAttribute(k_decode_attn_group<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(ATTN_GROUP_SMEM)));
+  LMB_CUDA(cudaFuncSetAttribute(k_decode_attn_group<4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(ATTN_GROUP_SMEM)));
+  LMB_CUDA(cudaFuncSetAttribute(k_decode_attn_group<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(ATTN_GROUP_SMEM)));
+  LMB_CUDA(cudaFuncSetAttribute(k_decode_attn_group<4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(ATTN_GROUP_SMEM)));
+  LMB_CUDA(cudaFuncSetAttribute(k_decode_attn_group<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(ATTN_GROUP_SMEM)));
   return LMB_OK;
 }
 
