@@ -115,9 +115,9 @@ def step_bytes_unsharded(spec, ctx_len: int, batch: int = 1) -> int:
 
 def run_decode(ctx, shape_name: str, kind: int, ctx_len: int, batch: int = 1, steps: int = 20, warmup: int = 3,
                seed: int = 0, shared_layers: int = 0, max_seq: int = 2048, tp_rank: int = 0, tp_size: int = 1,
-               random_kv: bool = False):
+               random_kv: bool = False, n_layers: int = 0):
     case = DecodeCase(ctx, shape_name, kind, max_batch=batch, max_seq=max_seq, seed=seed, shared_layers=shared_layers,
-                      tp_rank=tp_rank, tp_size=tp_size)
+                      tp_rank=tp_rank, tp_size=tp_size, n_layers=n_layers)
     out = case.time(ctx_len, batch, steps, warmup, random_kv)
     nbytes = step_bytes_unsharded(case.spec, ctx_len, batch)
     out["algorithmic_bytes_per_step"] = nbytes

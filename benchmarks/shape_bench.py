@@ -72,6 +72,8 @@ def main(argv=None):
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--random-kv", action="store_true", help="fill the KV cache with random values instead of prefilling")
     ap.add_argument("--shared-layers", type=int, default=0, help="generate this many distinct layers and repeat them")
+    ap.add_argument("--layers", type=int, default=0, help="with --decode: keep only this many layers of the named shape")
+    ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--tp", action="store_true", help="tensor parallel over the ranks of a torch.distributed.run launch")
     a = ap.parse_args(argv)
     rank, world = 0, 1
@@ -92,7 +94,7 @@ def main(argv=None):
     if a.decode:
         from .decode_bench import run_decode
         out = run_decode(ctx, a.decode, KIND_BY_NAME[a.kind], a.context, a.batch, steps=a.steps, random_kv=a.random_kv,
-                         shared_layers=a.shared_layers, tp_rank=rank, tp_size=world)
+                         warmup=a.warmup, shared_layers=a.shared_layers, tp_rank=rank, tp_size=world, n_layers=a.layers)
     else:
         out = run_shape(ctx, KIND_BY_NAME[a.kind], a.M, a.K, a.copies, a.reps, not a.no_graph,
                         0 if a.no_rotate else _lib.AUTO_ROTATE)
