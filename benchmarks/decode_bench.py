@@ -54,6 +54,8 @@ class DecodeCase:
         self.fill_cache(ctx_len, batch, random_kv)
         toks = self.rng.integers(0, vocab, size=batch)
         pos = [ctx_len] * batch
+        if barrier:
+            barrier()  # ranks finish building at different times: the device-side waits for other ranks are bounded (about a second)
         for _ in range(warmup):
             m.forward(toks, pos, fetch=False)
         ctx.sync()
