@@ -150,7 +150,7 @@ struct XchgHeader {
 };
 struct PeerXchg {
   bool ready = false;
-  unsigned spin_limit = 1u << 22;  // polls (about 40 ns apart) before a consumer gives up: about a second
+  unsigned spin_limit = 1u << 22;  // polls (a 40 ns sleep and a load each) before a consumer gives up: a few seconds; LMB_TP_WAIT_POLLS
   size_t cap = 0;            // floats per (parity, rank) slot
   void *local = nullptr;     // this rank's block
   void *peer[MAX_TP] = {};   // every rank's block as mapped here (own block included)

@@ -137,6 +137,10 @@ int lmb_tp_peer_open(lmb_ctx *ctx, const void *handles) {
     std::memcpy(&hnd, static_cast<const char *>(handles) + size_t(r) * 64, 64);
     LMB_CUDA(cudaIpcOpenMemHandle(&ctx->xchg.peer[r], hnd, cudaIpcMemLazyEnablePeerAccess));
   }
+  if (const char *e = std::getenv("LMB_TP_WAIT_POLLS")) {  // polls per word before a consumer gives up (default 1 << 22: seconds)
+    const long v = std::atol(e);
+    if (v > 0 && v < (1l << 31)) ctx->xchg.spin_limit = unsigned(v);
+  }
   ctx->xchg.ready = true;
   return LMB_OK;
 }
