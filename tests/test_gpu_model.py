@@ -190,3 +190,33 @@ def test_model_errors(ctx):
     with pytest.raises(LutmacError):
         m.forward(1, 8)  # beyond the KV cache
     m.close()
+
+
+def test_launch_timeline_records_every_launch_of_a_step():
+    """lmb_debug_launch_timeline: one slot of device time stamps per GEMV / attention launch of a
+    step (5 per layer + the head), in order: started <= past the wait <= activations ready <= main
+    loop done <= finished, and a launch does not finish before the one it depends on."""
+    import ctypes as C
+    from lutmac_b200 import _lib
+    from lutmac_b200.api import Context
+    ctx = Context(0)  # a context of its own: recording is switched on before anything is captured into a graph
+    L = _lib.lib()
+    n = C.c_size_t()
+    _lib.check(L.lmb_debug_launch_timeline(ctx.h, 256, None, C.byref(n)))
+    spec = synth.model_spec(synth.tiny_model_shape(n_layers=3), INT4, seed=2, max_seq=16)
+    m = Model(spec, ctx)
+    for p in range(3):
+        m.forward(7 + p, p)
+    _lib.check(L.lmb_debug_launch_timeline(ctx.h, 0, None, C.byref(n)))  # clears what the steps so far recorded
+    m.forward(11, 3)
+    out = (C.c_uint64 * (8 * 256))()
+    _lib.check(L.lmb_debug_launch_timeline(ctx.h, 0, out, C.byref(n)))
+    assert n.value == 5 * 3 + 1
+    t = np.array(list(out)[:8 * n.value], np.uint64).reshape(n.value, 8)
+    for i in range(n.value):
+        start, first_wait, last_wait, ready, main, done, first_done = (int(t[i][k]) for k in range(7))
+        assert 0 < start <= first_wait <= last_wait <= ready <= main <= done, (i, t[i])
+        assert first_wait <= first_done <= done + 1000, (i, t[i])  # each stamp reads the timer itself: a launch of one CTA stamps "first done" a few ns after "done"
+        if i:
+            assert done >= int(t[i - 1][5]), (i, "finished before its predecessor")
+    m.close()
