@@ -41,6 +41,19 @@ def test_drop_in_defines_the_reference_entry_points():
         assert re.search(r" T lutmac::" + name + r"\(", syms), name
 
 
+def test_range_checking_library_exports_the_same_abi():
+    """liblutmac_b200_dbg.so (python -m lutmac_b200.build --debug-bounds) is the same library compiled with
+    -DLMB_DEBUG_BOUNDS: every declared entry point, loadable without a GPU."""
+    import ctypes
+    from lutmac_b200 import _lib
+    path = os.path.join(ROOT, "lutmac_b200", "liblutmac_b200_dbg.so")
+    if not os.path.exists(path):
+        pytest.skip("liblutmac_b200_dbg.so not built")
+    L = ctypes.CDLL(path)
+    missing = [name for name in _lib.SIGNATURES if not hasattr(L, name)]
+    assert not missing, missing
+
+
 def test_block_sizes_match_the_reference_structs():
     L = _lib.lib()
     for kind in ALL_KINDS:
