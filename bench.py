@@ -336,6 +336,7 @@ def run_ours(args):
                        "kv_cache": head["kv_fill"], "finite_logits": head["finite_logits"],
                        "peer_wait_timed_out": bool(timed_out), "model_build_s": round(case.build_s, 1)},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,
+                         "frac_of_nominal_8000_gbs": achieved / 8000.0,
                          "peak_source": peak_src, "kernel": "decode step of one rank (all kernels of lmb_model_forward)",
                          "algorithmic_bytes_per_launch": rank_bytes,
                          "traffic": int(rank_bytes * NCU_DRAM_TO_ALGORITHMIC_BYTES) if world == 1 else None,
